@@ -1,0 +1,55 @@
+"""Build recipe of libbonsai_cuda.so (hand-written sm_100a kernels + the C ABI) and of the host
+tools. Everything is compiled in-tree with nvcc / g++; nothing is installed."""
+from __future__ import annotations
+
+import glob
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+LIB = os.path.join(HERE, "libbonsai_cuda.so")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    # no silent fused multiply-add: the kernels spell fmaf() where the arithmetic contract has one
+    "-fmad=false",
+    "-Xcompiler", "-fPIC", "-shared",
+]
+
+
+def _stale(target: str, sources: list[str]) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources)
+
+
+def build_lib(verbose: bool = False, force: bool = False) -> str:
+    srcs = sorted(glob.glob(os.path.join(HERE, "csrc", "*.cu")))
+    deps = srcs + glob.glob(os.path.join(HERE, "csrc", "*.cuh")) + glob.glob(os.path.join(ROOT, "include", "*.h"))
+    if not force and not _stale(LIB, deps):
+        return LIB
+    cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + srcs
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+    if r.returncode != 0:
+        raise RuntimeError("nvcc failed building libbonsai_cuda.so")
+    return LIB
+
+
+def build_oracle() -> None:
+    """Compile the CPU checker under oracle/ (and the reference shim when the reference tree is
+    present). Building the checker is not using it: only tests and the benchmark baselines load it."""
+    r = subprocess.run(["make", "-C", os.path.join(ROOT, "oracle")], capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("oracle build failed")
+
+
+if __name__ == "__main__":
+    build_lib(verbose="-v" in sys.argv, force=True)
+    build_oracle()
+    print("built", LIB)

@@ -1,0 +1,164 @@
+"""ctypes binding of libbonsai_cuda.so (C ABI: include/bonsai_cuda.h)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libbonsai_cuda.so")
+
+_lib = None
+
+
+class BonsaiError(RuntimeError):
+    pass
+
+
+def load_library() -> C.CDLL:
+    """Load the CUDA library. Raises if it has not been built (python bonsai_vk_b200/build.py)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise BonsaiError(f"{LIB_PATH} is missing: build it with `python bonsai_vk_b200/build.py` "
+                          "(there is no CPU fallback)")
+    lib = C.CDLL(LIB_PATH)
+    vp, sz, i32 = C.c_void_p, C.c_size_t, C.c_int
+    sig = {
+        "bn_last_error": (C.c_char_p, []),
+        "bn_init": (i32, [i32, C.POINTER(vp)]),
+        "bn_destroy": (None, [vp]),
+        "bn_device_info": (i32, [vp, C.POINTER(i32), C.POINTER(sz), C.POINTER(sz)]),
+        "bn_alloc": (i32, [vp, sz, C.POINTER(vp)]),
+        "bn_free": (i32, [vp, vp]),
+        "bn_buf_size": (sz, [vp]),
+        "bn_upload": (i32, [vp, vp, sz, vp, sz]),
+        "bn_download": (i32, [vp, vp, sz, vp, sz]),
+        "bn_memset": (i32, [vp, vp, sz, i32, sz]),
+        "bn_sync": (i32, [vp]),
+        "bn_host_alloc": (i32, [sz, C.POINTER(vp)]),
+        "bn_host_free": (i32, [vp]),
+        "bn_event_create": (i32, [vp, C.POINTER(vp)]),
+        "bn_event_record": (i32, [vp, vp]),
+        "bn_event_elapsed_ms": (i32, [vp, vp, vp, C.POINTER(C.c_float)]),
+        "bn_event_destroy": (i32, [vp, vp]),
+        "bn_launch_count": (C.c_uint64, [vp]),
+        "bn_act_pack_bytes": (sz, [i32]),
+        "bn_act_quant_q81": (i32, [vp, vp, sz, i32, vp, sz]),
+        "bn_gemv_q81": (i32, [vp, vp, sz, i32, i32, vp, sz, vp, sz, vp, sz]),
+    }
+    for name, (res, args) in sig.items():
+        f = getattr(lib, name)
+        f.restype = res
+        f.argtypes = args
+    lib._bn_signatures = sig
+    _lib = lib
+    return lib
+
+
+def declared_symbols() -> list[str]:
+    """Entry points declared in include/bonsai_cuda.h (parsed from the header text)."""
+    import re
+    hdr = os.path.join(os.path.dirname(HERE), "include", "bonsai_cuda.h")
+    text = open(hdr).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(bn_[a-z0-9_]+)\s*\(", text)))
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        msg = load_library().bn_last_error().decode()
+        raise BonsaiError(f"{what} failed ({rc}): {msg}")
+
+
+class Buffer:
+    """Device buffer owned by the library; named by handle + byte offset in every op."""
+
+    def __init__(self, ctx: "Context", nbytes: int):
+        self.ctx = ctx
+        self.nbytes = int(nbytes)
+        h = C.c_void_p()
+        _check(ctx.lib.bn_alloc(ctx.h, self.nbytes, C.byref(h)), "bn_alloc")
+        self.h = h
+
+    def upload(self, arr: np.ndarray, off: int = 0):
+        a = np.ascontiguousarray(arr)
+        _check(self.ctx.lib.bn_upload(self.ctx.h, self.h, off, a.ctypes.data_as(C.c_void_p), a.nbytes), "bn_upload")
+        return self
+
+    def download(self, dtype, count: int, off: int = 0) -> np.ndarray:
+        out = np.empty(count, dtype=dtype)
+        _check(self.ctx.lib.bn_download(self.ctx.h, self.h, off, out.ctypes.data_as(C.c_void_p), out.nbytes),
+               "bn_download")
+        return out
+
+    def memset(self, byte: int = 0, off: int = 0, n: int | None = None):
+        _check(self.ctx.lib.bn_memset(self.ctx.h, self.h, off, byte, self.nbytes - off if n is None else n), "bn_memset")
+
+    def free(self):
+        if self.h is not None:
+            self.ctx.lib.bn_free(self.ctx.h, self.h)
+            self.h = None
+
+
+class Context:
+    """One context per GPU (reference: the single Vulkan device + queue of vk_ctx_init)."""
+
+    def __init__(self, device: int = 0):
+        self.lib = load_library()
+        h = C.c_void_p()
+        _check(self.lib.bn_init(device, C.byref(h)), "bn_init")
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if self.h is not None:
+            self.lib.bn_destroy(self.h)
+            self.h = None
+
+    def alloc(self, nbytes: int) -> Buffer:
+        return Buffer(self, nbytes)
+
+    def from_numpy(self, arr: np.ndarray) -> Buffer:
+        a = np.ascontiguousarray(arr)
+        return Buffer(self, max(a.nbytes, 16)).upload(a)
+
+    def sync(self):
+        _check(self.lib.bn_sync(self.h), "bn_sync")
+
+    def info(self):
+        sm, fr, tot = C.c_int(), C.c_size_t(), C.c_size_t()
+        _check(self.lib.bn_device_info(self.h, C.byref(sm), C.byref(fr), C.byref(tot)), "bn_device_info")
+        return {"sm_count": sm.value, "free_bytes": fr.value, "total_bytes": tot.value}
+
+    @property
+    def launches(self) -> int:
+        return int(self.lib.bn_launch_count(self.h))
+
+    # events
+    def event(self):
+        h = C.c_void_p()
+        _check(self.lib.bn_event_create(self.h, C.byref(h)), "bn_event_create")
+        return h
+
+    def record(self, ev):
+        _check(self.lib.bn_event_record(self.h, ev), "bn_event_record")
+
+    def elapsed_ms(self, a, b) -> float:
+        ms = C.c_float()
+        _check(self.lib.bn_event_elapsed_ms(self.h, a, b, C.byref(ms)), "bn_event_elapsed_ms")
+        return float(ms.value)
+
+    # ops
+    def act_pack_bytes(self, K: int) -> int:
+        return int(self.lib.bn_act_pack_bytes(K))
+
+    def act_quant_q81(self, x: Buffer, K: int, pack: Buffer, x_off: int = 0, pack_off: int = 0):
+        _check(self.lib.bn_act_quant_q81(self.h, x.h, x_off, K, pack.h, pack_off), "bn_act_quant_q81")
+
+    def gemv_q81(self, w: Buffer, M: int, K: int, pack: Buffer, out: Buffer, w_off: int = 0, pack_off: int = 0,
+                 out_off: int = 0, dots: Buffer | None = None, dots_off: int = 0):
+        _check(self.lib.bn_gemv_q81(self.h, w.h, w_off, M, K, pack.h, pack_off, out.h, out_off,
+                                    dots.h if dots is not None else None, dots_off), "bn_gemv_q81")

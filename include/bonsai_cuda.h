@@ -1,0 +1,91 @@
+/* bonsai_cuda.h - C ABI of libbonsai_cuda.so: the device layer of the bonsai decode path on B200.
+ *
+ * What this replaces. The reference engine has no plugin interface; its device layer is a set of
+ * Vulkan helpers that the forward pass calls directly. Each entry point below names the reference
+ * helper (file:line, relative to the reference tree) whose role it takes over:
+ *
+ *   vk_ctx_init                      runtime_vk/bonsai_weights.h:45     -> bn_init
+ *   Arena::reserve/commit/create_at  runtime_vk/bonsai_weights.h:126    -> bn_alloc / bn_free
+ *   flush_batch (staging upload)     runtime_vk/bonsai_weights.h:446    -> bn_upload
+ *   act_store / act_rd               runtime_vk/bonsai_forward.h:1294   -> bn_upload / bn_download
+ *   dsp(pipeline, push constants)    runtime_vk/bonsai_forward.h:352    -> one bn_<op>() per kernel
+ *   begin_cmd / submit_wait_sig      runtime_vk/bonsai_weights.h:263,287-> bn_sync (ops are queued on
+ *                                                                          the context's stream)
+ *   timestamp query pool             runtime_vk/bonsai_forward.h:676    -> bn_event_*
+ *
+ * Conventions. Plain C types only. Device memory is owned by the library and named by opaque
+ * bn_buf handles plus byte offsets; every op checks offsets and sizes against the buffer before it
+ * launches anything and refuses (negative return, message in bn_last_error) instead of faulting.
+ * Every call returns 0 on success or a negative bn_err. Calls on one context must be serialised by
+ * the caller (the reference engine is single-threaded, runtime_vk/bonsai_http.h:458). There is no
+ * CPU fallback: without a CUDA device bn_init fails.
+ */
+#ifndef BONSAI_CUDA_H
+#define BONSAI_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct bn_ctx bn_ctx;
+typedef struct bn_buf bn_buf;
+typedef struct bn_event bn_event;
+
+enum bn_err {
+    BN_OK = 0,
+    BN_ERR_CUDA = -1,      /* a CUDA runtime call failed                       */
+    BN_ERR_ARG = -2,       /* bad argument: shape, alignment, range            */
+    BN_ERR_BOUNDS = -3,    /* offset + size exceeds the buffer                 */
+    BN_ERR_NOMEM = -4,     /* device allocation failed                         */
+    BN_ERR_TIMEOUT = -5,   /* a bounded device-side wait gave up               */
+    BN_ERR_STATE = -6      /* call not valid in the current state              */
+};
+
+/* last error message of the calling thread ("" if none) */
+const char *bn_last_error(void);
+
+/* ---- context and memory -------------------------------------------------------------------- */
+int bn_init(int device, bn_ctx **out);
+void bn_destroy(bn_ctx *ctx);
+int bn_device_info(bn_ctx *ctx, int *sm_count, size_t *free_bytes, size_t *total_bytes);
+int bn_alloc(bn_ctx *ctx, size_t bytes, bn_buf **out);
+int bn_free(bn_ctx *ctx, bn_buf *buf);
+size_t bn_buf_size(const bn_buf *buf);
+int bn_upload(bn_ctx *ctx, bn_buf *dst, size_t off, const void *src, size_t n);
+int bn_download(bn_ctx *ctx, const bn_buf *src, size_t off, void *dst, size_t n);
+int bn_memset(bn_ctx *ctx, bn_buf *dst, size_t off, int byte, size_t n);
+int bn_sync(bn_ctx *ctx);
+
+/* page-locked host staging memory (reference: the mapped host_buf, bonsai_weights.h:199) */
+int bn_host_alloc(size_t bytes, void **out);
+int bn_host_free(void *p);
+
+/* CUDA events on the context's stream (reference: VkQueryPool timestamps) */
+int bn_event_create(bn_ctx *ctx, bn_event **out);
+int bn_event_record(bn_ctx *ctx, bn_event *ev);
+int bn_event_elapsed_ms(bn_ctx *ctx, bn_event *start, bn_event *stop, float *ms);
+int bn_event_destroy(bn_ctx *ctx, bn_event *ev);
+
+/* number of kernels this library has launched on ctx since bn_init (for launch accounting) */
+uint64_t bn_launch_count(const bn_ctx *ctx);
+
+/* ---- PTQ1_0 x q8_1 GEMV (reference arithmetic: _mul_mat_vecq_ptq1_0.comp:92-202;
+ *      reference call site: gemv_ptq, runtime_vk/bonsai_forward.h:409-422) ------------------------
+ * An "activation pack" is what a GEMV consumes: for every 128 activations the block_q8_1_x4 record
+ * (36 dwords: 4 x (fp16 d | fp16 s << 16), then 128 int8) followed, after all records, by the
+ * tensor-core operand table derived from it (2048 bytes per 128 activations). */
+size_t bn_act_pack_bytes(int K);
+/* x: K fp32 values at (x, x_off). Writes the pack at (pack, pack_off). K % 128 == 0. */
+int bn_act_quant_q81(bn_ctx *ctx, const bn_buf *x, size_t x_off, int K, bn_buf *pack, size_t pack_off);
+/* W: M rows of K/128 PTQ1_0 blocks (28 bytes each, row-major) at (w, w_off); out: M fp32.
+ * dots (may be NULL): receives the int32 block dots [M][K/128][4] for bit-exact checking. */
+int bn_gemv_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const bn_buf *pack,
+                size_t pack_off, bn_buf *out, size_t out_off, bn_buf *dots, size_t dots_off);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,172 @@
+"""ctypes access to the CPU oracle (oracle/_build/liboracle.so) and to the reference shim
+(oracle/_ref/libref.so). Test infrastructure only."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE_SO = os.path.join(ROOT, "oracle", "_build", "liboracle.so")
+REF_SO = os.path.join(ROOT, "oracle", "_ref", "libref.so")
+
+_o = None
+_r = None
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def load_oracle():
+    global _o
+    if _o is None:
+        if not os.path.exists(ORACLE_SO):
+            subprocess.run(["make", "-C", os.path.join(ROOT, "oracle")], check=True, capture_output=True)
+        _o = Oracle(C.CDLL(ORACLE_SO))
+    return _o
+
+
+def load_ref():
+    global _r
+    if _r is None:
+        if not os.path.exists(REF_SO):
+            return None
+        _r = C.CDLL(REF_SO)
+    return _r
+
+
+class Oracle:
+    def __init__(self, lib):
+        self.lib = lib
+
+    def f16_to_f32(self, bits):
+        bits = np.ascontiguousarray(bits, dtype=np.uint16)
+        out = np.empty(bits.size, dtype=np.float32)
+        self.lib.bo_f16_to_f32(_p(bits), bits.size, _p(out))
+        return out
+
+    def f32_to_f16(self, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty(x.size, dtype=np.uint16)
+        self.lib.bo_f32_to_f16(_p(x), x.size, _p(out))
+        return out
+
+    def ptq_dequant(self, blocks):
+        b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, 28)
+        out = np.empty((b.shape[0], 128), dtype=np.float32)
+        self.lib.bo_ptq_dequant(_p(b), C.c_long(b.shape[0]), _p(out))
+        return out
+
+    def ptq_trits(self, blocks):
+        b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, 28)
+        out = np.empty((b.shape[0], 128), dtype=np.int8)
+        self.lib.bo_ptq_trits(_p(b), C.c_long(b.shape[0]), _p(out))
+        return out
+
+    def ptq_encode(self, sym, scale_bits):
+        s = np.ascontiguousarray(sym, dtype=np.int8).reshape(-1, 128)
+        sb = np.ascontiguousarray(scale_bits, dtype=np.uint16).reshape(-1)
+        out = np.empty((s.shape[0], 28), dtype=np.uint8)
+        self.lib.bo_ptq_encode(_p(s), _p(sb), C.c_long(s.shape[0]), _p(out))
+        return out
+
+    def quantize_q8_1(self, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty(x.size // 128 * 36, dtype=np.uint32)
+        self.lib.bo_quantize_q8_1(_p(x), x.size, _p(out))
+        return out
+
+    def quantize_q8_0(self, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        codes = np.empty(x.size, dtype=np.int8)
+        scales = np.empty(x.size // 32, dtype=np.uint16)
+        self.lib.bo_quantize_q8_0(_p(x), x.size, _p(codes), _p(scales))
+        return codes, scales
+
+    def block_dots(self, block, xq_block, shader=False):
+        b = np.ascontiguousarray(block, dtype=np.uint8)
+        xq = np.ascontiguousarray(xq_block, dtype=np.uint32)
+        out = np.empty(4, dtype=np.int32)
+        (self.lib.bo_block_dots_shader if shader else self.lib.bo_block_dots_def)(_p(b), _p(xq), _p(out))
+        return out
+
+    def gemv_q81(self, W, M, K, xq, want_dots=False, threads=8):
+        W = np.ascontiguousarray(W, dtype=np.uint8)
+        xq = np.ascontiguousarray(xq, dtype=np.uint32)
+        out = np.empty(M, dtype=np.float32)
+        exact = np.empty(M, dtype=np.float64)
+        dots = np.empty((M, K // 128, 4), dtype=np.int32) if want_dots else None
+        self.lib.bo_gemv_q81(_p(W), M, K, _p(xq), _p(out), _p(exact), _p(dots), threads)
+        return out, exact, dots
+
+    def gemv_f32act(self, W, M, K, x, n_splits=1, threads=8):
+        W = np.ascontiguousarray(W, dtype=np.uint8)
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty(M, dtype=np.float32)
+        exact = np.empty(M, dtype=np.float64)
+        self.lib.bo_gemv_f32act(_p(W), M, K, _p(x), n_splits, _p(out), _p(exact), threads)
+        return out, exact
+
+    def gemv_dequant_f64(self, W, M, K, x, threads=1):
+        W = np.ascontiguousarray(W, dtype=np.uint8)
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty(M, dtype=np.float64)
+        self.lib.bo_gemv_dequant_f64(_p(W), M, K, _p(x), _p(out), threads)
+        return out
+
+    def fwht(self, x, block):
+        s = np.array(x, dtype=np.float32, copy=True)
+        self.lib.bo_fwht(_p(s), s.size, block)
+        return s
+
+    def rotate_fwd(self, x, signs, block):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        sg = np.ascontiguousarray(signs, dtype=np.int32)
+        y = np.empty_like(x)
+        self.lib.bo_rotate_fwd(_p(x), _p(sg), x.size, block, _p(y))
+        return y
+
+    def rotate_inv(self, x, signs, block):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        sg = np.ascontiguousarray(signs, dtype=np.int32)
+        y = np.empty_like(x)
+        self.lib.bo_rotate_inv(_p(x), _p(sg), x.size, block, _p(y))
+        return y
+
+    def rms_norm(self, x, w, eps):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = None if w is None else np.ascontiguousarray(w, dtype=np.float32)
+        y = np.empty_like(x)
+        self.lib.bo_rms_norm(_p(x), _p(w), x.size, C.c_float(eps), _p(y))
+        return y
+
+    def l2_norm(self, x, eps):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.empty_like(x)
+        self.lib.bo_l2_norm(_p(x), x.size, C.c_float(eps), _p(y))
+        return y
+
+    def _unary(self, fn, x, *extra):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.empty_like(x)
+        fn(_p(x), x.size, *extra, _p(y))
+        return y
+
+    def silu(self, x):
+        return self._unary(self.lib.bo_silu, x)
+
+    def sigmoid(self, x):
+        return self._unary(self.lib.bo_sigmoid, x)
+
+    def softplus(self, x, thr=20.0):
+        return self._unary(self.lib.bo_softplus, x, C.c_float(thr))
+
+    def swiglu(self, a, b):
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        b = np.ascontiguousarray(b, dtype=np.float32)
+        y = np.empty_like(a)
+        self.lib.bo_swiglu(_p(a), _p(b), a.size, _p(y))
+        return y

@@ -1,0 +1,109 @@
+"""GPU parity of the PTQ1_0 x q8_1 GEMV (through the C ABI) against the CPU oracle.
+
+Bit-exact: q8_1 codes, fp16 d and s, and the int32 block dots I_sb. fp32 outputs: within 1e-5
+relative of the reference formula evaluated in double; because a row's terms can cancel, rows whose
+|reference| is below 1% of the RMS over rows are judged against that floor instead of their own
+magnitude (the floor is stated, not hidden). The oracle's own fp32 restatement uses the same
+operation order as the kernel, so that comparison is reported bit for bit as well.
+"""
+import numpy as np
+import pytest
+
+from bonsai_vk_b200 import ptq
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(ctx, oracle, W, M, K, x, want_dots=True):
+    xb = ctx.from_numpy(x)
+    pack = ctx.alloc(ctx.act_pack_bytes(K))
+    ctx.act_quant_q81(xb, K, pack)
+    nb = K // 128
+    q81 = pack.download(np.uint32, nb * 36)
+    wb = ctx.from_numpy(W)
+    out = ctx.alloc(M * 4)
+    dots = ctx.alloc(M * nb * 16) if want_dots else None
+    ctx.gemv_q81(wb, M, K, pack, out, dots=dots)
+    ctx.sync()
+    res = out.download(np.float32, M)
+    d = dots.download(np.int32, M * nb * 4).reshape(M, nb, 4) if want_dots else None
+    for b in (xb, pack, wb, out) + ((dots,) if dots else ()):
+        b.free()
+    return q81, res, d
+
+
+def _check_rows(got, exact, tol=1e-5):
+    rms = float(np.sqrt(np.mean(exact ** 2)))
+    denom = np.maximum(np.abs(exact), 0.01 * rms)
+    rel = np.abs(got.astype(np.float64) - exact) / np.where(denom > 0, denom, 1.0)
+    return float(rel.max())
+
+
+@pytest.mark.parametrize("M,K", [(4096, 4096), (1024, 4096), (4096, 12288), (100, 512), (16, 128), (37, 640)])
+def test_gemv_q81_parity(ctx, oracle, M, K):
+    rng = np.random.default_rng(M * 31 + K)
+    W = ptq.synth_matrix(rng, M, K)
+    x = rng.standard_normal(K).astype(np.float32)
+    q81, got, dots = _run(ctx, oracle, W, M, K, x)
+    xq = oracle.quantize_q8_1(x)
+    assert np.array_equal(q81, xq), "q8_1 codes / d / s differ from the oracle"
+    out, exact, odots = oracle.gemv_q81(W, M, K, xq, want_dots=True)
+    assert np.array_equal(dots, odots), "int32 block dots differ"
+    assert _check_rows(got, exact) <= 1e-5
+    assert np.array_equal(got.view(np.uint32), out.view(np.uint32)), "fp32 differs from the same-order restatement"
+
+
+def test_gemv_q81_raw_bytes_and_edge_scales(ctx, oracle):
+    """Kernel-lab style raw random bytes (incl. 243..255) and the reference's edge scale patterns
+    (zero, subnormal, negative, +-Inf, NaN): integer dots bit-exact, outputs NaN/Inf-class equal."""
+    rng = np.random.default_rng(99)
+    M, K = 64, 1024
+    W = rng.integers(0, 256, size=(M, K // 128, 28), dtype=np.uint8)
+    edge = np.array(ptq.EDGE_SCALE_BITS, dtype=np.uint16)
+    sel = edge[rng.integers(0, len(edge), size=(M, K // 128))]
+    sel[: M // 2] = rng.integers(0x2000, 0x3C00, size=(M // 2, K // 128)).astype(np.uint16)   # finite rows
+    W[:, :, 26] = (sel & 0xFF).astype(np.uint8)
+    W[:, :, 27] = (sel >> 8).astype(np.uint8)
+    x = (rng.standard_normal(K) * 2).astype(np.float32)
+    q81, got, dots = _run(ctx, oracle, W, M, K, x)
+    xq = oracle.quantize_q8_1(x)
+    assert np.array_equal(q81, xq)
+    out, exact, odots = oracle.gemv_q81(W, M, K, xq, want_dots=True)
+    assert np.array_equal(dots, odots)
+    assert np.array_equal(np.isnan(got), np.isnan(out))
+    fin = np.isfinite(out)
+    assert np.array_equal(got[~np.isnan(out) & ~fin], out[~np.isnan(out) & ~fin])     # +-Inf rows
+    assert np.array_equal(got[fin].view(np.uint32), out[fin].view(np.uint32))
+
+
+def test_act_quant_edge_inputs(ctx, oracle):
+    x = np.zeros(512, dtype=np.float32)
+    x[0:32] = 0.0
+    x[32] = 127.0
+    x[33:38] = [0.5, -0.5, 1.5, -2.5, 126.5]
+    x[64:96] = 1e-36
+    x[128:256] = np.linspace(-3, 3, 128, dtype=np.float32)
+    x[256:384] = np.float32(65504.0) * np.linspace(-1, 1, 128, dtype=np.float32)
+    x[384:512] = np.random.default_rng(1).standard_normal(128).astype(np.float32) * 1e-6
+    xb = ctx.from_numpy(x)
+    pack = ctx.alloc(ctx.act_pack_bytes(512))
+    ctx.act_quant_q81(xb, 512, pack)
+    got = pack.download(np.uint32, 4 * 36)
+    assert np.array_equal(got, oracle.quantize_q8_1(x))
+    xb.free(); pack.free()
+
+
+def test_gemv_refuses_bad_arguments(ctx):
+    from bonsai_vk_b200 import BonsaiError
+    w = ctx.alloc(28 * 4)
+    pack = ctx.alloc(ctx.act_pack_bytes(128))
+    out = ctx.alloc(16)
+    with pytest.raises(BonsaiError):
+        ctx.gemv_q81(w, 8, 128, pack, out)            # W too small for 8 rows
+    with pytest.raises(BonsaiError):
+        ctx.gemv_q81(w, 4, 100, pack, out)            # K not a multiple of 128
+    with pytest.raises(BonsaiError):
+        ctx.gemv_q81(w, 4, 128, pack, out, out_off=8)  # out range exceeds the buffer
+    ctx.sync()
+    for b in (w, pack, out):
+        b.free()
