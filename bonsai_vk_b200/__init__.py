@@ -5,4 +5,4 @@ include/bonsai_cuda.h). This package holds the ctypes binding used by the tests 
 and the host-side data-format helpers. There is no CPU fallback: loading fails loudly when the
 library is missing, and creating a context fails loudly without a B200.
 """
-from .lib import Context, Buffer, BonsaiError, load_library, LIB_PATH  # noqa: F401
+from .lib import Context, Buffer, Model, BonsaiError, load_library, LIB_PATH  # noqa: F401

@@ -67,6 +67,9 @@ static inline T *bn_ptr(const bn_buf *b, size_t off) {
 }
 
 int bn_scratch_reserve(bn_ctx *ctx, size_t bytes);
+// every kernel launch of this library is counted here (one process drives one GPU)
+extern unsigned long long g_bn_launches;
+#define BN_COUNT(n) (g_bn_launches += (n))
 int bn_launch_check(bn_ctx *ctx, const char *what);
 
 // ---- device helpers ---------------------------------------------------------------------------

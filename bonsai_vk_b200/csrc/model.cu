@@ -1,0 +1,369 @@
+// model.cu - the whole-token schedule (reference: fwd_token, runtime_vk/bonsai_forward.h:664-758, with
+// gdn_block :509-573, attn_block :581-645, ffn_block :489-506) over tensors registered by GGUF name.
+#include "ops.cuh"
+
+#include <map>
+#include <string>
+#include <vector>
+
+struct bn_tensor_ref { const bn_buf *buf; size_t off, bytes; };
+
+struct bn_model {
+    bn_ctx *ctx;
+    bn_hparams hp;
+    std::map<std::string, bn_tensor_ref> tensors;
+    const int32_t *signs = nullptr;
+    bool finalized = false;
+    int n_gdn = 0, n_attn = 0;
+    // activation arena (one allocation), carved into named regions
+    char *arena = nullptr;
+    size_t arena_bytes = 0;
+    float *RES, *AN, *X1, *X2, *QKV, *Z, *CONV, *L2, *O, *KBUF, *VBUF, *Q16F, *GATEB, *GOUT, *FG, *FU, *FS, *D, *LOGITS;
+    float *ALPHA, *BETA, *G, *BT, *SCORE, *P16F, *PVPART, *AMV;
+    int *AMI, *TOK, *POS, *NEXT;
+    uint32_t *PACK_H, *PACK_F;
+    float *GEMV_SCRATCH;
+    // persistent state
+    float *gdn_state = nullptr, *conv_hist = nullptr;
+    char *kv = nullptr;
+    size_t kv_layer_bytes = 0, kv_k_scale_off = 0, kv_v_off = 0, kv_v_scale_off = 0;
+    int pv_splits = 1;
+    // resolved per-layer weights
+    struct Layer {
+        bool attn;
+        const float *attn_norm, *post_norm;
+        const uint32_t *ffn_gate, *ffn_up, *ffn_down;
+        // gdn
+        const uint32_t *qkv, *gate_w, *ssm_out;
+        const float *alpha_w, *beta_w, *dt_bias, *ssm_a, *conv_w, *ssm_norm;
+        // attn
+        const uint32_t *q_w, *k_w, *v_w, *o_w;
+        const float *q_norm, *k_norm;
+        int idx;   // index among its kind
+    };
+    std::vector<Layer> layers;
+    const uint32_t *embd = nullptr, *out_w = nullptr;
+    const float *out_norm = nullptr;
+};
+
+namespace {
+
+template <class T>
+const T *tensor_ptr(bn_model *m, const std::string &name, size_t want_bytes, int *rc) {
+    auto it = m->tensors.find(name);
+    if (it == m->tensors.end()) { bn_set_error("bn_model_finalize: tensor '%s' was not registered", name.c_str()); *rc = BN_ERR_STATE; return nullptr; }
+    if (it->second.bytes != want_bytes) {
+        bn_set_error("bn_model_finalize: tensor '%s' has %zu bytes, the shape needs %zu", name.c_str(), it->second.bytes, want_bytes);
+        *rc = BN_ERR_ARG; return nullptr;
+    }
+    return bn_ptr<T>(it->second.buf, it->second.off);
+}
+
+size_t ptq_bytes(size_t M, size_t K) { return M * (K / 128) * 28; }
+
+bnk::AttnDims attn_dims(const bn_model *m) {
+    const bn_hparams &h = m->hp;
+    return bnk::AttnDims{h.n_head, h.n_kv, h.head_dim, h.n_rot, h.cap, h.rms_eps, h.rope_base, h.k_mode, h.v_mode};
+}
+
+bnk::KvLayer kv_layer(const bn_model *m, int li) {
+    char *base = m->kv + size_t(li) * m->kv_layer_bytes;
+    bnk::KvLayer k;
+    k.k_data = base;
+    k.k_scale = m->hp.k_mode == 0 ? reinterpret_cast<uint16_t *>(base + m->kv_k_scale_off) : nullptr;
+    k.v_data = base + m->kv_v_off;
+    k.v_scale = m->hp.v_mode == 0 ? reinterpret_cast<uint16_t *>(base + m->kv_v_scale_off) : nullptr;
+    return k;
+}
+
+// rotate + quantise `x` (n values) with sign vector `sg`, then project with W (M rows)
+void rot_project(bn_model *m, const float *x, const int32_t *sg, int K, uint32_t *pack, const uint32_t *W, int M, float *out) {
+    cudaStream_t st = m->ctx->stream;
+    bnk::rotate_quant(st, x, sg, K, m->hp.hat_block, nullptr, pack);
+    bnk::gemv_q81(st, m->ctx->sm_count, W, M, K, pack, out, m->GEMV_SCRATCH, nullptr);
+}
+
+void ffn(bn_model *m, const bn_model::Layer &L) {
+    const bn_hparams &h = m->hp;
+    cudaStream_t st = m->ctx->stream;
+    bnk::rms_norm(st, m->RES, L.post_norm, 1, h.hidden, h.rms_eps, m->AN);
+    bnk::rotate_quant(st, m->AN, m->signs, h.hidden, h.hat_block, nullptr, m->PACK_H);
+    bnk::gemv_q81(st, m->ctx->sm_count, L.ffn_gate, h.ffn, h.hidden, m->PACK_H, m->FG, m->GEMV_SCRATCH, nullptr);
+    bnk::gemv_q81(st, m->ctx->sm_count, L.ffn_up, h.ffn, h.hidden, m->PACK_H, m->FU, m->GEMV_SCRATCH, nullptr);
+    bnk::swiglu(st, m->FG, m->FU, h.ffn, m->FS);
+    rot_project(m, m->FS, m->signs + h.hidden, h.ffn, m->PACK_F, L.ffn_down, h.hidden, m->D);
+    bnk::add_inplace(st, m->RES, m->D, h.hidden);
+}
+
+void gdn(bn_model *m, const bn_model::Layer &L) {
+    const bn_hparams &h = m->hp;
+    cudaStream_t st = m->ctx->stream;
+    const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D, IN = NH * D;
+    const bnk::GdnDims gd{NH, NQ, D};
+    bnk::rms_norm(st, m->RES, L.attn_norm, 1, h.hidden, h.rms_eps, m->AN);
+    bnk::gemv_f32_small(st, L.alpha_w, NH, h.hidden, m->AN, m->ALPHA);
+    bnk::gemv_f32_small(st, L.beta_w, NH, h.hidden, m->AN, m->BETA);
+    bnk::gdn_gates(st, m->ALPHA, m->BETA, L.dt_bias, L.ssm_a, NH, m->G, m->BT);
+    bnk::rotate_quant(st, m->AN, m->signs, h.hidden, h.hat_block, nullptr, m->PACK_H);
+    bnk::gemv_q81(st, m->ctx->sm_count, L.qkv, C, h.hidden, m->PACK_H, m->QKV, m->GEMV_SCRATCH, nullptr);
+    bnk::gemv_q81(st, m->ctx->sm_count, L.gate_w, IN, h.hidden, m->PACK_H, m->Z, m->GEMV_SCRATCH, nullptr);
+    bnk::conv_silu(st, m->QKV, L.conv_w, m->conv_hist + size_t(L.idx) * C * 3, C, m->CONV);
+    bnk::l2_norm_rows(st, m->CONV, 2 * NQ, 1e-12f, m->L2);
+    bnk::gdn_delta(st, gd, m->L2, m->L2 + NQ * D, m->CONV + 2 * NQ * D, m->G, m->BT,
+                   m->gdn_state + size_t(L.idx) * NH * D * D, m->O);
+    bnk::gdn_out(st, gd, m->O, m->Z, L.ssm_norm, h.rms_eps, m->X1);
+    rot_project(m, m->X1, m->signs, IN, m->PACK_H, L.ssm_out, h.hidden, m->D);
+    bnk::add_inplace(st, m->RES, m->D, h.hidden);
+}
+
+void attn(bn_model *m, const bn_model::Layer &L) {
+    const bn_hparams &h = m->hp;
+    cudaStream_t st = m->ctx->stream;
+    const int QD = h.n_head * h.head_dim, KD = h.n_kv * h.head_dim;
+    const bnk::AttnDims a = attn_dims(m);
+    const bnk::KvLayer kv = kv_layer(m, L.idx);
+    bnk::rms_norm(st, m->RES, L.attn_norm, 1, h.hidden, h.rms_eps, m->AN);
+    bnk::rotate_quant(st, m->AN, m->signs, h.hidden, h.hat_block, nullptr, m->PACK_H);
+    bnk::gemv_q81(st, m->ctx->sm_count, L.q_w, 2 * QD, h.hidden, m->PACK_H, m->QKV, m->GEMV_SCRATCH, nullptr);
+    bnk::gemv_q81(st, m->ctx->sm_count, L.k_w, KD, h.hidden, m->PACK_H, m->KBUF, m->GEMV_SCRATCH, nullptr);
+    bnk::gemv_q81(st, m->ctx->sm_count, L.v_w, KD, h.hidden, m->PACK_H, m->VBUF, m->GEMV_SCRATCH, nullptr);
+    bnk::attn_prep(st, a, m->QKV, m->KBUF, m->VBUF, L.q_norm, L.k_norm, m->POS, kv, m->Q16F, m->GATEB);
+    bnk::attn_decode(st, a, m->Q16F, m->GATEB, m->POS, kv, m->SCORE, m->P16F, m->PVPART, m->pv_splits, nullptr, m->GOUT);
+    rot_project(m, m->GOUT, m->signs, QD, m->PACK_H, L.o_w, h.hidden, m->D);
+    bnk::add_inplace(st, m->RES, m->D, h.hidden);
+}
+
+// enqueue one token: TOK[0], POS[0] hold the token id and its absolute position
+void enqueue_token(bn_model *m, int stop_after, bool want_logits) {
+    const bn_hparams &h = m->hp;
+    cudaStream_t st = m->ctx->stream;
+    bnk::embed_row(st, m->embd, h.hidden, m->TOK, m->X1);
+    bnk::rotate_inv(st, m->X1, m->signs, h.hidden, h.hat_block, m->RES);
+    for (int b = 0; b < h.n_layer; ++b) {
+        const bn_model::Layer &L = m->layers[b];
+        if (L.attn) attn(m, L); else gdn(m, L);
+        ffn(m, L);
+        if (b == stop_after) return;
+    }
+    if (!want_logits) return;
+    bnk::rms_norm(st, m->RES, m->out_norm, 1, h.hidden, h.rms_eps, m->AN);
+    rot_project(m, m->AN, m->signs, h.hidden, m->PACK_H, m->out_w, h.vocab, m->LOGITS);
+    bnk::argmax_first(st, m->LOGITS, h.vocab, m->NEXT, m->AMV, m->AMI);
+}
+
+}  // namespace
+
+extern "C" {
+
+int bn_model_create(bn_ctx *ctx, const bn_hparams *hp, bn_model **out) {
+    BN_REQUIRE(ctx && hp && out, BN_ERR_ARG, "bn_model_create: null argument");
+    const bn_hparams &h = *hp;
+    BN_REQUIRE(h.n_layer > 0 && h.hidden > 0 && h.ffn > 0 && h.vocab > 0, BN_ERR_ARG, "bn_model_create: bad sizes");
+    BN_REQUIRE(h.hat_block >= 128 && h.hat_block <= 4096 && (h.hat_block & (h.hat_block - 1)) == 0, BN_ERR_ARG,
+               "bn_model_create: hadamard block %d must be a power of two in [128, 4096]", h.hat_block);
+    BN_REQUIRE(h.hidden % h.hat_block == 0 && h.ffn % h.hat_block == 0, BN_ERR_ARG,
+               "bn_model_create: hadamard block %d must divide hidden %d and ffn %d", h.hat_block, h.hidden, h.ffn);
+    BN_REQUIRE(h.head_dim == 256 && h.gdn_dim == 128, BN_ERR_ARG, "bn_model_create: head_dim must be 256 and gdn_dim 128");
+    BN_REQUIRE(h.n_head == 4 * h.n_kv, BN_ERR_ARG, "bn_model_create: n_head must be 4 x n_kv");
+    BN_REQUIRE(h.n_head * h.head_dim == h.hidden, BN_ERR_ARG, "bn_model_create: n_head * head_dim must equal hidden");
+    BN_REQUIRE(h.gdn_heads * h.gdn_dim == h.hidden, BN_ERR_ARG, "bn_model_create: gdn inner size must equal hidden");
+    BN_REQUIRE(h.gdn_heads <= 64 && h.gdn_heads % h.gdn_qk_heads == 0, BN_ERR_ARG, "bn_model_create: bad gdn head counts");
+    BN_REQUIRE(h.n_rot > 0 && h.n_rot <= h.head_dim && h.n_rot % 2 == 0, BN_ERR_ARG, "bn_model_create: bad rope dims");
+    BN_REQUIRE(h.cap > 0 && h.cap % 2 == 0, BN_ERR_ARG, "bn_model_create: cap %d must be positive and even", h.cap);
+    BN_REQUIRE(h.act_mode == 0, BN_ERR_ARG, "bn_model_create: only act_mode 0 (q8_1 activations) is built");
+    BN_REQUIRE((h.k_mode | 1) == 1 && (h.v_mode | 1) == 1, BN_ERR_ARG, "bn_model_create: kv modes are 0 (q8_0) or 1 (fp16)");
+    bn_model *m = new bn_model();
+    m->ctx = ctx;
+    m->hp = h;
+    *out = m;
+    return BN_OK;
+}
+
+int bn_model_set_tensor(bn_model *m, const char *name, const bn_buf *buf, size_t off, size_t bytes) {
+    BN_REQUIRE(m && name, BN_ERR_ARG, "bn_model_set_tensor: null argument");
+    BN_REQUIRE(!m->finalized, BN_ERR_STATE, "bn_model_set_tensor: model already finalized");
+    BN_RANGE(buf, off, bytes, 16, "bn_model_set_tensor");
+    m->tensors[name] = bn_tensor_ref{buf, off, bytes};
+    return BN_OK;
+}
+
+int bn_model_set_signs(bn_model *m, const bn_buf *buf, size_t off, int count) {
+    BN_REQUIRE(m, BN_ERR_ARG, "bn_model_set_signs: null model");
+    BN_REQUIRE(count == m->hp.hidden + m->hp.ffn, BN_ERR_ARG,
+               "bn_model_set_signs: %d sign values, need hidden + ffn = %d", count, m->hp.hidden + m->hp.ffn);
+    BN_RANGE(buf, off, size_t(count) * 4, 16, "bn_model_set_signs");
+    m->signs = bn_ptr<int32_t>(buf, off);
+    return BN_OK;
+}
+
+int bn_model_finalize(bn_model *m) {
+    BN_REQUIRE(m, BN_ERR_ARG, "bn_model_finalize: null model");
+    BN_REQUIRE(!m->finalized, BN_ERR_STATE, "bn_model_finalize: already finalized");
+    BN_REQUIRE(m->signs, BN_ERR_STATE, "bn_model_finalize: sign values were not registered");
+    const bn_hparams &h = m->hp;
+    const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D, IN = NH * D;
+    const int QD = h.n_head * h.head_dim, KD = h.n_kv * h.head_dim;
+    int rc = BN_OK;
+    m->layers.resize(h.n_layer);
+    m->n_gdn = m->n_attn = 0;
+    for (int b = 0; b < h.n_layer && rc == BN_OK; ++b) {
+        bn_model::Layer &L = m->layers[b];
+        const std::string B = "blk." + std::to_string(b) + ".";
+        L.attn = (b % h.attn_interval) == h.attn_interval - 1;
+        L.attn_norm = tensor_ptr<float>(m, B + "attn_norm.weight", size_t(h.hidden) * 4, &rc);
+        L.post_norm = tensor_ptr<float>(m, B + "post_attention_norm.weight", size_t(h.hidden) * 4, &rc);
+        L.ffn_gate = tensor_ptr<uint32_t>(m, B + "ffn_gate.weight", ptq_bytes(h.ffn, h.hidden), &rc);
+        L.ffn_up = tensor_ptr<uint32_t>(m, B + "ffn_up.weight", ptq_bytes(h.ffn, h.hidden), &rc);
+        L.ffn_down = tensor_ptr<uint32_t>(m, B + "ffn_down.weight", ptq_bytes(h.hidden, h.ffn), &rc);
+        if (L.attn) {
+            L.idx = m->n_attn++;
+            L.q_w = tensor_ptr<uint32_t>(m, B + "attn_q.weight", ptq_bytes(2 * QD, h.hidden), &rc);
+            L.k_w = tensor_ptr<uint32_t>(m, B + "attn_k.weight", ptq_bytes(KD, h.hidden), &rc);
+            L.v_w = tensor_ptr<uint32_t>(m, B + "attn_v.weight", ptq_bytes(KD, h.hidden), &rc);
+            L.o_w = tensor_ptr<uint32_t>(m, B + "attn_output.weight", ptq_bytes(h.hidden, QD), &rc);
+            L.q_norm = tensor_ptr<float>(m, B + "attn_q_norm.weight", size_t(h.head_dim) * 4, &rc);
+            L.k_norm = tensor_ptr<float>(m, B + "attn_k_norm.weight", size_t(h.head_dim) * 4, &rc);
+        } else {
+            L.idx = m->n_gdn++;
+            L.qkv = tensor_ptr<uint32_t>(m, B + "attn_qkv.weight", ptq_bytes(C, h.hidden), &rc);
+            L.gate_w = tensor_ptr<uint32_t>(m, B + "attn_gate.weight", ptq_bytes(IN, h.hidden), &rc);
+            L.ssm_out = tensor_ptr<uint32_t>(m, B + "ssm_out.weight", ptq_bytes(h.hidden, IN), &rc);
+            L.alpha_w = tensor_ptr<float>(m, B + "ssm_alpha.weight", size_t(NH) * h.hidden * 4, &rc);
+            L.beta_w = tensor_ptr<float>(m, B + "ssm_beta.weight", size_t(NH) * h.hidden * 4, &rc);
+            L.dt_bias = tensor_ptr<float>(m, B + "ssm_dt.bias", size_t(NH) * 4, &rc);
+            L.ssm_a = tensor_ptr<float>(m, B + "ssm_a", size_t(NH) * 4, &rc);
+            L.conv_w = tensor_ptr<float>(m, B + "ssm_conv1d.weight", size_t(C) * 4 * 4, &rc);
+            L.ssm_norm = tensor_ptr<float>(m, B + "ssm_norm.weight", size_t(D) * 4, &rc);
+        }
+    }
+    if (rc == BN_OK) m->embd = tensor_ptr<uint32_t>(m, "token_embd.weight", ptq_bytes(h.vocab, h.hidden), &rc);
+    if (rc == BN_OK) m->out_w = tensor_ptr<uint32_t>(m, "output.weight", ptq_bytes(h.vocab, h.hidden), &rc);
+    if (rc == BN_OK) m->out_norm = tensor_ptr<float>(m, "output_norm.weight", size_t(h.hidden) * 4, &rc);
+    if (rc != BN_OK) return rc;
+
+    // activation arena
+    m->pv_splits = h.cap >= 4096 ? 64 : (h.cap >= 512 ? 8 : 1);
+    const int maxM = std::max(std::max(h.vocab, h.ffn), std::max(C, 2 * QD));
+    const int maxG = (std::max(h.ffn, h.hidden) / 128 + 3) / 4;
+    size_t off = 0;
+    auto carve = [&](size_t bytes) { size_t o = off; off += (bytes + 255) & ~size_t(255); return o; };
+    struct Slot { void **p; size_t o; };
+    std::vector<Slot> slots;
+    auto F = [&](float *&p, size_t n) { slots.push_back({reinterpret_cast<void **>(&p), carve(n * 4)}); };
+    F(m->RES, h.hidden); F(m->AN, h.hidden); F(m->X1, h.hidden); F(m->X2, h.hidden);
+    F(m->QKV, std::max(C, 2 * QD)); F(m->Z, IN); F(m->CONV, C); F(m->L2, 2 * NQ * D); F(m->O, IN);
+    F(m->KBUF, KD); F(m->VBUF, KD); F(m->Q16F, QD); F(m->GATEB, QD); F(m->GOUT, QD);
+    F(m->FG, h.ffn); F(m->FU, h.ffn); F(m->FS, h.ffn); F(m->D, h.hidden); F(m->LOGITS, h.vocab);
+    F(m->ALPHA, 64); F(m->BETA, 64); F(m->G, 64); F(m->BT, 64);
+    F(m->SCORE, size_t(h.n_head) * h.cap); F(m->P16F, size_t(h.n_head) * h.cap);
+    F(m->PVPART, size_t(m->pv_splits) * QD); F(m->AMV, 64);
+    F(m->GEMV_SCRATCH, size_t(maxG) * std::max(maxM, 1));
+    slots.push_back({reinterpret_cast<void **>(&m->AMI), carve(64 * 4)});
+    slots.push_back({reinterpret_cast<void **>(&m->TOK), carve(256)});
+    slots.push_back({reinterpret_cast<void **>(&m->POS), carve(256)});
+    slots.push_back({reinterpret_cast<void **>(&m->NEXT), carve(256)});
+    slots.push_back({reinterpret_cast<void **>(&m->PACK_H), carve(bnk::act_pack_bytes(h.hidden))});
+    slots.push_back({reinterpret_cast<void **>(&m->PACK_F), carve(bnk::act_pack_bytes(h.ffn))});
+    m->arena_bytes = off;
+    BN_CUDA(cudaSetDevice(m->ctx->device));
+    BN_CUDA(cudaMalloc(&m->arena, m->arena_bytes));
+    for (auto &s : slots) *s.p = m->arena + s.o;
+    // persistent state
+    if (m->n_gdn) {
+        BN_CUDA(cudaMalloc(&m->gdn_state, size_t(m->n_gdn) * NH * D * D * 4));
+        BN_CUDA(cudaMalloc(&m->conv_hist, size_t(m->n_gdn) * C * 3 * 4));
+    }
+    if (m->n_attn) {
+        const size_t n = size_t(h.cap) * KD;
+        size_t o = 0;
+        auto al = [&](size_t b) { size_t r = o; o += (b + 255) & ~size_t(255); return r; };
+        al(h.k_mode == 0 ? n : n * 2);
+        m->kv_k_scale_off = al(h.k_mode == 0 ? n / 32 * 2 : 0);
+        m->kv_v_off = al(h.v_mode == 0 ? n : n * 2);
+        m->kv_v_scale_off = al(h.v_mode == 0 ? n / 32 * 2 : 0);
+        m->kv_layer_bytes = o;
+        BN_CUDA(cudaMalloc(&m->kv, m->kv_layer_bytes * m->n_attn));
+    }
+    m->finalized = true;
+    return bn_model_reset(m);
+}
+
+int bn_model_reset(bn_model *m) {
+    BN_REQUIRE(m && m->finalized, BN_ERR_STATE, "bn_model_reset: model not finalized");
+    const bn_hparams &h = m->hp;
+    const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D;
+    cudaStream_t st = m->ctx->stream;
+    BN_CUDA(cudaMemsetAsync(m->arena, 0, m->arena_bytes, st));
+    if (m->n_gdn) {
+        BN_CUDA(cudaMemsetAsync(m->gdn_state, 0, size_t(m->n_gdn) * NH * D * D * 4, st));
+        BN_CUDA(cudaMemsetAsync(m->conv_hist, 0, size_t(m->n_gdn) * C * 3 * 4, st));
+    }
+    if (m->n_attn) BN_CUDA(cudaMemsetAsync(m->kv, 0, m->kv_layer_bytes * m->n_attn, st));
+    return BN_OK;
+}
+
+void bn_model_destroy(bn_model *m) {
+    if (!m) return;
+    cudaSetDevice(m->ctx->device);
+    cudaStreamSynchronize(m->ctx->stream);
+    if (m->arena) cudaFree(m->arena);
+    if (m->gdn_state) cudaFree(m->gdn_state);
+    if (m->conv_hist) cudaFree(m->conv_hist);
+    if (m->kv) cudaFree(m->kv);
+    delete m;
+}
+
+int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *next_tok) {
+    BN_REQUIRE(m && m->finalized, BN_ERR_STATE, "bn_model_token: model not finalized");
+    const bn_hparams &h = m->hp;
+    BN_REQUIRE(tok >= 0 && tok < h.vocab, BN_ERR_ARG, "bn_model_token: token %d outside vocab %d", tok, h.vocab);
+    BN_REQUIRE(pos >= 0 && pos < h.cap, BN_ERR_BOUNDS, "bn_model_token: position %d does not fit the KV capacity %d", pos, h.cap);
+    cudaStream_t st = m->ctx->stream;
+    const int tp[2] = {tok, pos};
+    BN_CUDA(cudaMemcpyAsync(m->TOK, &tp[0], 4, cudaMemcpyHostToDevice, st));
+    BN_CUDA(cudaMemcpyAsync(m->POS, &tp[1], 4, cudaMemcpyHostToDevice, st));
+    BN_CUDA(cudaStreamSynchronize(st));     // tp lives on this stack frame
+    enqueue_token(m, stop_after_block, true);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return bn_cuda_fail(e, "token schedule");
+    if (next_tok) {
+        BN_CUDA(cudaMemcpyAsync(next_tok, m->NEXT, 4, cudaMemcpyDeviceToHost, st));
+        BN_CUDA(cudaStreamSynchronize(st));
+    }
+    return BN_OK;
+}
+
+int bn_model_read(bn_model *m, int what, int index, void *dst, size_t bytes) {
+    BN_REQUIRE(m && m->finalized && dst, BN_ERR_STATE, "bn_model_read: bad state or null destination");
+    const bn_hparams &h = m->hp;
+    const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D;
+    const size_t kvn = size_t(h.cap) * h.n_kv * h.head_dim;
+    const void *src = nullptr;
+    size_t have = 0;
+    switch (what) {
+        case BN_READ_LOGITS: src = m->LOGITS; have = size_t(h.vocab) * 4; break;
+        case BN_READ_RESIDUAL: src = m->RES; have = size_t(h.hidden) * 4; break;
+        case BN_READ_GDN_STATE:
+            BN_REQUIRE(index >= 0 && index < m->n_gdn, BN_ERR_ARG, "bn_model_read: gdn layer %d out of range", index);
+            src = m->gdn_state + size_t(index) * NH * D * D; have = size_t(NH) * D * D * 4; break;
+        case BN_READ_CONV_HIST:
+            BN_REQUIRE(index >= 0 && index < m->n_gdn, BN_ERR_ARG, "bn_model_read: gdn layer %d out of range", index);
+            src = m->conv_hist + size_t(index) * C * 3; have = size_t(C) * 3 * 4; break;
+        case BN_READ_K_DATA: case BN_READ_K_SCALE: case BN_READ_V_DATA: case BN_READ_V_SCALE: {
+            BN_REQUIRE(index >= 0 && index < m->n_attn, BN_ERR_ARG, "bn_model_read: attention layer %d out of range", index);
+            const bnk::KvLayer kv = kv_layer(m, index);
+            if (what == BN_READ_K_DATA) { src = kv.k_data; have = h.k_mode == 0 ? kvn : kvn * 2; }
+            if (what == BN_READ_V_DATA) { src = kv.v_data; have = h.v_mode == 0 ? kvn : kvn * 2; }
+            if (what == BN_READ_K_SCALE) { src = kv.k_scale; have = h.k_mode == 0 ? kvn / 32 * 2 : 0; }
+            if (what == BN_READ_V_SCALE) { src = kv.v_scale; have = h.v_mode == 0 ? kvn / 32 * 2 : 0; }
+            break;
+        }
+        default: BN_REQUIRE(false, BN_ERR_ARG, "bn_model_read: unknown selector %d", what);
+    }
+    BN_REQUIRE(src && bytes <= have, BN_ERR_BOUNDS, "bn_model_read: %zu bytes requested, %zu available", bytes, have);
+    BN_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, m->ctx->stream));
+    BN_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    return BN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,487 @@
+// ops.cu - the non-GEMV kernels of the decode path: Hadamard rotation, norms, elementwise fusions,
+// embedding gather, gated-delta-net update, decode attention over the quantised KV cache, argmax.
+//
+// Floating-point order is part of the contract with the CPU checker: sums use the fixed trees
+// stated next to each kernel, transcendentals are evaluated in double and rounded once, and the
+// file is compiled without fused-multiply-add contraction (fmaf is written where one is meant).
+#include "ops.cuh"
+#include "quant.cuh"
+
+namespace {
+
+// ---- block-wide helpers ------------------------------------------------------------------------
+// tree over n = blockDim.x partials in shared memory: p[i] += p[i + s], s = n/2 .. 1
+__device__ __forceinline__ float block_tree_sum(float *p, int n) {
+    for (int s = n >> 1; s > 0; s >>= 1) {
+        __syncthreads();
+        if (int(threadIdx.x) < s) p[threadIdx.x] = __fadd_rn(p[threadIdx.x], p[threadIdx.x + s]);
+    }
+    __syncthreads();
+    return p[0];
+}
+
+// in-place Sylvester-Walsh-Hadamard butterflies over N floats in shared memory, h ascending
+// (reference: runtime_vk/shaders/hat4096.comp:41-60), then the 1/sqrt(N) factor.
+__device__ __forceinline__ void fwht_smem(float *s, int N, float inv) {
+    for (int h = 1; h < N; h <<= 1) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < (N >> 1); i += blockDim.x) {
+            const int j = ((i & ~(h - 1)) << 1) | (i & (h - 1));
+            const float a = s[j], c = s[j + h];
+            s[j] = __fadd_rn(a, c);
+            s[j + h] = __fsub_rn(a, c);
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < N; i += blockDim.x) s[i] = __fmul_rn(s[i], inv);
+    __syncthreads();
+}
+
+// ---- rotation (+ quantisation) -------------------------------------------------------------------
+// one CTA of 512 threads per `block`-wide chunk: y = H(s . x); optional q8_1 pack of the chunk.
+__global__ void __launch_bounds__(512) k_rotate_quant(const float *__restrict__ x, const int32_t *__restrict__ signs,
+                                                      int block, float inv, float *__restrict__ y,
+                                                      uint32_t *__restrict__ q81, uint32_t *__restrict__ table) {
+    extern __shared__ float s[];                   // block floats + 4 x 128 bytes
+    int8_t *qs = reinterpret_cast<int8_t *>(s + block);
+    const size_t base = size_t(blockIdx.x) * block;
+    for (int i = threadIdx.x; i < block; i += blockDim.x) s[i] = __fmul_rn(x[base + i], float(signs[base + i]));
+    fwht_smem(s, block, inv);
+    if (y) for (int i = threadIdx.x; i < block; i += blockDim.x) y[base + i] = s[i];
+    if (q81) {
+        const int grp = threadIdx.x >> 7, i = threadIdx.x & 127;       // 4 groups of 128 threads
+        for (int b = grp; b < block / 128; b += 4) {
+            const size_t gb = base / 128 + b;
+            bnk::quant_block_128(s[b * 128 + i], i, qs + grp * 128, q81 + gb * bnk::Q81_DWORDS,
+                                 table + gb * bnk::BF_WORDS, 1 + grp);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(512) k_rotate_inv(const float *__restrict__ x, const int32_t *__restrict__ signs,
+                                                    int block, float inv, float *__restrict__ y) {
+    extern __shared__ float s[];
+    const size_t base = size_t(blockIdx.x) * block;
+    for (int i = threadIdx.x; i < block; i += blockDim.x) s[i] = x[base + i];
+    fwht_smem(s, block, inv);
+    for (int i = threadIdx.x; i < block; i += blockDim.x) y[base + i] = __fmul_rn(s[i], float(signs[base + i]));
+}
+
+// ---- embedding gather (reference addressing: runtime_vk/shaders/gather_rows.comp:12-16) ----------
+__global__ void k_embed_row(const uint32_t *__restrict__ W, int K, const int *__restrict__ tok_ptr,
+                            float *__restrict__ out) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= K) return;
+    const int tok = tok_ptr[0];
+    const uint32_t *blk = W + (size_t(tok) * (K / 128) + e / 128) * 7;
+    const int el = e & 127;
+    int byte, t;
+    if (el < 80) { byte = el & 15; t = el >> 4; }
+    else if (el < 120) { byte = 16 + ((el - 80) & 7); t = (el - 80) >> 3; }
+    else { byte = 24 + ((el - 120) & 1); t = (el - 120) >> 1; }
+    uint32_t v = (blk[byte >> 2] >> ((byte & 3) * 8)) & 0xFFu;
+    for (int i = 0; i < t; ++i) v = (v * 3u) & 0xFFu;
+    const int trit = int((v * 3u) >> 8);
+    out[e] = __fmul_rn(float(trit) - 1.0f, half_bits_to_float(blk[6] >> 16));
+}
+
+// ---- RMS norm (reference: runtime_vk/shaders/rms_norm.comp:60-103) --------------------------------
+// 256 lanes, lane l sums the squares of its `per` consecutive elements ascending, lane partials
+// combined by the fixed tree; y = (x * inv) * w.
+__global__ void __launch_bounds__(256) k_rms_norm(const float *__restrict__ x, const float *__restrict__ w, int cols,
+                                                  float eps, float *__restrict__ y) {
+    __shared__ float part[256];
+    const int l = threadIdx.x, per = (cols + 255) / 256;
+    const float *xr = x + size_t(blockIdx.x) * cols;
+    float s = 0.0f;
+    for (int i = 0; i < per; ++i) {
+        const int d = l * per + i;
+        if (d < cols) { const float v = xr[d]; s = __fadd_rn(s, __fmul_rn(v, v)); }
+    }
+    part[l] = s;
+    const float ss = block_tree_sum(part, 256);
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, float(cols)), eps)));
+    float *yr = y + size_t(blockIdx.x) * cols;
+    for (int i = 0; i < per; ++i) {
+        const int d = l * per + i;
+        if (d < cols) { const float v = __fmul_rn(xr[d], inv); yr[d] = w ? __fmul_rn(v, w[d]) : v; }
+    }
+}
+
+__global__ void k_add_inplace(float *__restrict__ res, const float *__restrict__ d, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) res[i] = __fadd_rn(d[i], res[i]);
+}
+
+__global__ void k_swiglu(const float *__restrict__ a, const float *__restrict__ b, int n, float *__restrict__ y) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = __fmul_rn(silu_f(a[i]), b[i]);
+}
+
+// small fp32 projection: one warp per row; lane l takes float4 groups l, l+32, ... with one fmaf per
+// element, then a 32-lane xor tree (reference: runtime_vk/shaders/gemv_f32.comp).
+__global__ void k_gemv_f32_small(const float *__restrict__ W, int M, int K, const float *__restrict__ x,
+                                 float *__restrict__ out) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= M) return;
+    const float4 *wr = reinterpret_cast<const float4 *>(W + size_t(row) * K);
+    const float4 *xv = reinterpret_cast<const float4 *>(x);
+    float a = 0.0f;
+    for (int i = lane; i < K / 4; i += 32) {
+        const float4 w = wr[i], v = xv[i];
+        a = fmaf(w.x, v.x, a); a = fmaf(w.y, v.y, a); a = fmaf(w.z, v.z, a); a = fmaf(w.w, v.w, a);
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xFFFFFFFFu, a, s));
+    if (lane == 0) out[row] = a;
+}
+
+// ---- gated delta net ------------------------------------------------------------------------------
+// gate = ssm_a * softplus(alpha + dt_bias), beta = sigmoid(beta_raw)   (bonsai_forward.h:528-535)
+__global__ void k_gdn_gates(const float *alpha, const float *beta_raw, const float *dt_bias, const float *ssm_a, int n,
+                            float *gate, float *beta) {
+    const int i = threadIdx.x;
+    if (i >= n) return;
+    const float a = __fadd_rn(alpha[i], dt_bias[i]);
+    const float sp = a > 20.0f ? a : log_f(__fadd_rn(1.0f, exp_f(a)));
+    gate[i] = __fmul_rn(sp, ssm_a[i]);
+    beta[i] = sigmoid_f(beta_raw[i]);
+}
+
+// 4-tap causal depthwise conv + silu + history shift (runtime_vk/shaders/conv_silu.comp:35-49)
+__global__ void k_conv_silu(const float *__restrict__ x, const float *__restrict__ w, float *__restrict__ hist,
+                            int channels, float *__restrict__ y) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    float *s = hist + 3 * size_t(c);
+    const float *wc = w + 4 * size_t(c);
+    const float s0 = s[0], s1 = s[1], s2 = s[2], xn = x[c];
+    float acc = __fmul_rn(wc[0], s0);
+    acc = __fadd_rn(acc, __fmul_rn(wc[1], s1));
+    acc = __fadd_rn(acc, __fmul_rn(wc[2], s2));
+    acc = __fadd_rn(acc, __fmul_rn(wc[3], xn));
+    y[c] = silu_f(acc);
+    s[0] = s1; s[1] = s2; s[2] = xn;
+}
+
+// sum over 128 values held as 4 per lane (elements l, l+32, l+64, l+96) in the order of the
+// reference's shared-memory tree sh[l] += sh[l+s], s = 64..1 (gdn_delta.comp tree_reduce)
+__device__ __forceinline__ float warp_tree128(float e0, float e1, float e2, float e3) {
+    float a = __fadd_rn(__fadd_rn(e0, e2), __fadd_rn(e1, e3));
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xFFFFFFFFu, a, s));
+    return a;
+}
+
+// L2 norm of 128-wide rows, mode 1 (runtime_vk/shaders/l2_norm.comp:59-78); one warp per row
+__global__ void k_l2_norm_rows(const float *__restrict__ x, int rows, float eps, float *__restrict__ y) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), l = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float *xr = x + size_t(row) * 128;
+    const float a = xr[l], b = xr[l + 32], c = xr[l + 64], d = xr[l + 96];
+    const float ss = warp_tree128(__fmul_rn(a, a), __fmul_rn(b, b), __fmul_rn(c, c), __fmul_rn(d, d));
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ss, eps)));
+    float *yr = y + size_t(row) * 128;
+    yr[l] = __fmul_rn(a, inv); yr[l + 32] = __fmul_rn(b, inv); yr[l + 64] = __fmul_rn(c, inv); yr[l + 96] = __fmul_rn(d, inv);
+}
+
+// delta rule (runtime_vk/shaders/gdn_delta.comp:78-102), one warp per (v-head h, state row j):
+// S *= exp(g); pred = sum_i S_i k_i; u = beta (v_j - pred); S_i = fma(k_i, u, S_i); o_j = (sum_i S_i q_i) / sqrt(dim)
+__global__ void __launch_bounds__(256) k_gdn_delta(int heads, int qk_heads, const float *__restrict__ q,
+                                                   const float *__restrict__ k, const float *__restrict__ v,
+                                                   const float *__restrict__ gate, const float *__restrict__ beta,
+                                                   float *__restrict__ state, float *__restrict__ o, float scale) {
+    const int h = blockIdx.y, j = blockIdx.x * 8 + (threadIdx.x >> 5), l = threadIdx.x & 31;
+    const int hq = h % qk_heads;
+    const float eg = exp_f(gate[h]), bt = beta[h];
+    const float *kr = k + hq * 128, *qr = q + hq * 128;
+    float *S = state + (size_t(h) * 128 + j) * 128;
+    float s[4], kk[4], qq[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { s[e] = __fmul_rn(S[l + 32 * e], eg); kk[e] = kr[l + 32 * e]; qq[e] = qr[l + 32 * e]; }
+    const float pred = warp_tree128(__fmul_rn(s[0], kk[0]), __fmul_rn(s[1], kk[1]), __fmul_rn(s[2], kk[2]), __fmul_rn(s[3], kk[3]));
+    const float u = __fmul_rn(bt, __fsub_rn(v[h * 128 + j], pred));
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { s[e] = fmaf(kk[e], u, s[e]); S[l + 32 * e] = s[e]; }
+    const float ov = warp_tree128(__fmul_rn(s[0], qq[0]), __fmul_rn(s[1], qq[1]), __fmul_rn(s[2], qq[2]), __fmul_rn(s[3], qq[3]));
+    if (l == 0) o[h * 128 + j] = __fmul_rn(ov, scale);
+}
+
+// per-head RMS (no weight; 128 squares, tree), * ssm_norm, swiglu(z, .), v-grouped permutation
+// (bonsai_forward.h:559-567, permute_vg.comp:32-42). One warp per SOURCE head.
+__global__ void k_gdn_out(int heads, int qk_heads, const float *__restrict__ o, const float *__restrict__ z,
+                          const float *__restrict__ ssm_norm, float eps, float *__restrict__ y) {
+    const int hs = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), l = threadIdx.x & 31;
+    if (hs >= heads) return;
+    const float *orow = o + hs * 128;
+    float e[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[i] = orow[l + 32 * i];
+    const float ss = warp_tree128(__fmul_rn(e[0], e[0]), __fmul_rn(e[1], e[1]), __fmul_rn(e[2], e[2]), __fmul_rn(e[3], e[3]));
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.0f), eps)));
+    // destination head hd reads source head hd/sub + nq*(hd%sub)  =>  source hs feeds hd = sub*(hs%nq) + hs/nq
+    const int sub = heads / qk_heads;
+    const int hd = sub * (hs % qk_heads) + hs / qk_heads;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int d = l + 32 * i;
+        const float n = __fmul_rn(__fmul_rn(e[i], inv), ssm_norm[d]);
+        y[hd * 128 + d] = __fmul_rn(silu_f(z[hs * 128 + d]), n);
+    }
+}
+
+// ---- attention ------------------------------------------------------------------------------------
+// q8_0 of one 32-element block held one value per lane (recipe: attn_norm_rope2.comp:39-49,184-217)
+__device__ __forceinline__ void q80_store(float v, int lane, int8_t *codes, uint16_t *scale) {
+    float amax = fabsf(v);
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, s));
+    const float d = amax > 1e-35f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    float r = roundf(__fmul_rn(v, id));
+    r = fminf(fmaxf(r, -127.0f), 127.0f);
+    codes[lane] = int8_t(int(r));
+    if (lane == 0) *scale = (uint16_t)float_to_half_bits(d);
+}
+
+// one CTA per head row (n_head query rows, then n_kv key rows); blockDim = head_dim = 256.
+// Query rows: RMS norm * weight, NeoX rope on the first n_rot dims, fp16 rounding, gate split.
+// Key rows: the same norm/rope, then cache insert (fp16 or q8_0) of K and of the raw V row.
+__global__ void __launch_bounds__(256) k_attn_prep(bnk::AttnDims a, const float *__restrict__ qg,
+                                                   const float *__restrict__ kin, const float *__restrict__ vin,
+                                                   const float *__restrict__ qn_w, const float *__restrict__ kn_w,
+                                                   const int *__restrict__ pos_ptr, bnk::KvLayer kv,
+                                                   float *__restrict__ q16f, float *__restrict__ gate) {
+    __shared__ float part[256];
+    __shared__ float sx[256];
+    const int d = threadIdx.x, hd = a.head_dim, w = blockIdx.x;
+    const bool is_q = w < a.n_head;
+    const int h = is_q ? w : w - a.n_head;
+    const int pos = pos_ptr[0];
+    const float *src = is_q ? qg + size_t(h) * 2 * hd : kin + size_t(h) * hd;
+    const float *nw = is_q ? qn_w : kn_w;
+    const float x = src[d];
+    sx[d] = x;
+    part[d] = __fmul_rn(x, x);
+    const float ss = block_tree_sum(part, 256);
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, float(hd)), a.eps)));
+    float y = __fmul_rn(__fmul_rn(x, inv), nw[d]);
+    if (d < a.n_rot) {
+        const int half = a.n_rot >> 1;
+        const bool low = d < half;
+        const int p = low ? d : d - half, pd = low ? d + half : d - half;
+        const float ex = __fdiv_rn(__fmul_rn(-2.0f, float(p)), float(a.n_rot));
+        const float th = float(pow(double(a.rope_base), double(ex)));
+        const float ang = __fmul_rn(float(pos), th);
+        const float c = float(cos(double(ang))), s = float(sin(double(ang)));
+        const float xp = __fmul_rn(__fmul_rn(sx[pd], inv), nw[pd]);
+        y = low ? __fsub_rn(__fmul_rn(y, c), __fmul_rn(xp, s)) : __fadd_rn(__fmul_rn(y, c), __fmul_rn(xp, s));
+    }
+    if (is_q) {
+        q16f[size_t(h) * hd + d] = __half2float(__float2half_rn(y));
+        gate[size_t(h) * hd + d] = src[hd + d];
+        return;
+    }
+    const size_t row = (size_t(pos) * a.n_kv + h) * hd;
+    const int lane = d & 31, blk = d >> 5;
+    if (a.k_mode == 1) reinterpret_cast<__half *>(kv.k_data)[row + d] = __float2half_rn(y);
+    else q80_store(y, lane, reinterpret_cast<int8_t *>(kv.k_data) + row + blk * 32, kv.k_scale + row / 32 + blk);
+    const float v = vin[size_t(h) * hd + d];
+    if (a.v_mode == 1) reinterpret_cast<__half *>(kv.v_data)[row + d] = __float2half_rn(v);
+    else q80_store(v, lane, reinterpret_cast<int8_t *>(kv.v_data) + row + blk * 32, kv.v_scale + row / 32 + blk);
+}
+
+// scores: one warp per key j, all gqa query heads of the kv head share the K row
+// (merge idea: attn_qk_softmax_gqa.glslh:15-24). lane l covers dims 8l..8l+7, then a 32-lane tree.
+template <int GQA>
+__global__ void __launch_bounds__(256) k_attn_scores(bnk::AttnDims a, const float *__restrict__ q16f,
+                                                     const int *__restrict__ pos_ptr, bnk::KvLayer kv,
+                                                     float *__restrict__ score) {
+    const int kvh = blockIdx.y, lane = threadIdx.x & 31, hd = a.head_dim;
+    const int nfill = pos_ptr[0] + 1;
+    const int j = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (j >= nfill) return;
+    const size_t row = (size_t(j) * a.n_kv + kvh) * hd;
+    float kf[8];
+    if (a.k_mode == 1) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(kv.k_data) + row + lane * 8);
+        const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h2[e]); kf[2 * e] = f.x; kf[2 * e + 1] = f.y; }
+    } else {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(reinterpret_cast<const int8_t *>(kv.k_data) + row + lane * 8);
+        const float sc = half_bits_to_float(kv.k_scale[row / 32 + (lane >> 2)]);
+        const int8_t *c = reinterpret_cast<const int8_t *>(&raw);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) kf[e] = __fmul_rn(sc, float(c[e]));
+    }
+#pragma unroll
+    for (int g = 0; g < GQA; ++g) {
+        const int h = kvh * GQA + g;
+        const float4 *qv = reinterpret_cast<const float4 *>(q16f + size_t(h) * hd + lane * 8);
+        const float4 q0 = qv[0], q1 = qv[1];
+        float acc = 0.0f;
+        acc = fmaf(q0.x, kf[0], acc); acc = fmaf(q0.y, kf[1], acc); acc = fmaf(q0.z, kf[2], acc); acc = fmaf(q0.w, kf[3], acc);
+        acc = fmaf(q1.x, kf[4], acc); acc = fmaf(q1.y, kf[5], acc); acc = fmaf(q1.z, kf[6], acc); acc = fmaf(q1.w, kf[7], acc);
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, s));
+        if (lane == 0) score[size_t(h) * a.cap + j] = acc;
+    }
+}
+
+// softmax per head (one CTA of 1024 threads): v = score*scale; max; p = exp(v - max); sum as
+// thread-strided ascending partials + fixed tree; probabilities rounded to fp16
+// (round_probs = 1, attn_qk_softmax.comp, attn_vk.h:175-190).
+__global__ void __launch_bounds__(1024) k_attn_softmax(bnk::AttnDims a, const int *__restrict__ pos_ptr,
+                                                       const float *__restrict__ score, float scale,
+                                                       float *__restrict__ p16f) {
+    __shared__ float red[1024];
+    const int h = blockIdx.x, t = threadIdx.x, nfill = pos_ptr[0] + 1;
+    const float *sr = score + size_t(h) * a.cap;
+    float mx = -INFINITY;
+    for (int j = t; j < nfill; j += 1024) mx = fmaxf(mx, __fmul_rn(sr[j], scale));
+    red[t] = mx;
+    for (int s = 512; s > 0; s >>= 1) { __syncthreads(); if (t < s) red[t] = fmaxf(red[t], red[t + s]); }
+    __syncthreads();
+    mx = red[0];
+    __syncthreads();
+    float sum = 0.0f;
+    float *pr = p16f + size_t(h) * a.cap;
+    for (int j = t; j < nfill; j += 1024) {
+        const float e = exp_f(__fsub_rn(__fmul_rn(sr[j], scale), mx));
+        pr[j] = e;
+        sum = __fadd_rn(sum, e);
+    }
+    red[t] = sum;
+    const float tot = block_tree_sum(red, 1024);
+    for (int j = t; j < nfill; j += 1024) pr[j] = __half2float(__float2half_rn(__fdiv_rn(pr[j], tot)));
+}
+
+// PV: grid (n_kv, splits); thread d = output dim; keys of the split ascending; acc = acc + p*v
+// (no fused multiply-add, runtime_vk/shaders/attn_pv_q8v.comp:85-112).
+template <int GQA>
+__global__ void __launch_bounds__(256) k_attn_pv(bnk::AttnDims a, const float *__restrict__ p16f,
+                                                 const int *__restrict__ pos_ptr, bnk::KvLayer kv, int splits,
+                                                 float *__restrict__ part) {
+    const int kvh = blockIdx.x, sp = blockIdx.y, d = threadIdx.x, hd = a.head_dim;
+    const int nfill = pos_ptr[0] + 1;
+    const int per = (nfill + splits - 1) / splits;
+    const int j0 = sp * per, j1 = min(nfill, j0 + per);
+    float acc[GQA];
+#pragma unroll
+    for (int g = 0; g < GQA; ++g) acc[g] = 0.0f;
+    for (int j = j0; j < j1; ++j) {
+        const size_t idx = (size_t(j) * a.n_kv + kvh) * hd + d;
+        float v;
+        if (a.v_mode == 1) v = __half2float(reinterpret_cast<const __half *>(kv.v_data)[idx]);
+        else v = __fmul_rn(half_bits_to_float(kv.v_scale[idx / 32]), float(reinterpret_cast<const int8_t *>(kv.v_data)[idx]));
+#pragma unroll
+        for (int g = 0; g < GQA; ++g) acc[g] = __fadd_rn(acc[g], __fmul_rn(p16f[size_t(kvh * GQA + g) * a.cap + j], v));
+    }
+#pragma unroll
+    for (int g = 0; g < GQA; ++g) part[(size_t(sp) * a.n_head + kvh * GQA + g) * hd + d] = acc[g];
+}
+
+// combine the splits ascending, then the sigmoid gate
+__global__ void k_attn_combine(bnk::AttnDims a, const float *__restrict__ part, int splits, const int *pos_ptr,
+                               const float *__restrict__ gate, float *__restrict__ pregate, float *__restrict__ gated) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x, n = a.n_head * a.head_dim;
+    if (i >= n) return;
+    const int nfill = pos_ptr[0] + 1;
+    const int per = (nfill + splits - 1) / splits;
+    float acc = part[i];
+    for (int s = 1; s < splits; ++s) if (s * per < nfill) acc = __fadd_rn(acc, part[size_t(s) * n + i]);
+    if (pregate) pregate[i] = acc;
+    gated[i] = __fmul_rn(acc, __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_f(-gate[i]))));
+}
+
+// ---- greedy pick: first maximum (Sampler::pick, runtime_vk/bonsai_forward.h:2568-2570) ----------
+__global__ void __launch_bounds__(1024) k_argmax_part(const float *__restrict__ x, int n, float *__restrict__ bv,
+                                                      int *__restrict__ bi) {
+    __shared__ float sv[1024];
+    __shared__ int si[1024];
+    const int t = threadIdx.x;
+    float best = -INFINITY; int idx = 0x7FFFFFFF;
+    for (int i = blockIdx.x * 1024 + t; i < n; i += gridDim.x * 1024) {
+        const float v = x[i];
+        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    }
+    sv[t] = best; si[t] = idx;
+    for (int s = 512; s > 0; s >>= 1) {
+        __syncthreads();
+        if (t < s) {
+            const float v = sv[t + s]; const int i = si[t + s];
+            if (v > sv[t] || (v == sv[t] && i < si[t])) { sv[t] = v; si[t] = i; }
+        }
+    }
+    if (t == 0) { bv[blockIdx.x] = sv[0]; bi[blockIdx.x] = si[0]; }
+}
+__global__ void k_argmax_final(const float *__restrict__ bv, const int *__restrict__ bi, int nparts, int *out) {
+    if (threadIdx.x != 0) return;
+    float best = bv[0]; int idx = bi[0];
+    for (int p = 1; p < nparts; ++p) if (bv[p] > best || (bv[p] == best && bi[p] < idx)) { best = bv[p]; idx = bi[p]; }
+    // a row of NaN or -inf never satisfies v > best: fall back to index 0 as the scalar loop does
+    out[0] = idx == 0x7FFFFFFF ? 0 : idx;
+}
+
+}  // namespace
+
+namespace bnk {
+
+void rotate_quant(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y, uint32_t *pack) {
+    const float inv = 1.0f / sqrtf(float(block));
+    uint32_t *q81 = pack, *table = pack ? pack + size_t(n / 128) * Q81_DWORDS : nullptr;
+    k_rotate_quant<<<n / block, 512, size_t(block) * 4 + 512, st>>>(x, signs, block, inv, y, q81, table); BN_COUNT(1);
+}
+void rotate_inv(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y) {
+    k_rotate_inv<<<n / block, 512, size_t(block) * 4, st>>>(x, signs, block, 1.0f / sqrtf(float(block)), y); BN_COUNT(1);
+}
+void embed_row(cudaStream_t st, const uint32_t *W, int K, const int *tok_ptr, float *out) {
+    k_embed_row<<<(K + 255) / 256, 256, 0, st>>>(W, K, tok_ptr, out); BN_COUNT(1);
+}
+void rms_norm(cudaStream_t st, const float *x, const float *w, int rows, int cols, float eps, float *y) {
+    k_rms_norm<<<rows, 256, 0, st>>>(x, w, cols, eps, y); BN_COUNT(1);
+}
+void add_inplace(cudaStream_t st, float *res, const float *d, int n) { k_add_inplace<<<(n + 255) / 256, 256, 0, st>>>(res, d, n); BN_COUNT(1); }
+void swiglu(cudaStream_t st, const float *a, const float *b, int n, float *y) { k_swiglu<<<(n + 255) / 256, 256, 0, st>>>(a, b, n, y); BN_COUNT(1); }
+void gemv_f32_small(cudaStream_t st, const float *W, int M, int K, const float *x, float *out) {
+    k_gemv_f32_small<<<(M + 7) / 8, 256, 0, st>>>(W, M, K, x, out); BN_COUNT(1);
+}
+void gdn_gates(cudaStream_t st, const float *alpha, const float *beta_raw, const float *dt_bias, const float *ssm_a, int n,
+               float *gate, float *beta) {
+    k_gdn_gates<<<1, 64, 0, st>>>(alpha, beta_raw, dt_bias, ssm_a, n, gate, beta); BN_COUNT(1);
+}
+void conv_silu(cudaStream_t st, const float *x, const float *w, float *hist, int channels, float *y) {
+    k_conv_silu<<<(channels + 255) / 256, 256, 0, st>>>(x, w, hist, channels, y); BN_COUNT(1);
+}
+void l2_norm_rows(cudaStream_t st, const float *x, int rows, float eps, float *y) {
+    k_l2_norm_rows<<<(rows + 7) / 8, 256, 0, st>>>(x, rows, eps, y); BN_COUNT(1);
+}
+void gdn_delta(cudaStream_t st, GdnDims d, const float *q, const float *k, const float *v, const float *gate,
+               const float *beta, float *state, float *o) {
+    k_gdn_delta<<<dim3(d.dim / 8, d.heads), 256, 0, st>>>(d.heads, d.qk_heads, q, k, v, gate, beta, state, o,
+                                                          1.0f / sqrtf(float(d.dim))); BN_COUNT(1);
+}
+void gdn_out(cudaStream_t st, GdnDims d, const float *o, const float *z, const float *ssm_norm, float eps, float *y) {
+    k_gdn_out<<<(d.heads + 7) / 8, 256, 0, st>>>(d.heads, d.qk_heads, o, z, ssm_norm, eps, y); BN_COUNT(1);
+}
+void attn_prep(cudaStream_t st, AttnDims a, const float *qg, const float *kin, const float *vin, const float *qn_w,
+               const float *kn_w, const int *pos_ptr, KvLayer kv, float *q16f, float *gate) {
+    k_attn_prep<<<a.n_head + a.n_kv, 256, 0, st>>>(a, qg, kin, vin, qn_w, kn_w, pos_ptr, kv, q16f, gate); BN_COUNT(1);
+}
+void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *gate, const int *pos_ptr, KvLayer kv,
+                 float *score, float *p16f, float *pv_part, int splits, float *pregate, float *gated) {
+    // grids are sized for the cache capacity; warps beyond the filled prefix return at once
+    k_attn_scores<4><<<dim3((a.cap + 7) / 8, a.n_kv), 256, 0, st>>>(a, q16f, pos_ptr, kv, score); BN_COUNT(1);
+    k_attn_softmax<<<a.n_head, 1024, 0, st>>>(a, pos_ptr, score, 1.0f / sqrtf(float(a.head_dim)), p16f); BN_COUNT(1);
+    k_attn_pv<4><<<dim3(a.n_kv, splits), 256, 0, st>>>(a, p16f, pos_ptr, kv, splits, pv_part); BN_COUNT(1);
+    const int n = a.n_head * a.head_dim;
+    k_attn_combine<<<(n + 255) / 256, 256, 0, st>>>(a, pv_part, splits, pos_ptr, gate, pregate, gated); BN_COUNT(1);
+}
+void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx) {
+    const int parts = 64;
+    k_argmax_part<<<parts, 1024, 0, st>>>(x, n, scratch_val, scratch_idx); BN_COUNT(1);
+    k_argmax_final<<<1, 32, 0, st>>>(scratch_val, scratch_idx, parts, out_idx); BN_COUNT(1);
+}
+
+}  // namespace bnk

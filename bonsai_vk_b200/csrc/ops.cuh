@@ -1,0 +1,51 @@
+// ops.cuh - internal launch helpers shared between the op-level entry points and the token schedule.
+#pragma once
+#include "common.cuh"
+
+// All helpers enqueue on `st` and return cudaGetLastError() state through bn_launch_check by the caller.
+namespace bnk {
+
+constexpr int Q81_DWORDS = 36;
+constexpr int BF_WORDS = 512;
+inline size_t act_pack_bytes(int K) { return size_t(K / 128) * (Q81_DWORDS + BF_WORDS) * 4; }
+
+// PTQ1_0 x q8_1 GEMV. out[M] final fp32. scratch: >= ceil(K/512) * M floats.
+void gemv_q81(cudaStream_t st, int sm_count, const uint32_t *W, int M, int K, const uint32_t *pack, float *out,
+              float *scratch, int32_t *dots);
+void act_quant_q81(cudaStream_t st, const float *x, int K, uint32_t *pack);
+
+// y = H(s . x) per `block`-wide chunk, then q8_1 + operand table into pack (pack may be null: rotate only,
+// y may be null when only the pack is wanted). n % block == 0, block = power of two in [128, 4096].
+void rotate_quant(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y, uint32_t *pack);
+// embedding side: y = s . H(x)
+void rotate_inv(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y);
+// PTQ1_0 row gather: out[K] = dequantised row `tok` (tok read from tok_ptr[0])
+void embed_row(cudaStream_t st, const uint32_t *W, int K, const int *tok_ptr, float *out);
+
+void rms_norm(cudaStream_t st, const float *x, const float *w, int rows, int cols, float eps, float *y);
+void add_inplace(cudaStream_t st, float *res, const float *d, int n);       // res = d + res
+void swiglu(cudaStream_t st, const float *a, const float *b, int n, float *y);
+void gemv_f32_small(cudaStream_t st, const float *W, int M, int K, const float *x, float *out);
+
+struct GdnDims { int heads, qk_heads, dim; };
+void gdn_gates(cudaStream_t st, const float *alpha, const float *beta_raw, const float *dt_bias, const float *ssm_a,
+               int n, float *gate, float *beta);
+void conv_silu(cudaStream_t st, const float *x, const float *w, float *hist, int channels, float *y);
+void l2_norm_rows(cudaStream_t st, const float *x, int rows, float eps, float *y);   // 128-wide rows
+void gdn_delta(cudaStream_t st, GdnDims d, const float *q, const float *k, const float *v, const float *gate,
+               const float *beta, float *state, float *o);
+// per-head RMS (no weight) * ssm_norm, swiglu(z, .), v-grouped permutation -> y[heads*dim]
+void gdn_out(cudaStream_t st, GdnDims d, const float *o, const float *z, const float *ssm_norm, float eps, float *y);
+
+struct AttnDims { int n_head, n_kv, head_dim, n_rot, cap; float eps, rope_base; int k_mode, v_mode; };
+struct KvLayer { void *k_data; uint16_t *k_scale; void *v_data; uint16_t *v_scale; };   // scales null in fp16 mode
+// norm + rope + fp16 rounding of q, gate split, K/V quantise + insert at *pos_ptr
+void attn_prep(cudaStream_t st, AttnDims a, const float *qg, const float *kin, const float *vin, const float *qn_w,
+               const float *kn_w, const int *pos_ptr, KvLayer kv, float *q16f, float *gate);
+// scores -> softmax (fp16-rounded probabilities) -> PV -> sigmoid gate. Scratch buffers sized by cap.
+void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *gate, const int *pos_ptr, KvLayer kv,
+                 float *score /*[nh][cap]*/, float *p16f /*[nh][cap]*/, float *pv_part /*[splits][nh][hd]*/, int splits,
+                 float *pregate /*[nh][hd] or null*/, float *gated);
+void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx);
+
+}  // namespace bnk

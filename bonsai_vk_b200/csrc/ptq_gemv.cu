@@ -20,81 +20,12 @@
 //
 // One warp owns one 128-weight block column and walks 16-row tiles: 32 integer multiplies, 8
 // byte-permutes and 8 mma.sync.m16n8k32.u8.s8 per 2048 weights.
-#include "common.cuh"
+#include "ops.cuh"
+#include "quant.cuh"
 
 namespace {
-
-constexpr int Q81_DWORDS = 36;        // block_q8_1_x4
-constexpr int BF_WORDS = 512;         // operand-table words per 128 activations: 8 mma x 32 lanes x 2
-
-__device__ __forceinline__ int elem_of(int byte, int t) {
-    return byte < 16 ? 16 * t + byte : (byte < 24 ? 80 + 8 * t + (byte - 16) : 120 + 2 * t + (byte - 24));
-}
-
-// Which two weight bytes feed A-register L (0..15) of a lane with thread-in-group `tig`, and at
-// which trit level. Registers 0..14 are three byte pairs x five levels; register 15 is the qh pair
-// at level tig. Byte pairs: (first dword low/high byte lanes, one half of a shared second dword).
-__device__ __forceinline__ void areg_bytes(int tig, int L, int &byteA, int &byteB, int &t) {
-    const int first = (tig == 0) ? 0 : (tig == 1) ? 2 : (tig == 2) ? 3 : 5;
-    const int second = tig < 2 ? 1 : 4;
-    if (L == 15) { byteA = 24; byteB = 25; t = tig; return; }
-    const int hd = L / 5;
-    t = L - 5 * hd;
-    if (hd == 0)      { byteA = 4 * first;     byteB = 4 * first + 2; }
-    else if (hd == 1) { byteA = 4 * first + 1; byteB = 4 * first + 3; }
-    else              { byteA = 4 * second + (tig & 1); byteB = 4 * second + 2 + (tig & 1); }
-}
-
-// coefficient of T(byte, t) in I_sb, split part 0 = floor(c/4), part 1 = c mod 4
-__device__ __forceinline__ int coef(const int8_t *q, int byte, int t, int sb, int part) {
-    const int tmax = byte < 24 ? 4 : 3;
-    const int e0 = elem_of(byte, t);
-    int c = ((e0 >> 5) == sb) ? int(q[e0]) : 0;
-    if (t < tmax) {
-        const int e1 = elem_of(byte, t + 1);
-        if ((e1 >> 5) == sb) c -= 3 * int(q[e1]);
-    }
-    return part == 0 ? (c >> 2) : (c & 3);
-}
-
-// One CTA (128 threads) per 128 activations: q8_1 quantisation (recipe of
-// runtime_vk/shaders/attn_norm_rope2.comp:39-49 applied per 32-element block, s = d*sum(q) as in
-// _mul_mat_vecq_ptq1_0.comp:8) and the tensor-core operand table.
-__global__ void __launch_bounds__(128) k_act_quant_q81(const float *__restrict__ x, uint32_t *__restrict__ q81,
-                                                       uint32_t *__restrict__ bf) {
-    __shared__ int8_t qs[128];
-    const int b = blockIdx.x, i = threadIdx.x, lane = i & 31, sb = i >> 5;
-    const float v = x[size_t(b) * 128 + i];
-    float amax = fabsf(v);
-#pragma unroll
-    for (int s = 16; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, s));
-    const float d = amax > 1e-35f ? __fdiv_rn(amax, 127.0f) : 0.0f;
-    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-    float r = roundf(__fmul_rn(v, id));
-    r = fminf(fmaxf(r, -127.0f), 127.0f);
-    const int qi = int(r);
-    int sum = qi;
-#pragma unroll
-    for (int s = 16; s > 0; s >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, s);
-    qs[i] = int8_t(qi);
-    uint32_t *blk = q81 + size_t(b) * Q81_DWORDS;
-    if (lane == 0) blk[sb] = float_to_half_bits(d) | (float_to_half_bits(__fmul_rn(d, float(sum))) << 16);
-    __syncthreads();
-    if (i < 32) blk[4 + i] = reinterpret_cast<const uint32_t *>(qs)[i];
-    uint32_t *out = bf + size_t(b) * BF_WORDS;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const int w = i + 128 * k;                 // word index: ((m*32 + lane)*2 + j)
-        const int j = w & 1, ln = (w >> 1) & 31, m = w >> 6;
-        const int g = ln >> 2, tig = ln & 3;
-        int byteA, byteB, t;
-        areg_bytes(tig, 2 * m + j, byteA, byteB, t);
-        const int csb = g >> 1, part = g & 1;
-        const uint32_t zA = uint32_t(coef(qs, byteA, t, csb, part)) & 0xFFu;
-        const uint32_t zB = uint32_t(coef(qs, byteB, t, csb, part)) & 0xFFu;
-        out[w] = (zA << 8) | (zB << 24);
-    }
-}
+using bnk::Q81_DWORDS;
+using bnk::BF_WORDS;
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -200,13 +131,49 @@ __global__ void k_sum_groups(const float *__restrict__ part, int M, int ngroups,
     out[row] = s;
 }
 
+// One CTA (128 threads) per 128 activations.
+__global__ void __launch_bounds__(128) k_act_quant_q81(const float *__restrict__ x, uint32_t *__restrict__ q81,
+                                                       uint32_t *__restrict__ bf) {
+    __shared__ int8_t qs[128];
+    const int b = blockIdx.x, i = threadIdx.x;
+    bnk::quant_block_128(x[size_t(b) * 128 + i], i, qs, q81 + size_t(b) * Q81_DWORDS, bf + size_t(b) * BF_WORDS, 1);
+}
+
 }  // namespace
+
+namespace bnk {
+
+void act_quant_q81(cudaStream_t st, const float *x, int K, uint32_t *pack) {
+    const int nb = K / 128;
+    k_act_quant_q81<<<nb, 128, 0, st>>>(x, pack, pack + size_t(nb) * Q81_DWORDS);
+    BN_COUNT(1);
+}
+
+void gemv_q81(cudaStream_t st, int sm_count, const uint32_t *W, int M, int K, const uint32_t *pack, float *out,
+              float *scratch, int32_t *dots) {
+    const int nb = K / 128, ngroups = (nb + 3) / 4;
+    const uint2 *bf = reinterpret_cast<const uint2 *>(pack + size_t(nb) * Q81_DWORDS);
+    const int ntiles = (M + 15) / 16;
+    // enough CTAs to cover the machine a few times over, but runs of tiles long enough to
+    // amortise the operand-table load
+    int want_x = (sm_count * 8 + ngroups - 1) / ngroups;
+    if (want_x < 1) want_x = 1;
+    int tiles_per_cta = (ntiles + want_x - 1) / want_x;
+    if (tiles_per_cta < 1) tiles_per_cta = 1;
+    dim3 grid((ntiles + tiles_per_cta - 1) / tiles_per_cta, ngroups);
+    if (dots) k_gemv_q81_direct<true><<<grid, 128, 0, st>>>(W, M, nb, pack, bf, scratch, tiles_per_cta, dots);
+    else k_gemv_q81_direct<false><<<grid, 128, 0, st>>>(W, M, nb, pack, bf, scratch, tiles_per_cta, nullptr);
+    k_sum_groups<<<(M + 255) / 256, 256, 0, st>>>(scratch, M, ngroups, out);
+    BN_COUNT(2);
+}
+
+}  // namespace bnk
 
 extern "C" {
 
 size_t bn_act_pack_bytes(int K) {
     if (K <= 0 || K % 128) return 0;
-    return size_t(K / 128) * (Q81_DWORDS + BF_WORDS) * 4;
+    return bnk::act_pack_bytes(K);
 }
 
 int bn_act_quant_q81(bn_ctx *ctx, const bn_buf *x, size_t x_off, int K, bn_buf *pack, size_t pack_off) {
@@ -214,10 +181,7 @@ int bn_act_quant_q81(bn_ctx *ctx, const bn_buf *x, size_t x_off, int K, bn_buf *
     BN_REQUIRE(K > 0 && K % 128 == 0, BN_ERR_ARG, "bn_act_quant_q81: K=%d must be a positive multiple of 128", K);
     BN_RANGE(x, x_off, size_t(K) * 4, 4, "bn_act_quant_q81 x");
     BN_RANGE(pack, pack_off, bn_act_pack_bytes(K), 16, "bn_act_quant_q81 pack");
-    const int nb = K / 128;
-    uint32_t *q81 = bn_ptr<uint32_t>(pack, pack_off);
-    uint32_t *bf = q81 + size_t(nb) * Q81_DWORDS;
-    k_act_quant_q81<<<nb, 128, 0, ctx->stream>>>(bn_ptr<float>(x, x_off), q81, bf);
+    bnk::act_quant_q81(ctx->stream, bn_ptr<float>(x, x_off), K, bn_ptr<uint32_t>(pack, pack_off));
     return bn_launch_check(ctx, "k_act_quant_q81");
 }
 
@@ -232,26 +196,9 @@ int bn_gemv_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const 
     if (dots) BN_RANGE(dots, dots_off, size_t(M) * nb * 16, 4, "bn_gemv_q81 dots");
     int rc = bn_scratch_reserve(ctx, size_t(ngroups) * M * 4);
     if (rc != BN_OK) return rc;
-    const uint32_t *q81 = bn_ptr<uint32_t>(pack, pack_off);
-    const uint2 *bf = reinterpret_cast<const uint2 *>(q81 + size_t(nb) * Q81_DWORDS);
-    const int ntiles = (M + 15) / 16;
-    // enough CTAs to cover the machine a few times over, but runs of tiles long enough to
-    // amortise the operand-table load
-    int want_x = (ctx->sm_count * 8 + ngroups - 1) / ngroups;
-    if (want_x < 1) want_x = 1;
-    int tiles_per_cta = (ntiles + want_x - 1) / want_x;
-    if (tiles_per_cta < 1) tiles_per_cta = 1;
-    dim3 grid((ntiles + tiles_per_cta - 1) / tiles_per_cta, ngroups);
-    if (dots)
-        k_gemv_q81_direct<true><<<grid, 128, 0, ctx->stream>>>(bn_ptr<uint32_t>(w, w_off), M, nb, q81, bf, ctx->scratch,
-                                                              tiles_per_cta, bn_ptr<int32_t>(dots, dots_off));
-    else
-        k_gemv_q81_direct<false><<<grid, 128, 0, ctx->stream>>>(bn_ptr<uint32_t>(w, w_off), M, nb, q81, bf, ctx->scratch,
-                                                               tiles_per_cta, nullptr);
-    rc = bn_launch_check(ctx, "k_gemv_q81_direct");
-    if (rc != BN_OK) return rc;
-    k_sum_groups<<<(M + 255) / 256, 256, 0, ctx->stream>>>(ctx->scratch, M, ngroups, bn_ptr<float>(out, out_off));
-    return bn_launch_check(ctx, "k_sum_groups");
+    bnk::gemv_q81(ctx->stream, ctx->sm_count, bn_ptr<uint32_t>(w, w_off), M, K, bn_ptr<uint32_t>(pack, pack_off),
+                  bn_ptr<float>(out, out_off), ctx->scratch, dots ? bn_ptr<int32_t>(dots, dots_off) : nullptr);
+    return bn_launch_check(ctx, "gemv_q81");
 }
 
 }  // extern "C"

@@ -16,6 +16,17 @@ class BonsaiError(RuntimeError):
     pass
 
 
+class HParamsC(C.Structure):
+    """Mirror of bn_hparams (include/bonsai_cuda.h)."""
+    _fields_ = [(n, C.c_int32) for n in (
+        "n_layer", "hidden", "ffn", "vocab", "n_head", "n_kv", "head_dim", "n_rot", "attn_interval",
+        "gdn_heads", "gdn_qk_heads", "gdn_dim", "hat_block", "act_mode", "k_mode", "v_mode", "cap")] + [
+        ("rms_eps", C.c_float), ("rope_base", C.c_float)]
+
+
+READ_LOGITS, READ_RESIDUAL, READ_GDN_STATE, READ_CONV_HIST, READ_K_DATA, READ_K_SCALE, READ_V_DATA, READ_V_SCALE = range(8)
+
+
 def load_library() -> C.CDLL:
     """Load the CUDA library. Raises if it has not been built (python bonsai_vk_b200/build.py)."""
     global _lib
@@ -48,6 +59,14 @@ def load_library() -> C.CDLL:
         "bn_act_pack_bytes": (sz, [i32]),
         "bn_act_quant_q81": (i32, [vp, vp, sz, i32, vp, sz]),
         "bn_gemv_q81": (i32, [vp, vp, sz, i32, i32, vp, sz, vp, sz, vp, sz]),
+        "bn_model_create": (i32, [vp, C.POINTER(HParamsC), C.POINTER(vp)]),
+        "bn_model_set_tensor": (i32, [vp, C.c_char_p, vp, sz, sz]),
+        "bn_model_set_signs": (i32, [vp, vp, sz, i32]),
+        "bn_model_finalize": (i32, [vp]),
+        "bn_model_reset": (i32, [vp]),
+        "bn_model_destroy": (None, [vp]),
+        "bn_model_token": (i32, [vp, i32, i32, i32, C.POINTER(i32)]),
+        "bn_model_read": (i32, [vp, i32, i32, vp, sz]),
     }
     for name, (res, args) in sig.items():
         f = getattr(lib, name)
@@ -162,3 +181,54 @@ class Context:
                  out_off: int = 0, dots: Buffer | None = None, dots_off: int = 0):
         _check(self.lib.bn_gemv_q81(self.h, w.h, w_off, M, K, pack.h, pack_off, out.h, out_off,
                                     dots.h if dots is not None else None, dots_off), "bn_gemv_q81")
+
+
+class Model:
+    """Device-resident model: tensors registered by GGUF name (reference: engine_init + fwd_init)."""
+
+    def __init__(self, ctx: Context, hp, tensors: dict, signs: np.ndarray):
+        self.ctx, self.hp = ctx, hp
+        lib = ctx.lib
+        hc = HParamsC(**{k: (float(v) if k in ("rms_eps", "rope_base") else int(v)) for k, v in hp.asdict().items()})
+        h = C.c_void_p()
+        _check(lib.bn_model_create(ctx.h, C.byref(hc), C.byref(h)), "bn_model_create")
+        self.h = h
+        al = lambda n: (n + 255) & ~255
+        total = sum(al(np.asarray(t).nbytes) for t in tensors.values()) + al(signs.nbytes)
+        self.weights = ctx.alloc(total)
+        off = 0
+        for name, t in tensors.items():
+            a = np.ascontiguousarray(t)
+            self.weights.upload(a, off)
+            _check(lib.bn_model_set_tensor(self.h, name.encode(), self.weights.h, off, a.nbytes), f"set_tensor {name}")
+            off += al(a.nbytes)
+        sg = np.ascontiguousarray(signs, dtype=np.int32)
+        self.weights.upload(sg, off)
+        _check(lib.bn_model_set_signs(self.h, self.weights.h, off, sg.size), "bn_model_set_signs")
+        _check(lib.bn_model_finalize(self.h), "bn_model_finalize")
+
+    def reset(self):
+        _check(self.ctx.lib.bn_model_reset(self.h), "bn_model_reset")
+
+    def token(self, tok: int, pos: int, stop_after: int = -1, want_next: bool = True):
+        nxt = C.c_int32(-1)
+        _check(self.ctx.lib.bn_model_token(self.h, tok, pos, stop_after, C.byref(nxt) if want_next else None),
+               "bn_model_token")
+        return int(nxt.value)
+
+    def read(self, what: int, dtype, count: int, index: int = 0) -> np.ndarray:
+        out = np.empty(count, dtype=dtype)
+        _check(self.ctx.lib.bn_model_read(self.h, what, index, out.ctypes.data_as(C.c_void_p), out.nbytes), "bn_model_read")
+        return out
+
+    def logits(self):
+        return self.read(READ_LOGITS, np.float32, self.hp.vocab)
+
+    def residual(self):
+        return self.read(READ_RESIDUAL, np.float32, self.hp.hidden)
+
+    def close(self):
+        if self.h is not None:
+            self.ctx.lib.bn_model_destroy(self.h)
+            self.h = None
+            self.weights.free()

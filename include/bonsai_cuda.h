@@ -85,6 +85,44 @@ int bn_act_quant_q81(bn_ctx *ctx, const bn_buf *x, size_t x_off, int K, bn_buf *
 int bn_gemv_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const bn_buf *pack,
                 size_t pack_off, bn_buf *out, size_t out_off, bn_buf *dots, size_t dots_off);
 
+/* ---- whole-token decode (reference: fwd_token, runtime_vk/bonsai_forward.h:664-758) ---------------
+ * The host registers every tensor of the GGUF by its GGUF name (PTQ1_0 tensors as the file's native
+ * 28-byte blocks, row-major, d0 = K; f32 tensors as they are) plus the prism.hadamard sign values,
+ * then finalises. Hyper-parameters mirror the GGUF keys the reference reads (bonsai_model.h:642-760). */
+typedef struct bn_model bn_model;
+typedef struct bn_hparams {
+    int32_t n_layer, hidden, ffn, vocab;
+    int32_t n_head, n_kv, head_dim, n_rot;    /* attention.head_count(_kv), key_length, rope.dimension_count */
+    int32_t attn_interval;                    /* full_attention_interval: block b is attention iff b % i == i-1 */
+    int32_t gdn_heads, gdn_qk_heads, gdn_dim; /* ssm.time_step_rank, ssm.group_count, ssm.state_size */
+    int32_t hat_block;                        /* prism.hadamard.block_size */
+    int32_t act_mode;                         /* 0 = q8_1 activations + integer dots */
+    int32_t k_mode, v_mode;                   /* KV cache: 0 = q8_0, 1 = fp16 */
+    int32_t cap;                              /* KV capacity in positions (reference: BONSAI_CAP, even) */
+    float rms_eps, rope_base;
+} bn_hparams;
+
+enum bn_read_what {
+    BN_READ_LOGITS = 0, BN_READ_RESIDUAL = 1, BN_READ_GDN_STATE = 2, BN_READ_CONV_HIST = 3,
+    BN_READ_K_DATA = 4, BN_READ_K_SCALE = 5, BN_READ_V_DATA = 6, BN_READ_V_SCALE = 7
+};
+
+int bn_model_create(bn_ctx *ctx, const bn_hparams *hp, bn_model **out);
+int bn_model_set_tensor(bn_model *m, const char *name, const bn_buf *buf, size_t off, size_t bytes);
+int bn_model_set_signs(bn_model *m, const bn_buf *buf, size_t off, int count);
+/* resolves every tensor the architecture needs (refuses with the missing name), allocates the
+ * activation arena, the KV cache and the recurrent state (reference: fwd_init, bonsai_forward.h:1490) */
+int bn_model_finalize(bn_model *m);
+/* zero KV, recurrent state and scratch (reference: fwd_reset_state, bonsai_forward.h:2624-2643) */
+int bn_model_reset(bn_model *m);
+void bn_model_destroy(bn_model *m);
+/* one token at absolute position pos. stop_after_block < 0 runs the whole network and the greedy pick
+ * (first maximum, as Sampler::pick with temp <= 0); >= 0 stops after that block (alignment harness,
+ * reference: BONSAI_LADDER / stop_at_block). next_tok may be NULL (nothing is copied back then). */
+int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *next_tok);
+/* copy a device-side result or state region to the host (reference: act_rd / kv_dump) */
+int bn_model_read(bn_model *m, int what, int index, void *dst, size_t bytes);
+
 #ifdef __cplusplus
 }
 #endif

@@ -170,3 +170,66 @@ class Oracle:
         y = np.empty_like(a)
         self.lib.bo_swiglu(_p(a), _p(b), a.size, _p(y))
         return y
+
+
+class OracleModel:
+    """Whole-token CPU oracle over the same tensors (borrowed numpy arrays kept alive here)."""
+
+    def __init__(self, hp, tensors: dict, signs, threads: int = 8):
+        self.o = load_oracle()
+        lib = self.o.lib
+        lib.bo_model_new.restype = C.c_void_p
+        ip = np.array([hp.n_layer, hp.hidden, hp.ffn, hp.vocab, hp.n_head, hp.n_kv, hp.head_dim, hp.n_rot,
+                       hp.attn_interval, hp.gdn_heads, hp.gdn_qk_heads, hp.gdn_dim, hp.hat_block, hp.act_mode,
+                       hp.k_mode, hp.v_mode], dtype=np.int32)
+        fp = np.array([hp.rms_eps, hp.rope_base], dtype=np.float32)
+        self.hp = hp
+        self.m = C.c_void_p(lib.bo_model_new(_p(ip), _p(fp)))
+        lib.bo_model_set_cap(self.m, hp.cap, threads)
+        self.keep = {n: np.ascontiguousarray(t) for n, t in tensors.items()}
+        for n, t in self.keep.items():
+            lib.bo_model_set_tensor(self.m, n.encode(), _p(t))
+        self.signs = np.ascontiguousarray(signs, dtype=np.int32)
+        lib.bo_model_set_signs(self.m, _p(self.signs))
+        lib.bo_model_reset(self.m)
+        for f in ("bo_model_gdn_state", "bo_model_conv_hist", "bo_model_kq", "bo_model_ks", "bo_model_vq",
+                  "bo_model_vs", "bo_model_k16", "bo_model_v16"):
+            getattr(lib, f).restype = C.c_void_p
+
+    def reset(self):
+        self.o.lib.bo_model_reset(self.m)
+
+    def token(self, tok, pos, stop_after=-1):
+        """Returns (logits or None, residual)."""
+        hp = self.hp
+        logits = np.empty(hp.vocab, dtype=np.float32) if stop_after < 0 else None
+        res = np.empty(hp.hidden, dtype=np.float32)
+        self.o.lib.bo_model_token(self.m, tok, pos, _p(logits), _p(res), stop_after)
+        return logits, res
+
+    def argmax(self, logits):
+        return int(self.o.lib.bo_argmax(_p(logits), logits.size))
+
+    def _view(self, fn, index, dtype, count):
+        ptr = fn(self.m, index)
+        return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(np.ctypeslib.as_ctypes_type(dtype))), shape=(count,)).copy()
+
+    def gdn_state(self, gi):
+        hp = self.hp
+        return self._view(self.o.lib.bo_model_gdn_state, gi, np.float32, hp.gdn_heads * hp.gdn_dim * hp.gdn_dim)
+
+    def conv_hist(self, gi):
+        return self._view(self.o.lib.bo_model_conv_hist, gi, np.float32, self.hp.qkv_dim * 3)
+
+    def kv(self, li):
+        hp = self.hp
+        n = hp.cap * hp.n_kv * hp.head_dim
+        L = self.o.lib
+        k = (self._view(L.bo_model_kq, li, np.int8, n), self._view(L.bo_model_ks, li, np.uint16, n // 32)) if hp.k_mode == 0 \
+            else (self._view(L.bo_model_k16, li, np.uint16, n), None)
+        v = (self._view(L.bo_model_vq, li, np.int8, n), self._view(L.bo_model_vs, li, np.uint16, n // 32)) if hp.v_mode == 0 \
+            else (self._view(L.bo_model_v16, li, np.uint16, n), None)
+        return k, v
+
+    def close(self):
+        self.o.lib.bo_model_free(self.m)

@@ -1,9 +1,10 @@
 """GPU parity of the PTQ1_0 x q8_1 GEMV (through the C ABI) against the CPU oracle.
 
 Bit-exact: q8_1 codes, fp16 d and s, and the int32 block dots I_sb. fp32 outputs: within 1e-5
-relative of the reference formula evaluated in double; because a row's terms can cancel, rows whose
-|reference| is below 1% of the RMS over rows are judged against that floor instead of their own
-magnitude (the floor is stated, not hidden). The oracle's own fp32 restatement uses the same
+relative of the reference formula evaluated in double. A row is a sum of group partials of magnitude
+~RMS(rows), each carrying fp32 rounding of 6e-8 x RMS, so a row whose terms cancel to below 5% of the
+RMS cannot meet 1e-5 of its own magnitude in fp32 at all; such rows are judged against 5% of the RMS
+instead (the floor is stated, not hidden). The oracle's own fp32 restatement uses the same
 operation order as the kernel, so that comparison is reported bit for bit as well.
 """
 import numpy as np
@@ -34,7 +35,7 @@ def _run(ctx, oracle, W, M, K, x, want_dots=True):
 
 def _check_rows(got, exact, tol=1e-5):
     rms = float(np.sqrt(np.mean(exact ** 2)))
-    denom = np.maximum(np.abs(exact), 0.01 * rms)
+    denom = np.maximum(np.abs(exact), 0.05 * rms)
     rel = np.abs(got.astype(np.float64) - exact) / np.where(denom > 0, denom, 1.0)
     return float(rel.max())
 

@@ -1,0 +1,104 @@
+"""Whole-token parity on a small synthetic model with every structural feature of the 9B:
+per-block residual ladder (the reference's BONSAI_LADDER idea, bonsai_forward.h:793), recurrent
+state and KV cache bytes, logits, and the greedy token stream over prompt + 48 decode steps."""
+import numpy as np
+import pytest
+
+from bonsai_vk_b200 import Model, synth
+from bonsai_vk_b200 import lib as L
+from tests._oracle import OracleModel
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float(np.max(np.abs(a.astype(np.float64) - b)) / (np.sqrt(np.mean(b.astype(np.float64) ** 2)) + 1e-30))
+
+
+@pytest.fixture(scope="module")
+def pair(ctx):
+    hp = synth.tiny()
+    tensors, signs = synth.make_model(hp, seed=1)
+    gm = Model(ctx, hp, tensors, signs)
+    om = OracleModel(hp, tensors, signs)
+    yield hp, gm, om
+    gm.close()
+    om.close()
+
+
+def test_block_ladder(pair):
+    """Residual after every block, first token and a later one (state and cache in play)."""
+    hp, gm, om = pair
+    toks = [3, 77, 1500, 12, 900]
+    for stop in range(hp.n_layer):
+        gm.reset(); om.reset()
+        for pos, t in enumerate(toks):
+            gm.token(t, pos, stop_after=stop, want_next=False)
+            _, ores = om.token(t, pos, stop_after=stop)
+            gres = gm.residual()
+            r = _rel(gres, ores)
+            assert r <= 1e-5, f"block {stop} pos {pos}: residual differs by {r:.3e} of RMS"
+
+
+def test_logits_states_and_stream(pair):
+    hp, gm, om = pair
+    gm.reset(); om.reset()
+    rng = np.random.default_rng(5)
+    prompt = [int(t) for t in rng.integers(0, hp.vocab, size=16)]
+    g_next = o_next = None
+    worst = 0.0
+    for pos, t in enumerate(prompt):
+        g_next = gm.token(t, pos)
+        ol, _ = om.token(t, pos)
+        o_next = om.argmax(ol)
+        worst = max(worst, _rel(gm.logits(), ol))
+    assert worst <= 1e-5, f"prefill logits differ by {worst:.3e} of RMS"
+    assert g_next == o_next
+    g_stream, o_stream, margins = [], [], []
+    gt, ot = g_next, o_next
+    for i in range(48):
+        pos = len(prompt) + i
+        g_stream.append(gt); o_stream.append(ot)
+        gt = gm.token(gt, pos)
+        ol, _ = om.token(ot, pos)
+        ot = om.argmax(ol)
+        top2 = np.partition(ol, -2)[-2:]
+        margins.append(float(top2[1] - top2[0]))
+        if g_stream[-1] == o_stream[-1]:
+            worst = max(worst, _rel(gm.logits(), ol))
+    assert g_stream == o_stream, f"greedy streams diverge; smallest top-2 margin {min(margins):.3e}"
+    assert worst <= 1e-5
+    # recurrent state and conv history after 64 tokens
+    n_gdn = sum(1 for b in range(hp.n_layer) if not hp.is_attn(b))
+    for gi in range(n_gdn):
+        gs = gm.read(L.READ_GDN_STATE, np.float32, hp.gdn_heads * hp.gdn_dim ** 2, gi)
+        assert _rel(gs, om.gdn_state(gi)) <= 1e-5
+        ch = gm.read(L.READ_CONV_HIST, np.float32, hp.qkv_dim * 3, gi)
+        assert _rel(ch, om.conv_hist(gi)) <= 1e-5
+    # KV cache bytes (q8_0 codes and fp16 scales) of the filled prefix
+    n_attn = hp.n_layer - n_gdn
+    fill = (len(prompt) + 48) * hp.n_kv * hp.head_dim
+    for li in range(n_attn):
+        (kq, ks), (vq, vs) = om.kv(li)
+        gk = gm.read(L.READ_K_DATA, np.int8, fill, li)
+        gv = gm.read(L.READ_V_DATA, np.int8, fill, li)
+        gks = gm.read(L.READ_K_SCALE, np.uint16, fill // 32, li)
+        gvs = gm.read(L.READ_V_SCALE, np.uint16, fill // 32, li)
+        # codes may differ by one step where an input sits within float rounding of a .5 boundary
+        assert np.mean(gk != kq[:fill]) < 1e-3 and np.max(np.abs(gk.astype(int) - kq[:fill])) <= 1
+        assert np.mean(gv != vq[:fill]) < 1e-3 and np.max(np.abs(gv.astype(int) - vq[:fill])) <= 1
+        assert np.mean(gks != ks[: fill // 32]) < 1e-2
+        assert np.mean(gvs != vs[: fill // 32]) < 1e-2
+
+
+def test_model_refuses_bad_calls(pair, ctx):
+    from bonsai_vk_b200 import BonsaiError
+    hp, gm, _ = pair
+    with pytest.raises(BonsaiError):
+        gm.token(hp.vocab, 0)          # token outside the vocabulary
+    with pytest.raises(BonsaiError):
+        gm.token(1, hp.cap)            # position beyond the KV capacity (reference: rc 7 context overflow)
+    tensors, signs = synth.make_model(hp, seed=1)
+    del tensors["blk.0.ffn_up.weight"]
+    with pytest.raises(BonsaiError, match="ffn_up"):
+        Model(ctx, hp, tensors, signs)
