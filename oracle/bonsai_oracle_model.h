@@ -28,6 +28,8 @@ struct HParams {
     float rms_eps = 1e-6f, rope_base = 1e7f;
     int act_mode = ACT_Q81, k_mode = KV_Q80, v_mode = KV_Q80;
     int cap = 256;          // KV capacity in positions
+    int attn_order = 0;     // 0: the reference's serial order; 1: the CUDA kernels' order (same arithmetic,
+    int pv_splits = 1;      //    sums regrouped as stated at attn_core_device_order)
     int threads = 8;        // row-parallel threads for the projections
     bool is_attn(int b) const { return (b % attn_interval) == attn_interval - 1; }   // bonsai_model.h:136-138
     int qkv_dim() const { return 2 * gdn_qk_heads * gdn_dim + gdn_heads * gdn_dim; }  // 8192
@@ -262,6 +264,69 @@ static inline void attn_core(const Model &m, int li, int pos, const float *q16f 
     }
 }
 
+// The same attention with the sums regrouped the way the CUDA kernels group them, so that a whole-token
+// run can be compared bit for bit. Differences from attn_core (each within float rounding of it):
+//   score: lane l of 32 covers dims 8l..8l+7 with an fmaf chain, lanes combined by the xor tree 16..1;
+//   sum of exp: thread t of 1024 adds keys t, t+1024, ... ascending, then the tree 512..1;
+//   PV: keys split into pv_splits contiguous runs of ceil(nfill/pv_splits), each run ascending with
+//       separate multiply and add, runs added ascending.
+static inline void attn_core_device_order(const Model &m, int li, int pos, const float *q16f, const float *gate,
+                                          float *gated, AttnTap *tap) {
+    const HParams &h = m.hp;
+    const int hd = h.head_dim, nkv = h.n_kv, nfill = pos + 1, gqa = h.n_head / h.n_kv;
+    const float scale = 1.0f / std::sqrt(float(hd));
+    std::vector<float> sc(nfill), p(nfill);
+    if (tap) { tap->pregate.assign(size_t(h.n_head) * hd, 0); tap->gated.assign(size_t(h.n_head) * hd, 0); tap->prob.assign(size_t(h.n_head) * nfill, 0); }
+    const int splits = h.pv_splits, per = (nfill + splits - 1) / splits;
+    for (int hh = 0; hh < h.n_head; ++hh) {
+        const int kv = hh / gqa;
+        const float *q = q16f + size_t(hh) * hd;
+        for (int j = 0; j < nfill; ++j) {
+            const size_t row = (size_t(j) * nkv + kv) * hd;
+            float part[32];
+            for (int l = 0; l < 32; ++l) {
+                float acc = 0.0f;
+                for (int e = 0; e < 8; ++e) {
+                    const int d = 8 * l + e;
+                    const float kvv = h.k_mode == KV_F16 ? f16_to_f32(m.k16[li][row + d])
+                                                        : f16_to_f32(m.ks[li][(row + d) / 32]) * float(m.kq[li][row + d]);
+                    acc = std::fmaf(q[d], kvv, acc);
+                }
+                part[l] = acc;
+            }
+            sc[j] = tree_sum(part, 32);
+        }
+        float mx = -INFINITY;
+        for (int j = 0; j < nfill; ++j) { const float v = sc[j] * scale; if (v > mx) mx = v; }
+        std::vector<float> red(1024, 0.0f);
+        for (int t = 0; t < 1024; ++t) {
+            float sum = 0.0f;
+            for (int j = t; j < nfill; j += 1024) { p[j] = exp_f(sc[j] * scale - mx); sum = sum + p[j]; }
+            red[t] = sum;
+        }
+        const float tot = tree_sum(red.data(), 1024);
+        for (int j = 0; j < nfill; ++j) { p[j] = p[j] / tot; if (tap) tap->prob[size_t(hh) * nfill + j] = p[j]; p[j] = f16_to_f32(f32_to_f16(p[j])); }
+        for (int d = 0; d < hd; ++d) {
+            float total = 0.0f;
+            for (int s = 0; s < splits; ++s) {
+                const int j0 = s * per, j1 = std::min(nfill, j0 + per);
+                if (s > 0 && j0 >= nfill) break;
+                float acc = 0.0f;
+                for (int j = j0; j < j1; ++j) {
+                    const size_t idx = (size_t(j) * nkv + kv) * hd + d;
+                    const float v = h.v_mode == KV_F16 ? f16_to_f32(m.v16[li][idx])
+                                                       : f16_to_f32(m.vs[li][idx / 32]) * float(m.vq[li][idx]);
+                    acc = acc + p[j] * v;
+                }
+                total = s == 0 ? acc : total + acc;
+            }
+            const float g = total * (1.0f / (1.0f + exp_f(-gate[size_t(hh) * hd + d])));
+            gated[size_t(hh) * hd + d] = g;
+            if (tap) { tap->pregate[size_t(hh) * hd + d] = total; tap->gated[size_t(hh) * hd + d] = g; }
+        }
+    }
+}
+
 // norm/rope/pack of q, k and the cache insert of k, v at `pos` (attn_norm_rope2.comp:117-218)
 static inline void attn_insert(Model &m, int li, int b, int pos, const float *qg /*[nh][2*hd]*/, const float *kin,
                                const float *vin, float *q16f, float *gate) {
@@ -296,7 +361,8 @@ static inline void attn_mix(Model &m, int b, int li, int pos, float *res, AttnTa
     project(m, m.ptq(B + "attn_k.weight"), KD, h.hidden, hr.data(), k.data());
     project(m, m.ptq(B + "attn_v.weight"), KD, h.hidden, hr.data(), v.data());
     attn_insert(m, li, b, pos, qg.data(), k.data(), v.data(), q16f.data(), gate.data());
-    attn_core(m, li, pos, q16f.data(), gate.data(), gout.data(), tap);
+    if (h.attn_order == 1) attn_core_device_order(m, li, pos, q16f.data(), gate.data(), gout.data(), tap);
+    else attn_core(m, li, pos, q16f.data(), gate.data(), gout.data(), tap);
     rot_project(m, B + "attn_output.weight", h.hidden, QD, gout.data(), m.signs, out.data());
     for (int i = 0; i < h.hidden; ++i) res[i] = out[i] + res[i];
 }

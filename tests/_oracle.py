@@ -175,7 +175,7 @@ class Oracle:
 class OracleModel:
     """Whole-token CPU oracle over the same tensors (borrowed numpy arrays kept alive here)."""
 
-    def __init__(self, hp, tensors: dict, signs, threads: int = 8):
+    def __init__(self, hp, tensors: dict, signs, threads: int = 8, attn_order: int = 1):
         self.o = load_oracle()
         lib = self.o.lib
         lib.bo_model_new.restype = C.c_void_p
@@ -186,6 +186,9 @@ class OracleModel:
         self.hp = hp
         self.m = C.c_void_p(lib.bo_model_new(_p(ip), _p(fp)))
         lib.bo_model_set_cap(self.m, hp.cap, threads)
+        # attn_order 1 = sums grouped as the CUDA kernels group them (pv split rule of bn_model_finalize)
+        self.pv_splits = 64 if hp.cap >= 4096 else (8 if hp.cap >= 512 else 1)
+        lib.bo_model_set_attn_order(self.m, attn_order, self.pv_splits)
         self.keep = {n: np.ascontiguousarray(t) for n, t in tensors.items()}
         for n, t in self.keep.items():
             lib.bo_model_set_tensor(self.m, n.encode(), _p(t))
@@ -195,6 +198,9 @@ class OracleModel:
         for f in ("bo_model_gdn_state", "bo_model_conv_hist", "bo_model_kq", "bo_model_ks", "bo_model_vq",
                   "bo_model_vs", "bo_model_k16", "bo_model_v16"):
             getattr(lib, f).restype = C.c_void_p
+
+    def set_attn_order(self, order, pv_splits=None):
+        self.o.lib.bo_model_set_attn_order(self.m, order, self.pv_splits if pv_splits is None else pv_splits)
 
     def reset(self):
         self.o.lib.bo_model_reset(self.m)

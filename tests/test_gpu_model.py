@@ -67,7 +67,11 @@ def test_logits_states_and_stream(pair):
         if g_stream[-1] == o_stream[-1]:
             worst = max(worst, _rel(gm.logits(), ol))
     assert g_stream == o_stream, f"greedy streams diverge; smallest top-2 margin {min(margins):.3e}"
-    assert worst <= 1e-5
+    # The oracle runs its attention sums in the kernels' grouping (tests/test_oracle_model.py shows that
+    # grouping within 1e-5 of the reference's serial order), every other op shares one operation order,
+    # so after 64 tokens the logits are expected to be the same floats, not merely close.
+    assert worst <= 1e-5, f"decode logits differ by {worst:.3e} of RMS"
+    assert np.array_equal(gm.logits().view(np.uint32), ol.view(np.uint32)), "final logits are not bit-identical"
     # recurrent state and conv history after 64 tokens
     n_gdn = sum(1 for b in range(hp.n_layer) if not hp.is_attn(b))
     for gi in range(n_gdn):
