@@ -1,0 +1,238 @@
+#!/usr/bin/env python
+"""Benchmark of the decode hot path: greedy decode tok/s of the 9B-shape synthetic PTQ1_0 model.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one decoded token (one pass of the whole-token schedule). Prints ONE JSON line.
+  value  - tok/s with everything resident in HBM: K tokens chained on the device (CUDA graph replay,
+           the greedy pick is fed back without a host round trip), CUDA events on the launch stream.
+  e2e    - the same metric through the per-token C-ABI call a host makes (bn_model_token): the token
+           id and position go host->device and the pick comes device->host inside the timed region.
+  roofline / cpu_baseline - see DESIGN.md ("Measurement").
+--impl reference times the reference's own CPU arithmetic for the path (dequantise + fp64 dot,
+oracle/_ref when built, else the oracle port) on all host cores, in the same unit.
+N > 1 (torchrun, one rank per GPU): independent replicas per rank until the layer pipeline lands.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PTQ_WEIGHTS_PER_TOKEN = 8_946_450_432 - 1_017_118_720      # the 201 projections (token_embd is only gathered)
+PTQ_BYTES_PER_TOKEN = 1_734_541_312                        # their PTQ1_0 bytes
+ALGO_BYTES_PER_TOKEN = 1_734_541_312 + 29_411_328 + 2 * 50_331_648 + 2 * 2_359_296 + 896   # + f32, GDN state r/w, conv
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return json.load(open(p)).get("hbm_gbs", 6650.0), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].startswith("Active") for r in self.rows)]
+        return {"sm_mhz": int(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def build_full_model(hp, seed=0):
+    """Seeded synthetic tensors of the 9B shape. Generating 8.9e9 trits in numpy takes minutes, so one
+    GDN block, one attention block and one FFN set are generated and reused for every block, and the two
+    vocab-sized tensors tile a 16384-row chunk. Timing depends on shapes and bytes, not on values."""
+    from bonsai_vk_b200 import ptq, synth
+    cache, tensors = {}, {}
+    for name, spec in synth.tensor_shapes(hp).items():
+        key = name.split(".", 2)[-1] if name.startswith("blk.") else name
+        if key in ("token_embd.weight", "output.weight"):
+            if "vocab" not in cache:
+                chunk = ptq.synth_matrix(np.random.default_rng(seed + 1), 16384, hp.hidden)
+                cache["vocab"] = np.concatenate([chunk] * ((hp.vocab + 16383) // 16384), axis=0)[:hp.vocab]
+            tensors[name] = cache["vocab"]
+            continue
+        if key not in cache:
+            cache[key] = synth.make_tensor(hp, seed, name, spec)
+        tensors[name] = cache[key]
+    return tensors, synth.make_signs(hp, seed)
+
+
+def cpu_gemv_tokens_per_s(seconds=12.0, threads=None):
+    """Reference CPU arithmetic for the path: dequantise each PTQ1_0 block and accumulate w*x in double
+    (runtime_vk/bonsai_weights.h:751-768 around ptq_dequant_ours). Bounded sample: repeated 4096x4096
+    GEMVs for about `seconds`; weights/s divided by the weights one token's 201 projections read."""
+    import ctypes as C
+    from bonsai_vk_b200 import ptq
+    from tests import _oracle
+    threads = threads or os.cpu_count() or 1
+    ref = _oracle.load_ref()
+    kind = "reference" if ref is not None else "port"
+    M = K = 4096
+    W = np.ascontiguousarray(ptq.synth_matrix(np.random.default_rng(0), M, K))
+    x = np.random.default_rng(1).standard_normal(K).astype(np.float32)
+    out = np.empty(M, dtype=np.float64)
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+    if ref is not None:
+        fn = lambda: ref.ref_gemv_dequant_f64(p(W), M, K, p(x), p(out), threads)
+    else:
+        o = _oracle.load_oracle()
+        fn = lambda: o.lib.bo_gemv_dequant_f64(p(W), M, K, p(x), p(out), threads)
+    fn()
+    n, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < seconds:
+        fn(); n += 1
+    dt = time.perf_counter() - t0
+    tok_s = (n * M * K / dt) / PTQ_WEIGHTS_PER_TOKEN
+    return {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": kind,
+            "sample": f"{n} x 4096x4096 PTQ1_0 GEMV (dequantise + fp64 dot) in {dt:.1f}s, scaled by the "
+                      f"{PTQ_WEIGHTS_PER_TOKEN} projection weights one token reads"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours")
+    a = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    K, Wm = max(1, a.steps), max(3, a.warmup)
+    base = {"metric": "decode tok/s, 9B ternary (PTQ1_0), B=1 greedy", "unit": "tok/s", "n_gpus": a.gpus, "steps": K,
+            "warmup": Wm, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8 trits x int8 -> int32, fp32 scale",
+            "data": "synthetic",
+            "config": {"workload": "config 3: 9B-shape synthetic PTQ1_0 model, 32 blocks (24 GDN + 8 attention), prompt 16 ids "
+                                   "then greedy decode, one stream per GPU", "l2": "inputs larger than L2 (1.87 GB read per token)",
+                       "kv": "q8_0 K and V", "act": "q8_1"}}
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        cb = cpu_gemv_tokens_per_s(seconds=min(60.0, 4.0 + 0.5 * (K + Wm)))
+        line = dict(base, impl="reference", value=cb["value"], ms_per_step=1000.0 / cb["value"], cpu_baseline=cb,
+                    e2e={"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                    gpu_launches=0)
+        print(json.dumps(line))
+        return
+
+    from bonsai_vk_b200 import Context, Model, synth
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = Context(local)
+    cap = max(256, (16 + 2 * (K + Wm) + 64 + 1) // 2 * 2)
+    hp = synth.HParams(cap=cap)
+    tensors, signs = build_full_model(hp)
+    m = Model(ctx, hp, tensors, signs)
+    del tensors
+    prompt = [int(t) for t in np.random.default_rng(42).integers(0, hp.vocab, size=16)]
+    nxt = 0
+    for pos, t in enumerate(prompt):
+        nxt = m.token(t, pos)
+    pos = len(prompt)
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+
+    # ---- device-resident: warm-up then K chained tokens ------------------------------------------------
+    out = m.decode(nxt, pos, Wm)
+    nxt, pos = out[-1], pos + Wm
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = ctx.event(), ctx.event()
+    barrier()
+    l0 = ctx.launches
+    ctx.record(e0)
+    m.decode(nxt, pos, K, fetch=False)
+    ctx.record(e1)
+    ms_dev = ctx.elapsed_ms(e0, e1)
+    barrier()
+    launches = ctx.launches - l0
+    clocks = sampler.stop()
+    pos += K
+    # ---- end to end through the per-token call ---------------------------------------------------------
+    t = 1
+    for i in range(3):
+        t = m.token(t, pos); pos += 1
+    barrier()
+    ctx.record(e0)
+    for i in range(K):
+        t = m.token(t, pos); pos += 1
+    ctx.record(e1)
+    ms_e2e = ctx.elapsed_ms(e0, e1)
+    barrier()
+
+    if dist is not None:
+        import torch
+        tt = torch.tensor([ms_dev, ms_e2e], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_dev, ms_e2e = float(tt[0]), float(tt[1])
+    tok_s = world * K / (ms_dev / 1000.0)
+    e2e_tok_s = world * K / (ms_e2e / 1000.0)
+
+    line = dict(base, value=tok_s, ms_per_step=ms_dev / K, clocks=clocks, gpu_launches=int(launches),
+                e2e={"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4})
+    if rank == 0:
+        peak, which = peaks()
+        # dominant kernel: the PTQ1_0 GEMV. Its 201 launches of one token, back to back over the model's own
+        # weights (1.73 GB, far larger than L2), timed with events on the launch stream.
+        ms_g = m.gemv_sweep_ms(reps=3)
+        ach = PTQ_BYTES_PER_TOKEN / (ms_g / 1000.0) / 1e9
+        line["roofline"] = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                            "traffic": None, "peak_source": which, "kernel": "PTQ1_0 x q8_1 GEMV (201 launches = one token's projections)",
+                            "algorithmic_bytes_per_launch": PTQ_BYTES_PER_TOKEN / 201.0,
+                            "avg_launch_us": ms_g * 1000.0 / 201.0,
+                            "token_level": {"algorithmic_bytes_per_token": ALGO_BYTES_PER_TOKEN,
+                                            "achieved_gbs": ALGO_BYTES_PER_TOKEN / (ms_dev / K / 1000.0) / 1e9,
+                                            "frac_of_measured": ALGO_BYTES_PER_TOKEN / (ms_dev / K / 1000.0) / 1e9 / peak,
+                                            "frac_of_8000": ALGO_BYTES_PER_TOKEN / (ms_dev / K / 1000.0) / 1e9 / 8000.0}}
+        line["cpu_baseline"] = cpu_gemv_tokens_per_s(seconds=12.0)
+        print(json.dumps(line))
+    m.close()
+    ctx.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

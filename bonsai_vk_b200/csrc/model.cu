@@ -20,7 +20,8 @@ struct bn_model {
     size_t arena_bytes = 0;
     float *RES, *AN, *X1, *X2, *QKV, *Z, *CONV, *L2, *O, *KBUF, *VBUF, *Q16F, *GATEB, *GOUT, *FG, *FU, *FS, *D, *LOGITS;
     float *ALPHA, *BETA, *G, *BT, *SCORE, *P16F, *PVPART, *AMV;
-    int *AMI, *TOK, *POS, *NEXT;
+    int *AMI, *TOK, *POS, *NEXT, *HIST, *STEP;
+    cudaGraphExec_t token_graph = nullptr;   // one whole token + advance, captured on first use
     uint32_t *PACK_H, *PACK_F;
     float *GEMV_SCRATCH;
     // persistent state
@@ -28,6 +29,7 @@ struct bn_model {
     char *kv = nullptr;
     size_t kv_layer_bytes = 0, kv_k_scale_off = 0, kv_v_off = 0, kv_v_scale_off = 0;
     int pv_splits = 1;
+    int graph_launches = 0;
     // resolved per-layer weights
     struct Layer {
         bool attn;
@@ -151,6 +153,16 @@ void enqueue_token(bn_model *m, int stop_after, bool want_logits) {
     bnk::argmax_first(st, m->LOGITS, h.vocab, m->NEXT, m->AMV, m->AMI);
 }
 
+// feed the greedy pick back as the next input, on the device
+__global__ void k_advance(int *tok, int *pos, const int *next, int *hist, int *step) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const int s = step[0];
+    hist[s] = next[0];
+    tok[0] = next[0];
+    pos[0] = pos[0] + 1;
+    step[0] = s + 1;
+}
+
 }  // namespace
 
 extern "C" {
@@ -262,6 +274,8 @@ int bn_model_finalize(bn_model *m) {
     slots.push_back({reinterpret_cast<void **>(&m->TOK), carve(256)});
     slots.push_back({reinterpret_cast<void **>(&m->POS), carve(256)});
     slots.push_back({reinterpret_cast<void **>(&m->NEXT), carve(256)});
+    slots.push_back({reinterpret_cast<void **>(&m->STEP), carve(256)});
+    slots.push_back({reinterpret_cast<void **>(&m->HIST), carve(size_t(h.cap) * 4)});
     slots.push_back({reinterpret_cast<void **>(&m->PACK_H), carve(bnk::act_pack_bytes(h.hidden))});
     slots.push_back({reinterpret_cast<void **>(&m->PACK_F), carve(bnk::act_pack_bytes(h.ffn))});
     m->arena_bytes = off;
@@ -310,6 +324,7 @@ void bn_model_destroy(bn_model *m) {
     if (m->gdn_state) cudaFree(m->gdn_state);
     if (m->conv_hist) cudaFree(m->conv_hist);
     if (m->kv) cudaFree(m->kv);
+    if (m->token_graph) cudaGraphExecDestroy(m->token_graph);
     delete m;
 }
 
@@ -330,6 +345,85 @@ int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *nex
         BN_CUDA(cudaMemcpyAsync(next_tok, m->NEXT, 4, cudaMemcpyDeviceToHost, st));
         BN_CUDA(cudaStreamSynchronize(st));
     }
+    return BN_OK;
+}
+
+int bn_model_decode(bn_model *m, int first_tok, int pos0, int n_steps, int *out_tokens) {
+    BN_REQUIRE(m && m->finalized, BN_ERR_STATE, "bn_model_decode: model not finalized");
+    const bn_hparams &h = m->hp;
+    BN_REQUIRE(first_tok >= 0 && first_tok < h.vocab, BN_ERR_ARG, "bn_model_decode: token %d outside vocab %d", first_tok, h.vocab);
+    BN_REQUIRE(n_steps > 0 && pos0 >= 0 && pos0 + n_steps <= h.cap, BN_ERR_BOUNDS,
+               "bn_model_decode: positions [%d, %d) do not fit the KV capacity %d", pos0, pos0 + n_steps, h.cap);
+    cudaStream_t st = m->ctx->stream;
+    if (!m->token_graph) {
+        cudaGraph_t g = nullptr;
+        const unsigned long long before = g_bn_launches;
+        BN_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        enqueue_token(m, -1, true);
+        k_advance<<<1, 32, 0, st>>>(m->TOK, m->POS, m->NEXT, m->HIST, m->STEP);
+        BN_COUNT(1);
+        cudaError_t e = cudaStreamEndCapture(st, &g);
+        if (e != cudaSuccess) return bn_cuda_fail(e, "cudaStreamEndCapture(token)");
+        m->graph_launches = int(g_bn_launches - before);
+        g_bn_launches = before;               // captured, not launched
+        e = cudaGraphInstantiate(&m->token_graph, g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) return bn_cuda_fail(e, "cudaGraphInstantiate(token)");
+    }
+    const int init[3] = {first_tok, pos0, 0};
+    BN_CUDA(cudaMemcpyAsync(m->TOK, &init[0], 4, cudaMemcpyHostToDevice, st));
+    BN_CUDA(cudaMemcpyAsync(m->POS, &init[1], 4, cudaMemcpyHostToDevice, st));
+    BN_CUDA(cudaMemcpyAsync(m->STEP, &init[2], 4, cudaMemcpyHostToDevice, st));
+    BN_CUDA(cudaStreamSynchronize(st));
+    for (int i = 0; i < n_steps; ++i) {
+        BN_CUDA(cudaGraphLaunch(m->token_graph, st));
+        BN_COUNT(m->graph_launches);
+    }
+    if (out_tokens) {
+        BN_CUDA(cudaMemcpyAsync(out_tokens, m->HIST, size_t(n_steps) * 4, cudaMemcpyDeviceToHost, st));
+        BN_CUDA(cudaStreamSynchronize(st));
+    }
+    return BN_OK;
+}
+
+int bn_model_gemv_sweep(bn_model *m, int reps, float *ms_per_sweep) {
+    BN_REQUIRE(m && m->finalized && ms_per_sweep && reps > 0, BN_ERR_ARG, "bn_model_gemv_sweep: bad argument");
+    const bn_hparams &h = m->hp;
+    const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D, IN = NH * D;
+    const int QD = h.n_head * h.head_dim, KD = h.n_kv * h.head_dim;
+    cudaStream_t st = m->ctx->stream;
+    const int sm = m->ctx->sm_count;
+    auto sweep = [&]() {
+        for (const bn_model::Layer &L : m->layers) {
+            if (L.attn) {
+                bnk::gemv_q81(st, sm, L.q_w, 2 * QD, h.hidden, m->PACK_H, m->QKV, m->GEMV_SCRATCH, nullptr);
+                bnk::gemv_q81(st, sm, L.k_w, KD, h.hidden, m->PACK_H, m->KBUF, m->GEMV_SCRATCH, nullptr);
+                bnk::gemv_q81(st, sm, L.v_w, KD, h.hidden, m->PACK_H, m->VBUF, m->GEMV_SCRATCH, nullptr);
+                bnk::gemv_q81(st, sm, L.o_w, h.hidden, QD, m->PACK_H, m->D, m->GEMV_SCRATCH, nullptr);
+            } else {
+                bnk::gemv_q81(st, sm, L.qkv, C, h.hidden, m->PACK_H, m->QKV, m->GEMV_SCRATCH, nullptr);
+                bnk::gemv_q81(st, sm, L.gate_w, IN, h.hidden, m->PACK_H, m->Z, m->GEMV_SCRATCH, nullptr);
+                bnk::gemv_q81(st, sm, L.ssm_out, h.hidden, IN, m->PACK_H, m->D, m->GEMV_SCRATCH, nullptr);
+            }
+            bnk::gemv_q81(st, sm, L.ffn_gate, h.ffn, h.hidden, m->PACK_H, m->FG, m->GEMV_SCRATCH, nullptr);
+            bnk::gemv_q81(st, sm, L.ffn_up, h.ffn, h.hidden, m->PACK_H, m->FU, m->GEMV_SCRATCH, nullptr);
+            bnk::gemv_q81(st, sm, L.ffn_down, h.hidden, h.ffn, m->PACK_F, m->D, m->GEMV_SCRATCH, nullptr);
+        }
+        bnk::gemv_q81(st, sm, m->out_w, h.vocab, h.hidden, m->PACK_H, m->LOGITS, m->GEMV_SCRATCH, nullptr);
+    };
+    cudaEvent_t e0, e1;
+    BN_CUDA(cudaEventCreate(&e0));
+    BN_CUDA(cudaEventCreate(&e1));
+    sweep();
+    BN_CUDA(cudaEventRecord(e0, st));
+    for (int r = 0; r < reps; ++r) sweep();
+    BN_CUDA(cudaEventRecord(e1, st));
+    BN_CUDA(cudaEventSynchronize(e1));
+    float ms = 0.0f;
+    BN_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *ms_per_sweep = ms / float(reps);
     return BN_OK;
 }
 

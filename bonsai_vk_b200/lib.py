@@ -67,6 +67,8 @@ def load_library() -> C.CDLL:
         "bn_model_destroy": (None, [vp]),
         "bn_model_token": (i32, [vp, i32, i32, i32, C.POINTER(i32)]),
         "bn_model_read": (i32, [vp, i32, i32, vp, sz]),
+        "bn_model_decode": (i32, [vp, i32, i32, i32, C.POINTER(i32)]),
+        "bn_model_gemv_sweep": (i32, [vp, i32, C.POINTER(C.c_float)]),
     }
     for name, (res, args) in sig.items():
         f = getattr(lib, name)
@@ -215,6 +217,17 @@ class Model:
         _check(self.ctx.lib.bn_model_token(self.h, tok, pos, stop_after, C.byref(nxt) if want_next else None),
                "bn_model_token")
         return int(nxt.value)
+
+    def decode(self, first_tok: int, pos0: int, n_steps: int, fetch: bool = True):
+        """n_steps greedy tokens chained on the device; returns the picks (or None when fetch=False)."""
+        out = (C.c_int32 * n_steps)() if fetch else None
+        _check(self.ctx.lib.bn_model_decode(self.h, first_tok, pos0, n_steps, out), "bn_model_decode")
+        return list(out) if fetch else None
+
+    def gemv_sweep_ms(self, reps: int = 3) -> float:
+        ms = C.c_float()
+        _check(self.ctx.lib.bn_model_gemv_sweep(self.h, reps, C.byref(ms)), "bn_model_gemv_sweep")
+        return float(ms.value)
 
     def read(self, what: int, dtype, count: int, index: int = 0) -> np.ndarray:
         out = np.empty(count, dtype=dtype)

@@ -120,6 +120,16 @@ void bn_model_destroy(bn_model *m);
  * (first maximum, as Sampler::pick with temp <= 0); >= 0 stops after that block (alignment harness,
  * reference: BONSAI_LADDER / stop_at_block). next_tok may be NULL (nothing is copied back then). */
 int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *next_tok);
+/* n_steps greedy tokens chained on the device: the pick of step i is the input of step i+1 with no
+ * host round trip (the reference reads 248 320 logits back and picks on the host every token,
+ * bonsai_forward.h:712,749,2890-2997). out_tokens (may be NULL) receives the n_steps picks; when it
+ * is NULL the call only enqueues and returns. The first call captures the token schedule into a CUDA
+ * graph. */
+int bn_model_decode(bn_model *m, int first_tok, int pos0, int n_steps, int *out_tokens);
+/* measurement aid (reference: the BONSAI_PIPE probe that brackets all 201 projections,
+ * runtime_vk/bonsai_vk.cpp:1452): launch every PTQ1_0 projection of one token back to back on the
+ * model's own weights, `reps` times after one untimed pass, and return the CUDA-event time of one sweep */
+int bn_model_gemv_sweep(bn_model *m, int reps, float *ms_per_sweep);
 /* copy a device-side result or state region to the host (reference: act_rd / kv_dump) */
 int bn_model_read(bn_model *m, int what, int index, void *dst, size_t bytes);
 

@@ -95,6 +95,27 @@ def test_logits_states_and_stream(pair):
         assert np.mean(gvs != vs[: fill // 32]) < 1e-2
 
 
+def test_device_chained_decode_matches_stepwise(pair):
+    """bn_model_decode (CUDA graph, pick fed back on the device) == bn_model_token called per step."""
+    hp, gm, om = pair
+    prompt = [11, 22, 33, 44]
+    gm.reset()
+    nxt = None
+    for pos, t in enumerate(prompt):
+        nxt = gm.token(t, pos)
+    step = []
+    t = nxt
+    for i in range(20):
+        t = gm.token(t, len(prompt) + i)
+        step.append(t)
+    gm.reset()
+    for pos, t in enumerate(prompt):
+        nxt2 = gm.token(t, pos)
+    assert nxt2 == nxt
+    assert gm.decode(nxt, len(prompt), 20) == step
+    assert gm.decode(step[-1], len(prompt) + 20, 5) is not None      # graph replays with a new start
+
+
 def test_model_refuses_bad_calls(pair, ctx):
     from bonsai_vk_b200 import BonsaiError
     hp, gm, _ = pair
