@@ -128,6 +128,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours")
+    ap.add_argument("--prompt", type=int, default=16, help="prompt length in tokens (16 = the benchmark config)")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -158,12 +159,12 @@ def main():
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ctx = Context(local)
-    cap = max(256, (16 + 2 * (K + Wm) + 64 + 1) // 2 * 2)
+    cap = max(256, (max(1, a.prompt) + 2 * (K + Wm) + 64 + 1) // 2 * 2)
     hp = synth.HParams(cap=cap)
     tensors, signs = build_full_model(hp)
     m = Model(ctx, hp, tensors, signs)
     del tensors
-    prompt = [int(t) for t in np.random.default_rng(42).integers(0, hp.vocab, size=16)]
+    prompt = [int(t) for t in np.random.default_rng(42).integers(0, hp.vocab, size=max(1, a.prompt))]
     nxt = 0
     for pos, t in enumerate(prompt):
         nxt = m.token(t, pos)

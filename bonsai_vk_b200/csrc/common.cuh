@@ -26,7 +26,12 @@ struct bn_ctx {
     // library-owned scratch for split-K partials, grown on demand (never during a graph capture)
     float *scratch;
     size_t scratch_bytes;
+    // row-tile arrival counters of the split-K finalisation (kept zero between kernels) and the
+    // device error word that bounded waits set
+    unsigned *counters;
+    int *err_dev;
 };
+constexpr int BN_MAX_TILES = 1 << 16;   // rows / 16 of the largest supported projection
 
 void bn_set_error(const char *fmt, ...);
 int bn_cuda_fail(cudaError_t e, const char *what);

@@ -69,6 +69,12 @@ int bn_init(int device, bn_ctx **out) {
     c->scratch_bytes = 0;
     e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) { delete c; return bn_cuda_fail(e, "cudaStreamCreate"); }
+    c->counters = nullptr;
+    c->err_dev = nullptr;
+    e = cudaMalloc(&c->counters, size_t(BN_MAX_TILES) * 4 + 256);
+    if (e != cudaSuccess) { delete c; return bn_cuda_fail(e, "cudaMalloc(counters)"); }
+    cudaMemset(c->counters, 0, size_t(BN_MAX_TILES) * 4 + 256);
+    c->err_dev = reinterpret_cast<int *>(c->counters + BN_MAX_TILES);
     *out = c;
     g_err[0] = 0;
     return BN_OK;
@@ -79,6 +85,7 @@ void bn_destroy(bn_ctx *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->counters) cudaFree(ctx->counters);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -147,6 +154,13 @@ int bn_memset(bn_ctx *ctx, bn_buf *dst, size_t off, int byte, size_t n) {
 int bn_sync(bn_ctx *ctx) {
     BN_REQUIRE(ctx, BN_ERR_ARG, "bn_sync: null context");
     BN_CUDA(cudaStreamSynchronize(ctx->stream));
+    int flag = 0;
+    BN_CUDA(cudaMemcpy(&flag, ctx->err_dev, 4, cudaMemcpyDeviceToHost));
+    if (flag) {
+        cudaMemset(ctx->err_dev, 0, 4);
+        bn_set_error("a bounded device-side wait gave up (copy ring); results of the last kernels are invalid");
+        return BN_ERR_TIMEOUT;
+    }
     return BN_OK;
 }
 

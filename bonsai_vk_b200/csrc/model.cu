@@ -2,6 +2,10 @@
 // gdn_block :509-573, attn_block :581-645, ffn_block :489-506) over tensors registered by GGUF name.
 #include "ops.cuh"
 
+#include "phase_gemv.cuh"
+
+#include <algorithm>
+#include <cstdlib>
 #include <map>
 #include <string>
 #include <vector>
@@ -25,11 +29,17 @@ struct bn_model {
     uint32_t *PACK_H, *PACK_F;
     float *GEMV_SCRATCH;
     // persistent state
-    float *gdn_state = nullptr, *conv_hist = nullptr;
+    float *gdn_state = nullptr, *conv_hist = nullptr, *conv_hist2 = nullptr;   // conv taps: two buffers (position parity)
+    int next_pos = 0;
     char *kv = nullptr;
     size_t kv_layer_bytes = 0, kv_k_scale_off = 0, kv_v_off = 0, kv_v_scale_off = 0;
     int pv_splits = 1;
     int graph_launches = 0;
+    bool fused = true;        // phase kernels (false: one kernel per reference dispatch, env BONSAI_NO_FUSE=1)
+    bool use_pdl = true;      // programmatic dependent launch between phases (env BONSAI_NO_PDL=1 turns it off)
+    cudaError_t launch_err = cudaSuccess;
+    unsigned long long *stamps = nullptr;   // profiling aid: 8 time stamps per phase kernel of one token
+    int stamp_idx = 0;
     // resolved per-layer weights
     struct Layer {
         bool attn;
@@ -78,14 +88,14 @@ bnk::KvLayer kv_layer(const bn_model *m, int li) {
     return k;
 }
 
-// rotate + quantise `x` (n values) with sign vector `sg`, then project with W (M rows)
+// ---- stand-alone kernel path (one kernel per reference dispatch; kept as the A/B control) ------------
 void rot_project(bn_model *m, const float *x, const int32_t *sg, int K, uint32_t *pack, const uint32_t *W, int M, float *out) {
     cudaStream_t st = m->ctx->stream;
     bnk::rotate_quant(st, x, sg, K, m->hp.hat_block, nullptr, pack);
     bnk::gemv_q81(st, m->ctx->sm_count, W, M, K, pack, out, m->GEMV_SCRATCH, nullptr);
 }
 
-void ffn(bn_model *m, const bn_model::Layer &L) {
+void ffn_plain(bn_model *m, const bn_model::Layer &L) {
     const bn_hparams &h = m->hp;
     cudaStream_t st = m->ctx->stream;
     bnk::rms_norm(st, m->RES, L.post_norm, 1, h.hidden, h.rms_eps, m->AN);
@@ -97,7 +107,18 @@ void ffn(bn_model *m, const bn_model::Layer &L) {
     bnk::add_inplace(st, m->RES, m->D, h.hidden);
 }
 
-void gdn(bn_model *m, const bn_model::Layer &L) {
+void gdn_core(bn_model *m, const bn_model::Layer &L) {
+    const bn_hparams &h = m->hp;
+    cudaStream_t st = m->ctx->stream;
+    const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D;
+    const bnk::GdnDims gd{NH, NQ, D};
+    bnk::conv_silu(st, m->QKV, L.conv_w, m->conv_hist + size_t(L.idx) * C * 3, C, m->CONV);
+    bnk::l2_norm_rows(st, m->CONV, 2 * NQ, 1e-12f, m->L2);
+    bnk::gdn_delta(st, gd, m->L2, m->L2 + NQ * D, m->CONV + 2 * NQ * D, m->G, m->BT,
+                   m->gdn_state + size_t(L.idx) * NH * D * D, m->O);
+}
+
+void gdn_plain(bn_model *m, const bn_model::Layer &L) {
     const bn_hparams &h = m->hp;
     cudaStream_t st = m->ctx->stream;
     const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D, IN = NH * D;
@@ -109,16 +130,13 @@ void gdn(bn_model *m, const bn_model::Layer &L) {
     bnk::rotate_quant(st, m->AN, m->signs, h.hidden, h.hat_block, nullptr, m->PACK_H);
     bnk::gemv_q81(st, m->ctx->sm_count, L.qkv, C, h.hidden, m->PACK_H, m->QKV, m->GEMV_SCRATCH, nullptr);
     bnk::gemv_q81(st, m->ctx->sm_count, L.gate_w, IN, h.hidden, m->PACK_H, m->Z, m->GEMV_SCRATCH, nullptr);
-    bnk::conv_silu(st, m->QKV, L.conv_w, m->conv_hist + size_t(L.idx) * C * 3, C, m->CONV);
-    bnk::l2_norm_rows(st, m->CONV, 2 * NQ, 1e-12f, m->L2);
-    bnk::gdn_delta(st, gd, m->L2, m->L2 + NQ * D, m->CONV + 2 * NQ * D, m->G, m->BT,
-                   m->gdn_state + size_t(L.idx) * NH * D * D, m->O);
+    gdn_core(m, L);
     bnk::gdn_out(st, gd, m->O, m->Z, L.ssm_norm, h.rms_eps, m->X1);
     rot_project(m, m->X1, m->signs, IN, m->PACK_H, L.ssm_out, h.hidden, m->D);
     bnk::add_inplace(st, m->RES, m->D, h.hidden);
 }
 
-void attn(bn_model *m, const bn_model::Layer &L) {
+void attn_plain(bn_model *m, const bn_model::Layer &L) {
     const bn_hparams &h = m->hp;
     cudaStream_t st = m->ctx->stream;
     const int QD = h.n_head * h.head_dim, KD = h.n_kv * h.head_dim;
@@ -130,9 +148,88 @@ void attn(bn_model *m, const bn_model::Layer &L) {
     bnk::gemv_q81(st, m->ctx->sm_count, L.k_w, KD, h.hidden, m->PACK_H, m->KBUF, m->GEMV_SCRATCH, nullptr);
     bnk::gemv_q81(st, m->ctx->sm_count, L.v_w, KD, h.hidden, m->PACK_H, m->VBUF, m->GEMV_SCRATCH, nullptr);
     bnk::attn_prep(st, a, m->QKV, m->KBUF, m->VBUF, L.q_norm, L.k_norm, m->POS, kv, m->Q16F, m->GATEB);
-    bnk::attn_decode(st, a, m->Q16F, m->GATEB, m->POS, kv, m->SCORE, m->P16F, m->PVPART, m->pv_splits, nullptr, m->GOUT);
+    bnk::attn_decode(st, a, m->Q16F, m->GATEB, m->POS, kv, m->SCORE, m->P16F, m->PVPART, m->pv_splits, nullptr, m->GOUT, true);
     rot_project(m, m->GOUT, m->signs, QD, m->PACK_H, L.o_w, h.hidden, m->D);
     bnk::add_inplace(st, m->RES, m->D, h.hidden);
+}
+
+// ---- fused path: one "phase" kernel per projection group (phase_gemv.cu) -------------------------------
+// Projections that read the same rotated input and lie back to back in device memory run as one matrix.
+bnk::PhaseArgs phase_base(bn_model *m, const uint32_t *W, int M, int K, const int32_t *sg) {
+    bnk::PhaseArgs a = {};
+    a.W = reinterpret_cast<const uint8_t *>(W); a.M = M; a.K = K;
+    a.signs = sg; a.hat_block = m->hp.hat_block; a.hat_inv = 1.0f / sqrtf(float(m->hp.hat_block)); a.eps = m->hp.rms_eps;
+    a.err = m->ctx->err_dev;
+    if (m->stamps && m->stamp_idx < 256) a.stamps = m->stamps + 8 * (m->stamp_idx++);
+    return a;
+}
+void launch(bn_model *m, const bnk::PhaseArgs &a) {
+    cudaError_t e = bnk::launch_phase(m->ctx->stream, m->ctx->sm_count, a, m->use_pdl);
+    if (e != cudaSuccess && m->launch_err == cudaSuccess) m->launch_err = e;
+}
+bool adjacent(const uint32_t *a, size_t a_bytes, const uint32_t *b) {
+    return reinterpret_cast<const uint8_t *>(a) + a_bytes == reinterpret_cast<const uint8_t *>(b);
+}
+
+void ffn_fused(bn_model *m, const bn_model::Layer &L) {
+    const bn_hparams &h = m->hp;
+    bnk::PhaseArgs a = phase_base(m, L.ffn_gate, h.ffn, h.hidden, m->signs);
+    a.pro = bnk::PRO_NORM; a.x0 = m->RES; a.w = L.post_norm;
+    if (adjacent(L.ffn_gate, ptq_bytes(h.ffn, h.hidden), L.ffn_up)) { a.M = 2 * h.ffn; a.out = m->FG; launch(m, a); }
+    else { a.out = m->FG; launch(m, a); a.W = reinterpret_cast<const uint8_t *>(L.ffn_up); a.out = m->FU; launch(m, a); }
+    bnk::PhaseArgs d = phase_base(m, L.ffn_down, h.hidden, h.ffn, m->signs + h.hidden);
+    // silu needs a double-precision exp per element: computed once by a small kernel, not by every CTA
+    bnk::swiglu(m->ctx->stream, m->FG, m->FU, h.ffn, m->FS);
+    d.pro = bnk::PRO_PLAIN; d.x0 = m->FS;
+    d.resid_in = m->RES; d.resid_out = m->RES;
+    launch(m, d);
+}
+
+void gdn_fused(bn_model *m, const bn_model::Layer &L) {
+    const bn_hparams &h = m->hp;
+    const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D, IN = NH * D;
+    bnk::PhaseArgs a = phase_base(m, L.qkv, C, h.hidden, m->signs);
+    a.pro = bnk::PRO_NORM; a.x0 = m->RES; a.w = L.attn_norm;
+    a.inv_out = m->G + 48;      // the norm factor, for the layer core's two small projections
+    if (adjacent(L.qkv, ptq_bytes(C, h.hidden), L.gate_w)) { a.M = C + IN; a.out = m->QKV; launch(m, a); }
+    else {
+        a.out = m->QKV; launch(m, a);
+        a.inv_out = nullptr; a.W = reinterpret_cast<const uint8_t *>(L.gate_w); a.M = IN; a.out = m->Z; launch(m, a);
+    }
+    {
+        const bnk::GdnDims gd{NH, NQ, D};
+        float *h0 = m->conv_hist + size_t(L.idx) * C * 3, *h1 = m->conv_hist2 + size_t(L.idx) * C * 3;
+        bnk::gdn_core_fused(m->ctx->stream, gd, h.hidden, m->QKV, L.conv_w, h0, h1, m->POS, m->RES, m->G + 48, L.attn_norm,
+                            L.alpha_w, L.beta_w, L.dt_bias, L.ssm_a, m->gdn_state + size_t(L.idx) * NH * D * D, m->O);
+    }
+    bnk::PhaseArgs o = phase_base(m, L.ssm_out, h.hidden, IN, m->signs);
+    bnk::gdn_out(m->ctx->stream, bnk::GdnDims{NH, NQ, D}, m->O, m->Z, L.ssm_norm, h.rms_eps, m->X1);
+    o.pro = bnk::PRO_PLAIN; o.x0 = m->X1;
+    o.resid_in = m->RES; o.resid_out = m->RES;
+    launch(m, o);
+}
+
+void attn_fused(bn_model *m, const bn_model::Layer &L) {
+    const bn_hparams &h = m->hp;
+    cudaStream_t st = m->ctx->stream;
+    const int QD = h.n_head * h.head_dim, KD = h.n_kv * h.head_dim;
+    const bnk::AttnDims ad = attn_dims(m);
+    const bnk::KvLayer kv = kv_layer(m, L.idx);
+    bnk::PhaseArgs a = phase_base(m, L.q_w, 2 * QD, h.hidden, m->signs);
+    a.pro = bnk::PRO_NORM; a.x0 = m->RES; a.w = L.attn_norm;
+    if (adjacent(L.q_w, ptq_bytes(2 * QD, h.hidden), L.k_w) && adjacent(L.k_w, ptq_bytes(KD, h.hidden), L.v_w)) {
+        a.M = 2 * QD + 2 * KD; a.out = m->QKV; launch(m, a);
+    } else {
+        a.out = m->QKV; launch(m, a);
+        a.W = reinterpret_cast<const uint8_t *>(L.k_w); a.M = KD; a.out = m->KBUF; launch(m, a);
+        a.W = reinterpret_cast<const uint8_t *>(L.v_w); a.out = m->VBUF; launch(m, a);
+    }
+    bnk::attn_prep(st, ad, m->QKV, m->KBUF, m->VBUF, L.q_norm, L.k_norm, m->POS, kv, m->Q16F, m->GATEB);
+    bnk::attn_decode(st, ad, m->Q16F, m->GATEB, m->POS, kv, m->SCORE, m->P16F, m->PVPART, m->pv_splits, nullptr, m->GOUT, true);
+    bnk::PhaseArgs o = phase_base(m, L.o_w, h.hidden, QD, m->signs);
+    o.pro = bnk::PRO_PLAIN; o.x0 = m->GOUT;
+    o.resid_in = m->RES; o.resid_out = m->RES;
+    launch(m, o);
 }
 
 // enqueue one token: TOK[0], POS[0] hold the token id and its absolute position
@@ -143,13 +240,19 @@ void enqueue_token(bn_model *m, int stop_after, bool want_logits) {
     bnk::rotate_inv(st, m->X1, m->signs, h.hidden, h.hat_block, m->RES);
     for (int b = 0; b < h.n_layer; ++b) {
         const bn_model::Layer &L = m->layers[b];
-        if (L.attn) attn(m, L); else gdn(m, L);
-        ffn(m, L);
+        if (m->fused) { if (L.attn) attn_fused(m, L); else gdn_fused(m, L); ffn_fused(m, L); }
+        else { if (L.attn) attn_plain(m, L); else gdn_plain(m, L); ffn_plain(m, L); }
         if (b == stop_after) return;
     }
     if (!want_logits) return;
-    bnk::rms_norm(st, m->RES, m->out_norm, 1, h.hidden, h.rms_eps, m->AN);
-    rot_project(m, m->AN, m->signs, h.hidden, m->PACK_H, m->out_w, h.vocab, m->LOGITS);
+    if (m->fused) {
+        bnk::PhaseArgs a = phase_base(m, m->out_w, h.vocab, h.hidden, m->signs);
+        a.pro = bnk::PRO_NORM; a.x0 = m->RES; a.w = m->out_norm; a.out = m->LOGITS;
+        launch(m, a);
+    } else {
+        bnk::rms_norm(st, m->RES, m->out_norm, 1, h.hidden, h.rms_eps, m->AN);
+        rot_project(m, m->AN, m->signs, h.hidden, m->PACK_H, m->out_w, h.vocab, m->LOGITS);
+    }
     bnk::argmax_first(st, m->LOGITS, h.vocab, m->NEXT, m->AMV, m->AMI);
 }
 
@@ -263,9 +366,9 @@ int bn_model_finalize(bn_model *m) {
     std::vector<Slot> slots;
     auto F = [&](float *&p, size_t n) { slots.push_back({reinterpret_cast<void **>(&p), carve(n * 4)}); };
     F(m->RES, h.hidden); F(m->AN, h.hidden); F(m->X1, h.hidden); F(m->X2, h.hidden);
-    F(m->QKV, std::max(C, 2 * QD)); F(m->Z, IN); F(m->CONV, C); F(m->L2, 2 * NQ * D); F(m->O, IN);
-    F(m->KBUF, KD); F(m->VBUF, KD); F(m->Q16F, QD); F(m->GATEB, QD); F(m->GOUT, QD);
-    F(m->FG, h.ffn); F(m->FU, h.ffn); F(m->FS, h.ffn); F(m->D, h.hidden); F(m->LOGITS, h.vocab);
+    F(m->QKV, std::max(C + IN, 2 * QD + 2 * KD)); m->Z = nullptr; F(m->CONV, C); F(m->L2, 2 * NQ * D); F(m->O, IN);
+    F(m->Q16F, QD); F(m->GATEB, QD); F(m->GOUT, QD);
+    F(m->FG, 2 * size_t(h.ffn)); F(m->FS, h.ffn); F(m->D, h.hidden); F(m->LOGITS, h.vocab);
     F(m->ALPHA, 64); F(m->BETA, 64); F(m->G, 64); F(m->BT, 64);
     F(m->SCORE, size_t(h.n_head) * h.cap); F(m->P16F, size_t(h.n_head) * h.cap);
     F(m->PVPART, size_t(m->pv_splits) * QD); F(m->AMV, 64);
@@ -282,10 +385,18 @@ int bn_model_finalize(bn_model *m) {
     BN_CUDA(cudaSetDevice(m->ctx->device));
     BN_CUDA(cudaMalloc(&m->arena, m->arena_bytes));
     for (auto &s : slots) *s.p = m->arena + s.o;
+    m->Z = m->QKV + C;               // [qkv | gate] of a GDN block, [q | k | v] of an attention block
+    m->KBUF = m->QKV + 2 * QD;
+    m->VBUF = m->KBUF + KD;
+    m->FU = m->FG + h.ffn;           // [gate | up]
+    m->fused = getenv("BONSAI_NO_FUSE") == nullptr && bnk::phase_supported(h.hidden, h.hidden, h.hat_block) &&
+               bnk::phase_supported(h.hidden, h.ffn, h.hat_block);
+    m->use_pdl = getenv("BONSAI_NO_PDL") == nullptr;
     // persistent state
     if (m->n_gdn) {
         BN_CUDA(cudaMalloc(&m->gdn_state, size_t(m->n_gdn) * NH * D * D * 4));
-        BN_CUDA(cudaMalloc(&m->conv_hist, size_t(m->n_gdn) * C * 3 * 4));
+        BN_CUDA(cudaMalloc(&m->conv_hist, size_t(m->n_gdn) * C * 3 * 4 * 2));
+        m->conv_hist2 = m->conv_hist + size_t(m->n_gdn) * C * 3;
     }
     if (m->n_attn) {
         const size_t n = size_t(h.cap) * KD;
@@ -310,7 +421,7 @@ int bn_model_reset(bn_model *m) {
     BN_CUDA(cudaMemsetAsync(m->arena, 0, m->arena_bytes, st));
     if (m->n_gdn) {
         BN_CUDA(cudaMemsetAsync(m->gdn_state, 0, size_t(m->n_gdn) * NH * D * D * 4, st));
-        BN_CUDA(cudaMemsetAsync(m->conv_hist, 0, size_t(m->n_gdn) * C * 3 * 4, st));
+        BN_CUDA(cudaMemsetAsync(m->conv_hist, 0, size_t(m->n_gdn) * C * 3 * 4 * 2, st));
     }
     if (m->n_attn) BN_CUDA(cudaMemsetAsync(m->kv, 0, m->kv_layer_bytes * m->n_attn, st));
     return BN_OK;
@@ -338,8 +449,11 @@ int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *nex
     BN_CUDA(cudaMemcpyAsync(m->TOK, &tp[0], 4, cudaMemcpyHostToDevice, st));
     BN_CUDA(cudaMemcpyAsync(m->POS, &tp[1], 4, cudaMemcpyHostToDevice, st));
     BN_CUDA(cudaStreamSynchronize(st));     // tp lives on this stack frame
+    m->next_pos = pos + 1;
     enqueue_token(m, stop_after_block, true);
     cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = m->launch_err;
+    m->launch_err = cudaSuccess;
     if (e != cudaSuccess) return bn_cuda_fail(e, "token schedule");
     if (next_tok) {
         BN_CUDA(cudaMemcpyAsync(next_tok, m->NEXT, 4, cudaMemcpyDeviceToHost, st));
@@ -375,6 +489,7 @@ int bn_model_decode(bn_model *m, int first_tok, int pos0, int n_steps, int *out_
     BN_CUDA(cudaMemcpyAsync(m->POS, &init[1], 4, cudaMemcpyHostToDevice, st));
     BN_CUDA(cudaMemcpyAsync(m->STEP, &init[2], 4, cudaMemcpyHostToDevice, st));
     BN_CUDA(cudaStreamSynchronize(st));
+    m->next_pos = pos0 + n_steps;
     for (int i = 0; i < n_steps; ++i) {
         BN_CUDA(cudaGraphLaunch(m->token_graph, st));
         BN_COUNT(m->graph_launches);
@@ -427,6 +542,31 @@ int bn_model_gemv_sweep(bn_model *m, int reps, float *ms_per_sweep) {
     return BN_OK;
 }
 
+int bn_model_profile_token(bn_model *m, int tok, int pos, unsigned long long *stamps_out, int max_phases, int *n_phases) {
+    BN_REQUIRE(m && m->finalized && stamps_out && n_phases, BN_ERR_ARG, "bn_model_profile_token: bad argument");
+    BN_REQUIRE(pos >= 0 && pos < m->hp.cap && tok >= 0 && tok < m->hp.vocab, BN_ERR_ARG, "bn_model_profile_token: bad token or position");
+    if (!m->stamps) BN_CUDA(cudaMalloc(&m->stamps, 256 * 8 * sizeof(unsigned long long)));
+    BN_CUDA(cudaMemset(m->stamps, 0, 256 * 8 * sizeof(unsigned long long)));
+    cudaStream_t st = m->ctx->stream;
+    const int tp[2] = {tok, pos};
+    BN_CUDA(cudaMemcpyAsync(m->TOK, &tp[0], 4, cudaMemcpyHostToDevice, st));
+    BN_CUDA(cudaMemcpyAsync(m->POS, &tp[1], 4, cudaMemcpyHostToDevice, st));
+    BN_CUDA(cudaStreamSynchronize(st));
+    m->stamp_idx = 0;
+    unsigned long long *keep = m->stamps;
+    enqueue_token(m, -1, true);
+    const int n = m->stamp_idx;
+    m->stamps = nullptr;                 // later tokens run unstamped
+    BN_CUDA(cudaStreamSynchronize(st));
+    *n_phases = n < max_phases ? n : max_phases;
+    BN_CUDA(cudaMemcpy(stamps_out, keep, size_t(*n_phases) * 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    m->stamps = keep;
+    cudaMemset(keep, 0, 8);
+    m->stamps = nullptr;
+    cudaFree(keep);
+    return BN_OK;
+}
+
 int bn_model_read(bn_model *m, int what, int index, void *dst, size_t bytes) {
     BN_REQUIRE(m && m->finalized && dst, BN_ERR_STATE, "bn_model_read: bad state or null destination");
     const bn_hparams &h = m->hp;
@@ -442,7 +582,8 @@ int bn_model_read(bn_model *m, int what, int index, void *dst, size_t bytes) {
             src = m->gdn_state + size_t(index) * NH * D * D; have = size_t(NH) * D * D * 4; break;
         case BN_READ_CONV_HIST:
             BN_REQUIRE(index >= 0 && index < m->n_gdn, BN_ERR_ARG, "bn_model_read: gdn layer %d out of range", index);
-            src = m->conv_hist + size_t(index) * C * 3; have = size_t(C) * 3 * 4; break;
+            // fused path: the taps the next token will read live in the buffer of its position parity
+            src = ((m->fused && (m->next_pos & 1)) ? m->conv_hist2 : m->conv_hist) + size_t(index) * C * 3; have = size_t(C) * 3 * 4; break;
         case BN_READ_K_DATA: case BN_READ_K_SCALE: case BN_READ_V_DATA: case BN_READ_V_SCALE: {
             BN_REQUIRE(index >= 0 && index < m->n_attn, BN_ERR_ARG, "bn_model_read: attention layer %d out of range", index);
             const bnk::KvLayer kv = kv_layer(m, index);

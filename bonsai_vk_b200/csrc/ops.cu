@@ -207,6 +207,115 @@ __global__ void __launch_bounds__(256) k_gdn_delta(int heads, int qk_heads, cons
     if (l == 0) o[h * 128 + j] = __fmul_rn(ov, scale);
 }
 
+// Fused gated-delta-net core of one layer: the two small fp32 projections of the normed residual and their
+// gate functions (bonsai_forward.h:523-535), conv + silu of the channels this CTA needs, L2 norms of its q/k
+// head, and the delta rule on 32 state rows. grid (128/32 row chunks, v-heads), 256 threads.
+// The conv history is double-buffered by position parity: several CTAs read the taps of a shared q/k head
+// while exactly one of them (and, for the v channels, their only reader) writes the shifted taps into the
+// other buffer. Arithmetic and its order are those of the stand-alone kernels above.
+__global__ void __launch_bounds__(256) k_gdn_core(int heads, int qk_heads, int hidden, const float *__restrict__ qkv,
+                                                  const float *__restrict__ conv_w, float *__restrict__ hist0,
+                                                  float *__restrict__ hist1, const int *__restrict__ pos_ptr,
+                                                  const float *__restrict__ x,
+                                                  const float *__restrict__ inv_ptr, const float *__restrict__ norm_w,
+                                                  const float *__restrict__ alpha_w, const float *__restrict__ beta_w,
+                                                  const float *__restrict__ dt_bias, const float *__restrict__ ssm_a,
+                                                  float *__restrict__ state, float *__restrict__ o, float scale) {
+    __shared__ float sq[128], sk[128], sv[32], sgb[2];
+    extern __shared__ float4 rows[];               // [2][hidden/4]: row h of ssm_alpha and of ssm_beta
+    const int h = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    {   // all loads of the two rows in flight at once (they come from HBM), the dependent chains run from shared memory
+        const float4 *ra = reinterpret_cast<const float4 *>(alpha_w + size_t(h) * hidden), *rb = reinterpret_cast<const float4 *>(beta_w + size_t(h) * hidden);
+        for (int i = tid; i < hidden / 4; i += 256) { rows[i] = ra[i]; rows[hidden / 4 + i] = rb[i]; }
+    }
+    const int hq = h % qk_heads;
+    // a token at position p reads the taps from buffer p & 1 and writes the shifted taps to the other one
+    const bool odd = pos_ptr[0] & 1;
+    const float *hist_rd = odd ? hist1 : hist0;
+    float *hist_wr = odd ? hist0 : hist1;
+    auto conv1 = [&](int c, bool store) -> float {
+        const float *sr = hist_rd + 3 * size_t(c);
+        const float *wc = conv_w + 4 * size_t(c);
+        const float s0 = sr[0], s1 = sr[1], s2 = sr[2], xn = qkv[c];
+        float acc = __fmul_rn(wc[0], s0);
+        acc = __fadd_rn(acc, __fmul_rn(wc[1], s1));
+        acc = __fadd_rn(acc, __fmul_rn(wc[2], s2));
+        acc = __fadd_rn(acc, __fmul_rn(wc[3], xn));
+        if (store) { float *sw = hist_wr + 3 * size_t(c); sw[0] = s1; sw[1] = s2; sw[2] = xn; }
+        return silu_f(acc);
+    };
+    const bool own_qk = h < qk_heads && chunk == 0;
+    if (tid < 128) sq[tid] = conv1(hq * 128 + tid, own_qk);
+    else sk[tid - 128] = conv1(qk_heads * 128 + hq * 128 + (tid - 128), own_qk);
+    if (tid < 32) sv[tid] = conv1(2 * qk_heads * 128 + h * 128 + chunk * 32 + tid, true);
+    __syncthreads();
+    if (warp >= 6) {
+        // row h of ssm_alpha (warp 6) or ssm_beta (warp 7) times the normed residual (x * inv) * norm_w
+        const float inv = inv_ptr[0];
+        const float4 *wr = rows + (warp == 6 ? 0 : hidden / 4);
+        const float4 *xv = reinterpret_cast<const float4 *>(x), *nw = reinterpret_cast<const float4 *>(norm_w);
+        float acc = 0.0f;
+        for (int i0 = lane; i0 < hidden / 4; i0 += 128) {
+            float4 w4[4], x4[4], n4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + 32 * u;
+                if (i < hidden / 4) { w4[u] = wr[i]; x4[u] = xv[i]; n4[u] = nw[i]; }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (i0 + 32 * u < hidden / 4) {
+                    acc = fmaf(w4[u].x, __fmul_rn(__fmul_rn(x4[u].x, inv), n4[u].x), acc);
+                    acc = fmaf(w4[u].y, __fmul_rn(__fmul_rn(x4[u].y, inv), n4[u].y), acc);
+                    acc = fmaf(w4[u].z, __fmul_rn(__fmul_rn(x4[u].z, inv), n4[u].z), acc);
+                    acc = fmaf(w4[u].w, __fmul_rn(__fmul_rn(x4[u].w, inv), n4[u].w), acc);
+                }
+            }
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, s));
+        if (lane == 0) {
+            if (warp == 6) {
+                const float al = __fadd_rn(acc, dt_bias[h]);
+                const float sp = al > 20.0f ? al : log_f(__fadd_rn(1.0f, exp_f(al)));
+                sgb[0] = __fmul_rn(sp, ssm_a[h]);
+            } else sgb[1] = sigmoid_f(acc);
+        }
+    }
+    __syncthreads();
+    float qq[4], kk[4];
+    {
+        const float a0 = sq[lane], a1 = sq[lane + 32], a2 = sq[lane + 64], a3 = sq[lane + 96];
+        const float iq = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(warp_tree128(__fmul_rn(a0, a0), __fmul_rn(a1, a1), __fmul_rn(a2, a2), __fmul_rn(a3, a3)), 1e-12f)));
+        qq[0] = __fmul_rn(a0, iq); qq[1] = __fmul_rn(a1, iq); qq[2] = __fmul_rn(a2, iq); qq[3] = __fmul_rn(a3, iq);
+        const float b0 = sk[lane], b1 = sk[lane + 32], b2 = sk[lane + 64], b3 = sk[lane + 96];
+        const float ik = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(warp_tree128(__fmul_rn(b0, b0), __fmul_rn(b1, b1), __fmul_rn(b2, b2), __fmul_rn(b3, b3)), 1e-12f)));
+        kk[0] = __fmul_rn(b0, ik); kk[1] = __fmul_rn(b1, ik); kk[2] = __fmul_rn(b2, ik); kk[3] = __fmul_rn(b3, ik);
+    }
+    const float eg = exp_f(sgb[0]), bt = sgb[1];
+    float S[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const float *Sr = state + (size_t(h) * 128 + chunk * 32 + warp * 4 + r) * 128;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[r][e] = Sr[lane + 32 * e];
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int jl = warp * 4 + r;
+        float *Sr = state + (size_t(h) * 128 + chunk * 32 + jl) * 128;
+        float s[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[e] = __fmul_rn(S[r][e], eg);
+        const float pred = warp_tree128(__fmul_rn(s[0], kk[0]), __fmul_rn(s[1], kk[1]), __fmul_rn(s[2], kk[2]), __fmul_rn(s[3], kk[3]));
+        const float u = __fmul_rn(bt, __fsub_rn(sv[jl], pred));
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { s[e] = fmaf(kk[e], u, s[e]); Sr[lane + 32 * e] = s[e]; }
+        const float ov = warp_tree128(__fmul_rn(s[0], qq[0]), __fmul_rn(s[1], qq[1]), __fmul_rn(s[2], qq[2]), __fmul_rn(s[3], qq[3]));
+        if (lane == 0) o[h * 128 + chunk * 32 + jl] = __fmul_rn(ov, scale);
+    }
+}
+
 // per-head RMS (no weight; 128 squares, tree), * ssm_norm, swiglu(z, .), v-grouped permutation
 // (bonsai_forward.h:559-567, permute_vg.comp:32-42). One warp per SOURCE head.
 __global__ void k_gdn_out(int heads, int qk_heads, const float *__restrict__ o, const float *__restrict__ z,
@@ -462,6 +571,13 @@ void gdn_delta(cudaStream_t st, GdnDims d, const float *q, const float *k, const
     k_gdn_delta<<<dim3(d.dim / 8, d.heads), 256, 0, st>>>(d.heads, d.qk_heads, q, k, v, gate, beta, state, o,
                                                           1.0f / sqrtf(float(d.dim))); BN_COUNT(1);
 }
+void gdn_core_fused(cudaStream_t st, GdnDims d, int hidden, const float *qkv, const float *conv_w, float *hist0,
+                    float *hist1, const int *pos_ptr, const float *x, const float *inv_ptr, const float *norm_w, const float *alpha_w,
+                    const float *beta_w, const float *dt_bias, const float *ssm_a, float *state, float *o) {
+    k_gdn_core<<<dim3(d.dim / 32, d.heads), 256, size_t(hidden) * 8, st>>>(d.heads, d.qk_heads, hidden, qkv, conv_w, hist0, hist1, pos_ptr, x, inv_ptr,
+                                                          norm_w, alpha_w, beta_w, dt_bias, ssm_a, state, o, 1.0f / sqrtf(float(d.dim)));
+    BN_COUNT(1);
+}
 void gdn_out(cudaStream_t st, GdnDims d, const float *o, const float *z, const float *ssm_norm, float eps, float *y) {
     k_gdn_out<<<(d.heads + 7) / 8, 256, 0, st>>>(d.heads, d.qk_heads, o, z, ssm_norm, eps, y); BN_COUNT(1);
 }
@@ -470,11 +586,12 @@ void attn_prep(cudaStream_t st, AttnDims a, const float *qg, const float *kin, c
     k_attn_prep<<<a.n_head + a.n_kv, 256, 0, st>>>(a, qg, kin, vin, qn_w, kn_w, pos_ptr, kv, q16f, gate); BN_COUNT(1);
 }
 void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *gate, const int *pos_ptr, KvLayer kv,
-                 float *score, float *p16f, float *pv_part, int splits, float *pregate, float *gated) {
+                 float *score, float *p16f, float *pv_part, int splits, float *pregate, float *gated, bool combine) {
     // grids are sized for the cache capacity; warps beyond the filled prefix return at once
     k_attn_scores<4><<<dim3((a.cap + 7) / 8, a.n_kv), 256, 0, st>>>(a, q16f, pos_ptr, kv, score); BN_COUNT(1);
     k_attn_softmax<<<a.n_head, 1024, 0, st>>>(a, pos_ptr, score, 1.0f / sqrtf(float(a.head_dim)), p16f); BN_COUNT(1);
     k_attn_pv<4><<<dim3(a.n_kv, splits), 256, 0, st>>>(a, p16f, pos_ptr, kv, splits, pv_part); BN_COUNT(1);
+    if (!combine) return;
     const int n = a.n_head * a.head_dim;
     k_attn_combine<<<(n + 255) / 256, 256, 0, st>>>(a, pv_part, splits, pos_ptr, gate, pregate, gated); BN_COUNT(1);
 }

@@ -34,6 +34,11 @@ void conv_silu(cudaStream_t st, const float *x, const float *w, float *hist, int
 void l2_norm_rows(cudaStream_t st, const float *x, int rows, float eps, float *y);   // 128-wide rows
 void gdn_delta(cudaStream_t st, GdnDims d, const float *q, const float *k, const float *v, const float *gate,
                const float *beta, float *state, float *o);
+// fused layer core: alpha/beta projections of the normed residual + gates, conv + silu, L2 norms, delta rule.
+// hist0 / hist1: the two conv-history buffers; position parity picks which is read and which is written.
+void gdn_core_fused(cudaStream_t st, GdnDims d, int hidden, const float *qkv, const float *conv_w, float *hist0,
+                    float *hist1, const int *pos_ptr, const float *x, const float *inv_ptr, const float *norm_w, const float *alpha_w,
+                    const float *beta_w, const float *dt_bias, const float *ssm_a, float *state, float *o);
 // per-head RMS (no weight) * ssm_norm, swiglu(z, .), v-grouped permutation -> y[heads*dim]
 void gdn_out(cudaStream_t st, GdnDims d, const float *o, const float *z, const float *ssm_norm, float eps, float *y);
 
@@ -45,7 +50,7 @@ void attn_prep(cudaStream_t st, AttnDims a, const float *qg, const float *kin, c
 // scores -> softmax (fp16-rounded probabilities) -> PV -> sigmoid gate. Scratch buffers sized by cap.
 void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *gate, const int *pos_ptr, KvLayer kv,
                  float *score /*[nh][cap]*/, float *p16f /*[nh][cap]*/, float *pv_part /*[splits][nh][hd]*/, int splits,
-                 float *pregate /*[nh][hd] or null*/, float *gated);
+                 float *pregate /*[nh][hd] or null*/, float *gated, bool combine /*false: leave the split partials*/);
 void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx);
 
 }  // namespace bnk

@@ -1,0 +1,49 @@
+// phase_gemv.cuh - the fused "phase" kernel: [prologue that rebuilds the rotated, quantised input of a
+// projection from the previous phase's outputs] + [PTQ1_0 x q8_1 GEMV streamed through a bulk-copy ring]
+// + [split-K finalisation and residual add by the last CTA to touch a row tile].
+#pragma once
+#include "ops.cuh"
+
+namespace bnk {
+
+enum Prologue {
+    PRO_PACKED = 0,   // activation pack already in global memory (op-level entry point)
+    PRO_PLAIN = 1,    // x0 is the plain fp32 input: rotate + quantise
+    PRO_NORM = 2,     // x = rms_norm(x0) * w                                   (pre_norm, bonsai_forward.h:480)
+    PRO_SWIGLU = 3,   // x = silu(x0) * x1                                       (ffn_block :498)
+    PRO_GDN_OUT = 4,  // x = permute(silu(z = x1) * (rms_head(o = x0) * w))      (gdn_block :559-567)
+    PRO_ATTN_OUT = 5  // x = (sum_s pv[s]) * sigmoid(gate = x1)                  (attn_pv_q8v.comp tail)
+};
+
+struct PhaseArgs {
+    // projection
+    const uint8_t *W;        // M rows of K/128 PTQ1_0 blocks
+    int M, K;                // K % 512 == 0
+    float *out;              // [M] final sums (may be null when resid_out is set)
+    const float *resid_in;   // optional [M]
+    float *resid_out;        // optional [M]: resid_out = out + resid_in
+    float *part;             // [K/512][M] scratch
+    unsigned *counters;      // [ceil(M/16)] zero before launch; left zero
+    // prologue
+    int pro;
+    const float *x0, *x1, *w;
+    const uint32_t *pack;    // PRO_PACKED
+    const int32_t *signs;    // K sign values
+    int hat_block;
+    float hat_inv, eps;
+    int gdn_heads, gdn_qk_heads;   // PRO_GDN_OUT
+    int pv_splits;                 // PRO_ATTN_OUT: x0 = pv partials [splits][K]
+    const int *pos_ptr;            // PRO_ATTN_OUT: number of filled keys = pos + 1
+    float *inv_out;                // PRO_NORM: optional, receives 1/sqrt(mean(x0^2) + eps) for a later consumer
+    int *err;                      // device error word (bounded waits)
+    unsigned long long *stamps;    // optional: 8 nanosecond time stamps of CTA 0 (start, copies issued, previous grid
+                                   // done, norm, input built, quantised, operands built, end) for profiling
+};
+
+constexpr int PHASE_THREADS = 512;
+size_t phase_smem_bytes(int hat_block);
+// launches with programmatic dependent launch when pdl is true
+cudaError_t launch_phase(cudaStream_t st, int sm_count, const PhaseArgs &a, bool pdl);
+bool phase_supported(int M, int K, int hat_block);
+
+}  // namespace bnk

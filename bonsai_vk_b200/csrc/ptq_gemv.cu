@@ -12,15 +12,17 @@
 // the T_t:  sum_t trit_t*y_t = sum_t T_t*(y_t - 3*y_(t+1)).  Two weight bytes sit in the 16-bit
 // halves of a register; ONE integer multiply by 3^(t+1) (no carry between the halves, 255*243 <
 // 65536) yields a register whose bytes are [r, T, r', T'] - exactly an int8 tensor-core operand
-// in which the residue bytes r are multiplied by zero. The coefficients (y_t - 3*y_(t+1)),
-// restricted to one q8_1 sub-block and split as 4*hi + lo so that each part fits an int8, form
-// the 8 columns of the B operand: column 2*sb is the "hi" part and 2*sb+1 the "lo" part of
-// sub-block sb, so I_sb = 4*D[2sb] + D[2sb+1] exactly. That table depends only on the
-// activations and is built once per activation vector by k_act_quant_q81.
+// in which the residue bytes r are multiplied by zero. The two sums sum_t T_t*y_t and
+// sum_t T_t*y_(t+1), each restricted to one q8_1 sub-block, are the 8 columns of the B operand:
+// column 2*sb pairs T_t with the activation of its own element, column 2*sb+1 with the activation of
+// the next level's element, so I_sb = D[2sb] - 3*D[2sb+1] exactly and every B byte is a plain int8
+// activation code (or zero). That table depends only on the activations and is built once per
+// activation vector by k_act_quant_q81.
 //
 // One warp owns one 128-weight block column and walks 16-row tiles: 32 integer multiplies, 8
 // byte-permutes and 8 mma.sync.m16n8k32.u8.s8 per 2048 weights.
 #include "ops.cuh"
+#include "phase_gemv.cuh"
 #include "quant.cuh"
 
 namespace {
@@ -96,7 +98,7 @@ __global__ void __launch_bounds__(128) k_gemv_q81_direct(const uint32_t *__restr
             const RowRegs rb = split_row(b_first, b_second, b6, tig);
             int c[4] = {0, 0, 0, 0};
             tile_mma(c, ra, rb, B, cq);
-            const int I0 = 4 * c[0] + c[1], I1 = 4 * c[2] + c[3];
+            const int I0 = c[0] - 3 * c[1], I1 = c[2] - 3 * c[3];
             if (DUMP) {
                 if (row0 < M) dots[(size_t(row0) * nb + b) * 4 + tig] = I0;
                 if (row1 < M) dots[(size_t(row1) * nb + b) * 4 + tig] = I1;
@@ -196,6 +198,18 @@ int bn_gemv_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const 
     if (dots) BN_RANGE(dots, dots_off, size_t(M) * nb * 16, 4, "bn_gemv_q81 dots");
     int rc = bn_scratch_reserve(ctx, size_t(ngroups) * M * 4);
     if (rc != BN_OK) return rc;
+    if (!dots && bnk::phase_supported(M, K, 512) && (M + 15) / 16 <= BN_MAX_TILES) {
+        // streamed kernel; the op-level call hands it a ready-made activation pack
+        bnk::PhaseArgs a = {};
+        a.W = bn_ptr<uint8_t>(w, w_off); a.M = M; a.K = K;
+        a.out = bn_ptr<float>(out, out_off);
+        a.part = ctx->scratch; a.counters = ctx->counters;
+        a.pro = bnk::PRO_PACKED; a.pack = bn_ptr<uint32_t>(pack, pack_off);
+        a.hat_block = 512; a.err = ctx->err_dev;
+        cudaError_t e = bnk::launch_phase(ctx->stream, ctx->sm_count, a, false);
+        if (e != cudaSuccess) return bn_cuda_fail(e, "k_phase_gemv");
+        return bn_launch_check(ctx, "k_phase_gemv");
+    }
     bnk::gemv_q81(ctx->stream, ctx->sm_count, bn_ptr<uint32_t>(w, w_off), M, K, bn_ptr<uint32_t>(pack, pack_off),
                   bn_ptr<float>(out, out_off), ctx->scratch, dots ? bn_ptr<int32_t>(dots, dots_off) : nullptr);
     return bn_launch_check(ctx, "gemv_q81");

@@ -22,16 +22,15 @@ __device__ __forceinline__ void areg_bytes(int tig, int L, int &byteA, int &byte
     else              { byteA = 4 * second + (tig & 1); byteB = 4 * second + 2 + (tig & 1); }
 }
 
-// coefficient of T(byte, t) in I_sb, split part 0 = floor(c/4), part 1 = c mod 4
+// Column pair of sub-block sb: I_sb = D[2sb] - 3*D[2sb+1]. T(byte, t) enters D[2sb] with the activation
+// of its own element (level t) and D[2sb+1] with the activation of the next level's element, each only
+// when that element lies in sub-block sb: sum_t trit_t*y_t = sum_t T_t*y_t - 3*sum_t T_t*y_(t+1).
 __device__ __forceinline__ int coef(const int8_t *q, int byte, int t, int sb, int part) {
     const int tmax = byte < 24 ? 4 : 3;
-    const int e0 = elem_of(byte, t);
-    int c = ((e0 >> 5) == sb) ? int(q[e0]) : 0;
-    if (t < tmax) {
-        const int e1 = elem_of(byte, t + 1);
-        if ((e1 >> 5) == sb) c -= 3 * int(q[e1]);
-    }
-    return part == 0 ? (c >> 2) : (c & 3);
+    const int tt = t + part;
+    if (tt > tmax) return 0;
+    const int e = elem_of(byte, tt);
+    return ((e >> 5) == sb) ? int(q[e]) : 0;
 }
 
 // 128 threads cooperate on one 128-activation block: thread i owns value v (element i). q8_1

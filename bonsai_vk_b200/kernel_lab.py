@@ -1,0 +1,62 @@
+"""Kernel lab: one synthetic PTQ1_0 x q8_1 GEMV, checked and timed (the counterpart of the reference's
+`bonsai_vk <M> <K> <S> <ITER>` mode, runtime_vk/bonsai_vk.cpp:227-924).
+
+  python -m bonsai_vk_b200.kernel_lab M K [ITER] [--nocheck]
+
+Prints max|err| and rel against the CPU checker (when oracle/ is built), then ms/op, Gop/s and GB/s of
+PTQ1_0 bytes from CUDA events. Timing rotates through enough copies of the matrix to exceed L2.
+"""
+from __future__ import annotations
+
+import sys
+
+import numpy as np
+
+
+def main(argv):
+    from bonsai_vk_b200 import Context, ptq
+    M, K = int(argv[0]), int(argv[1])
+    iters = int(argv[2]) if len(argv) > 2 and not argv[2].startswith("-") else 3
+    check = "--nocheck" not in argv
+    ctx = Context(0)
+    rng = np.random.default_rng(0x2545F491)
+    nb = K // 128
+    rows = min(M, 8192)
+    base = ptq.synth_matrix(rng, rows, K)
+    W = np.concatenate([base] * ((M + rows - 1) // rows), axis=0)[:M]
+    x = rng.standard_normal(K).astype(np.float32)
+    nbytes = M * nb * 28
+    ncopies = max(2, int(300e6 // nbytes) + 1)
+    wb = ctx.alloc(ncopies * nbytes)
+    for i in range(ncopies):
+        wb.upload(W, off=i * nbytes)
+    xb = ctx.from_numpy(x)
+    pack = ctx.alloc(ctx.act_pack_bytes(K))
+    out = ctx.alloc(M * 4)
+    ctx.act_quant_q81(xb, K, pack)
+    ctx.gemv_q81(wb, M, K, pack, out)
+    ctx.sync()
+    if check:
+        sys.path.insert(0, __import__("os").path.dirname(__import__("os").path.dirname(__import__("os").path.abspath(__file__))))
+        from tests import _oracle
+        o = _oracle.load_oracle()
+        ref, exact, _ = o.gemv_q81(W, M, K, o.quantize_q8_1(x))
+        got = out.download(np.float32, M)
+        err = np.abs(got - exact)
+        print(f"max|err| {err.max():.3e}  rel {err.max() / np.sqrt(np.mean(exact ** 2)):.3e}  bit-identical to the order-matched restatement: {np.array_equal(got.view(np.uint32), ref.view(np.uint32))}")
+    for i in range(ncopies):
+        ctx.gemv_q81(wb, M, K, pack, out, w_off=i * nbytes)
+    e0, e1 = ctx.event(), ctx.event()
+    ctx.record(e0)
+    for _ in range(iters):
+        for i in range(ncopies):
+            ctx.gemv_q81(wb, M, K, pack, out, w_off=i * nbytes)
+    ctx.record(e1)
+    ms = ctx.elapsed_ms(e0, e1) / (iters * ncopies)
+    print(f"M={M} K={K}: {ms:.5f} ms/op, {2.0 * M * K / ms / 1e6:.1f} Gop/s, {nbytes / ms / 1e6:.1f} GB/s of PTQ1_0 bytes "
+          f"({ncopies} matrix copies = {ncopies * nbytes / 1e6:.0f} MB rotation)")
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

@@ -69,6 +69,7 @@ def load_library() -> C.CDLL:
         "bn_model_read": (i32, [vp, i32, i32, vp, sz]),
         "bn_model_decode": (i32, [vp, i32, i32, i32, C.POINTER(i32)]),
         "bn_model_gemv_sweep": (i32, [vp, i32, C.POINTER(C.c_float)]),
+        "bn_model_profile_token": (i32, [vp, i32, i32, vp, i32, C.POINTER(i32)]),
     }
     for name, (res, args) in sig.items():
         f = getattr(lib, name)
@@ -223,6 +224,14 @@ class Model:
         out = (C.c_int32 * n_steps)() if fetch else None
         _check(self.ctx.lib.bn_model_decode(self.h, first_tok, pos0, n_steps, out), "bn_model_decode")
         return list(out) if fetch else None
+
+    def profile_token(self, tok: int, pos: int, max_phases: int = 256) -> np.ndarray:
+        """[n_phases, 8] device time stamps (ns) of the fused projection kernels of one token."""
+        out = np.zeros((max_phases, 8), dtype=np.uint64)
+        n = C.c_int32()
+        _check(self.ctx.lib.bn_model_profile_token(self.h, tok, pos, out.ctypes.data_as(C.c_void_p), max_phases, C.byref(n)),
+               "bn_model_profile_token")
+        return out[: n.value]
 
     def gemv_sweep_ms(self, reps: int = 3) -> float:
         ms = C.c_float()

@@ -130,6 +130,11 @@ int bn_model_decode(bn_model *m, int first_tok, int pos0, int n_steps, int *out_
  * runtime_vk/bonsai_vk.cpp:1452): launch every PTQ1_0 projection of one token back to back on the
  * model's own weights, `reps` times after one untimed pass, and return the CUDA-event time of one sweep */
 int bn_model_gemv_sweep(bn_model *m, int reps, float *ms_per_sweep);
+/* profiling aid (reference: BONSAI_PROFILE per-token ledger, bonsai_forward.h:650-662): run one token with
+ * every fused projection kernel recording 8 device time stamps in ns (CTA 0: start, first copies issued,
+ * previous kernel done, norm done, rotated input built, quantised, first weights awaited, end).
+ * stamps_out receives [n_phases][8]. */
+int bn_model_profile_token(bn_model *m, int tok, int pos, unsigned long long *stamps_out, int max_phases, int *n_phases);
 /* copy a device-side result or state region to the host (reference: act_rd / kv_dump) */
 int bn_model_read(bn_model *m, int what, int index, void *dst, size_t bytes);
 

@@ -108,3 +108,19 @@ def test_gemv_refuses_bad_arguments(ctx):
     ctx.sync()
     for b in (w, pack, out):
         b.free()
+
+
+@pytest.mark.parametrize("M,K", [(4096, 4096), (12288, 4096), (1024, 4096), (4096, 12288), (100, 512), (37, 1024),
+                                 (16, 4096), (20000, 4096)])
+def test_gemv_q81_streamed_kernel(ctx, oracle, M, K):
+    """The bulk-copy ring kernel (taken when no integer dump is requested and K % 512 == 0) gives the same
+    floats as the order-matched oracle, twice in a row (its arrival counters must be left at zero)."""
+    rng = np.random.default_rng(M * 7 + K)
+    W = ptq.synth_matrix(rng, M, K)
+    x = rng.standard_normal(K).astype(np.float32)
+    xq = oracle.quantize_q8_1(x)
+    out, exact, _ = oracle.gemv_q81(W, M, K, xq)
+    for _ in range(2):
+        _, got, _ = _run(ctx, oracle, W, M, K, x, want_dots=False)
+        assert _check_rows(got, exact) <= 1e-5
+        assert np.array_equal(got.view(np.uint32), out.view(np.uint32))
