@@ -215,4 +215,46 @@ int bn_gemv_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const 
     return bn_launch_check(ctx, "gemv_q81");
 }
 
+// ---- projection without any allocation ----------------------------------------------------------------
+// Some hosts may not allocate device memory once they are running: a server that sized every device buffer
+// when it loaded the model and promised the rest of the card to other tenants, an engine that (like the
+// reference, which refuses at start-up rather than grow later) treats a mid-generation allocation as a bug,
+// or code that is inside a stream capture, where cudaMalloc is not allowed. bn_gemv_q81 keeps its split-K
+// partial sums in a library buffer that it grows with cudaMalloc on demand; this variant keeps them in a
+// fixed array that is part of the library image instead, so it never allocates.
+//
+// The array lives on every GPU that loads the library, for the life of the process: 8 MiB.
+// Its name is only a stand-in on the host; the address a kernel needs comes from cudaGetSymbolAddress, asked
+// once per device with that device current. That happens inside the first call on a device, so make that
+// first call before any stream capture begins. All calls share the one array and it keeps whatever the
+// last call left: nothing in it has to start at zero (each call writes every partial sum before reading
+// it), but two calls that overlap on the GPU - different streams or contexts on the same device - would
+// overwrite each other's partial sums. Run them one after another.
+constexpr size_t BN_STATIC_PARTIAL_FLOATS = size_t(2) << 20;       // (K / 512) * M must not exceed this
+static __device__ __align__(256) float g_static_partials[BN_STATIC_PARTIAL_FLOATS];
+static float *g_static_partials_ptr[64] = {};                       // per device, filled on first use
+
+int bn_gemv_q81_static(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const bn_buf *pack, size_t pack_off,
+                       bn_buf *out, size_t out_off) {
+    BN_REQUIRE(ctx, BN_ERR_ARG, "bn_gemv_q81_static: null context");
+    BN_REQUIRE(M > 0 && K > 0 && K % 128 == 0, BN_ERR_ARG, "bn_gemv_q81_static: bad shape M=%d K=%d (K %% 128 != 0)", M, K);
+    const int nb = K / 128, ngroups = (nb + 3) / 4;
+    BN_REQUIRE(size_t(ngroups) * size_t(M) <= BN_STATIC_PARTIAL_FLOATS, BN_ERR_ARG,
+               "bn_gemv_q81_static: ceil(K/512) * M = %zu partial sums exceed the built-in scratch of %zu floats; "
+               "use bn_gemv_q81 (which allocates) for this shape", size_t(ngroups) * size_t(M), BN_STATIC_PARTIAL_FLOATS);
+    BN_REQUIRE(ctx->device >= 0 && ctx->device < 64, BN_ERR_ARG, "bn_gemv_q81_static: device index %d out of range", ctx->device);
+    BN_RANGE(w, w_off, size_t(M) * nb * 28, 4, "bn_gemv_q81_static W");
+    BN_RANGE(pack, pack_off, bn_act_pack_bytes(K), 16, "bn_gemv_q81_static pack");
+    BN_RANGE(out, out_off, size_t(M) * 4, 4, "bn_gemv_q81_static out");
+    if (!g_static_partials_ptr[ctx->device]) {
+        BN_CUDA(cudaSetDevice(ctx->device));
+        float *p = nullptr;
+        BN_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_partials));
+        g_static_partials_ptr[ctx->device] = p;
+    }
+    bnk::gemv_q81(ctx->stream, ctx->sm_count, bn_ptr<uint32_t>(w, w_off), M, K, bn_ptr<uint32_t>(pack, pack_off),
+                  bn_ptr<float>(out, out_off), g_static_partials_ptr[ctx->device], nullptr);
+    return bn_launch_check(ctx, "gemv_q81 (static scratch)");
+}
+
 }  // extern "C"

@@ -59,6 +59,7 @@ def load_library() -> C.CDLL:
         "bn_act_pack_bytes": (sz, [i32]),
         "bn_act_quant_q81": (i32, [vp, vp, sz, i32, vp, sz]),
         "bn_gemv_q81": (i32, [vp, vp, sz, i32, i32, vp, sz, vp, sz, vp, sz]),
+        "bn_gemv_q81_static": (i32, [vp, vp, sz, i32, i32, vp, sz, vp, sz]),
         "bn_model_create": (i32, [vp, C.POINTER(HParamsC), C.POINTER(vp)]),
         "bn_model_set_tensor": (i32, [vp, C.c_char_p, vp, sz, sz]),
         "bn_model_set_signs": (i32, [vp, vp, sz, i32]),
@@ -184,6 +185,11 @@ class Context:
                  out_off: int = 0, dots: Buffer | None = None, dots_off: int = 0):
         _check(self.lib.bn_gemv_q81(self.h, w.h, w_off, M, K, pack.h, pack_off, out.h, out_off,
                                     dots.h if dots is not None else None, dots_off), "bn_gemv_q81")
+
+    def gemv_q81_static(self, w: Buffer, M: int, K: int, pack: Buffer, out: Buffer, w_off: int = 0, pack_off: int = 0,
+                        out_off: int = 0):
+        """The projection with its scratch in the library's built-in array: no device allocation."""
+        _check(self.lib.bn_gemv_q81_static(self.h, w.h, w_off, M, K, pack.h, pack_off, out.h, out_off), "bn_gemv_q81_static")
 
 
 class Model:

@@ -85,6 +85,15 @@ int bn_act_quant_q81(bn_ctx *ctx, const bn_buf *x, size_t x_off, int K, bn_buf *
 int bn_gemv_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const bn_buf *pack,
                 size_t pack_off, bn_buf *out, size_t out_off, bn_buf *dots, size_t dots_off);
 
+/* The same projection for callers that must not allocate device memory while running (a host that fixed its
+ * device budget at load time, or one inside a stream capture). No counterpart in the reference: its engine
+ * sizes everything in fwd_init and has no such call. The split-K partial sums live in an 8 MiB array built
+ * into the library (present on every GPU that loads it), so ceil(K/512) * M must be <= 2 097 152; larger
+ * shapes are refused. The first call on a device looks the array's address up - make it before any stream
+ * capture. Calls share the array: do not let two of them overlap on one GPU. Same results as bn_gemv_q81. */
+int bn_gemv_q81_static(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const bn_buf *pack,
+                       size_t pack_off, bn_buf *out, size_t out_off);
+
 /* ---- whole-token decode (reference: fwd_token, runtime_vk/bonsai_forward.h:664-758) ---------------
  * The host registers every tensor of the GGUF by its GGUF name (PTQ1_0 tensors as the file's native
  * 28-byte blocks, row-major, d0 = K; f32 tensors as they are) plus the prism.hadamard sign values,
