@@ -11,7 +11,11 @@ One "step" is one decoded token (one pass of the whole-token schedule). Prints O
   roofline / cpu_baseline - see DESIGN.md ("Measurement").
 --impl reference times the reference's own CPU arithmetic for the path (dequantise + fp64 dot,
 oracle/_ref when built, else the oracle port) on all host cores, in the same unit.
-N > 1 (torchrun, one rank per GPU): independent replicas per rank until the layer pipeline lands.
+N > 1 (torchrun, one rank per GPU): BASELINE config 4 - the model is layer-pipelined over the N GPUs
+(contiguous block stages, hidden state handed off over NVLink with NCCL send/recv), 64 concurrent sequences at
+context 8192 are micro-batched through the stages; a step is one decode step of all 64 sequences and `value`
+is the aggregate tok/s. The KV caches are marked filled up to the start position (the reference's own
+BONSAI_KVFILL practice for long-context timing): timings are valid, token values are not meaningful.
 """
 from __future__ import annotations
 
@@ -122,6 +126,89 @@ def cpu_gemv_tokens_per_s(seconds=12.0, threads=None):
                       f"{PTQ_WEIGHTS_PER_TOKEN} projection weights one token reads"}
 
 
+def pipeline_main(a, base, rank, world, local, K, Wm):
+    """N > 1: layer pipeline, 64 streams, context 8192 (see the module docstring)."""
+    import torch
+    import torch.distributed as dist
+    from bonsai_vk_b200 import Context, Model, synth
+    from bonsai_vk_b200.pipeline import Pipeline, split_blocks
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    fwd, back = dist.new_group(list(range(world))), dist.new_group(list(range(world)))
+    S, CTX = 64, 8192
+    b0, b1 = split_blocks(32, world)[rank]
+    ctx = Context(local)
+    ctx.use_stream(torch.cuda.current_stream().cuda_stream)
+    hp = synth.HParams(cap=CTX, n_streams=S, block_begin=b0, block_end=b1)
+    tensors, signs = build_full_model(hp)
+    m = Model(ctx, hp, tensors, signs)
+    del tensors
+    total = 2 * (K + Wm) + 8
+    pos0 = [CTX - total - 1] * S
+    for s in range(S):
+        m.fill_kv(s, pos0[s])
+    dev = torch.device("cuda", local)
+    wraps = {}
+
+    def wrap(t):
+        key = t.data_ptr()
+        if key not in wraps:
+            wraps[key] = ctx.wrap(key, t.numel() * t.element_size())
+        return wraps[key]
+
+    def stage(s, step, pos, tok_first, tok_in, hin, out):
+        if rank == 0:
+            m.stage(s, tok_first if tok_first is not None else -1, pos, wrap(tok_in) if tok_in is not None else None, wrap(out))
+        else:
+            m.stage(s, 0, pos, wrap(hin), wrap(out))
+
+    pipe = Pipeline(dist, rank, world, S, stage, lambda: torch.zeros(hp.hidden, dtype=torch.float32, device=dev),
+                    lambda: torch.zeros(1, dtype=torch.int32, device=dev), fwd, back)
+    first = [int(t) for t in np.random.default_rng(42).integers(0, hp.vocab, size=S)]
+
+    def timed(n_steps, p0, collect):
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = ctx.launches
+        e0.record()
+        pipe.run(first, p0, n_steps, collect=collect)
+        e1.record()
+        torch.cuda.synchronize(); dist.barrier()
+        tt = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt[0]), ctx.launches - l0
+
+    timed(Wm, pos0, False)
+    sampler = ClockSampler(local)
+    sampler.start()
+    p1 = [p + Wm for p in pos0]
+    ms_dev, launches = timed(K, p1, False)
+    clocks = sampler.stop()
+    p2 = [p + K for p in p1]
+    t0 = time.perf_counter()
+    ms_e2e, _ = timed(K, p2, True)           # every pick is brought back to the host
+    tok_s = S * K / (ms_dev / 1000.0)
+    e2e = S * K / (ms_e2e / 1000.0)
+    cfg = dict(base["config"], workload=f"config 4: 9B-shape synthetic model layer-pipelined over {world} GPUs "
+               f"({b1 - b0} blocks per stage), 64 concurrent sequences at context {CTX} (KV marked filled), greedy decode",
+               parallelism=f"pp{world}", streams=S, context=CTX)
+    line = dict(base, metric="decode tok/s, 9B ternary (PTQ1_0), 64 streams pipelined", config=cfg, value=tok_s,
+                ms_per_step=ms_dev / K, clocks=clocks, gpu_launches=int(launches),
+                e2e={"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4 * S})
+    if rank == 0:
+        peak, which = peaks()
+        # per GPU and step: every sequence re-reads the stage's weights (no batched GEMM yet) plus its own state and KV
+        w_stage = (PTQ_BYTES_PER_TOKEN - 222_494_720) / world
+        per_gpu = S * (w_stage + (2 * 50_331_648 + 29_411_328) / world) + S * (8 / world) * CTX * 2176
+        ach = per_gpu / (ms_dev / K / 1000.0) / 1e9
+        line["roofline"] = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                            "peak_source": which, "kernel": "per-GPU stage bytes per step (weights re-read per sequence + state + KV)"}
+        print(json.dumps(line))
+    m.close()
+    ctx.close()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -154,10 +241,7 @@ def main():
     from bonsai_vk_b200 import Context, Model, synth
     dist = None
     if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return pipeline_main(a, base, rank, world, local, K, Wm)
     ctx = Context(local)
     cap = max(256, (max(1, a.prompt) + 2 * (K + Wm) + 64 + 1) // 2 * 2)
     hp = synth.HParams(cap=cap)

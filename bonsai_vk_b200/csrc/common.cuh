@@ -12,6 +12,7 @@
 struct bn_buf {
     void *dptr;
     size_t bytes;
+    bool owned;      // false: wraps memory of the caller
 };
 
 struct bn_event {
@@ -22,6 +23,7 @@ struct bn_ctx {
     int device;
     int sm_count;
     cudaStream_t stream;
+    bool own_stream;
     uint64_t launches;
     // library-owned scratch for split-K partials, grown on demand (never during a graph capture)
     float *scratch;

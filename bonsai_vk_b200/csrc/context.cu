@@ -69,6 +69,7 @@ int bn_init(int device, bn_ctx **out) {
     c->scratch_bytes = 0;
     e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) { delete c; return bn_cuda_fail(e, "cudaStreamCreate"); }
+    c->own_stream = true;
     c->counters = nullptr;
     c->err_dev = nullptr;
     e = cudaMalloc(&c->counters, size_t(BN_MAX_TILES) * 4 + 256);
@@ -86,7 +87,7 @@ void bn_destroy(bn_ctx *ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->counters) cudaFree(ctx->counters);
-    cudaStreamDestroy(ctx->stream);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
 
@@ -110,6 +111,7 @@ int bn_alloc(bn_ctx *ctx, size_t bytes, bn_buf **out) {
     bn_buf *b = new bn_buf();
     b->dptr = p;
     b->bytes = bytes;
+    b->owned = true;
     *out = b;
     return BN_OK;
 }
@@ -118,12 +120,31 @@ int bn_free(bn_ctx *ctx, bn_buf *buf) {
     BN_REQUIRE(ctx && buf, BN_ERR_ARG, "bn_free: null argument");
     BN_CUDA(cudaSetDevice(ctx->device));
     BN_CUDA(cudaStreamSynchronize(ctx->stream));
-    BN_CUDA(cudaFree(buf->dptr));
+    if (buf->owned) BN_CUDA(cudaFree(buf->dptr));
     delete buf;
     return BN_OK;
 }
 
 size_t bn_buf_size(const bn_buf *buf) { return buf ? buf->bytes : 0; }
+
+int bn_wrap(bn_ctx *ctx, void *device_ptr, size_t bytes, bn_buf **out) {
+    BN_REQUIRE(ctx && device_ptr && bytes && out, BN_ERR_ARG, "bn_wrap: bad argument");
+    bn_buf *b = new bn_buf();
+    b->dptr = device_ptr;
+    b->bytes = bytes;
+    b->owned = false;
+    *out = b;
+    return BN_OK;
+}
+
+int bn_use_stream(bn_ctx *ctx, void *cuda_stream) {
+    BN_REQUIRE(ctx, BN_ERR_ARG, "bn_use_stream: null context");
+    BN_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    ctx->own_stream = false;
+    return BN_OK;
+}
 
 int bn_upload(bn_ctx *ctx, bn_buf *dst, size_t off, const void *src, size_t n) {
     BN_REQUIRE(ctx && src, BN_ERR_ARG, "bn_upload: null argument");

@@ -31,6 +31,9 @@ struct bn_model {
     // persistent state
     float *gdn_state = nullptr, *conv_hist = nullptr, *conv_hist2 = nullptr;   // conv taps: two buffers (position parity)
     int next_pos = 0;
+    int cur = 0;              // stream whose state the next enqueue works on
+    int b0 = 0, b1 = 0;       // local block range [b0, b1): a pipeline stage owns a contiguous run of blocks
+    size_t gdn_stream_stride = 0, conv_stream_stride = 0;
     char *kv = nullptr;
     size_t kv_layer_bytes = 0, kv_k_scale_off = 0, kv_v_off = 0, kv_v_scale_off = 0;
     int pv_splits = 1;
@@ -78,8 +81,17 @@ bnk::AttnDims attn_dims(const bn_model *m) {
     return bnk::AttnDims{h.n_head, h.n_kv, h.head_dim, h.n_rot, h.cap, h.rms_eps, h.rope_base, h.k_mode, h.v_mode};
 }
 
+float *gdn_state_of(const bn_model *m, int idx) {
+    const bn_hparams &h = m->hp;
+    return m->gdn_state + size_t(m->cur) * m->gdn_stream_stride + size_t(idx) * h.gdn_heads * h.gdn_dim * h.gdn_dim;
+}
+float *conv_of(const bn_model *m, int which, int idx) {
+    const bn_hparams &h = m->hp;
+    const size_t C = size_t(2 * h.gdn_qk_heads + h.gdn_heads) * h.gdn_dim;
+    return (which ? m->conv_hist2 : m->conv_hist) + size_t(m->cur) * m->conv_stream_stride + size_t(idx) * C * 3;
+}
 bnk::KvLayer kv_layer(const bn_model *m, int li) {
-    char *base = m->kv + size_t(li) * m->kv_layer_bytes;
+    char *base = m->kv + (size_t(m->cur) * m->n_attn + size_t(li)) * m->kv_layer_bytes;
     bnk::KvLayer k;
     k.k_data = base;
     k.k_scale = m->hp.k_mode == 0 ? reinterpret_cast<uint16_t *>(base + m->kv_k_scale_off) : nullptr;
@@ -112,10 +124,10 @@ void gdn_core(bn_model *m, const bn_model::Layer &L) {
     cudaStream_t st = m->ctx->stream;
     const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D;
     const bnk::GdnDims gd{NH, NQ, D};
-    bnk::conv_silu(st, m->QKV, L.conv_w, m->conv_hist + size_t(L.idx) * C * 3, C, m->CONV);
+    bnk::conv_silu(st, m->QKV, L.conv_w, conv_of(m, 0, L.idx), C, m->CONV);
     bnk::l2_norm_rows(st, m->CONV, 2 * NQ, 1e-12f, m->L2);
     bnk::gdn_delta(st, gd, m->L2, m->L2 + NQ * D, m->CONV + 2 * NQ * D, m->G, m->BT,
-                   m->gdn_state + size_t(L.idx) * NH * D * D, m->O);
+                   gdn_state_of(m, L.idx), m->O);
 }
 
 void gdn_plain(bn_model *m, const bn_model::Layer &L) {
@@ -198,9 +210,9 @@ void gdn_fused(bn_model *m, const bn_model::Layer &L) {
     }
     {
         const bnk::GdnDims gd{NH, NQ, D};
-        float *h0 = m->conv_hist + size_t(L.idx) * C * 3, *h1 = m->conv_hist2 + size_t(L.idx) * C * 3;
+        float *h0 = conv_of(m, 0, L.idx), *h1 = conv_of(m, 1, L.idx);
         bnk::gdn_core_fused(m->ctx->stream, gd, h.hidden, m->QKV, L.conv_w, h0, h1, m->POS, m->RES, m->G + 48, L.attn_norm,
-                            L.alpha_w, L.beta_w, L.dt_bias, L.ssm_a, m->gdn_state + size_t(L.idx) * NH * D * D, m->O);
+                            L.alpha_w, L.beta_w, L.dt_bias, L.ssm_a, gdn_state_of(m, L.idx), m->O);
     }
     bnk::PhaseArgs o = phase_base(m, L.ssm_out, h.hidden, IN, m->signs);
     bnk::gdn_out(m->ctx->stream, bnk::GdnDims{NH, NQ, D}, m->O, m->Z, L.ssm_norm, h.rms_eps, m->X1);
@@ -236,15 +248,17 @@ void attn_fused(bn_model *m, const bn_model::Layer &L) {
 void enqueue_token(bn_model *m, int stop_after, bool want_logits) {
     const bn_hparams &h = m->hp;
     cudaStream_t st = m->ctx->stream;
-    bnk::embed_row(st, m->embd, h.hidden, m->TOK, m->X1);
-    bnk::rotate_inv(st, m->X1, m->signs, h.hidden, h.hat_block, m->RES);
-    for (int b = 0; b < h.n_layer; ++b) {
+    if (m->b0 == 0) {
+        bnk::embed_row(st, m->embd, h.hidden, m->TOK, m->X1);
+        bnk::rotate_inv(st, m->X1, m->signs, h.hidden, h.hat_block, m->RES);
+    }
+    for (int b = m->b0; b < m->b1; ++b) {
         const bn_model::Layer &L = m->layers[b];
         if (m->fused) { if (L.attn) attn_fused(m, L); else gdn_fused(m, L); ffn_fused(m, L); }
         else { if (L.attn) attn_plain(m, L); else gdn_plain(m, L); ffn_plain(m, L); }
         if (b == stop_after) return;
     }
-    if (!want_logits) return;
+    if (!want_logits || m->b1 != h.n_layer) return;
     if (m->fused) {
         bnk::PhaseArgs a = phase_base(m, m->out_w, h.vocab, h.hidden, m->signs);
         a.pro = bnk::PRO_NORM; a.x0 = m->RES; a.w = m->out_norm; a.out = m->LOGITS;
@@ -264,6 +278,13 @@ __global__ void k_advance(int *tok, int *pos, const int *next, int *hist, int *s
     tok[0] = next[0];
     pos[0] = pos[0] + 1;
     step[0] = s + 1;
+}
+
+__global__ void k_set_tok_pos(int *tok, int *pos, int t, int p, const int *tok_src) {
+    if (threadIdx.x == 0) { tok[0] = tok_src ? tok_src[0] : t; pos[0] = p; }
+}
+__global__ void k_fill_u16(uint16_t *p, size_t n, uint16_t v) {
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) p[i] = v;
 }
 
 }  // namespace
@@ -287,6 +308,9 @@ int bn_model_create(bn_ctx *ctx, const bn_hparams *hp, bn_model **out) {
     BN_REQUIRE(h.cap > 0 && h.cap % 2 == 0, BN_ERR_ARG, "bn_model_create: cap %d must be positive and even", h.cap);
     BN_REQUIRE(h.act_mode == 0, BN_ERR_ARG, "bn_model_create: only act_mode 0 (q8_1 activations) is built");
     BN_REQUIRE((h.k_mode | 1) == 1 && (h.v_mode | 1) == 1, BN_ERR_ARG, "bn_model_create: kv modes are 0 (q8_0) or 1 (fp16)");
+    BN_REQUIRE(h.n_streams >= 0 && h.n_streams <= 1024, BN_ERR_ARG, "bn_model_create: n_streams %d out of range", h.n_streams);
+    BN_REQUIRE(h.block_begin >= 0 && h.block_begin < h.n_layer && (h.block_end == 0 || (h.block_end > h.block_begin && h.block_end <= h.n_layer)),
+               BN_ERR_ARG, "bn_model_create: block range [%d, %d) is not inside [0, %d)", h.block_begin, h.block_end, h.n_layer);
     bn_model *m = new bn_model();
     m->ctx = ctx;
     m->hp = h;
@@ -321,7 +345,10 @@ int bn_model_finalize(bn_model *m) {
     int rc = BN_OK;
     m->layers.resize(h.n_layer);
     m->n_gdn = m->n_attn = 0;
-    for (int b = 0; b < h.n_layer && rc == BN_OK; ++b) {
+    m->b0 = h.block_begin;
+    m->b1 = h.block_end > 0 ? h.block_end : h.n_layer;
+    const int S = h.n_streams > 0 ? h.n_streams : 1;
+    for (int b = m->b0; b < m->b1 && rc == BN_OK; ++b) {
         bn_model::Layer &L = m->layers[b];
         const std::string B = "blk." + std::to_string(b) + ".";
         L.attn = (b % h.attn_interval) == h.attn_interval - 1;
@@ -351,9 +378,11 @@ int bn_model_finalize(bn_model *m) {
             L.ssm_norm = tensor_ptr<float>(m, B + "ssm_norm.weight", size_t(D) * 4, &rc);
         }
     }
-    if (rc == BN_OK) m->embd = tensor_ptr<uint32_t>(m, "token_embd.weight", ptq_bytes(h.vocab, h.hidden), &rc);
-    if (rc == BN_OK) m->out_w = tensor_ptr<uint32_t>(m, "output.weight", ptq_bytes(h.vocab, h.hidden), &rc);
-    if (rc == BN_OK) m->out_norm = tensor_ptr<float>(m, "output_norm.weight", size_t(h.hidden) * 4, &rc);
+    if (rc == BN_OK && m->b0 == 0) m->embd = tensor_ptr<uint32_t>(m, "token_embd.weight", ptq_bytes(h.vocab, h.hidden), &rc);
+    if (rc == BN_OK && m->b1 == h.n_layer) {
+        m->out_w = tensor_ptr<uint32_t>(m, "output.weight", ptq_bytes(h.vocab, h.hidden), &rc);
+        if (rc == BN_OK) m->out_norm = tensor_ptr<float>(m, "output_norm.weight", size_t(h.hidden) * 4, &rc);
+    }
     if (rc != BN_OK) return rc;
 
     // activation arena
@@ -394,9 +423,11 @@ int bn_model_finalize(bn_model *m) {
     m->use_pdl = getenv("BONSAI_NO_PDL") == nullptr;
     // persistent state
     if (m->n_gdn) {
-        BN_CUDA(cudaMalloc(&m->gdn_state, size_t(m->n_gdn) * NH * D * D * 4));
-        BN_CUDA(cudaMalloc(&m->conv_hist, size_t(m->n_gdn) * C * 3 * 4 * 2));
-        m->conv_hist2 = m->conv_hist + size_t(m->n_gdn) * C * 3;
+        m->gdn_stream_stride = size_t(m->n_gdn) * NH * D * D;
+        m->conv_stream_stride = size_t(m->n_gdn) * C * 3;
+        BN_CUDA(cudaMalloc(&m->gdn_state, m->gdn_stream_stride * S * 4));
+        BN_CUDA(cudaMalloc(&m->conv_hist, m->conv_stream_stride * S * 4 * 2));
+        m->conv_hist2 = m->conv_hist + m->conv_stream_stride * S;
     }
     if (m->n_attn) {
         const size_t n = size_t(h.cap) * KD;
@@ -407,7 +438,7 @@ int bn_model_finalize(bn_model *m) {
         m->kv_v_off = al(h.v_mode == 0 ? n : n * 2);
         m->kv_v_scale_off = al(h.v_mode == 0 ? n / 32 * 2 : 0);
         m->kv_layer_bytes = o;
-        BN_CUDA(cudaMalloc(&m->kv, m->kv_layer_bytes * m->n_attn));
+        BN_CUDA(cudaMalloc(&m->kv, m->kv_layer_bytes * m->n_attn * S));
     }
     m->finalized = true;
     return bn_model_reset(m);
@@ -420,10 +451,11 @@ int bn_model_reset(bn_model *m) {
     cudaStream_t st = m->ctx->stream;
     BN_CUDA(cudaMemsetAsync(m->arena, 0, m->arena_bytes, st));
     if (m->n_gdn) {
-        BN_CUDA(cudaMemsetAsync(m->gdn_state, 0, size_t(m->n_gdn) * NH * D * D * 4, st));
-        BN_CUDA(cudaMemsetAsync(m->conv_hist, 0, size_t(m->n_gdn) * C * 3 * 4 * 2, st));
+        const int S = h.n_streams > 0 ? h.n_streams : 1;
+        BN_CUDA(cudaMemsetAsync(m->gdn_state, 0, m->gdn_stream_stride * S * 4, st));
+        BN_CUDA(cudaMemsetAsync(m->conv_hist, 0, m->conv_stream_stride * S * 4 * 2, st));
     }
-    if (m->n_attn) BN_CUDA(cudaMemsetAsync(m->kv, 0, m->kv_layer_bytes * m->n_attn, st));
+    if (m->n_attn) BN_CUDA(cudaMemsetAsync(m->kv, 0, m->kv_layer_bytes * m->n_attn * (h.n_streams > 0 ? h.n_streams : 1), st));
     return BN_OK;
 }
 
@@ -442,6 +474,8 @@ void bn_model_destroy(bn_model *m) {
 int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *next_tok) {
     BN_REQUIRE(m && m->finalized, BN_ERR_STATE, "bn_model_token: model not finalized");
     const bn_hparams &h = m->hp;
+    BN_REQUIRE(m->b0 == 0 && m->b1 == h.n_layer, BN_ERR_STATE, "bn_model_token: this model holds blocks [%d, %d) only; use bn_model_stage", m->b0, m->b1);
+    m->cur = 0;
     BN_REQUIRE(tok >= 0 && tok < h.vocab, BN_ERR_ARG, "bn_model_token: token %d outside vocab %d", tok, h.vocab);
     BN_REQUIRE(pos >= 0 && pos < h.cap, BN_ERR_BOUNDS, "bn_model_token: position %d does not fit the KV capacity %d", pos, h.cap);
     cudaStream_t st = m->ctx->stream;
@@ -465,6 +499,8 @@ int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *nex
 int bn_model_decode(bn_model *m, int first_tok, int pos0, int n_steps, int *out_tokens) {
     BN_REQUIRE(m && m->finalized, BN_ERR_STATE, "bn_model_decode: model not finalized");
     const bn_hparams &h = m->hp;
+    BN_REQUIRE(m->b0 == 0 && m->b1 == h.n_layer, BN_ERR_STATE, "bn_model_decode: this model holds blocks [%d, %d) only; use bn_model_stage", m->b0, m->b1);
+    m->cur = 0;
     BN_REQUIRE(first_tok >= 0 && first_tok < h.vocab, BN_ERR_ARG, "bn_model_decode: token %d outside vocab %d", first_tok, h.vocab);
     BN_REQUIRE(n_steps > 0 && pos0 >= 0 && pos0 + n_steps <= h.cap, BN_ERR_BOUNDS,
                "bn_model_decode: positions [%d, %d) do not fit the KV capacity %d", pos0, pos0 + n_steps, h.cap);
@@ -501,8 +537,56 @@ int bn_model_decode(bn_model *m, int first_tok, int pos0, int n_steps, int *out_
     return BN_OK;
 }
 
+int bn_model_stage(bn_model *m, int stream, int tok, int pos, const bn_buf *in, size_t in_off, bn_buf *out, size_t out_off) {
+    BN_REQUIRE(m && m->finalized, BN_ERR_STATE, "bn_model_stage: model not finalized");
+    const bn_hparams &h = m->hp;
+    const int S = h.n_streams > 0 ? h.n_streams : 1;
+    BN_REQUIRE(stream >= 0 && stream < S, BN_ERR_ARG, "bn_model_stage: stream %d outside [0, %d)", stream, S);
+    BN_REQUIRE(pos >= 0 && pos < h.cap, BN_ERR_BOUNDS, "bn_model_stage: position %d does not fit the KV capacity %d", pos, h.cap);
+    const bool first = m->b0 == 0, last = m->b1 == h.n_layer;
+    cudaStream_t st = m->ctx->stream;
+    if (first) {
+        BN_REQUIRE(tok < h.vocab, BN_ERR_ARG, "bn_model_stage: token %d outside vocab %d", tok, h.vocab);
+        if (tok < 0) BN_RANGE(in, in_off, 4, 4, "bn_model_stage token input");
+    } else BN_RANGE(in, in_off, size_t(h.hidden) * 4, 16, "bn_model_stage hidden input");
+    BN_RANGE(out, out_off, last ? 4 : size_t(h.hidden) * 4, 4, "bn_model_stage output");
+    m->cur = stream;
+    m->next_pos = pos + 1;
+    k_set_tok_pos<<<1, 32, 0, st>>>(m->TOK, m->POS, tok, pos, (first && tok < 0) ? bn_ptr<int>(in, in_off) : nullptr);
+    BN_COUNT(1);
+    if (!first) BN_CUDA(cudaMemcpyAsync(m->RES, bn_ptr<char>(in, in_off), size_t(h.hidden) * 4, cudaMemcpyDeviceToDevice, st));
+    enqueue_token(m, -1, true);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = m->launch_err;
+    m->launch_err = cudaSuccess;
+    if (e != cudaSuccess) return bn_cuda_fail(e, "stage schedule");
+    if (last) BN_CUDA(cudaMemcpyAsync(bn_ptr<char>(out, out_off), m->NEXT, 4, cudaMemcpyDeviceToDevice, st));
+    else BN_CUDA(cudaMemcpyAsync(bn_ptr<char>(out, out_off), m->RES, size_t(h.hidden) * 4, cudaMemcpyDeviceToDevice, st));
+    return BN_OK;
+}
+
+int bn_model_fill_kv(bn_model *m, int stream, int n_positions) {
+    BN_REQUIRE(m && m->finalized, BN_ERR_STATE, "bn_model_fill_kv: model not finalized");
+    const bn_hparams &h = m->hp;
+    const int S = h.n_streams > 0 ? h.n_streams : 1;
+    BN_REQUIRE(stream >= 0 && stream < S && n_positions >= 0 && n_positions <= h.cap, BN_ERR_ARG, "bn_model_fill_kv: bad stream or count");
+    const size_t n = size_t(n_positions) * h.n_kv * h.head_dim;
+    m->cur = stream;
+    for (int li = 0; li < m->n_attn && n; ++li) {
+        const bnk::KvLayer kv = kv_layer(m, li);
+        // every stored key / value element = 1.0: codes 127 with scale 1/127 (q8_0) or fp16 1.0
+        if (h.k_mode == 0) { BN_CUDA(cudaMemsetAsync(kv.k_data, 127, n, m->ctx->stream)); k_fill_u16<<<256, 256, 0, m->ctx->stream>>>(kv.k_scale, n / 32, 0x2008); }
+        else k_fill_u16<<<256, 256, 0, m->ctx->stream>>>(reinterpret_cast<uint16_t *>(kv.k_data), n, 0x3C00);
+        if (h.v_mode == 0) { BN_CUDA(cudaMemsetAsync(kv.v_data, 127, n, m->ctx->stream)); k_fill_u16<<<256, 256, 0, m->ctx->stream>>>(kv.v_scale, n / 32, 0x2008); }
+        else k_fill_u16<<<256, 256, 0, m->ctx->stream>>>(reinterpret_cast<uint16_t *>(kv.v_data), n, 0x3C00);
+        BN_COUNT(2);
+    }
+    return bn_launch_check(m->ctx, "bn_model_fill_kv");
+}
+
 int bn_model_gemv_sweep(bn_model *m, int reps, float *ms_per_sweep) {
     BN_REQUIRE(m && m->finalized && ms_per_sweep && reps > 0, BN_ERR_ARG, "bn_model_gemv_sweep: bad argument");
+    BN_REQUIRE(m->b0 == 0 && m->b1 == m->hp.n_layer, BN_ERR_STATE, "bn_model_gemv_sweep: whole model only");
     const bn_hparams &h = m->hp;
     const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D, IN = NH * D;
     const int QD = h.n_head * h.head_dim, KD = h.n_kv * h.head_dim;
@@ -579,11 +663,11 @@ int bn_model_read(bn_model *m, int what, int index, void *dst, size_t bytes) {
         case BN_READ_RESIDUAL: src = m->RES; have = size_t(h.hidden) * 4; break;
         case BN_READ_GDN_STATE:
             BN_REQUIRE(index >= 0 && index < m->n_gdn, BN_ERR_ARG, "bn_model_read: gdn layer %d out of range", index);
-            src = m->gdn_state + size_t(index) * NH * D * D; have = size_t(NH) * D * D * 4; break;
+            src = gdn_state_of(m, index); have = size_t(NH) * D * D * 4; break;
         case BN_READ_CONV_HIST:
             BN_REQUIRE(index >= 0 && index < m->n_gdn, BN_ERR_ARG, "bn_model_read: gdn layer %d out of range", index);
             // fused path: the taps the next token will read live in the buffer of its position parity
-            src = ((m->fused && (m->next_pos & 1)) ? m->conv_hist2 : m->conv_hist) + size_t(index) * C * 3; have = size_t(C) * 3 * 4; break;
+            src = conv_of(m, (m->fused && (m->next_pos & 1)) ? 1 : 0, index); have = size_t(C) * 3 * 4; break;
         case BN_READ_K_DATA: case BN_READ_K_SCALE: case BN_READ_V_DATA: case BN_READ_V_SCALE: {
             BN_REQUIRE(index >= 0 && index < m->n_attn, BN_ERR_ARG, "bn_model_read: attention layer %d out of range", index);
             const bnk::KvLayer kv = kv_layer(m, index);

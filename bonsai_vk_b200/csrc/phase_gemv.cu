@@ -10,7 +10,7 @@
 //
 // Data movement. Per (chunk, tile) the 16 row slices (28 bytes x blocks-per-chunk each, contiguous in
 // global memory) are fetched by 16 cp.async.bulk copies into a shared-memory stage with a padded row
-// pitch (bank-conflict-free register loads); 4 stages. A 17th warp only issues copies: it refills a
+// pitch (bank-conflict-free register loads); 8 stages (117 KB in flight per SM). A 17th warp only issues copies: it refills a
 // stage when all 16 compute warps have arrived on the stage's "empty" mbarrier, which they do as soon as
 // the rows are in registers, so warps drift apart by up to 4 tiles and their multiply, tensor-core and
 // epilogue phases overlap instead of running in lock-step. The cross-warp sum of a tile is deferred:
@@ -30,10 +30,11 @@
 namespace {
 using namespace bnk;
 
-constexpr int NT = PHASE_THREADS, NWARP = NT / 32, STAGES = 4, MAXCH = 32, MAXK = 12288 + 4096;
+constexpr int NT = PHASE_THREADS, NWARP = NT / 32, STAGES = 8, MAXCH = 32, MAXK = 12288 + 4096;
 constexpr int NTHREADS = NT + 32;      // 16 compute warps + 1 copy-issuing warp
 constexpr int RB = 8;                  // tiles per cross-warp reduction batch (2 batches of slots)
-constexpr int STAGE_BYTES = 16 * (MAXCH * 28 + 16);     // 14592
+constexpr int RPC = 1;                 // matrix rows per bulk copy (rows are contiguous in global memory)
+constexpr int STAGE_BYTES = 16 * (MAXCH * 28 + 16);     // 14592 (upper bound for every RPC)
 
 struct SL {   // shared-memory layout, byte offsets from a 128-byte aligned base
     static constexpr int ring = 0;
@@ -157,28 +158,32 @@ __device__ __forceinline__ Pow5 pow5(uint32_t v) {
     r.p3 = v * 27u; r.p4 = v * 81u; r.p5 = v * 243u;
     return r;
 }
-// two blocks of the same 16 rows: two independent accumulator chains, interleaved
+// two blocks of the same 16 rows: four independent accumulator chains of four tensor-core steps each
+// (a dependent mma.sync costs tens of cycles; integer adds are exact, so splitting the sum changes nothing)
 __device__ __forceinline__ void tile_mma2(int (&c)[4], int (&d)[4], const RowRegs &ra, const RowRegs &rb, const uint2 (&B)[8],
                                           const RowRegs &sa, const RowRegs &sb, const uint2 (&C)[8], uint32_t cq) {
+    int c2[4] = {0, 0, 0, 0}, d2[4] = {0, 0, 0, 0};
     Pow5 a = pow5(ra.h0), b = pow5(rb.h0), e = pow5(sa.h0), f = pow5(sb.h0);
     mma_u8s8(c, a.p1, b.p1, a.p2, b.p2, B[0].x, B[0].y);
     mma_u8s8(d, e.p1, f.p1, e.p2, f.p2, C[0].x, C[0].y);
-    mma_u8s8(c, a.p3, b.p3, a.p4, b.p4, B[1].x, B[1].y);
-    mma_u8s8(d, e.p3, f.p3, e.p4, f.p4, C[1].x, C[1].y);
+    mma_u8s8(c2, a.p3, b.p3, a.p4, b.p4, B[1].x, B[1].y);
+    mma_u8s8(d2, e.p3, f.p3, e.p4, f.p4, C[1].x, C[1].y);
     Pow5 a1 = pow5(ra.h1), b1 = pow5(rb.h1), e1 = pow5(sa.h1), f1 = pow5(sb.h1);
     mma_u8s8(c, a.p5, b.p5, a1.p1, b1.p1, B[2].x, B[2].y);
     mma_u8s8(d, e.p5, f.p5, e1.p1, f1.p1, C[2].x, C[2].y);
-    mma_u8s8(c, a1.p2, b1.p2, a1.p3, b1.p3, B[3].x, B[3].y);
-    mma_u8s8(d, e1.p2, f1.p2, e1.p3, f1.p3, C[3].x, C[3].y);
+    mma_u8s8(c2, a1.p2, b1.p2, a1.p3, b1.p3, B[3].x, B[3].y);
+    mma_u8s8(d2, e1.p2, f1.p2, e1.p3, f1.p3, C[3].x, C[3].y);
     mma_u8s8(c, a1.p4, b1.p4, a1.p5, b1.p5, B[4].x, B[4].y);
     mma_u8s8(d, e1.p4, f1.p4, e1.p5, f1.p5, C[4].x, C[4].y);
     a = pow5(ra.h2); b = pow5(rb.h2); e = pow5(sa.h2); f = pow5(sb.h2);
-    mma_u8s8(c, a.p1, b.p1, a.p2, b.p2, B[5].x, B[5].y);
-    mma_u8s8(d, e.p1, f.p1, e.p2, f.p2, C[5].x, C[5].y);
+    mma_u8s8(c2, a.p1, b.p1, a.p2, b.p2, B[5].x, B[5].y);
+    mma_u8s8(d2, e.p1, f.p1, e.p2, f.p2, C[5].x, C[5].y);
     mma_u8s8(c, a.p3, b.p3, a.p4, b.p4, B[6].x, B[6].y);
     mma_u8s8(d, e.p3, f.p3, e.p4, f.p4, C[6].x, C[6].y);
-    mma_u8s8(c, a.p5, b.p5, ra.hq * cq, rb.hq * cq, B[7].x, B[7].y);
-    mma_u8s8(d, e.p5, f.p5, sa.hq * cq, sb.hq * cq, C[7].x, C[7].y);
+    mma_u8s8(c2, a.p5, b.p5, ra.hq * cq, rb.hq * cq, B[7].x, B[7].y);
+    mma_u8s8(d2, e.p5, f.p5, sa.hq * cq, sb.hq * cq, C[7].x, C[7].y);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { c[i] += c2[i]; d[i] += d2[i]; }
 }
 // exact int -> float for |i| < 2^22 without the conversion unit
 __device__ __forceinline__ float small_int_to_float(int i) { return __fsub_rn(__int_as_float(0x4B400000 + i), 12582912.0f); }
@@ -205,7 +210,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_phase_gemv(const PhaseArgs a) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const int M = a.M, K = a.K, nb = K >> 7, ntiles = (M + 15) >> 4;
     const int CH = nb <= MAXCH ? nb : MAXCH, nchunks = nb / CH;      // blocks per chunk, chunks
-    const int pitch = CH * 28 + 16;
+    // a copy brings RPC consecutive rows when the chunk spans whole rows (they are contiguous in memory)
+    const int rpc = (nchunks == 1 && M % RPC == 0) ? RPC : 1;
+    const int rowb = CH * 28;                       // bytes of one row slice
+    const int gpitch = rpc * rowb + 16;             // pitch of a group of rpc rows
     const int t0 = int((long long)blockIdx.x * ntiles / gridDim.x), t1 = int((long long)(blockIdx.x + 1) * ntiles / gridDim.x);
     const int nt = t1 - t0, items = nt * nchunks;                     // item = (chunk, tile), chunk-major
 
@@ -220,10 +228,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_phase_gemv(const PhaseArgs a) {
         const int chunk = it / nt, tile = t0 + (it - chunk * nt), stage = it % STAGES;
         if (lane == 0) mbar_expect_tx(full + stage, 16u * uint32_t(CH) * 28u);
         __syncwarp();
-        if (lane < 16) {
-            const int row = min(tile * 16 + lane, M - 1);
-            bulk_copy(ring + stage * STAGE_BYTES + lane * pitch, a.W + (size_t(row) * nb + size_t(chunk) * CH) * 28,
-                      uint32_t(CH) * 28u, full + stage);
+        if (lane < 16 / rpc) {
+            // the last tile of the matrix may be short: clamp the group so it stays inside the matrix
+            const int row = min(tile * 16 + lane * rpc, M - rpc);
+            bulk_copy(ring + stage * STAGE_BYTES + lane * gpitch, a.W + (size_t(row) * nb + size_t(chunk) * CH) * 28,
+                      uint32_t(rpc * rowb), full + stage);
         }
     };
     const bool copy_warp = warp == NWARP;
@@ -496,8 +505,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_phase_gemv(const PhaseArgs a) {
         mbar_wait(full + stage, (it / STAGES) & 1, a.err);
         float va = 0.0f, vb = 0.0f;      // rows g and g+8: v_(2w) + v_(2w+1)
         if (active) {
-            const uint32_t *r0 = reinterpret_cast<const uint32_t *>(ring + stage * STAGE_BYTES + g * pitch + warp * 56);
-            const uint32_t *r1 = reinterpret_cast<const uint32_t *>(ring + stage * STAGE_BYTES + (g + 8) * pitch + warp * 56);
+            const int ga = g, gb = g + 8;
+            const uint32_t *r0 = reinterpret_cast<const uint32_t *>(ring + stage * STAGE_BYTES + (ga / rpc) * gpitch + (ga % rpc) * rowb + warp * 56);
+            const uint32_t *r1 = reinterpret_cast<const uint32_t *>(ring + stage * STAGE_BYTES + (gb / rpc) * gpitch + (gb % rpc) * rowb + warp * 56);
             const uint32_t a6 = r0[6], b6 = r1[6], e6 = r0[13], f6 = r1[13];
             const uint32_t af = r0[first], as = r0[second], bf = r1[first], bs = r1[second];
             const uint32_t ef = r0[7 + first], es = r0[7 + second], ff = r1[7 + first], fs = r1[7 + second];

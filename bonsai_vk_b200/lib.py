@@ -21,7 +21,7 @@ class HParamsC(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "n_layer", "hidden", "ffn", "vocab", "n_head", "n_kv", "head_dim", "n_rot", "attn_interval",
         "gdn_heads", "gdn_qk_heads", "gdn_dim", "hat_block", "act_mode", "k_mode", "v_mode", "cap")] + [
-        ("rms_eps", C.c_float), ("rope_base", C.c_float)]
+        ("rms_eps", C.c_float), ("rope_base", C.c_float)] + [(n, C.c_int32) for n in ("n_streams", "block_begin", "block_end")]
 
 
 READ_LOGITS, READ_RESIDUAL, READ_GDN_STATE, READ_CONV_HIST, READ_K_DATA, READ_K_SCALE, READ_V_DATA, READ_V_SCALE = range(8)
@@ -69,6 +69,10 @@ def load_library() -> C.CDLL:
         "bn_model_token": (i32, [vp, i32, i32, i32, C.POINTER(i32)]),
         "bn_model_read": (i32, [vp, i32, i32, vp, sz]),
         "bn_model_decode": (i32, [vp, i32, i32, i32, C.POINTER(i32)]),
+        "bn_model_stage": (i32, [vp, i32, i32, i32, vp, sz, vp, sz]),
+        "bn_model_fill_kv": (i32, [vp, i32, i32]),
+        "bn_wrap": (i32, [vp, vp, sz, C.POINTER(vp)]),
+        "bn_use_stream": (i32, [vp, vp]),
         "bn_model_gemv_sweep": (i32, [vp, i32, C.POINTER(C.c_float)]),
         "bn_model_profile_token": (i32, [vp, i32, i32, vp, i32, C.POINTER(i32)]),
     }
@@ -151,6 +155,19 @@ class Context:
     def sync(self):
         _check(self.lib.bn_sync(self.h), "bn_sync")
 
+    def use_stream(self, cuda_stream: int):
+        """Run this context's kernels on a stream owned by the caller (e.g. torch's current stream)."""
+        _check(self.lib.bn_use_stream(self.h, C.c_void_p(cuda_stream)), "bn_use_stream")
+
+    def wrap(self, device_ptr: int, nbytes: int) -> "Buffer":
+        """A Buffer over device memory the caller owns (e.g. a torch tensor used for NCCL send/recv)."""
+        b = Buffer.__new__(Buffer)
+        b.ctx, b.nbytes = self, int(nbytes)
+        h = C.c_void_p()
+        _check(self.lib.bn_wrap(self.h, C.c_void_p(device_ptr), int(nbytes), C.byref(h)), "bn_wrap")
+        b.h = h
+        return b
+
     def info(self):
         sm, fr, tot = C.c_int(), C.c_size_t(), C.c_size_t()
         _check(self.lib.bn_device_info(self.h, C.byref(sm), C.byref(fr), C.byref(tot)), "bn_device_info")
@@ -198,7 +215,8 @@ class Model:
     def __init__(self, ctx: Context, hp, tensors: dict, signs: np.ndarray):
         self.ctx, self.hp = ctx, hp
         lib = ctx.lib
-        hc = HParamsC(**{k: (float(v) if k in ("rms_eps", "rope_base") else int(v)) for k, v in hp.asdict().items()})
+        fields = {f[0] for f in HParamsC._fields_}
+        hc = HParamsC(**{k: (float(v) if k in ("rms_eps", "rope_base") else int(v)) for k, v in hp.asdict().items() if k in fields})
         h = C.c_void_p()
         _check(lib.bn_model_create(ctx.h, C.byref(hc), C.byref(h)), "bn_model_create")
         self.h = h
@@ -206,6 +224,19 @@ class Model:
         total = sum(al(np.asarray(t).nbytes) for t in tensors.values()) + al(signs.nbytes)
         self.weights = ctx.alloc(total)
         off = 0
+        b0, b1 = getattr(hp, "block_begin", 0), (getattr(hp, "block_end", 0) or hp.n_layer)
+
+        def local(name: str) -> bool:
+            if name.startswith("blk."):
+                return b0 <= int(name.split(".")[1]) < b1
+            if name == "token_embd.weight":
+                return b0 == 0
+            return b1 == hp.n_layer           # output.weight, output_norm.weight
+
+        tensors = {n: t for n, t in tensors.items() if local(n)}
+        total = sum(al(np.asarray(t).nbytes) for t in tensors.values()) + al(signs.nbytes)
+        self.weights.free()
+        self.weights = ctx.alloc(total)
         for name, t in tensors.items():
             a = np.ascontiguousarray(t)
             self.weights.upload(a, off)
@@ -224,6 +255,14 @@ class Model:
         _check(self.ctx.lib.bn_model_token(self.h, tok, pos, stop_after, C.byref(nxt) if want_next else None),
                "bn_model_token")
         return int(nxt.value)
+
+    def stage(self, stream: int, tok: int, pos: int, inp: "Buffer | None", out: "Buffer", in_off: int = 0, out_off: int = 0):
+        """One pipeline stage for one token of one stream (enqueue only)."""
+        _check(self.ctx.lib.bn_model_stage(self.h, stream, tok, pos, inp.h if inp is not None else None, in_off, out.h, out_off),
+               "bn_model_stage")
+
+    def fill_kv(self, stream: int, n_positions: int):
+        _check(self.ctx.lib.bn_model_fill_kv(self.h, stream, n_positions), "bn_model_fill_kv")
 
     def decode(self, first_tok: int, pos0: int, n_steps: int, fetch: bool = True):
         """n_steps greedy tokens chained on the device; returns the picks (or None when fetch=False)."""

@@ -1,0 +1,120 @@
+"""Layer-pipelined decode over several GPUs of one box (one process per GPU, torch.distributed).
+
+Semantics taken from the reference's multi-GPU rig (runtime_vk/gpu_fleet.h:949-1115 split, :1414-1626 runner):
+contiguous block ranges, the embedding on the first stage and the output head on the last, recurrent state and
+KV cache never leave their stage, one hand-off of the `hidden` fp32 values (16 KiB at hidden 4096) per stage
+boundary per token, and micro-batching = several sequences in flight so that every stage is busy. The transport
+here is NCCL send/recv over NVLink into the consumer's own buffer (the reference stages through a host-pinned
+ring); the only other message is the picked token id going from the last stage back to the first.
+
+Two process groups are used on purpose: hidden states flow forward on one communicator and token ids flow
+backward on another, so a token send that is waiting for the first stage to reach the next step can never
+sit in front of a hidden-state receive on the same NCCL stream (that ordering would deadlock the ring).
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Tuple
+
+
+def split_blocks(n_layer: int, world: int, balance: str = "equal", block_bytes=None, head_bytes: int = 0,
+                 embed_bytes: int = 0) -> List[Tuple[int, int]]:
+    """Contiguous block ranges per stage. "equal": the same number of blocks per stage (the benchmark config:
+    16/8/4 blocks on 2/4/8 GPUs). "bytes": ranges balanced by bytes read per token, with the head's bytes
+    charged to the last stage and the embedding's to the first, as fleet_split_schedule does
+    (runtime_vk/gpu_fleet.h:1013-1020). Refuses more stages than blocks."""
+    if world < 1 or world > n_layer:
+        raise ValueError(f"cannot split {n_layer} blocks over {world} stages")
+    if balance == "equal":
+        base, extra = divmod(n_layer, world)
+        out, b = [], 0
+        for r in range(world):
+            n = base + (1 if r < extra else 0)
+            out.append((b, b + n))
+            b += n
+        return out
+    if balance != "bytes":
+        raise ValueError(f"unknown balance mode {balance!r}")
+    w = list(block_bytes) if block_bytes is not None else [1] * n_layer
+    if len(w) != n_layer:
+        raise ValueError("block_bytes must have one entry per block")
+    total = sum(w) + head_bytes + embed_bytes
+    out, b, acc = [], 0, float(embed_bytes)
+    for r in range(world):
+        remaining_stages = world - r
+        if r == world - 1:
+            out.append((b, n_layer))
+            break
+        target = total * (r + 1) / world
+        e = b + 1
+        acc += w[b]
+        # take blocks while we are below this stage's cumulative target and enough blocks remain for the others
+        while e < n_layer - (remaining_stages - 1) and acc + w[e] / 2 <= target:
+            acc += w[e]
+            e += 1
+        out.append((b, e))
+        b = e
+    return out
+
+
+class Pipeline:
+    """Runs `n_steps` greedy decode steps of `n_streams` sequences through the stages.
+
+    stage_fn(stream, step, pos, tok_first, tok_in, hidden_in, out) enqueues this rank's blocks:
+      first stage : tok_first (int, step 0) or tok_in (tensor holding one int32, later steps) -> out (hidden)
+      middle      : hidden_in -> out (hidden)
+      last stage  : hidden_in -> out (tensor holding one int32: the pick)
+    new_hidden() / new_token() allocate the message tensors on the right device."""
+
+    def __init__(self, dist, rank: int, world: int, n_streams: int, stage_fn: Callable, new_hidden: Callable,
+                 new_token: Callable, fwd_group=None, back_group=None):
+        self.dist, self.rank, self.world, self.S = dist, rank, world, n_streams
+        self.stage_fn = stage_fn
+        self.first, self.last = rank == 0, rank == world - 1
+        self.fwd, self.back = fwd_group, back_group
+        self.h_in = [new_hidden() for _ in range(n_streams)] if not self.first else None
+        self.h_out = [new_hidden() for _ in range(n_streams)] if not self.last else None
+        self.t_in = [new_token() for _ in range(n_streams)] if self.first and world > 1 else None
+        self.t_out = [new_token() for _ in range(n_streams)] if self.last else None
+        self.picks: List[list] = [[] for _ in range(n_streams)]
+
+    def run(self, first_tokens, pos0, n_steps: int, collect: bool = True):
+        d, S, P = self.dist, self.S, self.world
+        send_h = [None] * S
+        send_t = [None] * S
+        for step in range(n_steps):
+            for s in range(S):
+                pos = pos0[s] + step
+                tok_in = None
+                if self.first:
+                    if step > 0:
+                        if P > 1:
+                            d.irecv(self.t_in[s], src=P - 1, group=self.back).wait()
+                            tok_in = self.t_in[s]
+                        else:
+                            tok_in = self.t_out[s]
+                    hin = None
+                else:
+                    d.irecv(self.h_in[s], src=self.rank - 1, group=self.fwd).wait()
+                    hin = self.h_in[s]
+                if self.last:
+                    if send_t[s] is not None:
+                        send_t[s].wait()            # the previous pick of this stream has left the buffer
+                        send_t[s] = None            # (a send handle is waited on exactly once)
+                    out = self.t_out[s]
+                else:
+                    if send_h[s] is not None:
+                        send_h[s].wait()
+                        send_h[s] = None
+                    out = self.h_out[s]
+                self.stage_fn(s, step, pos, first_tokens[s] if (self.first and step == 0) else None, tok_in, hin, out)
+                if self.last:
+                    if collect:
+                        self.picks[s].append(out.clone())
+                    if P > 1 and step + 1 < n_steps:
+                        send_t[s] = d.isend(out, dst=0, group=self.back)
+                else:
+                    send_h[s] = d.isend(out, dst=self.rank + 1, group=self.fwd)
+        for h in send_h + send_t:
+            if h is not None:
+                h.wait()
+        return [[int(t.item()) for t in row] for row in self.picks] if (self.last and collect) else None

@@ -34,6 +34,9 @@ class HParams:
     cap: int = 256
     rms_eps: float = 1e-6
     rope_base: float = 1e7
+    n_streams: int = 1          # independent sequences resident on the device
+    block_begin: int = 0        # pipeline stage: this device holds blocks [block_begin, block_end)
+    block_end: int = 0          # 0 = n_layer
 
     def is_attn(self, b: int) -> bool:
         return b % self.attn_interval == self.attn_interval - 1

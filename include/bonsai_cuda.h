@@ -109,6 +109,10 @@ typedef struct bn_hparams {
     int32_t k_mode, v_mode;                   /* KV cache: 0 = q8_0, 1 = fp16 */
     int32_t cap;                              /* KV capacity in positions (reference: BONSAI_CAP, even) */
     float rms_eps, rope_base;
+    /* multi-stream / pipeline-stage extensions (0 = one stream, whole model) */
+    int32_t n_streams;                        /* independent sequences, each with its own KV cache and recurrent state */
+    int32_t block_begin, block_end;           /* this device holds blocks [begin, end); end 0 = n_layer. The embedding
+                                                 belongs to the stage with block 0, the output head to the last one */
 } bn_hparams;
 
 enum bn_read_what {
@@ -129,6 +133,20 @@ void bn_model_destroy(bn_model *m);
  * (first maximum, as Sampler::pick with temp <= 0); >= 0 stops after that block (alignment harness,
  * reference: BONSAI_LADDER / stop_at_block). next_tok may be NULL (nothing is copied back then). */
 int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *next_tok);
+/* One pipeline stage (reference: the contiguous layer ranges of fleet_split_schedule, runtime_vk/gpu_fleet.h:990,
+ * and the per-hop 16 KiB hidden-state hand-off, gpu_fleet.h:97): run this device's blocks for one token of
+ * sequence `stream` at position pos. First stage: tok >= 0 is the token id, tok < 0 reads it from the int at
+ * (in, in_off). Other stages: (in, in_off) holds the `hidden` fp32 values from the previous stage. Output: the
+ * hidden state at (out, out_off), or on the last stage the greedy pick as one int. Enqueues only - no host wait. */
+int bn_model_stage(bn_model *m, int stream, int tok, int pos, const bn_buf *in, size_t in_off, bn_buf *out, size_t out_off);
+/* timing fixture (reference: BONSAI_KVFILL, bonsai_forward.h:1338-1378): mark the first n_positions of a
+ * stream's KV caches as filled with 1.0 so long-context steps can be timed without a long prefill */
+int bn_model_fill_kv(bn_model *m, int stream, int n_positions);
+/* wrap device memory owned by the caller (the benchmark's NCCL buffers) as a bn_buf; bn_free releases only the handle */
+int bn_wrap(bn_ctx *ctx, void *device_ptr, size_t bytes, bn_buf **out);
+/* run this context's work on a stream owned by the caller (so it orders with the caller's NCCL calls) */
+int bn_use_stream(bn_ctx *ctx, void *cuda_stream);
+
 /* n_steps greedy tokens chained on the device: the pick of step i is the input of step i+1 with no
  * host round trip (the reference reads 248 320 logits back and picks on the host every token,
  * bonsai_forward.h:712,749,2890-2997). out_tokens (may be NULL) receives the n_steps picks; when it

@@ -1,0 +1,110 @@
+"""Host-side logic of the layer pipeline, without a GPU: split arithmetic (reference: the 55 host-only checks of
+`bonsai_fleet selftest`, runtime_vk/bonsai_fleet.cpp:817-1069) and the message schedule run as two / three gloo
+ranks on CPU with a stand-in stage function."""
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+
+import pytest
+
+from bonsai_vk_b200.pipeline import split_blocks
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_equal_split_matches_benchmark_config():
+    assert split_blocks(32, 2) == [(0, 16), (16, 32)]
+    assert split_blocks(32, 4) == [(0, 8), (8, 16), (16, 24), (24, 32)]
+    assert [b - a for a, b in split_blocks(32, 8)] == [4] * 8
+    assert split_blocks(32, 1) == [(0, 32)]
+    assert split_blocks(5, 2) == [(0, 3), (3, 5)]
+
+
+def test_split_is_contiguous_and_refuses_bad_requests():
+    for world in (1, 2, 3, 4, 8):
+        for mode in ("equal", "bytes"):
+            r = split_blocks(32, world, mode, block_bytes=[48923392 if b % 4 != 3 else 45910016 for b in range(32)],
+                             head_bytes=222494720)
+            assert r[0][0] == 0 and r[-1][1] == 32
+            assert all(a < b for a, b in r) and all(r[i][1] == r[i + 1][0] for i in range(len(r) - 1))
+    with pytest.raises(ValueError):
+        split_blocks(4, 5)
+    with pytest.raises(ValueError):
+        split_blocks(4, 0)
+
+
+def test_byte_balanced_split_gives_the_head_stage_fewer_blocks():
+    """Per-block bytes of the 9B in native PTQ1_0 form: GDN 48 923 392, attention 45 910 016
+    (runtime_vk/gpu_fleet.h:984-988); the 222 MB head sits on the last stage."""
+    bb = [48923392 if b % 4 != 3 else 45910016 for b in range(32)]
+    r = split_blocks(32, 8, "bytes", block_bytes=bb, head_bytes=222494720)
+    sizes = [b - a for a, b in r]
+    assert sizes[-1] < 4 and sum(sizes) == 32
+    loads = [sum(bb[a:b]) for a, b in r]
+    loads[-1] += 222494720
+    assert max(loads) < 1.35 * (sum(bb) + 222494720) / 8
+
+
+WORKER = textwrap.dedent('''
+    import os, sys, torch, torch.distributed as dist
+    sys.path.insert(0, os.environ["BONSAI_ROOT"])
+    from bonsai_vk_b200.pipeline import Pipeline
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    fwd, back = dist.new_group(list(range(world))), dist.new_group(list(range(world)))
+    S, T, H, V = 5, 4, 8, 97
+    def stage(s, step, pos, tok_first, tok_in, hin, out):
+        if rank == 0:
+            tok = tok_first if tok_first is not None else int(tok_in.item())
+            h = torch.arange(H, dtype=torch.float32) * (tok + 1) + pos
+        else:
+            h = hin.clone()
+        h = h * 1.5 + (rank + 1)
+        if rank == world - 1:
+            out.fill_(int(h.sum().item()) % V)
+        else:
+            out.copy_(h)
+    p = Pipeline(dist, rank, world, S, stage, lambda: torch.zeros(H), lambda: torch.zeros(1, dtype=torch.int32), fwd, back)
+    first = [3 + s for s in range(S)]
+    picks = p.run(first, [10 * s for s in range(S)], T)
+    if rank == world - 1:
+        # the same recurrence in one process
+        want = []
+        for s in range(S):
+            tok, row = first[s], []
+            for step in range(T):
+                h = torch.arange(H, dtype=torch.float32) * (tok + 1) + (10 * s + step)
+                for r in range(world):
+                    h = h * 1.5 + (r + 1)
+                tok = int(h.sum().item()) % V
+                row.append(tok)
+            want.append(row)
+        assert picks == want, (picks, want)
+        print("PIPELINE_OK")
+    dist.barrier()
+    dist.destroy_process_group()
+''')
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_message_schedule_on_gloo(world, tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    with socket.socket() as sck:
+        sck.bind(("127.0.0.1", 0))
+        port = sck.getsockname()[1]
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   BONSAI_ROOT=ROOT)
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    try:
+        outs = [p.communicate(timeout=120)[0] for p in procs]
+    finally:
+        for p in procs:            # never leave a rank behind (each is ended through its own handle)
+            if p.poll() is None:
+                p.kill()
+    assert all(p.returncode == 0 for p in procs), outs
+    assert "PIPELINE_OK" in outs[-1]
