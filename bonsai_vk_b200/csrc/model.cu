@@ -43,6 +43,7 @@ struct bn_model {
     cudaError_t launch_err = cudaSuccess;
     unsigned long long *stamps = nullptr;   // profiling aid: 8 time stamps per phase kernel of one token
     int stamp_idx = 0;
+    unsigned long long *graph_stamps = nullptr;
     // resolved per-layer weights
     struct Layer {
         bool attn;
@@ -212,10 +213,9 @@ void gdn_fused(bn_model *m, const bn_model::Layer &L) {
         const bnk::GdnDims gd{NH, NQ, D};
         float *h0 = conv_of(m, 0, L.idx), *h1 = conv_of(m, 1, L.idx);
         bnk::gdn_core_fused(m->ctx->stream, gd, h.hidden, m->QKV, L.conv_w, h0, h1, m->POS, m->RES, m->G + 48, L.attn_norm,
-                            L.alpha_w, L.beta_w, L.dt_bias, L.ssm_a, gdn_state_of(m, L.idx), m->O);
+                            L.alpha_w, L.beta_w, L.dt_bias, L.ssm_a, gdn_state_of(m, L.idx), m->Z, L.ssm_norm, h.rms_eps, m->X1);
     }
     bnk::PhaseArgs o = phase_base(m, L.ssm_out, h.hidden, IN, m->signs);
-    bnk::gdn_out(m->ctx->stream, bnk::GdnDims{NH, NQ, D}, m->O, m->Z, L.ssm_norm, h.rms_eps, m->X1);
     o.pro = bnk::PRO_PLAIN; o.x0 = m->X1;
     o.resid_in = m->RES; o.resid_out = m->RES;
     launch(m, o);
@@ -272,6 +272,7 @@ void enqueue_token(bn_model *m, int stop_after, bool want_logits) {
 
 // feed the greedy pick back as the next input, on the device
 __global__ void k_advance(int *tok, int *pos, const int *next, int *hist, int *step) {
+    bnk::pdl_sync();
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     const int s = step[0];
     hist[s] = next[0];
@@ -281,6 +282,7 @@ __global__ void k_advance(int *tok, int *pos, const int *next, int *hist, int *s
 }
 
 __global__ void k_set_tok_pos(int *tok, int *pos, int t, int p, const int *tok_src) {
+    bnk::pdl_sync();
     if (threadIdx.x == 0) { tok[0] = tok_src ? tok_src[0] : t; pos[0] = p; }
 }
 __global__ void k_fill_u16(uint16_t *p, size_t n, uint16_t v) {
@@ -421,6 +423,7 @@ int bn_model_finalize(bn_model *m) {
     m->fused = getenv("BONSAI_NO_FUSE") == nullptr && bnk::phase_supported(h.hidden, h.hidden, h.hat_block) &&
                bnk::phase_supported(h.hidden, h.ffn, h.hat_block);
     m->use_pdl = getenv("BONSAI_NO_PDL") == nullptr;
+    bnk::g_pdl = m->use_pdl;
     // persistent state
     if (m->n_gdn) {
         m->gdn_stream_stride = size_t(m->n_gdn) * NH * D * D;
@@ -508,10 +511,16 @@ int bn_model_decode(bn_model *m, int first_tok, int pos0, int n_steps, int *out_
     if (!m->token_graph) {
         cudaGraph_t g = nullptr;
         const unsigned long long before = g_bn_launches;
+        if (getenv("BONSAI_STAMP_GRAPH")) {      // profiling aid: the captured kernels keep writing their time stamps
+            BN_CUDA(cudaMalloc(&m->stamps, 256 * 8 * sizeof(unsigned long long)));
+            BN_CUDA(cudaMemset(m->stamps, 0, 256 * 8 * sizeof(unsigned long long)));
+            m->stamp_idx = 0;
+        }
         BN_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
         enqueue_token(m, -1, true);
-        k_advance<<<1, 32, 0, st>>>(m->TOK, m->POS, m->NEXT, m->HIST, m->STEP);
-        BN_COUNT(1);
+        m->graph_stamps = m->stamps;
+        m->stamps = nullptr;
+        bnk::launch(k_advance, dim3(1), dim3(32), 0, st, m->TOK, m->POS, m->NEXT, m->HIST, m->STEP);
         cudaError_t e = cudaStreamEndCapture(st, &g);
         if (e != cudaSuccess) return bn_cuda_fail(e, "cudaStreamEndCapture(token)");
         m->graph_launches = int(g_bn_launches - before);
@@ -677,6 +686,7 @@ int bn_model_read(bn_model *m, int what, int index, void *dst, size_t bytes) {
             if (what == BN_READ_V_SCALE) { src = kv.v_scale; have = h.v_mode == 0 ? kvn / 32 * 2 : 0; }
             break;
         }
+        case 8: src = m->graph_stamps; have = m->graph_stamps ? 256 * 8 * sizeof(unsigned long long) : 0; break;
         default: BN_REQUIRE(false, BN_ERR_ARG, "bn_model_read: unknown selector %d", what);
     }
     BN_REQUIRE(src && bytes <= have, BN_ERR_BOUNDS, "bn_model_read: %zu bytes requested, %zu available", bytes, have);

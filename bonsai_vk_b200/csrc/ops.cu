@@ -42,6 +42,7 @@ __device__ __forceinline__ void fwht_smem(float *s, int N, float inv) {
 __global__ void __launch_bounds__(512) k_rotate_quant(const float *__restrict__ x, const int32_t *__restrict__ signs,
                                                       int block, float inv, float *__restrict__ y,
                                                       uint32_t *__restrict__ q81, uint32_t *__restrict__ table) {
+    bnk::pdl_sync();
     extern __shared__ float s[];                   // block floats + 4 x 128 bytes
     int8_t *qs = reinterpret_cast<int8_t *>(s + block);
     const size_t base = size_t(blockIdx.x) * block;
@@ -60,6 +61,7 @@ __global__ void __launch_bounds__(512) k_rotate_quant(const float *__restrict__ 
 
 __global__ void __launch_bounds__(512) k_rotate_inv(const float *__restrict__ x, const int32_t *__restrict__ signs,
                                                     int block, float inv, float *__restrict__ y) {
+    bnk::pdl_sync();
     extern __shared__ float s[];
     const size_t base = size_t(blockIdx.x) * block;
     for (int i = threadIdx.x; i < block; i += blockDim.x) s[i] = x[base + i];
@@ -70,6 +72,7 @@ __global__ void __launch_bounds__(512) k_rotate_inv(const float *__restrict__ x,
 // ---- embedding gather (reference addressing: runtime_vk/shaders/gather_rows.comp:12-16) ----------
 __global__ void k_embed_row(const uint32_t *__restrict__ W, int K, const int *__restrict__ tok_ptr,
                             float *__restrict__ out) {
+    bnk::pdl_sync();
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= K) return;
     const int tok = tok_ptr[0];
@@ -90,6 +93,7 @@ __global__ void k_embed_row(const uint32_t *__restrict__ W, int K, const int *__
 // combined by the fixed tree; y = (x * inv) * w.
 __global__ void __launch_bounds__(256) k_rms_norm(const float *__restrict__ x, const float *__restrict__ w, int cols,
                                                   float eps, float *__restrict__ y) {
+    bnk::pdl_sync();
     __shared__ float part[256];
     const int l = threadIdx.x, per = (cols + 255) / 256;
     const float *xr = x + size_t(blockIdx.x) * cols;
@@ -109,11 +113,13 @@ __global__ void __launch_bounds__(256) k_rms_norm(const float *__restrict__ x, c
 }
 
 __global__ void k_add_inplace(float *__restrict__ res, const float *__restrict__ d, int n) {
+    bnk::pdl_sync();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) res[i] = __fadd_rn(d[i], res[i]);
 }
 
 __global__ void k_swiglu(const float *__restrict__ a, const float *__restrict__ b, int n, float *__restrict__ y) {
+    bnk::pdl_sync();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) y[i] = __fmul_rn(silu_f(a[i]), b[i]);
 }
@@ -122,6 +128,7 @@ __global__ void k_swiglu(const float *__restrict__ a, const float *__restrict__ 
 // element, then a 32-lane xor tree (reference: runtime_vk/shaders/gemv_f32.comp).
 __global__ void k_gemv_f32_small(const float *__restrict__ W, int M, int K, const float *__restrict__ x,
                                  float *__restrict__ out) {
+    bnk::pdl_sync();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= M) return;
     const float4 *wr = reinterpret_cast<const float4 *>(W + size_t(row) * K);
@@ -140,6 +147,7 @@ __global__ void k_gemv_f32_small(const float *__restrict__ W, int M, int K, cons
 // gate = ssm_a * softplus(alpha + dt_bias), beta = sigmoid(beta_raw)   (bonsai_forward.h:528-535)
 __global__ void k_gdn_gates(const float *alpha, const float *beta_raw, const float *dt_bias, const float *ssm_a, int n,
                             float *gate, float *beta) {
+    bnk::pdl_sync();
     const int i = threadIdx.x;
     if (i >= n) return;
     const float a = __fadd_rn(alpha[i], dt_bias[i]);
@@ -151,6 +159,7 @@ __global__ void k_gdn_gates(const float *alpha, const float *beta_raw, const flo
 // 4-tap causal depthwise conv + silu + history shift (runtime_vk/shaders/conv_silu.comp:35-49)
 __global__ void k_conv_silu(const float *__restrict__ x, const float *__restrict__ w, float *__restrict__ hist,
                             int channels, float *__restrict__ y) {
+    bnk::pdl_sync();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= channels) return;
     float *s = hist + 3 * size_t(c);
@@ -175,6 +184,7 @@ __device__ __forceinline__ float warp_tree128(float e0, float e1, float e2, floa
 
 // L2 norm of 128-wide rows, mode 1 (runtime_vk/shaders/l2_norm.comp:59-78); one warp per row
 __global__ void k_l2_norm_rows(const float *__restrict__ x, int rows, float eps, float *__restrict__ y) {
+    bnk::pdl_sync();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), l = threadIdx.x & 31;
     if (row >= rows) return;
     const float *xr = x + size_t(row) * 128;
@@ -191,6 +201,7 @@ __global__ void __launch_bounds__(256) k_gdn_delta(int heads, int qk_heads, cons
                                                    const float *__restrict__ k, const float *__restrict__ v,
                                                    const float *__restrict__ gate, const float *__restrict__ beta,
                                                    float *__restrict__ state, float *__restrict__ o, float scale) {
+    bnk::pdl_sync();
     const int h = blockIdx.y, j = blockIdx.x * 8 + (threadIdx.x >> 5), l = threadIdx.x & 31;
     const int hq = h % qk_heads;
     const float eg = exp_f(gate[h]), bt = beta[h];
@@ -207,32 +218,42 @@ __global__ void __launch_bounds__(256) k_gdn_delta(int heads, int qk_heads, cons
     if (l == 0) o[h * 128 + j] = __fmul_rn(ov, scale);
 }
 
-// Fused gated-delta-net core of one layer: the two small fp32 projections of the normed residual and their
-// gate functions (bonsai_forward.h:523-535), conv + silu of the channels this CTA needs, L2 norms of its q/k
-// head, and the delta rule on 32 state rows. grid (128/32 row chunks, v-heads), 256 threads.
-// The conv history is double-buffered by position parity: several CTAs read the taps of a shared q/k head
-// while exactly one of them (and, for the v channels, their only reader) writes the shifted taps into the
-// other buffer. Arithmetic and its order are those of the stand-alone kernels above.
-__global__ void __launch_bounds__(256) k_gdn_core(int heads, int qk_heads, int hidden, const float *__restrict__ qkv,
+// Fused gated-delta-net mixer of one layer, one CTA of 512 threads per v-head: the two small fp32 projections
+// of the normed residual and their gate functions (bonsai_forward.h:523-535), conv + silu of the head's q, k
+// and v channels, L2 norms, the delta rule on the head's 128 state rows, then the per-head RMS, ssm_norm,
+// swiglu(z, .) and the v-grouped permutation (bonsai_forward.h:559-567) straight into the next projection's
+// input. The conv history is double-buffered by position parity: the two v-heads that share a q/k head both
+// read its taps while one of them writes the shifted taps into the other buffer.
+// Arithmetic and its order are those of the stand-alone kernels above.
+__global__ void __launch_bounds__(512) k_gdn_core(int heads, int qk_heads, int hidden, const float *__restrict__ qkv,
                                                   const float *__restrict__ conv_w, float *__restrict__ hist0,
                                                   float *__restrict__ hist1, const int *__restrict__ pos_ptr,
-                                                  const float *__restrict__ x,
-                                                  const float *__restrict__ inv_ptr, const float *__restrict__ norm_w,
-                                                  const float *__restrict__ alpha_w, const float *__restrict__ beta_w,
-                                                  const float *__restrict__ dt_bias, const float *__restrict__ ssm_a,
-                                                  float *__restrict__ state, float *__restrict__ o, float scale) {
-    __shared__ float sq[128], sk[128], sv[32], sgb[2];
-    extern __shared__ float4 rows[];               // [2][hidden/4]: row h of ssm_alpha and of ssm_beta
-    const int h = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    {   // all loads of the two rows in flight at once (they come from HBM), the dependent chains run from shared memory
-        const float4 *ra = reinterpret_cast<const float4 *>(alpha_w + size_t(h) * hidden), *rb = reinterpret_cast<const float4 *>(beta_w + size_t(h) * hidden);
-        for (int i = tid; i < hidden / 4; i += 256) { rows[i] = ra[i]; rows[hidden / 4 + i] = rb[i]; }
-    }
-    const int hq = h % qk_heads;
-    // a token at position p reads the taps from buffer p & 1 and writes the shifted taps to the other one
-    const bool odd = pos_ptr[0] & 1;
+                                                  const float *__restrict__ x, const float *__restrict__ inv_ptr,
+                                                  const float *__restrict__ norm_w, const float *__restrict__ alpha_w,
+                                                  const float *__restrict__ beta_w, const float *__restrict__ dt_bias,
+                                                  const float *__restrict__ ssm_a, float *__restrict__ state,
+                                                  const float *__restrict__ z, const float *__restrict__ ssm_norm, float eps,
+                                                  float *__restrict__ y, float scale) {
+    bnk::pdl_sync();
+    __shared__ float sq[128], sk[128], sv[128], so[128], sgb[2];
+    extern __shared__ float4 dyn[];                // [3][hidden/4]: normed residual, row h of ssm_alpha, row h of ssm_beta
+    const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hq = h % qk_heads, n4 = hidden / 4;
+    const bool odd = pos_ptr[0] & 1;               // a token at position p reads taps from buffer p & 1, writes the other
     const float *hist_rd = odd ? hist1 : hist0;
     float *hist_wr = odd ? hist0 : hist1;
+    {   // everything the two dependent dot-product chains will touch goes to shared memory first, all loads in flight
+        const float inv = inv_ptr[0];
+        const float4 *xv = reinterpret_cast<const float4 *>(x), *nw = reinterpret_cast<const float4 *>(norm_w);
+        const float4 *ra = reinterpret_cast<const float4 *>(alpha_w + size_t(h) * hidden), *rb = reinterpret_cast<const float4 *>(beta_w + size_t(h) * hidden);
+        for (int i = tid; i < n4; i += 512) {
+            const float4 a4 = xv[i], w4 = nw[i];
+            dyn[i] = make_float4(__fmul_rn(__fmul_rn(a4.x, inv), w4.x), __fmul_rn(__fmul_rn(a4.y, inv), w4.y),
+                                 __fmul_rn(__fmul_rn(a4.z, inv), w4.z), __fmul_rn(__fmul_rn(a4.w, inv), w4.w));
+            dyn[n4 + i] = ra[i];
+            dyn[2 * n4 + i] = rb[i];
+        }
+    }
     auto conv1 = [&](int c, bool store) -> float {
         const float *sr = hist_rd + 3 * size_t(c);
         const float *wc = conv_w + 4 * size_t(c);
@@ -244,45 +265,38 @@ __global__ void __launch_bounds__(256) k_gdn_core(int heads, int qk_heads, int h
         if (store) { float *sw = hist_wr + 3 * size_t(c); sw[0] = s1; sw[1] = s2; sw[2] = xn; }
         return silu_f(acc);
     };
-    const bool own_qk = h < qk_heads && chunk == 0;
+    const bool own_qk = h < qk_heads;              // the first of the v-heads sharing q/k head hq writes its taps
     if (tid < 128) sq[tid] = conv1(hq * 128 + tid, own_qk);
-    else sk[tid - 128] = conv1(qk_heads * 128 + hq * 128 + (tid - 128), own_qk);
-    if (tid < 32) sv[tid] = conv1(2 * qk_heads * 128 + h * 128 + chunk * 32 + tid, true);
+    else if (tid < 256) sk[tid - 128] = conv1(qk_heads * 128 + hq * 128 + (tid - 128), own_qk);
+    else if (tid < 384) sv[tid - 256] = conv1(2 * qk_heads * 128 + h * 128 + (tid - 256), true);
     __syncthreads();
-    if (warp >= 6) {
-        // row h of ssm_alpha (warp 6) or ssm_beta (warp 7) times the normed residual (x * inv) * norm_w
-        const float inv = inv_ptr[0];
-        const float4 *wr = rows + (warp == 6 ? 0 : hidden / 4);
-        const float4 *xv = reinterpret_cast<const float4 *>(x), *nw = reinterpret_cast<const float4 *>(norm_w);
+    if (warp >= 14) {
+        // row h of ssm_alpha (warp 14) or ssm_beta (warp 15) times the normed residual: lane l takes float4 groups
+        // l, l+32, ... with one fmaf per element, then a 32-lane xor tree (k_gemv_f32_small)
+        const float4 *wr = dyn + (warp == 14 ? n4 : 2 * n4);
         float acc = 0.0f;
-        for (int i0 = lane; i0 < hidden / 4; i0 += 128) {
-            float4 w4[4], x4[4], n4[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int i = i0 + 32 * u;
-                if (i < hidden / 4) { w4[u] = wr[i]; x4[u] = xv[i]; n4[u] = nw[i]; }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (i0 + 32 * u < hidden / 4) {
-                    acc = fmaf(w4[u].x, __fmul_rn(__fmul_rn(x4[u].x, inv), n4[u].x), acc);
-                    acc = fmaf(w4[u].y, __fmul_rn(__fmul_rn(x4[u].y, inv), n4[u].y), acc);
-                    acc = fmaf(w4[u].z, __fmul_rn(__fmul_rn(x4[u].z, inv), n4[u].z), acc);
-                    acc = fmaf(w4[u].w, __fmul_rn(__fmul_rn(x4[u].w, inv), n4[u].w), acc);
-                }
-            }
+        for (int i = lane; i < n4; i += 32) {
+            const float4 w4 = wr[i], a4 = dyn[i];
+            acc = fmaf(w4.x, a4.x, acc); acc = fmaf(w4.y, a4.y, acc); acc = fmaf(w4.z, a4.z, acc); acc = fmaf(w4.w, a4.w, acc);
         }
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, s));
         if (lane == 0) {
-            if (warp == 6) {
+            if (warp == 14) {
                 const float al = __fadd_rn(acc, dt_bias[h]);
                 const float sp = al > 20.0f ? al : log_f(__fadd_rn(1.0f, exp_f(al)));
                 sgb[0] = __fmul_rn(sp, ssm_a[h]);
             } else sgb[1] = sigmoid_f(acc);
         }
     }
-    __syncthreads();
+    // state rows of this warp (8 of the head's 128), loaded while the two chains run
+    float S[8][4];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        const float *Sr = state + (size_t(h) * 128 + warp * 8 + r) * 128;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[r][e] = Sr[lane + 32 * e];
+    }
     float qq[4], kk[4];
     {
         const float a0 = sq[lane], a1 = sq[lane + 32], a2 = sq[lane + 64], a3 = sq[lane + 96];
@@ -292,27 +306,37 @@ __global__ void __launch_bounds__(256) k_gdn_core(int heads, int qk_heads, int h
         const float ik = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(warp_tree128(__fmul_rn(b0, b0), __fmul_rn(b1, b1), __fmul_rn(b2, b2), __fmul_rn(b3, b3)), 1e-12f)));
         kk[0] = __fmul_rn(b0, ik); kk[1] = __fmul_rn(b1, ik); kk[2] = __fmul_rn(b2, ik); kk[3] = __fmul_rn(b3, ik);
     }
+    __syncthreads();
     const float eg = exp_f(sgb[0]), bt = sgb[1];
-    float S[4][4];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-        const float *Sr = state + (size_t(h) * 128 + chunk * 32 + warp * 4 + r) * 128;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) S[r][e] = Sr[lane + 32 * e];
-    }
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-        const int jl = warp * 4 + r;
-        float *Sr = state + (size_t(h) * 128 + chunk * 32 + jl) * 128;
+    for (int r = 0; r < 8; ++r) {
+        const int j = warp * 8 + r;
+        float *Sr = state + (size_t(h) * 128 + j) * 128;
         float s[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[e] = __fmul_rn(S[r][e], eg);
         const float pred = warp_tree128(__fmul_rn(s[0], kk[0]), __fmul_rn(s[1], kk[1]), __fmul_rn(s[2], kk[2]), __fmul_rn(s[3], kk[3]));
-        const float u = __fmul_rn(bt, __fsub_rn(sv[jl], pred));
+        const float u = __fmul_rn(bt, __fsub_rn(sv[j], pred));
 #pragma unroll
         for (int e = 0; e < 4; ++e) { s[e] = fmaf(kk[e], u, s[e]); Sr[lane + 32 * e] = s[e]; }
         const float ov = warp_tree128(__fmul_rn(s[0], qq[0]), __fmul_rn(s[1], qq[1]), __fmul_rn(s[2], qq[2]), __fmul_rn(s[3], qq[3]));
-        if (lane == 0) o[h * 128 + chunk * 32 + jl] = __fmul_rn(ov, scale);
+        if (lane == 0) so[j] = __fmul_rn(ov, scale);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // per-head RMS (no weight), * ssm_norm, swiglu(z, .), destination head of the v-grouped permutation
+        float e[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) e[i] = so[lane + 32 * i];
+        const float ss = warp_tree128(__fmul_rn(e[0], e[0]), __fmul_rn(e[1], e[1]), __fmul_rn(e[2], e[2]), __fmul_rn(e[3], e[3]));
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.0f), eps)));
+        const int sub = heads / qk_heads, hd = sub * (h % qk_heads) + h / qk_heads;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int d = lane + 32 * i;
+            const float nrm = __fmul_rn(__fmul_rn(e[i], inv), ssm_norm[d]);
+            y[hd * 128 + d] = __fmul_rn(silu_f(z[h * 128 + d]), nrm);
+        }
     }
 }
 
@@ -320,6 +344,7 @@ __global__ void __launch_bounds__(256) k_gdn_core(int heads, int qk_heads, int h
 // (bonsai_forward.h:559-567, permute_vg.comp:32-42). One warp per SOURCE head.
 __global__ void k_gdn_out(int heads, int qk_heads, const float *__restrict__ o, const float *__restrict__ z,
                           const float *__restrict__ ssm_norm, float eps, float *__restrict__ y) {
+    bnk::pdl_sync();
     const int hs = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), l = threadIdx.x & 31;
     if (hs >= heads) return;
     const float *orow = o + hs * 128;
@@ -361,6 +386,7 @@ __global__ void __launch_bounds__(256) k_attn_prep(bnk::AttnDims a, const float 
                                                    const float *__restrict__ qn_w, const float *__restrict__ kn_w,
                                                    const int *__restrict__ pos_ptr, bnk::KvLayer kv,
                                                    float *__restrict__ q16f, float *__restrict__ gate) {
+    bnk::pdl_sync();
     __shared__ float part[256];
     __shared__ float sx[256];
     const int d = threadIdx.x, hd = a.head_dim, w = blockIdx.x;
@@ -406,6 +432,7 @@ template <int GQA>
 __global__ void __launch_bounds__(256) k_attn_scores(bnk::AttnDims a, const float *__restrict__ q16f,
                                                      const int *__restrict__ pos_ptr, bnk::KvLayer kv,
                                                      float *__restrict__ score) {
+    bnk::pdl_sync();
     const int kvh = blockIdx.y, lane = threadIdx.x & 31, hd = a.head_dim;
     const int nfill = pos_ptr[0] + 1;
     const int j = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -444,6 +471,7 @@ __global__ void __launch_bounds__(256) k_attn_scores(bnk::AttnDims a, const floa
 __global__ void __launch_bounds__(1024) k_attn_softmax(bnk::AttnDims a, const int *__restrict__ pos_ptr,
                                                        const float *__restrict__ score, float scale,
                                                        float *__restrict__ p16f) {
+    bnk::pdl_sync();
     __shared__ float red[1024];
     const int h = blockIdx.x, t = threadIdx.x, nfill = pos_ptr[0] + 1;
     const float *sr = score + size_t(h) * a.cap;
@@ -472,6 +500,7 @@ template <int GQA>
 __global__ void __launch_bounds__(256) k_attn_pv(bnk::AttnDims a, const float *__restrict__ p16f,
                                                  const int *__restrict__ pos_ptr, bnk::KvLayer kv, int splits,
                                                  float *__restrict__ part) {
+    bnk::pdl_sync();
     const int kvh = blockIdx.x, sp = blockIdx.y, d = threadIdx.x, hd = a.head_dim;
     const int nfill = pos_ptr[0] + 1;
     const int per = (nfill + splits - 1) / splits;
@@ -494,6 +523,7 @@ __global__ void __launch_bounds__(256) k_attn_pv(bnk::AttnDims a, const float *_
 // combine the splits ascending, then the sigmoid gate
 __global__ void k_attn_combine(bnk::AttnDims a, const float *__restrict__ part, int splits, const int *pos_ptr,
                                const float *__restrict__ gate, float *__restrict__ pregate, float *__restrict__ gated) {
+    bnk::pdl_sync();
     const int i = blockIdx.x * blockDim.x + threadIdx.x, n = a.n_head * a.head_dim;
     if (i >= n) return;
     const int nfill = pos_ptr[0] + 1;
@@ -507,6 +537,7 @@ __global__ void k_attn_combine(bnk::AttnDims a, const float *__restrict__ part, 
 // ---- greedy pick: first maximum (Sampler::pick, runtime_vk/bonsai_forward.h:2568-2570) ----------
 __global__ void __launch_bounds__(1024) k_argmax_part(const float *__restrict__ x, int n, float *__restrict__ bv,
                                                       int *__restrict__ bi) {
+    bnk::pdl_sync();
     __shared__ float sv[1024];
     __shared__ int si[1024];
     const int t = threadIdx.x;
@@ -526,6 +557,7 @@ __global__ void __launch_bounds__(1024) k_argmax_part(const float *__restrict__ 
     if (t == 0) { bv[blockIdx.x] = sv[0]; bi[blockIdx.x] = si[0]; }
 }
 __global__ void k_argmax_final(const float *__restrict__ bv, const int *__restrict__ bi, int nparts, int *out) {
+    bnk::pdl_sync();
     if (threadIdx.x != 0) return;
     float best = bv[0]; int idx = bi[0];
     for (int p = 1; p < nparts; ++p) if (bv[p] > best || (bv[p] == best && bi[p] < idx)) { best = bv[p]; idx = bi[p]; }
@@ -537,68 +569,73 @@ __global__ void k_argmax_final(const float *__restrict__ bv, const int *__restri
 
 namespace bnk {
 
+bool g_pdl = true;
+
 void rotate_quant(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y, uint32_t *pack) {
     const float inv = 1.0f / sqrtf(float(block));
     uint32_t *q81 = pack, *table = pack ? pack + size_t(n / 128) * Q81_DWORDS : nullptr;
-    k_rotate_quant<<<n / block, 512, size_t(block) * 4 + 512, st>>>(x, signs, block, inv, y, q81, table); BN_COUNT(1);
+    launch(k_rotate_quant, dim3(n / block), dim3(512), size_t(block) * 4 + 512, st, x, signs, block, inv, y, q81, table); 
 }
 void rotate_inv(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y) {
-    k_rotate_inv<<<n / block, 512, size_t(block) * 4, st>>>(x, signs, block, 1.0f / sqrtf(float(block)), y); BN_COUNT(1);
+    launch(k_rotate_inv, dim3(n / block), dim3(512), size_t(block) * 4, st, x, signs, block, 1.0f / sqrtf(float(block)), y); 
 }
 void embed_row(cudaStream_t st, const uint32_t *W, int K, const int *tok_ptr, float *out) {
-    k_embed_row<<<(K + 255) / 256, 256, 0, st>>>(W, K, tok_ptr, out); BN_COUNT(1);
+    launch(k_embed_row, dim3((K + 255) / 256), dim3(256), 0, st, W, K, tok_ptr, out); 
 }
 void rms_norm(cudaStream_t st, const float *x, const float *w, int rows, int cols, float eps, float *y) {
-    k_rms_norm<<<rows, 256, 0, st>>>(x, w, cols, eps, y); BN_COUNT(1);
+    launch(k_rms_norm, dim3(rows), dim3(256), 0, st, x, w, cols, eps, y); 
 }
-void add_inplace(cudaStream_t st, float *res, const float *d, int n) { k_add_inplace<<<(n + 255) / 256, 256, 0, st>>>(res, d, n); BN_COUNT(1); }
-void swiglu(cudaStream_t st, const float *a, const float *b, int n, float *y) { k_swiglu<<<(n + 255) / 256, 256, 0, st>>>(a, b, n, y); BN_COUNT(1); }
+void add_inplace(cudaStream_t st, float *res, const float *d, int n) { launch(k_add_inplace, dim3((n + 255) / 256), dim3(256), 0, st, res, d, n);  }
+void swiglu(cudaStream_t st, const float *a, const float *b, int n, float *y) { launch(k_swiglu, dim3((n + 255) / 256), dim3(256), 0, st, a, b, n, y);  }
 void gemv_f32_small(cudaStream_t st, const float *W, int M, int K, const float *x, float *out) {
-    k_gemv_f32_small<<<(M + 7) / 8, 256, 0, st>>>(W, M, K, x, out); BN_COUNT(1);
+    launch(k_gemv_f32_small, dim3((M + 7) / 8), dim3(256), 0, st, W, M, K, x, out); 
 }
 void gdn_gates(cudaStream_t st, const float *alpha, const float *beta_raw, const float *dt_bias, const float *ssm_a, int n,
                float *gate, float *beta) {
-    k_gdn_gates<<<1, 64, 0, st>>>(alpha, beta_raw, dt_bias, ssm_a, n, gate, beta); BN_COUNT(1);
+    launch(k_gdn_gates, dim3(1), dim3(64), 0, st, alpha, beta_raw, dt_bias, ssm_a, n, gate, beta); 
 }
 void conv_silu(cudaStream_t st, const float *x, const float *w, float *hist, int channels, float *y) {
-    k_conv_silu<<<(channels + 255) / 256, 256, 0, st>>>(x, w, hist, channels, y); BN_COUNT(1);
+    launch(k_conv_silu, dim3((channels + 255) / 256), dim3(256), 0, st, x, w, hist, channels, y); 
 }
 void l2_norm_rows(cudaStream_t st, const float *x, int rows, float eps, float *y) {
-    k_l2_norm_rows<<<(rows + 7) / 8, 256, 0, st>>>(x, rows, eps, y); BN_COUNT(1);
+    launch(k_l2_norm_rows, dim3((rows + 7) / 8), dim3(256), 0, st, x, rows, eps, y); 
 }
 void gdn_delta(cudaStream_t st, GdnDims d, const float *q, const float *k, const float *v, const float *gate,
                const float *beta, float *state, float *o) {
-    k_gdn_delta<<<dim3(d.dim / 8, d.heads), 256, 0, st>>>(d.heads, d.qk_heads, q, k, v, gate, beta, state, o,
-                                                          1.0f / sqrtf(float(d.dim))); BN_COUNT(1);
+    launch(k_gdn_delta, dim3(dim3(d.dim / 8, d.heads)), dim3(256), 0, st, d.heads, d.qk_heads, q, k, v, gate, beta, state, o,
+                                                          1.0f / sqrtf(float(d.dim))); 
 }
 void gdn_core_fused(cudaStream_t st, GdnDims d, int hidden, const float *qkv, const float *conv_w, float *hist0,
                     float *hist1, const int *pos_ptr, const float *x, const float *inv_ptr, const float *norm_w, const float *alpha_w,
-                    const float *beta_w, const float *dt_bias, const float *ssm_a, float *state, float *o) {
-    k_gdn_core<<<dim3(d.dim / 32, d.heads), 256, size_t(hidden) * 8, st>>>(d.heads, d.qk_heads, hidden, qkv, conv_w, hist0, hist1, pos_ptr, x, inv_ptr,
-                                                          norm_w, alpha_w, beta_w, dt_bias, ssm_a, state, o, 1.0f / sqrtf(float(d.dim)));
-    BN_COUNT(1);
+                    const float *beta_w, const float *dt_bias, const float *ssm_a, float *state, const float *z,
+                    const float *ssm_norm, float eps, float *y) {
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(k_gdn_core, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 16384 * 4); attr = true; }
+    launch(k_gdn_core, dim3(d.heads), dim3(512), size_t(hidden) * 12, st, d.heads, d.qk_heads, hidden, qkv, conv_w, hist0, hist1, pos_ptr, x, inv_ptr,
+                                                         norm_w, alpha_w, beta_w, dt_bias, ssm_a, state, z, ssm_norm, eps, y,
+                                                         1.0f / sqrtf(float(d.dim))); 
 }
 void gdn_out(cudaStream_t st, GdnDims d, const float *o, const float *z, const float *ssm_norm, float eps, float *y) {
-    k_gdn_out<<<(d.heads + 7) / 8, 256, 0, st>>>(d.heads, d.qk_heads, o, z, ssm_norm, eps, y); BN_COUNT(1);
+    launch(k_gdn_out, dim3((d.heads + 7) / 8), dim3(256), 0, st, d.heads, d.qk_heads, o, z, ssm_norm, eps, y); 
 }
 void attn_prep(cudaStream_t st, AttnDims a, const float *qg, const float *kin, const float *vin, const float *qn_w,
                const float *kn_w, const int *pos_ptr, KvLayer kv, float *q16f, float *gate) {
-    k_attn_prep<<<a.n_head + a.n_kv, 256, 0, st>>>(a, qg, kin, vin, qn_w, kn_w, pos_ptr, kv, q16f, gate); BN_COUNT(1);
+    launch(k_attn_prep, dim3(a.n_head + a.n_kv), dim3(256), 0, st, a, qg, kin, vin, qn_w, kn_w, pos_ptr, kv, q16f, gate); 
 }
 void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *gate, const int *pos_ptr, KvLayer kv,
                  float *score, float *p16f, float *pv_part, int splits, float *pregate, float *gated, bool combine) {
     // grids are sized for the cache capacity; warps beyond the filled prefix return at once
-    k_attn_scores<4><<<dim3((a.cap + 7) / 8, a.n_kv), 256, 0, st>>>(a, q16f, pos_ptr, kv, score); BN_COUNT(1);
-    k_attn_softmax<<<a.n_head, 1024, 0, st>>>(a, pos_ptr, score, 1.0f / sqrtf(float(a.head_dim)), p16f); BN_COUNT(1);
-    k_attn_pv<4><<<dim3(a.n_kv, splits), 256, 0, st>>>(a, p16f, pos_ptr, kv, splits, pv_part); BN_COUNT(1);
+    launch(k_attn_scores<4>, dim3(dim3((a.cap + 7) / 8, a.n_kv)), dim3(256), 0, st, a, q16f, pos_ptr, kv, score); 
+    launch(k_attn_softmax, dim3(a.n_head), dim3(1024), 0, st, a, pos_ptr, score, 1.0f / sqrtf(float(a.head_dim)), p16f); 
+    launch(k_attn_pv<4>, dim3(dim3(a.n_kv, splits)), dim3(256), 0, st, a, p16f, pos_ptr, kv, splits, pv_part); 
     if (!combine) return;
     const int n = a.n_head * a.head_dim;
-    k_attn_combine<<<(n + 255) / 256, 256, 0, st>>>(a, pv_part, splits, pos_ptr, gate, pregate, gated); BN_COUNT(1);
+    launch(k_attn_combine, dim3((n + 255) / 256), dim3(256), 0, st, a, pv_part, splits, pos_ptr, gate, pregate, gated); 
 }
 void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx) {
     const int parts = 64;
-    k_argmax_part<<<parts, 1024, 0, st>>>(x, n, scratch_val, scratch_idx); BN_COUNT(1);
-    k_argmax_final<<<1, 32, 0, st>>>(scratch_val, scratch_idx, parts, out_idx); BN_COUNT(1);
+    launch(k_argmax_part, dim3(parts), dim3(1024), 0, st, x, n, scratch_val, scratch_idx); 
+    launch(k_argmax_final, dim3(1), dim3(32), 0, st, scratch_val, scratch_idx, parts, out_idx); 
 }
 
 }  // namespace bnk

@@ -5,6 +5,29 @@
 // All helpers enqueue on `st` and return cudaGetLastError() state through bn_launch_check by the caller.
 namespace bnk {
 
+// Programmatic dependent launch for every kernel of the token schedule: a kernel may be scheduled while its
+// predecessor drains; it blocks in pdl_sync() (first statement of every kernel) until the predecessor's
+// memory is visible. Hides the launch latency between the ~230 small kernels of a token.
+extern bool g_pdl;
+template <class... KArgs, class... Args>
+inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = g_pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    BN_COUNT(1);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+#endif
+
 constexpr int Q81_DWORDS = 36;
 constexpr int BF_WORDS = 512;
 inline size_t act_pack_bytes(int K) { return size_t(K / 128) * (Q81_DWORDS + BF_WORDS) * 4; }
@@ -34,11 +57,13 @@ void conv_silu(cudaStream_t st, const float *x, const float *w, float *hist, int
 void l2_norm_rows(cudaStream_t st, const float *x, int rows, float eps, float *y);   // 128-wide rows
 void gdn_delta(cudaStream_t st, GdnDims d, const float *q, const float *k, const float *v, const float *gate,
                const float *beta, float *state, float *o);
-// fused layer core: alpha/beta projections of the normed residual + gates, conv + silu, L2 norms, delta rule.
-// hist0 / hist1: the two conv-history buffers; position parity picks which is read and which is written.
+// fused layer mixer: alpha/beta projections of the normed residual + gates, conv + silu, L2 norms, delta rule,
+// per-head RMS * ssm_norm, swiglu(z, .), v-grouped permutation -> y. hist0 / hist1: the two conv-history
+// buffers; position parity picks which is read and which is written. hidden <= 16384.
 void gdn_core_fused(cudaStream_t st, GdnDims d, int hidden, const float *qkv, const float *conv_w, float *hist0,
                     float *hist1, const int *pos_ptr, const float *x, const float *inv_ptr, const float *norm_w, const float *alpha_w,
-                    const float *beta_w, const float *dt_bias, const float *ssm_a, float *state, float *o);
+                    const float *beta_w, const float *dt_bias, const float *ssm_a, float *state, const float *z,
+                    const float *ssm_norm, float eps, float *y);
 // per-head RMS (no weight) * ssm_norm, swiglu(z, .), v-grouped permutation -> y[heads*dim]
 void gdn_out(cudaStream_t st, GdnDims d, const float *o, const float *z, const float *ssm_norm, float eps, float *y);
 

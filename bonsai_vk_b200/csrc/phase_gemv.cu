@@ -238,6 +238,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_phase_gemv(const PhaseArgs a) {
     const bool copy_warp = warp == NWARP;
     if (copy_warp) for (int it = 0; it < min(items, STAGES); ++it) issue(it);
 
+    // constants of the prologue (norm weights, sign vector) do not depend on the previous grid either
+    const bool pre = (a.pro == PRO_NORM || a.pro == PRO_PLAIN) && a.hat_block >= 256 && tid < a.hat_block / 8;
+    int pre_sg[8];
+    float pre_w[8];
+    if (pre) {
+        const int4 s0 = *reinterpret_cast<const int4 *>(a.signs + tid * 8), s1 = *reinterpret_cast<const int4 *>(a.signs + tid * 8 + 4);
+        pre_sg[0] = s0.x; pre_sg[1] = s0.y; pre_sg[2] = s0.z; pre_sg[3] = s0.w; pre_sg[4] = s1.x; pre_sg[5] = s1.y; pre_sg[6] = s1.z; pre_sg[7] = s1.w;
+        if (a.pro == PRO_NORM) {
+            const float4 n0 = *reinterpret_cast<const float4 *>(a.w + tid * 8), n1 = *reinterpret_cast<const float4 *>(a.w + tid * 8 + 4);
+            pre_w[0] = n0.x; pre_w[1] = n0.y; pre_w[2] = n0.z; pre_w[3] = n0.w; pre_w[4] = n1.x; pre_w[5] = n1.y; pre_w[6] = n1.z; pre_w[7] = n1.w;
+        }
+    }
     STAMP(1);
     // everything above touched only constant weights; from here on we read the previous grid's output
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -259,7 +271,43 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_phase_gemv(const PhaseArgs a) {
         for (int i = tid; i < nb * 4; i += NT) dsw[i] = a.pack[size_t(i >> 2) * Q81_DWORDS + (i & 3)];
     } else {
         float inv = 1.0f;
-        if (a.pro == PRO_NORM) {
+        float xe[8];
+        const bool merged = a.pro == PRO_NORM && K == 4096 && a.hat_block == 4096;   // one pass over x0: norm and input
+        if (merged) {
+            const float4 x0 = *reinterpret_cast<const float4 *>(a.x0 + tid * 8), x1 = *reinterpret_cast<const float4 *>(a.x0 + tid * 8 + 4);
+            xe[0] = x0.x; xe[1] = x0.y; xe[2] = x0.z; xe[3] = x0.w; xe[4] = x1.x; xe[5] = x1.y; xe[6] = x1.z; xe[7] = x1.w;
+            // lane slice l = elements 16l .. 16l+15 summed ascending: the even thread sums its 8 squares, hands the
+            // running sum to its odd neighbour, which continues the same chain
+            float sq = 0.0f;
+            if (!(tid & 1)) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sq = __fadd_rn(sq, __fmul_rn(xe[i], xe[i]));
+            }
+            const float up = __shfl_up_sync(0xFFFFFFFFu, sq, 1);
+            if (tid & 1) {
+                sq = up;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sq = __fadd_rn(sq, __fmul_rn(xe[i], xe[i]));
+                red[tid >> 1] = sq;
+            }
+            csync();
+            if (warp == 0) {
+                float v[8];
+#pragma unroll
+                for (int w = 0; w < 8; ++w) v[w] = red[32 * w + lane];
+                float t = __fadd_rn(__fadd_rn(__fadd_rn(v[0], v[4]), __fadd_rn(v[2], v[6])),
+                                    __fadd_rn(__fadd_rn(v[1], v[5]), __fadd_rn(v[3], v[7])));
+#pragma unroll
+                for (int s2 = 16; s2 > 0; s2 >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xFFFFFFFFu, t, s2));
+                if (lane == 0) {
+                    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, float(K)), a.eps)));
+                    hinv[0] = r;
+                    if (a.inv_out && blockIdx.x == 0) a.inv_out[0] = r;
+                }
+            }
+            csync();
+            inv = hinv[0];
+        } else if (a.pro == PRO_NORM) {
             // rms_norm.comp order: 256 lane slices of `per` consecutive elements summed ascending, then the
             // fixed tree p[i] += p[i+s], s = 128..1 (steps 128, 64, 32 across warps, 16..1 inside warp 0)
             const int per = (K + 255) / 256;
@@ -334,9 +382,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_phase_gemv(const PhaseArgs a) {
                 float v[8];
                 if (on) {
                     const int tb = base + tid * 8;
-                    const int4 sg0 = *reinterpret_cast<const int4 *>(a.signs + tb), sg1 = *reinterpret_cast<const int4 *>(a.signs + tb + 4);
-                    const int sg[8] = {sg0.x, sg0.y, sg0.z, sg0.w, sg1.x, sg1.y, sg1.z, sg1.w};
-                    if (a.pro == PRO_PLAIN || a.pro == PRO_NORM) {
+                    int sg[8];
+                    if (pre && hb == 0) {
+#pragma unroll
+                        for (int r = 0; r < 8; ++r) sg[r] = pre_sg[r];
+                    } else {
+                        const int4 sg0 = *reinterpret_cast<const int4 *>(a.signs + tb), sg1 = *reinterpret_cast<const int4 *>(a.signs + tb + 4);
+                        sg[0] = sg0.x; sg[1] = sg0.y; sg[2] = sg0.z; sg[3] = sg0.w; sg[4] = sg1.x; sg[5] = sg1.y; sg[6] = sg1.z; sg[7] = sg1.w;
+                    }
+                    if (merged) {
+#pragma unroll
+                        for (int r = 0; r < 8; ++r) v[r] = __fmul_rn(__fmul_rn(__fmul_rn(xe[r], inv), pre_w[r]), float(sg[r]));
+                    } else if (a.pro == PRO_PLAIN || a.pro == PRO_NORM) {
                         const float4 x0 = *reinterpret_cast<const float4 *>(a.x0 + tb), x1 = *reinterpret_cast<const float4 *>(a.x0 + tb + 4);
                         const float xe[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
                         if (a.pro == PRO_NORM) {
