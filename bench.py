@@ -138,16 +138,30 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     S, CTX = 64, 8192
     b0, b1 = split_blocks(32, world)[rank]
     ctx = Context(local)
-    ctx.use_stream(torch.cuda.current_stream().cuda_stream)
+    # one explicit (non-default) stream for our kernels and, through torch, for the NCCL dependencies: the legacy
+    # default stream cannot be captured into the per-stream stage graphs
+    work_stream = torch.cuda.Stream(device=local)
+    torch.cuda.set_stream(work_stream)
+    ctx.use_stream(work_stream.cuda_stream)
     hp = synth.HParams(cap=CTX, n_streams=S, block_begin=b0, block_end=b1)
     tensors, signs = build_full_model(hp)
     m = Model(ctx, hp, tensors, signs)
     del tensors
     total = 2 * (K + Wm) + 8
     pos0 = [CTX - total - 1] * S
+    dev = torch.device("cuda", local)
+    # Capture and instantiate every stream's stage graph now, before any NCCL kernel is in flight: a graph
+    # instantiation may synchronise the device, and a device that is running a send/recv kernel which waits
+    # for its peer must not be asked to do that.
+    scratch_in = ctx.wrap(torch.zeros(hp.hidden, dtype=torch.float32, device=dev).data_ptr(), hp.hidden * 4)
+    scratch_out = ctx.alloc(hp.hidden * 4)
+    for s in range(S):
+        m.stage(s, 1 if rank == 0 else 0, pos0[s], None if rank == 0 else scratch_in, scratch_out)
+    torch.cuda.synchronize()
+    m.reset()
     for s in range(S):
         m.fill_kv(s, pos0[s])
-    dev = torch.device("cuda", local)
+    torch.cuda.synchronize()
     wraps = {}
 
     def wrap(t):

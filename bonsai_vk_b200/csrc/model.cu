@@ -23,9 +23,10 @@ struct bn_model {
     char *arena = nullptr;
     size_t arena_bytes = 0;
     float *RES, *AN, *X1, *X2, *QKV, *Z, *CONV, *L2, *O, *KBUF, *VBUF, *Q16F, *GATEB, *GOUT, *FG, *FU, *FS, *D, *LOGITS;
-    float *ALPHA, *BETA, *G, *BT, *SCORE, *P16F, *PVPART, *AMV;
+    float *ALPHA, *BETA, *G, *BT, *SCORE, *P16F, *ESUM, *PVPART, *AMV;
     int *AMI, *TOK, *POS, *NEXT, *HIST, *STEP;
     cudaGraphExec_t token_graph = nullptr;   // one whole token + advance, captured on first use
+    std::vector<cudaGraphExec_t> stage_graphs;   // pipeline stage: one captured schedule per stream (its state pointers are baked in)
     uint32_t *PACK_H, *PACK_F;
     float *GEMV_SCRATCH;
     // persistent state
@@ -161,7 +162,7 @@ void attn_plain(bn_model *m, const bn_model::Layer &L) {
     bnk::gemv_q81(st, m->ctx->sm_count, L.k_w, KD, h.hidden, m->PACK_H, m->KBUF, m->GEMV_SCRATCH, nullptr);
     bnk::gemv_q81(st, m->ctx->sm_count, L.v_w, KD, h.hidden, m->PACK_H, m->VBUF, m->GEMV_SCRATCH, nullptr);
     bnk::attn_prep(st, a, m->QKV, m->KBUF, m->VBUF, L.q_norm, L.k_norm, m->POS, kv, m->Q16F, m->GATEB);
-    bnk::attn_decode(st, a, m->Q16F, m->GATEB, m->POS, kv, m->SCORE, m->P16F, m->PVPART, m->pv_splits, nullptr, m->GOUT, true);
+    bnk::attn_decode(st, a, m->Q16F, m->GATEB, m->POS, kv, m->SCORE, m->P16F, m->ESUM, m->PVPART, m->pv_splits, nullptr, m->GOUT, true);
     rot_project(m, m->GOUT, m->signs, QD, m->PACK_H, L.o_w, h.hidden, m->D);
     bnk::add_inplace(st, m->RES, m->D, h.hidden);
 }
@@ -237,7 +238,7 @@ void attn_fused(bn_model *m, const bn_model::Layer &L) {
         a.W = reinterpret_cast<const uint8_t *>(L.v_w); a.out = m->VBUF; launch(m, a);
     }
     bnk::attn_prep(st, ad, m->QKV, m->KBUF, m->VBUF, L.q_norm, L.k_norm, m->POS, kv, m->Q16F, m->GATEB);
-    bnk::attn_decode(st, ad, m->Q16F, m->GATEB, m->POS, kv, m->SCORE, m->P16F, m->PVPART, m->pv_splits, nullptr, m->GOUT, true);
+    bnk::attn_decode(st, ad, m->Q16F, m->GATEB, m->POS, kv, m->SCORE, m->P16F, m->ESUM, m->PVPART, m->pv_splits, nullptr, m->GOUT, true);
     bnk::PhaseArgs o = phase_base(m, L.o_w, h.hidden, QD, m->signs);
     o.pro = bnk::PRO_PLAIN; o.x0 = m->GOUT;
     o.resid_in = m->RES; o.resid_out = m->RES;
@@ -388,7 +389,7 @@ int bn_model_finalize(bn_model *m) {
     if (rc != BN_OK) return rc;
 
     // activation arena
-    m->pv_splits = h.cap >= 4096 ? 64 : (h.cap >= 512 ? 8 : 1);
+    m->pv_splits = h.cap >= 16384 ? 256 : (h.cap >= 4096 ? 64 : (h.cap >= 512 ? 8 : 1));
     const int maxM = std::max(std::max(h.vocab, h.ffn), std::max(C, 2 * QD));
     const int maxG = (std::max(h.ffn, h.hidden) / 128 + 3) / 4;
     size_t off = 0;
@@ -401,7 +402,7 @@ int bn_model_finalize(bn_model *m) {
     F(m->Q16F, QD); F(m->GATEB, QD); F(m->GOUT, QD);
     F(m->FG, 2 * size_t(h.ffn)); F(m->FS, h.ffn); F(m->D, h.hidden); F(m->LOGITS, h.vocab);
     F(m->ALPHA, 64); F(m->BETA, 64); F(m->G, 64); F(m->BT, 64);
-    F(m->SCORE, size_t(h.n_head) * h.cap); F(m->P16F, size_t(h.n_head) * h.cap);
+    F(m->SCORE, size_t(h.n_head) * h.cap); F(m->P16F, size_t(h.n_head) * h.cap); F(m->ESUM, size_t(h.n_head) * 1024);
     F(m->PVPART, size_t(m->pv_splits) * QD); F(m->AMV, 64);
     F(m->GEMV_SCRATCH, size_t(maxG) * std::max(maxM, 1));
     slots.push_back({reinterpret_cast<void **>(&m->AMI), carve(64 * 4)});
@@ -471,6 +472,7 @@ void bn_model_destroy(bn_model *m) {
     if (m->conv_hist) cudaFree(m->conv_hist);
     if (m->kv) cudaFree(m->kv);
     if (m->token_graph) cudaGraphExecDestroy(m->token_graph);
+    for (cudaGraphExec_t g : m->stage_graphs) if (g) cudaGraphExecDestroy(g);
     delete m;
 }
 
@@ -564,8 +566,29 @@ int bn_model_stage(bn_model *m, int stream, int tok, int pos, const bn_buf *in, 
     k_set_tok_pos<<<1, 32, 0, st>>>(m->TOK, m->POS, tok, pos, (first && tok < 0) ? bn_ptr<int>(in, in_off) : nullptr);
     BN_COUNT(1);
     if (!first) BN_CUDA(cudaMemcpyAsync(m->RES, bn_ptr<char>(in, in_off), size_t(h.hidden) * 4, cudaMemcpyDeviceToDevice, st));
-    enqueue_token(m, -1, true);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = cudaSuccess;
+    if (getenv("BONSAI_NO_STAGE_GRAPH")) {
+        enqueue_token(m, -1, true);
+        e = cudaGetLastError();
+    } else {
+        // the ~100 launches of a stage are replayed as one graph: the host only feeds copies and NCCL calls
+        if (m->stage_graphs.empty()) m->stage_graphs.assign(S, nullptr);
+        if (!m->stage_graphs[stream]) {
+            cudaGraph_t g = nullptr;
+            const unsigned long long before = g_bn_launches;
+            BN_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+            enqueue_token(m, -1, true);
+            e = cudaStreamEndCapture(st, &g);
+            if (e != cudaSuccess) return bn_cuda_fail(e, "cudaStreamEndCapture(stage)");
+            m->graph_launches = int(g_bn_launches - before);
+            g_bn_launches = before;
+            e = cudaGraphInstantiate(&m->stage_graphs[stream], g, 0);
+            cudaGraphDestroy(g);
+            if (e != cudaSuccess) return bn_cuda_fail(e, "cudaGraphInstantiate(stage)");
+        }
+        e = cudaGraphLaunch(m->stage_graphs[stream], st);
+        BN_COUNT(m->graph_launches);
+    }
     if (e == cudaSuccess) e = m->launch_err;
     m->launch_err = cudaSuccess;
     if (e != cudaSuccess) return bn_cuda_fail(e, "stage schedule");

@@ -426,8 +426,9 @@ __global__ void __launch_bounds__(256) k_attn_prep(bnk::AttnDims a, const float 
     else q80_store(v, lane, reinterpret_cast<int8_t *>(kv.v_data) + row + blk * 32, kv.v_scale + row / 32 + blk);
 }
 
-// scores: one warp per key j, all gqa query heads of the kv head share the K row
-// (merge idea: attn_qk_softmax_gqa.glslh:15-24). lane l covers dims 8l..8l+7, then a 32-lane tree.
+// scores: each warp takes 8 consecutive keys of one kv head; the gqa query heads of that kv head share every K row
+// (merge idea: attn_qk_softmax_gqa.glslh:15-24) and stay in registers. Per key: lane l covers dims 8l..8l+7 with
+// an fmaf chain, then a 32-lane xor tree. The 8 K rows are requested before any of them is used.
 template <int GQA>
 __global__ void __launch_bounds__(256) k_attn_scores(bnk::AttnDims a, const float *__restrict__ q16f,
                                                      const int *__restrict__ pos_ptr, bnk::KvLayer kv,
@@ -435,45 +436,65 @@ __global__ void __launch_bounds__(256) k_attn_scores(bnk::AttnDims a, const floa
     bnk::pdl_sync();
     const int kvh = blockIdx.y, lane = threadIdx.x & 31, hd = a.head_dim;
     const int nfill = pos_ptr[0] + 1;
-    const int j = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (j >= nfill) return;
-    const size_t row = (size_t(j) * a.n_kv + kvh) * hd;
-    float kf[8];
-    if (a.k_mode == 1) {
-        const uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(kv.k_data) + row + lane * 8);
-        const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h2[e]); kf[2 * e] = f.x; kf[2 * e + 1] = f.y; }
-    } else {
-        const uint2 raw = *reinterpret_cast<const uint2 *>(reinterpret_cast<const int8_t *>(kv.k_data) + row + lane * 8);
-        const float sc = half_bits_to_float(kv.k_scale[row / 32 + (lane >> 2)]);
-        const int8_t *c = reinterpret_cast<const int8_t *>(&raw);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) kf[e] = __fmul_rn(sc, float(c[e]));
-    }
+    const int jb = (blockIdx.x * 8 + (threadIdx.x >> 5)) * 8;
+    if (jb >= nfill) return;
+    float q[GQA][8];
 #pragma unroll
     for (int g = 0; g < GQA; ++g) {
-        const int h = kvh * GQA + g;
-        const float4 *qv = reinterpret_cast<const float4 *>(q16f + size_t(h) * hd + lane * 8);
+        const float4 *qv = reinterpret_cast<const float4 *>(q16f + size_t(kvh * GQA + g) * hd + lane * 8);
         const float4 q0 = qv[0], q1 = qv[1];
-        float acc = 0.0f;
-        acc = fmaf(q0.x, kf[0], acc); acc = fmaf(q0.y, kf[1], acc); acc = fmaf(q0.z, kf[2], acc); acc = fmaf(q0.w, kf[3], acc);
-        acc = fmaf(q1.x, kf[4], acc); acc = fmaf(q1.y, kf[5], acc); acc = fmaf(q1.z, kf[6], acc); acc = fmaf(q1.w, kf[7], acc);
+        q[g][0] = q0.x; q[g][1] = q0.y; q[g][2] = q0.z; q[g][3] = q0.w; q[g][4] = q1.x; q[g][5] = q1.y; q[g][6] = q1.z; q[g][7] = q1.w;
+    }
+    uint4 raw16[8];
+    uint2 raw8[8];
+    float sc[8];
 #pragma unroll
-        for (int s = 16; s > 0; s >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, s));
-        if (lane == 0) score[size_t(h) * a.cap + j] = acc;
+    for (int u = 0; u < 8; ++u) {
+        const int j = min(jb + u, nfill - 1);
+        const size_t row = (size_t(j) * a.n_kv + kvh) * hd;
+        if (a.k_mode == 1) raw16[u] = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(kv.k_data) + row + lane * 8);
+        else {
+            raw8[u] = *reinterpret_cast<const uint2 *>(reinterpret_cast<const int8_t *>(kv.k_data) + row + lane * 8);
+            sc[u] = half_bits_to_float(kv.k_scale[row / 32 + (lane >> 2)]);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int j = jb + u;
+        float kf[8];
+        if (a.k_mode == 1) {
+            const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw16[u]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h2[e]); kf[2 * e] = f.x; kf[2 * e + 1] = f.y; }
+        } else {
+            const int8_t *c = reinterpret_cast<const int8_t *>(&raw8[u]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) kf[e] = __fmul_rn(sc[u], float(c[e]));
+        }
+#pragma unroll
+        for (int g = 0; g < GQA; ++g) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc = fmaf(q[g][e], kf[e], acc);
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, s));
+            if (lane == 0 && j < nfill) score[size_t(kvh * GQA + g) * a.cap + j] = acc;
+        }
     }
 }
 
-// softmax per head (one CTA of 1024 threads): v = score*scale; max; p = exp(v - max); sum as
-// thread-strided ascending partials + fixed tree; probabilities rounded to fp16
-// (round_probs = 1, attn_qk_softmax.comp, attn_vk.h:175-190).
-__global__ void __launch_bounds__(1024) k_attn_softmax(bnk::AttnDims a, const int *__restrict__ pos_ptr,
-                                                       const float *__restrict__ score, float scale,
-                                                       float *__restrict__ p16f) {
+// Softmax numerators and their sum, spread over EXPSUM_PARTS CTAs per head with the summation order of one
+// 1024-thread CTA: "virtual thread" vt adds the keys vt, vt+1024, ... ascending, and the 1024 partial sums are
+// later combined by the fixed tree (attn_qk_softmax.comp / attn_vk.h:175-190 in the regrouped order the CPU
+// checker also carries). Every CTA recomputes the row maximum (a maximum does not depend on order); the
+// exponentials of one virtual thread are evaluated by 8 real threads, then its owner adds them in order.
+constexpr int EXPSUM_PARTS = 8;
+__global__ void __launch_bounds__(1024) k_attn_expsum(bnk::AttnDims a, const int *__restrict__ pos_ptr,
+                                                      const float *__restrict__ score, float scale,
+                                                      float *__restrict__ pe, float *__restrict__ partial) {
     bnk::pdl_sync();
     __shared__ float red[1024];
-    const int h = blockIdx.x, t = threadIdx.x, nfill = pos_ptr[0] + 1;
+    const int h = blockIdx.x, c = blockIdx.y, t = threadIdx.x, nfill = pos_ptr[0] + 1;
     const float *sr = score + size_t(h) * a.cap;
     float mx = -INFINITY;
     for (int j = t; j < nfill; j += 1024) mx = fmaxf(mx, __fmul_rn(sr[j], scale));
@@ -481,40 +502,67 @@ __global__ void __launch_bounds__(1024) k_attn_softmax(bnk::AttnDims a, const in
     for (int s = 512; s > 0; s >>= 1) { __syncthreads(); if (t < s) red[t] = fmaxf(red[t], red[t + s]); }
     __syncthreads();
     mx = red[0];
+    float *pr = pe + size_t(h) * a.cap;
+    const int vt = c * 128 + (t & 127), sub = t >> 7;
+    for (int j = vt + 1024 * sub; j < nfill; j += 1024 * 8) pr[j] = exp_f(__fsub_rn(__fmul_rn(sr[j], scale), mx));
     __syncthreads();
-    float sum = 0.0f;
-    float *pr = p16f + size_t(h) * a.cap;
-    for (int j = t; j < nfill; j += 1024) {
-        const float e = exp_f(__fsub_rn(__fmul_rn(sr[j], scale), mx));
-        pr[j] = e;
-        sum = __fadd_rn(sum, e);
+    if (sub == 0) {
+        float sum = 0.0f;
+        for (int j = vt; j < nfill; j += 1024) sum = __fadd_rn(sum, pr[j]);
+        partial[size_t(h) * 1024 + vt] = sum;
     }
-    red[t] = sum;
+}
+
+// probabilities: p = fp16(e / total), total = the fixed tree over the head's 1024 partial sums (recomputed by
+// every CTA of the head). grid (n_head, ceil(cap / 4096)), 1024 threads, 4 keys per thread.
+__global__ void __launch_bounds__(1024) k_attn_normalise(bnk::AttnDims a, const int *__restrict__ pos_ptr,
+                                                         const float *__restrict__ partial, float *__restrict__ pe) {
+    bnk::pdl_sync();
+    __shared__ float red[1024];
+    const int h = blockIdx.x, t = threadIdx.x, nfill = pos_ptr[0] + 1;
+    if (int(blockIdx.y) * 4096 >= nfill) return;
+    red[t] = partial[size_t(h) * 1024 + t];
     const float tot = block_tree_sum(red, 1024);
-    for (int j = t; j < nfill; j += 1024) pr[j] = __half2float(__float2half_rn(__fdiv_rn(pr[j], tot)));
+    float *pr = pe + size_t(h) * a.cap;
+    for (int j = blockIdx.y * 4096 + t; j < min(nfill, (int(blockIdx.y) + 1) * 4096); j += 1024)
+        pr[j] = __half2float(__float2half_rn(__fdiv_rn(pr[j], tot)));
 }
 
 // PV: grid (n_kv, splits); thread d = output dim; keys of the split ascending; acc = acc + p*v
-// (no fused multiply-add, runtime_vk/shaders/attn_pv_q8v.comp:85-112).
+// (no fused multiply-add, runtime_vk/shaders/attn_pv_q8v.comp:85-112). The split's probabilities are staged in
+// shared memory and the V bytes of 8 keys are requested before the 8 dependent adds run.
 template <int GQA>
 __global__ void __launch_bounds__(256) k_attn_pv(bnk::AttnDims a, const float *__restrict__ p16f,
                                                  const int *__restrict__ pos_ptr, bnk::KvLayer kv, int splits,
                                                  float *__restrict__ part) {
     bnk::pdl_sync();
+    extern __shared__ float ps[];                     // [GQA][per]
     const int kvh = blockIdx.x, sp = blockIdx.y, d = threadIdx.x, hd = a.head_dim;
     const int nfill = pos_ptr[0] + 1;
     const int per = (nfill + splits - 1) / splits;
     const int j0 = sp * per, j1 = min(nfill, j0 + per);
+    const int n = max(0, j1 - j0);
+    for (int i = d; i < GQA * n; i += 256) { const int g = i / n, jj = i - g * n; ps[g * per + jj] = p16f[size_t(kvh * GQA + g) * a.cap + j0 + jj]; }
+    __syncthreads();
     float acc[GQA];
 #pragma unroll
     for (int g = 0; g < GQA; ++g) acc[g] = 0.0f;
-    for (int j = j0; j < j1; ++j) {
-        const size_t idx = (size_t(j) * a.n_kv + kvh) * hd + d;
-        float v;
-        if (a.v_mode == 1) v = __half2float(reinterpret_cast<const __half *>(kv.v_data)[idx]);
-        else v = __fmul_rn(half_bits_to_float(kv.v_scale[idx / 32]), float(reinterpret_cast<const int8_t *>(kv.v_data)[idx]));
+    for (int jb = 0; jb < n; jb += 8) {
+        float v[8];
 #pragma unroll
-        for (int g = 0; g < GQA; ++g) acc[g] = __fadd_rn(acc[g], __fmul_rn(p16f[size_t(kvh * GQA + g) * a.cap + j], v));
+        for (int u = 0; u < 8; ++u) {
+            const int jj = min(jb + u, n - 1);
+            const size_t idx = (size_t(j0 + jj) * a.n_kv + kvh) * hd + d;
+            if (a.v_mode == 1) v[u] = __half2float(reinterpret_cast<const __half *>(kv.v_data)[idx]);
+            else v[u] = __fmul_rn(half_bits_to_float(kv.v_scale[idx / 32]), float(reinterpret_cast<const int8_t *>(kv.v_data)[idx]));
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (jb + u < n) {
+#pragma unroll
+                for (int g = 0; g < GQA; ++g) acc[g] = __fadd_rn(acc[g], __fmul_rn(ps[g * per + jb + u], v[u]));
+            }
+        }
     }
 #pragma unroll
     for (int g = 0; g < GQA; ++g) part[(size_t(sp) * a.n_head + kvh * GQA + g) * hd + d] = acc[g];
@@ -529,7 +577,13 @@ __global__ void k_attn_combine(bnk::AttnDims a, const float *__restrict__ part, 
     const int nfill = pos_ptr[0] + 1;
     const int per = (nfill + splits - 1) / splits;
     float acc = part[i];
-    for (int s = 1; s < splits; ++s) if (s * per < nfill) acc = __fadd_rn(acc, part[size_t(s) * n + i]);
+    for (int sb = 1; sb < splits; sb += 16) {          // 16 partials in flight, added in ascending order
+        float v[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) v[u] = (sb + u < splits && (sb + u) * per < nfill) ? part[size_t(sb + u) * n + i] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 16; ++u) if (sb + u < splits && (sb + u) * per < nfill) acc = __fadd_rn(acc, v[u]);
+    }
     if (pregate) pregate[i] = acc;
     gated[i] = __fmul_rn(acc, __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_f(-gate[i]))));
 }
@@ -623,11 +677,12 @@ void attn_prep(cudaStream_t st, AttnDims a, const float *qg, const float *kin, c
     launch(k_attn_prep, dim3(a.n_head + a.n_kv), dim3(256), 0, st, a, qg, kin, vin, qn_w, kn_w, pos_ptr, kv, q16f, gate); 
 }
 void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *gate, const int *pos_ptr, KvLayer kv,
-                 float *score, float *p16f, float *pv_part, int splits, float *pregate, float *gated, bool combine) {
+                 float *score, float *p16f, float *esum, float *pv_part, int splits, float *pregate, float *gated, bool combine) {
     // grids are sized for the cache capacity; warps beyond the filled prefix return at once
-    launch(k_attn_scores<4>, dim3(dim3((a.cap + 7) / 8, a.n_kv)), dim3(256), 0, st, a, q16f, pos_ptr, kv, score); 
-    launch(k_attn_softmax, dim3(a.n_head), dim3(1024), 0, st, a, pos_ptr, score, 1.0f / sqrtf(float(a.head_dim)), p16f); 
-    launch(k_attn_pv<4>, dim3(dim3(a.n_kv, splits)), dim3(256), 0, st, a, p16f, pos_ptr, kv, splits, pv_part); 
+    launch(k_attn_scores<4>, dim3((a.cap + 63) / 64, a.n_kv), dim3(256), 0, st, a, q16f, pos_ptr, kv, score);
+    launch(k_attn_expsum, dim3(a.n_head, EXPSUM_PARTS), dim3(1024), 0, st, a, pos_ptr, score, 1.0f / sqrtf(float(a.head_dim)), p16f, esum);
+    launch(k_attn_normalise, dim3(a.n_head, (a.cap + 4095) / 4096), dim3(1024), 0, st, a, pos_ptr, esum, p16f);
+    launch(k_attn_pv<4>, dim3(a.n_kv, splits), dim3(256), size_t(4) * ((a.cap + splits - 1) / splits) * 4, st, a, p16f, pos_ptr, kv, splits, pv_part);
     if (!combine) return;
     const int n = a.n_head * a.head_dim;
     launch(k_attn_combine, dim3((n + 255) / 256), dim3(256), 0, st, a, pv_part, splits, pos_ptr, gate, pregate, gated); 

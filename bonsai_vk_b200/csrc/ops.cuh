@@ -74,7 +74,8 @@ void attn_prep(cudaStream_t st, AttnDims a, const float *qg, const float *kin, c
                const float *kn_w, const int *pos_ptr, KvLayer kv, float *q16f, float *gate);
 // scores -> softmax (fp16-rounded probabilities) -> PV -> sigmoid gate. Scratch buffers sized by cap.
 void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *gate, const int *pos_ptr, KvLayer kv,
-                 float *score /*[nh][cap]*/, float *p16f /*[nh][cap]*/, float *pv_part /*[splits][nh][hd]*/, int splits,
+                 float *score /*[nh][cap]*/, float *p16f /*[nh][cap]*/, float *esum /*[nh][1024]*/,
+                 float *pv_part /*[splits][nh][hd]*/, int splits,
                  float *pregate /*[nh][hd] or null*/, float *gated, bool combine /*false: leave the split partials*/);
 void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx);
 

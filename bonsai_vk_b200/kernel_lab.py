@@ -2,6 +2,7 @@
 `bonsai_vk <M> <K> <S> <ITER>` mode, runtime_vk/bonsai_vk.cpp:227-924).
 
   python -m bonsai_vk_b200.kernel_lab M K [ITER] [--nocheck]
+  python -m bonsai_vk_b200.kernel_lab attn CTX [ITER]      one decode-attention layer (16/4 heads x 256, q8_0 K and V)
 
 Prints max|err| and rel against the CPU checker (when oracle/ is built), then ms/op, Gop/s and GB/s of
 PTQ1_0 bytes from CUDA events. Timing rotates through enough copies of the matrix to exceed L2.
@@ -13,8 +14,51 @@ import sys
 import numpy as np
 
 
+def attn_lab(argv):
+    """BASELINE config 2: 16 query / 4 KV heads, head_dim 256, q8_0 cache of CTX keys, one query token."""
+    from bonsai_vk_b200 import Context
+    from bonsai_vk_b200 import lib as L
+    ctx_len = int(argv[0])
+    iters = int(argv[1]) if len(argv) > 1 else 20
+    n_head, n_kv, hd = 16, 4, 256
+    QD, KD = n_head * hd, n_kv * hd
+    rng = np.random.default_rng(1)
+    ctx = Context(0)
+    dims = L.AttnDimsC(n_head=n_head, n_kv=n_kv, head_dim=hd, n_rot=64, cap=ctx_len + (ctx_len & 1), k_mode=0, v_mode=0,
+                       rms_eps=1e-6, rope_base=1e7)
+    kvb, scb = ctx.attn_sizes(dims)
+    nlay = max(2, int(300e6 // kvb) + 1)                 # rotate over layers so the cache does not sit in L2
+    kvs = [ctx.alloc(kvb) for _ in range(nlay)]
+    scratch = ctx.alloc(scb)
+    rows = 4096
+    bk = ctx.from_numpy(rng.standard_normal((rows, KD)).astype(np.float32))
+    bv = ctx.from_numpy(rng.standard_normal((rows, KD)).astype(np.float32))
+    bq = ctx.from_numpy(rng.standard_normal((n_head, 2 * hd)).astype(np.float32))
+    ones = ctx.from_numpy(np.ones(hd, dtype=np.float32))
+    for kv in kvs:
+        for p0 in range(0, ctx_len, rows):
+            ctx.attn_insert(dims, kv, bk, bv, min(rows, ctx_len - p0), p0, bq, ones, ones, scratch)
+    out = ctx.alloc(QD * 4)
+    for kv in kvs:
+        ctx.attn_attend(dims, kv, ctx_len - 1, scratch, None, out)
+    ctx.sync()
+    e0, e1 = ctx.event(), ctx.event()
+    ctx.record(e0)
+    for _ in range(iters):
+        for kv in kvs:
+            ctx.attn_attend(dims, kv, ctx_len - 1, scratch, None, out)
+    ctx.record(e1)
+    ms = ctx.elapsed_ms(e0, e1) / (iters * nlay)
+    nbytes = ctx_len * n_kv * hd * 34 // 32 * 2
+    print(f"attention ctx={ctx_len}: {ms * 1000:.2f} us/layer, {nbytes / ms / 1e6:.1f} GB/s of q8_0 K+V bytes "
+          f"({nbytes} algorithmic bytes; {nlay} caches = {nlay * kvb / 1e6:.0f} MB rotation)")
+    ctx.close()
+
+
 def main(argv):
     from bonsai_vk_b200 import Context, ptq
+    if argv and argv[0] == "attn":
+        return attn_lab(argv[1:])
     M, K = int(argv[0]), int(argv[1])
     iters = int(argv[2]) if len(argv) > 2 and not argv[2].startswith("-") else 3
     check = "--nocheck" not in argv

@@ -24,6 +24,12 @@ class HParamsC(C.Structure):
         ("rms_eps", C.c_float), ("rope_base", C.c_float)] + [(n, C.c_int32) for n in ("n_streams", "block_begin", "block_end")]
 
 
+class AttnDimsC(C.Structure):
+    """Mirror of bn_attn_dims."""
+    _fields_ = [(n, C.c_int32) for n in ("n_head", "n_kv", "head_dim", "n_rot", "cap", "k_mode", "v_mode")] + [
+        ("rms_eps", C.c_float), ("rope_base", C.c_float)]
+
+
 READ_LOGITS, READ_RESIDUAL, READ_GDN_STATE, READ_CONV_HIST, READ_K_DATA, READ_K_SCALE, READ_V_DATA, READ_V_SCALE = range(8)
 
 
@@ -60,6 +66,10 @@ def load_library() -> C.CDLL:
         "bn_act_quant_q81": (i32, [vp, vp, sz, i32, vp, sz]),
         "bn_gemv_q81": (i32, [vp, vp, sz, i32, i32, vp, sz, vp, sz, vp, sz]),
         "bn_gemv_q81_static": (i32, [vp, vp, sz, i32, i32, vp, sz, vp, sz]),
+        "bn_attn_kv_bytes": (sz, [C.POINTER(AttnDimsC)]),
+        "bn_attn_scratch_bytes": (sz, [C.POINTER(AttnDimsC)]),
+        "bn_attn_insert": (i32, [vp, C.POINTER(AttnDimsC), vp, sz, vp, sz, vp, sz, i32, i32, vp, sz, vp, sz, vp, sz, vp, sz]),
+        "bn_attn_attend": (i32, [vp, C.POINTER(AttnDimsC), vp, sz, i32, vp, sz, vp, sz, vp, sz]),
         "bn_model_create": (i32, [vp, C.POINTER(HParamsC), C.POINTER(vp)]),
         "bn_model_set_tensor": (i32, [vp, C.c_char_p, vp, sz, sz]),
         "bn_model_set_signs": (i32, [vp, vp, sz, i32]),
@@ -202,6 +212,18 @@ class Context:
                  out_off: int = 0, dots: Buffer | None = None, dots_off: int = 0):
         _check(self.lib.bn_gemv_q81(self.h, w.h, w_off, M, K, pack.h, pack_off, out.h, out_off,
                                     dots.h if dots is not None else None, dots_off), "bn_gemv_q81")
+
+    def attn_sizes(self, dims: "AttnDimsC"):
+        return int(self.lib.bn_attn_kv_bytes(C.byref(dims))), int(self.lib.bn_attn_scratch_bytes(C.byref(dims)))
+
+    def attn_insert(self, dims, kv: Buffer, k_rows: Buffer, v_rows: Buffer, n: int, pos0: int, qg: Buffer, q_norm: Buffer,
+                    k_norm: Buffer, scratch: Buffer, k_off: int = 0, v_off: int = 0):
+        _check(self.lib.bn_attn_insert(self.h, C.byref(dims), kv.h, 0, k_rows.h, k_off, v_rows.h, v_off, n, pos0, qg.h, 0,
+                                       q_norm.h, 0, k_norm.h, 0, scratch.h, 0), "bn_attn_insert")
+
+    def attn_attend(self, dims, kv: Buffer, pos: int, scratch: Buffer, pregate: "Buffer | None", gated: Buffer):
+        _check(self.lib.bn_attn_attend(self.h, C.byref(dims), kv.h, 0, pos, scratch.h, 0,
+                                       pregate.h if pregate is not None else None, 0, gated.h, 0), "bn_attn_attend")
 
     def gemv_q81_static(self, w: Buffer, M: int, K: int, pack: Buffer, out: Buffer, w_off: int = 0, pack_off: int = 0,
                         out_off: int = 0):

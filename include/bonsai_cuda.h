@@ -94,6 +94,26 @@ int bn_gemv_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const 
 int bn_gemv_q81_static(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const bn_buf *pack,
                        size_t pack_off, bn_buf *out, size_t out_off);
 
+/* ---- decode attention as stand-alone ops (reference: attn_block, runtime_vk/bonsai_forward.h:581-645; kernels
+ *      attn_norm_rope2.comp, attn_qk_softmax*.comp, attn_pv_q8v*.comp; test harness align_attn.cpp) ------------
+ * One layer's cache lives in a caller buffer of bn_attn_kv_bytes(); working memory of bn_attn_scratch_bytes(). */
+typedef struct bn_attn_dims {
+    int32_t n_head, n_kv, head_dim, n_rot, cap;   /* cap = cache capacity in positions */
+    int32_t k_mode, v_mode;                        /* 0 = q8_0, 1 = fp16 */
+    float rms_eps, rope_base;
+} bn_attn_dims;
+size_t bn_attn_kv_bytes(const bn_attn_dims *d);
+size_t bn_attn_scratch_bytes(const bn_attn_dims *d);
+/* n consecutive tokens at positions pos0.. : per token the K row gets head norm * k_norm, rope, then (like the raw
+ * V row) is quantised / rounded into the cache; the q|gate row [n_head][2*head_dim] (layout of attn_q's output,
+ * deint_qg.comp) is normed, roped at the LAST position and kept in scratch for bn_attn_attend. */
+int bn_attn_insert(bn_ctx *ctx, const bn_attn_dims *d, bn_buf *kv, size_t kv_off, const bn_buf *k_rows, size_t k_off,
+                   const bn_buf *v_rows, size_t v_off, int n, int pos0, const bn_buf *qg, size_t qg_off,
+                   const bn_buf *q_norm, size_t qn_off, const bn_buf *k_norm, size_t kn_off, bn_buf *scratch, size_t scratch_off);
+/* softmax attention of the kept query over positions 0..pos; pregate (may be NULL) and gated: [n_head][head_dim] */
+int bn_attn_attend(bn_ctx *ctx, const bn_attn_dims *d, const bn_buf *kv, size_t kv_off, int pos, bn_buf *scratch,
+                   size_t scratch_off, bn_buf *pregate, size_t pg_off, bn_buf *gated, size_t g_off);
+
 /* ---- whole-token decode (reference: fwd_token, runtime_vk/bonsai_forward.h:664-758) ---------------
  * The host registers every tensor of the GGUF by its GGUF name (PTQ1_0 tensors as the file's native
  * 28-byte blocks, row-major, d0 = K; f32 tensors as they are) plus the prism.hadamard sign values,

@@ -187,7 +187,7 @@ class OracleModel:
         self.m = C.c_void_p(lib.bo_model_new(_p(ip), _p(fp)))
         lib.bo_model_set_cap(self.m, hp.cap, threads)
         # attn_order 1 = sums grouped as the CUDA kernels group them (pv split rule of bn_model_finalize)
-        self.pv_splits = 64 if hp.cap >= 4096 else (8 if hp.cap >= 512 else 1)
+        self.pv_splits = 256 if hp.cap >= 16384 else (64 if hp.cap >= 4096 else (8 if hp.cap >= 512 else 1))
         lib.bo_model_set_attn_order(self.m, attn_order, self.pv_splits)
         self.keep = {n: np.ascontiguousarray(t) for n, t in tensors.items()}
         for n, t in self.keep.items():
