@@ -40,6 +40,24 @@ def build_lib(verbose: bool = False, force: bool = False) -> str:
     return LIB
 
 
+HOST_BIN = os.path.join(HERE, "host", "bonsai_run")
+
+
+def build_host(force: bool = False) -> str:
+    """The C++ command-line host (GGUF reader, contract checks, loader, run mode). Links the library by
+    path and finds it next to the package at run time ($ORIGIN/..)."""
+    srcs = [os.path.join(HERE, "host", "bonsai_run.cpp")]
+    deps = srcs + [os.path.join(HERE, "host", "bonsai_host.h"), LIB] + glob.glob(os.path.join(ROOT, "include", "*.h"))
+    if not force and not _stale(HOST_BIN, deps):
+        return HOST_BIN
+    cmd = ["g++", "-O2", "-std=c++17", "-Wall", "-o", HOST_BIN] + srcs + ["-L" + HERE, "-lbonsai_cuda", "-Wl,-rpath,$ORIGIN/.."]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("g++ failed building bonsai_run")
+    return HOST_BIN
+
+
 def build_oracle() -> None:
     """Compile the CPU checker under oracle/ (and the reference shim when the reference tree is
     present). Building the checker is not using it: only tests and the benchmark baselines load it."""
@@ -51,5 +69,6 @@ def build_oracle() -> None:
 
 if __name__ == "__main__":
     build_lib(verbose="-v" in sys.argv, force=True)
+    build_host(force=True)
     build_oracle()
     print("built", LIB)

@@ -40,6 +40,7 @@ struct bn_model {
     int pv_splits = 1;
     int graph_launches = 0;
     bool fused = true;        // phase kernels (false: one kernel per reference dispatch, env BONSAI_NO_FUSE=1)
+    bool phases_only = false; // measurement: enqueue only the projection kernels of the fused schedule
     bool use_pdl = true;      // programmatic dependent launch between phases (env BONSAI_NO_PDL=1 turns it off)
     cudaError_t launch_err = cudaSuccess;
     unsigned long long *stamps = nullptr;   // profiling aid: 8 time stamps per phase kernel of one token
@@ -193,7 +194,7 @@ void ffn_fused(bn_model *m, const bn_model::Layer &L) {
     else { a.out = m->FG; launch(m, a); a.W = reinterpret_cast<const uint8_t *>(L.ffn_up); a.out = m->FU; launch(m, a); }
     bnk::PhaseArgs d = phase_base(m, L.ffn_down, h.hidden, h.ffn, m->signs + h.hidden);
     // silu needs a double-precision exp per element: computed once by a small kernel, not by every CTA
-    bnk::swiglu(m->ctx->stream, m->FG, m->FU, h.ffn, m->FS);
+    if (!m->phases_only) bnk::swiglu(m->ctx->stream, m->FG, m->FU, h.ffn, m->FS);
     d.pro = bnk::PRO_PLAIN; d.x0 = m->FS;
     d.resid_in = m->RES; d.resid_out = m->RES;
     launch(m, d);
@@ -210,7 +211,7 @@ void gdn_fused(bn_model *m, const bn_model::Layer &L) {
         a.out = m->QKV; launch(m, a);
         a.inv_out = nullptr; a.W = reinterpret_cast<const uint8_t *>(L.gate_w); a.M = IN; a.out = m->Z; launch(m, a);
     }
-    {
+    if (!m->phases_only) {
         const bnk::GdnDims gd{NH, NQ, D};
         float *h0 = conv_of(m, 0, L.idx), *h1 = conv_of(m, 1, L.idx);
         bnk::gdn_core_fused(m->ctx->stream, gd, h.hidden, m->QKV, L.conv_w, h0, h1, m->POS, m->RES, m->G + 48, L.attn_norm,
@@ -237,8 +238,10 @@ void attn_fused(bn_model *m, const bn_model::Layer &L) {
         a.W = reinterpret_cast<const uint8_t *>(L.k_w); a.M = KD; a.out = m->KBUF; launch(m, a);
         a.W = reinterpret_cast<const uint8_t *>(L.v_w); a.out = m->VBUF; launch(m, a);
     }
-    bnk::attn_prep(st, ad, m->QKV, m->KBUF, m->VBUF, L.q_norm, L.k_norm, m->POS, kv, m->Q16F, m->GATEB);
-    bnk::attn_decode(st, ad, m->Q16F, m->GATEB, m->POS, kv, m->SCORE, m->P16F, m->ESUM, m->PVPART, m->pv_splits, nullptr, m->GOUT, true);
+    if (!m->phases_only) {
+        bnk::attn_prep(st, ad, m->QKV, m->KBUF, m->VBUF, L.q_norm, L.k_norm, m->POS, kv, m->Q16F, m->GATEB);
+        bnk::attn_decode(st, ad, m->Q16F, m->GATEB, m->POS, kv, m->SCORE, m->P16F, m->ESUM, m->PVPART, m->pv_splits, nullptr, m->GOUT, true);
+    }
     bnk::PhaseArgs o = phase_base(m, L.o_w, h.hidden, QD, m->signs);
     o.pro = bnk::PRO_PLAIN; o.x0 = m->GOUT;
     o.resid_in = m->RES; o.resid_out = m->RES;
@@ -268,7 +271,7 @@ void enqueue_token(bn_model *m, int stop_after, bool want_logits) {
         bnk::rms_norm(st, m->RES, m->out_norm, 1, h.hidden, h.rms_eps, m->AN);
         rot_project(m, m->AN, m->signs, h.hidden, m->PACK_H, m->out_w, h.vocab, m->LOGITS);
     }
-    bnk::argmax_first(st, m->LOGITS, h.vocab, m->NEXT, m->AMV, m->AMI);
+    if (!m->phases_only) bnk::argmax_first(st, m->LOGITS, h.vocab, m->NEXT, m->AMV, m->AMI);
 }
 
 // feed the greedy pick back as the next input, on the device
@@ -625,6 +628,15 @@ int bn_model_gemv_sweep(bn_model *m, int reps, float *ms_per_sweep) {
     cudaStream_t st = m->ctx->stream;
     const int sm = m->ctx->sm_count;
     auto sweep = [&]() {
+        if (m->fused) {      // the production launches: every fused projection kernel of one token, nothing else
+            m->phases_only = true;
+            for (const bn_model::Layer &L : m->layers) { if (L.attn) attn_fused(m, L); else gdn_fused(m, L); ffn_fused(m, L); }
+            bnk::PhaseArgs a = phase_base(m, m->out_w, h.vocab, h.hidden, m->signs);
+            a.pro = bnk::PRO_NORM; a.x0 = m->RES; a.w = m->out_norm; a.out = m->LOGITS;
+            launch(m, a);
+            m->phases_only = false;
+            return;
+        }
         for (const bn_model::Layer &L : m->layers) {
             if (L.attn) {
                 bnk::gemv_q81(st, sm, L.q_w, 2 * QD, h.hidden, m->PACK_H, m->QKV, m->GEMV_SCRATCH, nullptr);

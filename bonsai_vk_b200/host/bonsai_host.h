@@ -1,0 +1,256 @@
+// bonsai_host.h - C++17 host above the C ABI: GGUF reader, model plan with the prism.hadamard contract, loader.
+//
+// Mirrors the reference host's behaviour for the decode path (all paths relative to the reference tree):
+//   gguf_load            runtime_vk/bonsai_gguf.h:72-155      v3 header, KV types 0-12, tensor table, data start
+//   model_plan_hparams   runtime_vk/bonsai_model.h:642-760    hyper-parameters only from GGUF metadata
+//   model_plan_contract  runtime_vk/bonsai_model.h:773-912    prism.hadamard.* gate (refuse before any GPU work)
+//   model_plan_build     runtime_vk/bonsai_model.h:1013-1078  dtype 143 (PTQ1_0) / 0 (f32) only, K % 128 == 0
+//   load_ptq_weights     runtime_vk/bonsai_weights.h:502-558  file -> staging -> device, here without any repack
+// Written from the documented behaviour; no reference source text is reproduced.
+#pragma once
+
+#include "../../include/bonsai_cuda.h"
+
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+namespace bh {
+
+struct Tensor {
+    std::string name;
+    uint32_t n_dims = 0;
+    uint64_t d[4] = {1, 1, 1, 1};
+    uint32_t dtype = 0;
+    uint64_t off = 0;        // relative to data_start
+    uint64_t bytes = 0;
+};
+
+struct Gguf {
+    uint32_t version = 0, alignment = 32;
+    uint64_t data_start = 0;
+    std::map<std::string, int64_t> ki;
+    std::map<std::string, double> kf;
+    std::map<std::string, std::string> ks;
+    std::map<std::string, std::vector<int64_t>> ai;       // numeric arrays
+    std::map<std::string, std::vector<std::string>> as;   // string arrays
+    std::vector<Tensor> tensors;
+};
+
+class Reader {
+public:
+    explicit Reader(FILE *f) : f_(f) {}
+    bool ok() const { return ok_; }
+    template <class T> T get() { T v{}; if (fread(&v, sizeof v, 1, f_) != 1) ok_ = false; return v; }
+    std::string str() {
+        const uint64_t n = get<uint64_t>();
+        if (!ok_ || n > (1ull << 30)) { ok_ = false; return {}; }
+        std::string s(n, '\0');
+        if (n && fread(&s[0], 1, n, f_) != n) ok_ = false;
+        return s;
+    }
+private:
+    FILE *f_;
+    bool ok_ = true;
+};
+
+inline bool read_scalar(Reader &r, uint32_t ty, int64_t &iv, double &fv, std::string &sv) {
+    switch (ty) {
+        case 0: iv = r.get<uint8_t>(); break;
+        case 1: iv = r.get<int8_t>(); break;
+        case 2: iv = r.get<uint16_t>(); break;
+        case 3: iv = r.get<int16_t>(); break;
+        case 4: iv = r.get<uint32_t>(); break;
+        case 5: iv = r.get<int32_t>(); break;
+        case 6: fv = r.get<float>(); break;
+        case 7: iv = r.get<uint8_t>(); break;
+        case 8: sv = r.str(); break;
+        case 10: iv = int64_t(r.get<uint64_t>()); break;
+        case 11: iv = r.get<int64_t>(); break;
+        case 12: fv = r.get<double>(); break;
+        default: return false;
+    }
+    return r.ok();
+}
+
+inline uint64_t tensor_bytes(const Tensor &t, std::string &why) {
+    uint64_t n = 1;
+    for (uint32_t i = 0; i < t.n_dims; ++i) n *= t.d[i];
+    if (t.dtype == 0) return n * 4;
+    if (t.dtype == 143) {
+        if (t.d[0] % 128) { why = "tensor " + t.name + ": PTQ1_0 needs d0 (the reduction length) to be a multiple of 128"; return 0; }
+        return n / 128 * 28;
+    }
+    why = "tensor " + t.name + ": dtype " + std::to_string(t.dtype) + " is neither PTQ1_0 (143) nor f32 (0)";
+    return 0;
+}
+
+inline bool gguf_load(const char *path, Gguf &g, std::string &why) {
+    FILE *f = fopen(path, "rb");
+    if (!f) { why = std::string("cannot open ") + path; return false; }
+    Reader r(f);
+    char magic[4] = {};
+    if (fread(magic, 1, 4, f) != 4 || memcmp(magic, "GGUF", 4) != 0) { why = std::string(path) + " is not a GGUF file"; fclose(f); return false; }
+    g.version = r.get<uint32_t>();
+    const uint64_t n_tensors = r.get<uint64_t>(), n_kv = r.get<uint64_t>();
+    if (!r.ok() || n_tensors > (1u << 20) || n_kv > (1u << 20)) { why = "truncated or implausible GGUF header"; fclose(f); return false; }
+    for (uint64_t i = 0; i < n_kv; ++i) {
+        const std::string key = r.str();
+        const uint32_t ty = r.get<uint32_t>();
+        if (ty == 9) {
+            const uint32_t et = r.get<uint32_t>();
+            const uint64_t n = r.get<uint64_t>();
+            if (et == 8) { auto &v = g.as[key]; v.resize(n); for (auto &s : v) s = r.str(); }
+            else {
+                auto &v = g.ai[key]; v.resize(n);
+                for (auto &x : v) { int64_t iv = 0; double fv = 0; std::string sv; if (!read_scalar(r, et, iv, fv, sv)) { why = "bad array element type in " + key; fclose(f); return false; } x = (et == 6 || et == 12) ? int64_t(fv) : iv; }
+            }
+        } else {
+            int64_t iv = 0; double fv = 0; std::string sv;
+            if (!read_scalar(r, ty, iv, fv, sv)) { why = "bad value type for key " + key; fclose(f); return false; }
+            if (ty == 8) g.ks[key] = sv; else if (ty == 6 || ty == 12) g.kf[key] = fv; else g.ki[key] = iv;
+        }
+        if (!r.ok()) { why = "truncated GGUF metadata at key " + key; fclose(f); return false; }
+    }
+    for (uint64_t i = 0; i < n_tensors; ++i) {
+        Tensor t;
+        t.name = r.str();
+        t.n_dims = r.get<uint32_t>();
+        if (t.n_dims > 4) { why = "tensor " + t.name + " has more than 4 dims"; fclose(f); return false; }
+        for (uint32_t k = 0; k < t.n_dims; ++k) t.d[k] = r.get<uint64_t>();
+        t.dtype = r.get<uint32_t>();
+        t.off = r.get<uint64_t>();
+        if (!r.ok()) { why = "truncated GGUF tensor table"; fclose(f); return false; }
+        t.bytes = tensor_bytes(t, why);
+        if (!t.bytes) { fclose(f); return false; }
+        g.tensors.push_back(t);
+    }
+    auto it = g.ki.find("general.alignment");
+    if (it != g.ki.end() && it->second > 0) g.alignment = uint32_t(it->second);
+    const uint64_t pos = uint64_t(ftell(f));
+    g.data_start = (pos + g.alignment - 1) / g.alignment * g.alignment;
+    fclose(f);
+    return true;
+}
+
+struct Plan {
+    bn_hparams hp = {};
+    std::vector<int32_t> signs;
+    int64_t hat_version = 0;
+};
+
+// hyper-parameters and the rotation contract; `why` explains a refusal. rc: 0 ok, 2 contract/metadata, 6 rotation refusal
+inline int plan_build(const Gguf &g, Plan &p, int cap, std::string &why) {
+    auto arch_it = g.ks.find("general.architecture");
+    if (arch_it == g.ks.end()) { why = "general.architecture is missing"; return 2; }
+    const std::string A = arch_it->second + ".";
+    auto I = [&](const std::string &k, int64_t &out) { auto it = g.ki.find(A + k); if (it == g.ki.end()) { why = "metadata key " + A + k + " is missing"; return false; } out = it->second; return true; };
+    auto F = [&](const std::string &k, double &out) { auto it = g.kf.find(A + k); if (it == g.kf.end()) { why = "metadata key " + A + k + " is missing"; return false; } out = it->second; return true; };
+    int64_t v = 0; double d = 0;
+    bn_hparams &h = p.hp;
+    if (!I("block_count", v)) return 2; h.n_layer = int(v);
+    if (!I("embedding_length", v)) return 2; h.hidden = int(v);
+    if (!I("feed_forward_length", v)) return 2; h.ffn = int(v);
+    if (!I("attention.head_count", v)) return 2; h.n_head = int(v);
+    if (!I("attention.head_count_kv", v)) return 2; h.n_kv = int(v);
+    if (!I("attention.key_length", v)) return 2; h.head_dim = int(v);
+    int64_t vl = 0;
+    if (!I("attention.value_length", vl)) return 2;
+    if (vl != h.head_dim) { why = "attention.value_length differs from key_length"; return 2; }
+    if (!I("rope.dimension_count", v)) return 2; h.n_rot = int(v);
+    if (!I("full_attention_interval", v)) return 2; h.attn_interval = int(v);
+    if (!I("ssm.conv_kernel", v)) return 2; if (v != 4) { why = "ssm.conv_kernel must be 4"; return 2; }
+    if (!I("ssm.state_size", v)) return 2; h.gdn_dim = int(v);
+    if (!I("ssm.group_count", v)) return 2; h.gdn_qk_heads = int(v);
+    if (!I("ssm.time_step_rank", v)) return 2; h.gdn_heads = int(v);
+    if (!I("ssm.inner_size", v)) return 2; if (v != int64_t(h.gdn_heads) * h.gdn_dim) { why = "ssm.inner_size != time_step_rank * state_size"; return 2; }
+    if (!F("attention.layer_norm_rms_epsilon", d)) return 2; h.rms_eps = float(d);
+    if (!F("rope.freq_base", d)) return 2; h.rope_base = float(d);
+    auto tok = g.as.find("tokenizer.ggml.tokens");
+    if (tok == g.as.end() || tok->second.empty()) { why = "tokenizer.ggml.tokens is missing (its length is the vocabulary size)"; return 2; }
+    h.vocab = int(tok->second.size());
+    if (int64_t(h.n_head) * h.head_dim != h.hidden) { why = "head_count * key_length != embedding_length"; return 2; }
+    h.cap = cap; h.act_mode = 0; h.k_mode = 0; h.v_mode = 0;
+    // ---- prism.hadamard.* (absent / 0 = no rotation -> this forward refuses; > 1 refused)
+    auto hv = g.ki.find("prism.hadamard.version");
+    p.hat_version = hv == g.ki.end() ? 0 : hv->second;
+    if (p.hat_version == 0) { why = "prism.hadamard.version = 0: the file declares no activation rotation, but this forward applies signs + Hadamard before every ternary projection; refusing instead of rotating a model that was never rotated"; return 6; }
+    if (p.hat_version != 1) { why = "prism.hadamard.version = " + std::to_string(p.hat_version) + ": only version 1 (normalized Sylvester-Walsh block transform) is implemented"; return 2; }
+    auto tx = g.ks.find("prism.hadamard.transform");
+    if (tx == g.ks.end() || tx->second != "normalized-sylvester-walsh-hadamard") { why = "prism.hadamard.transform must be normalized-sylvester-walsh-hadamard"; return 2; }
+    auto bs = g.ki.find("prism.hadamard.block_size");
+    if (bs == g.ki.end()) { why = "prism.hadamard.block_size is missing"; return 2; }
+    h.hat_block = int(bs->second);
+    if (h.hat_block < 16 || h.hat_block > 4096 || (h.hat_block & (h.hat_block - 1)) || h.hidden % h.hat_block || h.ffn % h.hat_block) { why = "prism.hadamard.block_size must be a power of two in [16, 4096] dividing hidden and ffn"; return 2; }
+    auto sw = g.ai.find("prism.hadamard.sign_widths"), sv = g.ai.find("prism.hadamard.sign_values");
+    if (sw == g.ai.end() || sv == g.ai.end()) { why = "prism.hadamard.sign_widths / sign_values are missing"; return 2; }
+    int64_t sum = 0;
+    for (int64_t w : sw->second) { if (w != h.hidden && w != h.ffn) { why = "prism.hadamard.sign_widths must be a subset of {hidden, ffn}"; return 2; } sum += w; }
+    if (sum != int64_t(sv->second.size()) || sum != int64_t(h.hidden) + h.ffn) { why = "prism.hadamard.sign_values length must equal the sum of sign_widths = hidden + ffn"; return 2; }
+    p.signs.resize(sv->second.size());
+    for (size_t i = 0; i < p.signs.size(); ++i) { const int64_t s = sv->second[i]; if (s != 1 && s != -1) { why = "prism.hadamard.sign_values must be +-1"; return 2; } p.signs[i] = int32_t(s); }
+    return 0;
+}
+
+struct Engine {
+    bn_ctx *ctx = nullptr;
+    bn_buf *weights = nullptr;
+    bn_model *model = nullptr;
+    Plan plan;
+    double load_ms = 0;
+};
+
+// Device order of the weights: projections that read the same input are placed back to back (qkv|gate, q|k|v,
+// ffn_gate|ffn_up) whatever their order in the file, so that the token schedule can run each group as one launch.
+inline long layout_rank(const std::string &n) {
+    static const char *order[] = {"attn_norm.weight", "attn_qkv.weight", "attn_gate.weight", "attn_q.weight", "attn_k.weight",
+                                  "attn_v.weight", "attn_output.weight", "ssm_out.weight", "post_attention_norm.weight",
+                                  "ffn_gate.weight", "ffn_up.weight", "ffn_down.weight"};
+    if (n.rfind("blk.", 0) != 0) return n == "token_embd.weight" ? -2 : (n == "output.weight" ? 1L << 40 : -1);
+    const long b = strtol(n.c_str() + 4, nullptr, 10);
+    const size_t dot = n.find('.', 4);
+    const std::string suffix = dot == std::string::npos ? "" : n.substr(dot + 1);
+    long r = 63;
+    for (int i = 0; i < int(sizeof order / sizeof *order); ++i) if (suffix == order[i]) r = i;
+    return b * 64 + r;
+}
+
+// Upload every tensor (native bytes; 256-byte aligned starts) and register it by name. rc 3 = load error.
+inline int engine_load(Engine &e, const char *path, const Gguf &g, size_t chunk_bytes, std::string &why) {
+    auto al = [](uint64_t n) { return (n + 255) & ~uint64_t(255); };
+    std::vector<const Tensor *> order;
+    for (const Tensor &t : g.tensors) order.push_back(&t);
+    std::stable_sort(order.begin(), order.end(), [](const Tensor *a, const Tensor *b) { return layout_rank(a->name) < layout_rank(b->name); });
+    uint64_t total = al(e.plan.signs.size() * 4);
+    for (const Tensor &t : g.tensors) total += al(t.bytes);
+    if (bn_alloc(e.ctx, total, &e.weights)) { why = bn_last_error(); return 3; }
+    if (bn_model_create(e.ctx, &e.plan.hp, &e.model)) { why = bn_last_error(); return 2; }
+    FILE *f = fopen(path, "rb");
+    if (!f) { why = "cannot reopen the GGUF"; return 3; }
+    void *stage = nullptr;
+    if (bn_host_alloc(chunk_bytes, &stage)) { why = bn_last_error(); fclose(f); return 3; }
+    uint64_t off = 0;
+    for (const Tensor *tp : order) {
+        const Tensor &t = *tp;
+        if (fseeko(f, off_t(g.data_start + t.off), SEEK_SET) != 0) { why = "seek failed for " + t.name; fclose(f); return 3; }
+        for (uint64_t done = 0; done < t.bytes; done += chunk_bytes) {
+            const size_t n = size_t(std::min<uint64_t>(chunk_bytes, t.bytes - done));
+            if (fread(stage, 1, n, f) != n) { why = "short read in " + t.name; fclose(f); return 3; }
+            if (bn_upload(e.ctx, e.weights, off + done, stage, n)) { why = bn_last_error(); fclose(f); return 3; }
+        }
+        if (bn_model_set_tensor(e.model, t.name.c_str(), e.weights, off, t.bytes)) { why = bn_last_error(); fclose(f); return 3; }
+        off += al(t.bytes);
+    }
+    fclose(f);
+    bn_host_free(stage);
+    if (bn_upload(e.ctx, e.weights, off, e.plan.signs.data(), e.plan.signs.size() * 4)) { why = bn_last_error(); return 3; }
+    if (bn_model_set_signs(e.model, e.weights, off, int(e.plan.signs.size()))) { why = bn_last_error(); return 2; }
+    if (bn_model_finalize(e.model)) { why = bn_last_error(); return 2; }
+    return 0;
+}
+
+}  // namespace bh

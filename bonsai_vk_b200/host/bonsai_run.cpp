@@ -1,0 +1,183 @@
+// bonsai_run - command-line host for the decode path on one B200.
+//
+//   bonsai_run <model.gguf> info                 metadata, contract and tensor census; no GPU work
+//   bonsai_run <model.gguf> run [n_gen]          prefill BONSAI_PROMPT_IDS, then n_gen greedy tokens (default 48)
+//
+// Behaviour mirrors the reference engine's `run` mode (runtime_vk/bonsai_forward.h:2645-3000 fwd_run,
+// :3240-3300 fwd_main): hyper-parameters only from GGUF metadata, the rotation gate before any GPU work
+// (exit 6), capacity checks (exit 4), context-fit guard (exit 7), the bitwise lineage gate behind
+// BONSAI_QCHECK=1 (exit 6, "REFUSING TO GENERATE"), and the same report lines
+// ("... generated tokens in ... ms  ->  ... tok/s", "steady-state: ... ms/token", "gate: PASS (bitmask 0 = ...)").
+// The tokenizer and chat template stay on the host side of the boundary and are not part of this tool: the
+// prompt is given as token ids.
+//
+// Environment: BONSAI_PROMPT_IDS (comma separated ids; default "1,2,3,4,5,6,7,8"), BONSAI_CAP (KV capacity in
+// positions, even; default 4096), BONSAI_QCHECK=1 (run the gate after the prefill), BONSAI_DEVICE (CUDA ordinal),
+// BONSAI_STEPWISE=1 (one host call per generated token instead of the device-chained loop).
+#include "bonsai_host.h"
+
+#include <chrono>
+#include <cmath>
+#include <cstdlib>
+
+namespace {
+
+double now_ms() {
+    using namespace std::chrono;
+    return duration<double, std::milli>(steady_clock::now().time_since_epoch()).count();
+}
+
+std::vector<int> parse_ids(const char *s) {
+    std::vector<int> out;
+    while (s && *s) {
+        char *end = nullptr;
+        const long v = strtol(s, &end, 10);
+        if (end == s) break;
+        out.push_back(int(v));
+        s = *end == ',' ? end + 1 : end;
+    }
+    return out;
+}
+
+int fail(int rc, const std::string &why) {
+    fprintf(stderr, "bonsai_run: %s (exit %d)\n", why.c_str(), rc);
+    return rc;
+}
+
+// Two kernel lineages of the same forward (fused phase kernels vs one stand-alone kernel per reference dispatch)
+// must leave bit-identical logits, residual, KV bytes and recurrent state after the same prompt. Extra
+// invariants: cache slots beyond the prompt are still zero bytes; every logit is finite.
+int lineage_gate(bh::Engine &e, const bh::Gguf &g, const char *path, const std::vector<int> &prompt, std::string &why) {
+    bh::Engine ref;
+    ref.ctx = e.ctx;
+    ref.plan = e.plan;
+    setenv("BONSAI_NO_FUSE", "1", 1);
+    const int rc = bh::engine_load(ref, path, g, 64u << 20, why);
+    unsetenv("BONSAI_NO_FUSE");
+    if (rc) return -1;
+    for (size_t i = 0; i < prompt.size(); ++i)
+        if (bn_model_token(ref.model, prompt[i], int(i), -1, nullptr)) { why = bn_last_error(); return -1; }
+    const bn_hparams &h = e.plan.hp;
+    int n_attn = 0, n_gdn = 0;
+    for (int b = 0; b < h.n_layer; ++b) (b % h.attn_interval == h.attn_interval - 1 ? n_attn : n_gdn)++;
+    int mask = 0;
+    std::vector<uint8_t> a, b;
+    auto same = [&](int what, int index, size_t bytes, int bit) {
+        a.resize(bytes); b.resize(bytes);
+        if (bn_model_read(e.model, what, index, a.data(), bytes) || bn_model_read(ref.model, what, index, b.data(), bytes)) { mask |= 1 << 7; return; }
+        if (memcmp(a.data(), b.data(), bytes) != 0) mask |= 1 << bit;
+    };
+    same(BN_READ_LOGITS, 0, size_t(h.vocab) * 4, 0);
+    {
+        const float *l = reinterpret_cast<const float *>(a.data());
+        for (int i = 0; i < h.vocab; ++i) if (!std::isfinite(l[i])) { mask |= 1 << 5; break; }
+    }
+    same(BN_READ_RESIDUAL, 0, size_t(h.hidden) * 4, 1);
+    const size_t kvn = size_t(h.cap) * h.n_kv * h.head_dim, row = size_t(h.n_kv) * h.head_dim;
+    for (int l = 0; l < n_attn; ++l) {
+        same(BN_READ_K_DATA, l, kvn, 2);
+        for (size_t i = prompt.size() * row; i < kvn; ++i) if (a[i]) { mask |= 1 << 4; break; }
+        same(BN_READ_K_SCALE, l, kvn / 32 * 2, 2);
+        same(BN_READ_V_DATA, l, kvn, 2);
+        for (size_t i = prompt.size() * row; i < kvn; ++i) if (a[i]) { mask |= 1 << 4; break; }
+        same(BN_READ_V_SCALE, l, kvn / 32 * 2, 2);
+    }
+    const size_t state = size_t(h.gdn_heads) * h.gdn_dim * h.gdn_dim * 4;
+    const size_t taps = size_t(2 * h.gdn_qk_heads * h.gdn_dim + h.gdn_heads * h.gdn_dim) * 3 * 4;
+    for (int l = 0; l < n_gdn; ++l) { same(BN_READ_GDN_STATE, l, state, 3); same(BN_READ_CONV_HIST, l, taps, 3); }
+    bn_model_destroy(ref.model);
+    bn_free(e.ctx, ref.weights);
+    return mask;
+}
+
+}  // namespace
+
+int main(int argc, char **argv) {
+    if (argc < 3) {
+        fprintf(stderr, "usage: %s <model.gguf> info | run [n_gen]\n", argv[0]);
+        return 2;
+    }
+    const char *path = argv[1];
+    const std::string mode = argv[2];
+    std::string why;
+    bh::Gguf g;
+    double t0 = now_ms();
+    if (!bh::gguf_load(path, g, why)) return fail(3, why);
+    const char *cap_s = getenv("BONSAI_CAP");
+    const int cap = cap_s ? atoi(cap_s) : 4096;
+    bh::Engine e;
+    const int prc = bh::plan_build(g, e.plan, cap, why);
+    uint64_t n_ptq = 0, b_ptq = 0, n_f32 = 0, b_f32 = 0;
+    for (const bh::Tensor &t : g.tensors) { if (t.dtype == 143) { ++n_ptq; b_ptq += t.bytes; } else { ++n_f32; b_f32 += t.bytes; } }
+    if (mode == "info") {
+        printf("gguf v%u, %zu tensors: %llu PTQ1_0 (%.3f GB) + %llu f32 (%.1f MB), data at %llu, alignment %u\n", g.version,
+               g.tensors.size(), (unsigned long long)n_ptq, b_ptq / 1e9, (unsigned long long)n_f32, b_f32 / 1e6,
+               (unsigned long long)g.data_start, g.alignment);
+        if (prc) return fail(prc, why);
+        const bn_hparams &h = e.plan.hp;
+        printf("n_layer %d hidden %d ffn %d vocab %d heads %d/%d x %d rot %d interval %d gdn %d/%d x %d hat_block %d signs %zu\n", h.n_layer,
+               h.hidden, h.ffn, h.vocab, h.n_head, h.n_kv, h.head_dim, h.n_rot, h.attn_interval, h.gdn_heads, h.gdn_qk_heads, h.gdn_dim,
+               h.hat_block, e.plan.signs.size());
+        return 0;
+    }
+    if (mode != "run") return fail(2, "unknown mode " + mode);
+    if (prc) return fail(prc, why);                       // rotation gate and contract: before any GPU work
+    if (cap <= 0 || (cap & 1)) return fail(4, "BONSAI_CAP must be a positive even number of positions");
+    const int n_gen = argc > 3 ? atoi(argv[3]) : 48;
+    if (n_gen < 1) return fail(2, "n_gen must be >= 1");
+    const char *ids_s = getenv("BONSAI_PROMPT_IDS");
+    const std::vector<int> prompt = parse_ids(ids_s ? ids_s : "1,2,3,4,5,6,7,8");
+    if (prompt.empty()) return fail(2, "BONSAI_PROMPT_IDS holds no token id");
+    for (int id : prompt) if (id < 0 || id >= e.plan.hp.vocab) return fail(2, "prompt id " + std::to_string(id) + " is outside the vocabulary");
+    if (int(prompt.size()) + n_gen > cap)
+        return fail(7, "prompt (" + std::to_string(prompt.size()) + ") + generation (" + std::to_string(n_gen) + ") does not fit the KV capacity " + std::to_string(cap));
+
+    const char *dev_s = getenv("BONSAI_DEVICE");
+    if (bn_init(dev_s ? atoi(dev_s) : 0, &e.ctx)) return fail(3, bn_last_error());
+    int rc = bh::engine_load(e, path, g, 64u << 20, why);
+    if (rc) return fail(rc, why);
+    e.load_ms = now_ms() - t0;
+    printf("loaded %zu tensors (%.3f GB) in %.1f ms\n", g.tensors.size(), (b_ptq + b_f32) / 1e9, e.load_ms);
+
+    t0 = now_ms();
+    int next = -1;
+    for (size_t i = 0; i < prompt.size(); ++i)
+        if (bn_model_token(e.model, prompt[i], int(i), -1, i + 1 == prompt.size() ? &next : nullptr)) return fail(3, bn_last_error());
+    if (bn_sync(e.ctx)) return fail(3, bn_last_error());
+    const double prefill_ms = now_ms() - t0;
+    printf("prefill: %zu tokens in %.1f ms (%.2f ms/token, token-serial)\n", prompt.size(), prefill_ms, prefill_ms / prompt.size());
+
+    if (getenv("BONSAI_QCHECK")) {
+        const int mask = lineage_gate(e, g, path, prompt, why);
+        if (mask < 0) return fail(3, "gate could not run: " + why);
+        printf("gate: %s (bitmask %d = A logits, A2 residual, A3 KV bytes, A4 recurrent state, B dead slots, C finite)\n", mask ? "FAIL" : "PASS", mask);
+        if (mask) { fprintf(stderr, "REFUSING TO GENERATE\n"); return 6; }
+    }
+
+    std::vector<int> out(n_gen);
+    out[0] = next;
+    t0 = now_ms();
+    double t_first = 0;
+    if (getenv("BONSAI_STEPWISE")) {
+        for (int i = 1; i < n_gen; ++i) {
+            if (bn_model_token(e.model, out[i - 1], int(prompt.size()) + i - 1, -1, &out[i])) return fail(3, bn_last_error());
+            if (i == 1) t_first = now_ms() - t0;
+        }
+    } else if (n_gen > 1) {
+        // one warm call captures the token graph; it also produces the second token
+        if (bn_model_decode(e.model, out[0], int(prompt.size()), 1, &out[1])) return fail(3, bn_last_error());
+        t_first = now_ms() - t0;
+        if (n_gen > 2 && bn_model_decode(e.model, out[1], int(prompt.size()) + 1, n_gen - 2, &out[2])) return fail(3, bn_last_error());
+    }
+    const double gen_ms = now_ms() - t0;
+    printf("ids:");
+    for (int id : out) printf(" %d", id);
+    printf("\n");
+    printf("%d generated tokens in %.1f ms  ->  %.2f tok/s\n", n_gen, gen_ms + prefill_ms / prompt.size(), n_gen * 1e3 / (gen_ms + prefill_ms / prompt.size()));
+    if (n_gen > 2) printf("steady-state: %.3f ms/token\n", (gen_ms - t_first) / (n_gen - 2));
+    printf("launches: %llu\n", (unsigned long long)bn_launch_count(e.ctx));
+    bn_model_destroy(e.model);
+    bn_free(e.ctx, e.weights);
+    bn_destroy(e.ctx);
+    return 0;
+}

@@ -1,0 +1,126 @@
+"""The C++ host: GGUF reader, hyper-parameter / prism.hadamard contract and its exit codes (reference behaviour:
+runtime_vk/bonsai_gguf.h:72-155, bonsai_model.h:642-912, bonsai_forward.h:2725-2775,3260-3290), and on a GPU the
+`run` mode end to end: loader -> prefill -> device-chained greedy decode -> token ids equal to the CPU checker's,
+lineage gate PASS, file order irrelevant."""
+import os
+import re
+import struct
+import subprocess
+
+import numpy as np
+import pytest
+
+from bonsai_vk_b200 import build, gguf_writer, synth
+
+
+@pytest.fixture(scope="module")
+def exe():
+    build.build_lib()
+    return build.build_host()
+
+
+@pytest.fixture(scope="module")
+def files(tmp_path_factory):
+    d = tmp_path_factory.mktemp("gguf")
+    hp = synth.tiny()
+    out = {"hp": hp}
+    for tag, kw in [("ok", {}), ("sorted", {"shuffle": True}), ("norot", {"hat_version": 0}), ("absent", {"hat_version": None}),
+                    ("v2", {"hat_version": 2}), ("q4", {"override_dtype": {"blk.0.ffn_up.weight": 2}})]:
+        p = str(d / f"{tag}.gguf")
+        gguf_writer.write(p, hp, seed=1, **kw)
+        out[tag] = p
+    return out
+
+
+def run(exe, *args, env=None):
+    e = dict(os.environ)
+    e.update(env or {})
+    return subprocess.run([exe, *args], capture_output=True, text=True, env=e, timeout=600)
+
+
+def test_info_reports_the_metadata(exe, files):
+    r = run(exe, files["ok"], "info")
+    assert r.returncode == 0, r.stderr
+    hp = files["hp"]
+    assert "56 tensors: 27 PTQ1_0" in r.stdout and "29 f32" in r.stdout
+    assert f"n_layer {hp.n_layer} hidden {hp.hidden} ffn {hp.ffn} vocab {hp.vocab}" in r.stdout
+    assert f"hat_block {hp.hat_block} signs {hp.hidden + hp.ffn}" in r.stdout
+
+
+def test_rotation_gate_refuses_before_gpu_work(exe, files):
+    for tag in ("norot", "absent"):
+        r = run(exe, files[tag], "run")
+        assert r.returncode == 6 and "refusing" in r.stderr
+    r = run(exe, files["v2"], "run")
+    assert r.returncode == 2 and "only version 1" in r.stderr
+
+
+def test_capacity_and_context_guards(exe, files):
+    assert run(exe, files["ok"], "run", env={"BONSAI_CAP": "7"}).returncode == 4
+    r = run(exe, files["ok"], "run", "100", env={"BONSAI_CAP": "64"})
+    assert r.returncode == 7 and "does not fit" in r.stderr
+    assert run(exe, files["ok"], "run", env={"BONSAI_PROMPT_IDS": "5,999999"}).returncode == 2
+
+
+def test_foreign_dtype_and_broken_files(exe, files, tmp_path):
+    r = run(exe, files["q4"], "info")
+    assert r.returncode == 3 and "neither PTQ1_0 (143) nor f32 (0)" in r.stderr
+    bad = tmp_path / "bad.gguf"
+    bad.write_bytes(b"GGML" + b"\0" * 64)
+    assert run(exe, str(bad), "info").returncode == 3
+    whole = open(files["ok"], "rb").read()
+    cut = tmp_path / "cut.gguf"
+    cut.write_bytes(whole[:2000])
+    assert run(exe, str(cut), "info").returncode == 3
+    # K not a multiple of 128 on a PTQ1_0 tensor
+    odd = tmp_path / "odd.gguf"
+    name = b"w"
+    head = b"GGUF" + struct.pack("<IQQ", 3, 1, 0) + struct.pack("<Q", 1) + name + struct.pack("<IQQIQ", 2, 100, 4, 143, 0)
+    odd.write_bytes(head + b"\0" * 256)
+    r = run(exe, str(odd), "info")
+    assert r.returncode == 3 and "multiple of 128" in r.stderr
+
+
+def test_missing_key_names_the_key(exe, files, tmp_path):
+    whole = open(files["ok"], "rb").read()
+    broken = tmp_path / "nokey.gguf"
+    broken.write_bytes(whole.replace(b"qwen35.ssm.group_count", b"qwen35.ssm.group_c0unt"))
+    r = run(exe, str(broken), "info")
+    assert r.returncode == 2 and "qwen35.ssm.group_count is missing" in r.stderr
+
+
+def _ids(stdout):
+    m = re.search(r"^ids:(.*)$", stdout, re.M)
+    return [int(x) for x in m.group(1).split()]
+
+
+@pytest.mark.gpu
+def test_run_matches_the_checker_and_passes_the_gate(exe, files):
+    from tests._oracle import OracleModel
+
+    hp = files["hp"]
+    tensors, signs = synth.make_model(hp, seed=1)
+    om = OracleModel(hp, tensors, signs)
+    prompt = [3, 77, 1500, 12, 900, 41, 7, 2047]
+    want, logits = [], None
+    for pos, t in enumerate(prompt):
+        logits, _ = om.token(t, pos)
+    tok = om.argmax(logits)
+    for i in range(24):
+        want.append(tok)
+        logits, _ = om.token(tok, len(prompt) + i)
+        tok = om.argmax(logits)
+    om.close()
+    env = {"BONSAI_PROMPT_IDS": ",".join(map(str, prompt)), "BONSAI_CAP": "64", "BONSAI_QCHECK": "1"}
+    r = run(exe, files["ok"], "run", "24", env=env)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "gate: PASS (bitmask 0 =" in r.stdout
+    assert re.search(r"24 generated tokens in [\d.]+ ms  ->  [\d.]+ tok/s", r.stdout)
+    assert re.search(r"steady-state: [\d.]+ ms/token", r.stdout)
+    assert _ids(r.stdout) == want
+    # name-sorted file order (as real checkpoints are stored) and the stepwise loop give the same stream
+    env.pop("BONSAI_QCHECK")
+    env["BONSAI_STEPWISE"] = "1"
+    r2 = run(exe, files["sorted"], "run", "24", env=env)
+    assert r2.returncode == 0, r2.stdout + r2.stderr
+    assert _ids(r2.stdout) == want
