@@ -1,0 +1,90 @@
+// gemm_abi.cu - C entry points of the multi-column tensor-core projection (declared in include/bonsai_cuda.h).
+#include "gemm_tc.cuh"
+
+#include <cstdio>
+#include <cstdlib>
+
+extern "C" {
+
+size_t bn_gemm_image_bytes(int K, int ncol) {
+    if (K <= 0 || K % 128 || ncol < 1 || ncol > bnk::GEMM_MAX_COLS) return 0;
+    return bnk::gemm_image_bytes(K, ncol);
+}
+
+int bn_gemm_act_quant(bn_ctx *ctx, const bn_buf *x, size_t x_off, size_t x_stride, int K, int ncol, const bn_buf *signs,
+                      size_t signs_off, int hat_block, bn_buf *image, size_t image_off) {
+    BN_REQUIRE(ctx, BN_ERR_ARG, "bn_gemm_act_quant: null context");
+    BN_REQUIRE(K > 0 && K % 1024 == 0, BN_ERR_ARG, "bn_gemm_act_quant: K=%d must be a multiple of 1024", K);
+    BN_REQUIRE(ncol >= 1 && ncol <= bnk::GEMM_MAX_COLS, BN_ERR_ARG, "bn_gemm_act_quant: %d columns (1..%d)", ncol, bnk::GEMM_MAX_COLS);
+    BN_REQUIRE(x_stride >= size_t(K), BN_ERR_ARG, "bn_gemm_act_quant: column stride %zu is shorter than K", x_stride);
+    BN_RANGE(x, x_off, (size_t(ncol - 1) * x_stride + K) * 4, 4, "bn_gemm_act_quant x");
+    BN_RANGE(image, image_off, bnk::gemm_image_bytes(K, ncol), 128, "bn_gemm_act_quant image");
+    if (signs) {
+        BN_REQUIRE(hat_block >= 32 && hat_block <= 4096 && (hat_block & (hat_block - 1)) == 0 && K % hat_block == 0, BN_ERR_ARG,
+                   "bn_gemm_act_quant: hadamard block %d must be a power of two in [32, 4096] dividing K", hat_block);
+        BN_RANGE(signs, signs_off, size_t(K) * 4, 4, "bn_gemm_act_quant signs");
+    }
+    bnk::PrepArgs a = {};
+    a.x = bn_ptr<float>(x, x_off); a.x_stride = x_stride;
+    a.signs = signs ? bn_ptr<int32_t>(signs, signs_off) : nullptr;
+    a.K = K; a.hat_block = hat_block; a.ncol = ncol; a.image = bn_ptr<uint8_t>(image, image_off); a.mode = bnk::PREP_PLAIN;
+    bnk::prep_cols(ctx->stream, a);
+    return bn_launch_check(ctx, "k_prep_cols");
+}
+
+size_t bn_gemm_tiled_bytes(int M, int K) {
+    if (M <= 0 || K <= 0 || K % 1024) return 0;
+    return bnk::gemm_tiled_bytes(M, K);
+}
+
+int bn_gemm_repack(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, bn_buf *tiled, size_t tiled_off) {
+    BN_REQUIRE(ctx, BN_ERR_ARG, "bn_gemm_repack: null context");
+    BN_REQUIRE(M > 0 && K > 0 && K % 1024 == 0, BN_ERR_ARG, "bn_gemm_repack: bad shape M=%d K=%d (K %% 1024 != 0)", M, K);
+    BN_RANGE(w, w_off, size_t(M) * (K / 128) * 28, 4, "bn_gemm_repack W");
+    BN_RANGE(tiled, tiled_off, bnk::gemm_tiled_bytes(M, K), 128, "bn_gemm_repack out");
+    bnk::repack_tiles(ctx->stream, bn_ptr<uint32_t>(w, w_off), M, K, bn_ptr<uint32_t>(tiled, tiled_off));
+    return bn_launch_check(ctx, "k_repack_tiles");
+}
+
+int bn_gemm_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int w_tiled, int M, int K, const bn_buf *image, size_t image_off, int ncol,
+                bn_buf *out, size_t out_off, size_t out_stride) {
+    BN_REQUIRE(ctx, BN_ERR_ARG, "bn_gemm_q81: null context");
+    BN_REQUIRE(bnk::gemm_supported(M, K, ncol), BN_ERR_ARG, "bn_gemm_q81: unsupported shape M=%d K=%d columns=%d (K %% 1024 == 0, 1..%d columns)",
+               M, K, ncol, bnk::GEMM_MAX_COLS);
+    BN_REQUIRE(out_stride >= size_t(M), BN_ERR_ARG, "bn_gemm_q81: column stride %zu is shorter than M", out_stride);
+    if (w_tiled) BN_RANGE(w, w_off, bnk::gemm_tiled_bytes(M, K), 128, "bn_gemm_q81 W (tiled)");
+    else BN_RANGE(w, w_off, size_t(M) * (K / 128) * 28, 16, "bn_gemm_q81 W");
+    BN_RANGE(image, image_off, bnk::gemm_image_bytes(K, ncol), 128, "bn_gemm_q81 image");
+    BN_RANGE(out, out_off, (size_t(ncol - 1) * out_stride + M) * 4, 4, "bn_gemm_q81 out");
+    bnk::GemmArgs a = {};
+    a.W = bn_ptr<uint8_t>(w, w_off); a.M = M; a.K = K; a.tiled = w_tiled ? 1 : 0;
+    a.image = bn_ptr<uint8_t>(image, image_off); a.ncol = ncol;
+    a.out = bn_ptr<float>(out, out_off); a.out_stride = out_stride;
+    a.err = ctx->err_dev;
+    // profiling aid: BONSAI_GEMM_PROF=1 prints where the roles of CTA 0 spent their cycles (waiting vs working)
+    static const bool want_prof = getenv("BONSAI_GEMM_PROF") != nullptr;
+    long long *prof = nullptr;
+    if (want_prof) {
+        BN_CUDA(cudaMalloc(&prof, 12 * sizeof(long long)));
+        BN_CUDA(cudaMemsetAsync(prof, 0, 12 * sizeof(long long), ctx->stream));
+        a.prof = prof;
+    }
+    cudaError_t e = bnk::launch_gemm(ctx->stream, ctx->sm_count, a, false);
+    if (e != cudaSuccess) return bn_cuda_fail(e, "k_ptq_gemm_tc");
+    // timing aid: BONSAI_GEMM_REPS=n repeats the launch n-1 more times (same result) so that a host loop in an
+    // interpreted language does not become the bottleneck when small shapes are timed
+    static const int reps = getenv("BONSAI_GEMM_REPS") ? atoi(getenv("BONSAI_GEMM_REPS")) : 1;
+    for (int r = 1; r < reps; ++r) bnk::launch_gemm(ctx->stream, ctx->sm_count, a, false);
+    if (want_prof) {
+        long long h[12];
+        BN_CUDA(cudaStreamSynchronize(ctx->stream));
+        BN_CUDA(cudaMemcpy(h, prof, sizeof h, cudaMemcpyDeviceToHost));
+        cudaFree(prof);
+        fprintf(stderr, "gemm prof (cycles, CTA 0): decode[wait full %lld, unpack %lld, publish %lld, wait slot %lld] "
+                        "mma[wait full %lld, wait A %lld, wait D %lld] epilogue[wait D %lld, wait ld %lld, combine %lld]\n",
+                h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[8], h[9], h[10]);
+    }
+    return bn_launch_check(ctx, "k_ptq_gemm_tc");
+}
+
+}  // extern "C"

@@ -1,0 +1,600 @@
+// gemm_tc.cu - multi-column PTQ1_0 x q8_1 projection on tcgen05 (see gemm_tc.cuh).
+//
+// Arithmetic (reference: _mul_mat_vecq_ptq1_0.comp:92-202 per column; multi-column shader :204-347): for every
+// row, column and 128-weight block the four integer sub-block dots I_sb = sum code * q (code = trit + 1 in
+// {0,1,2}, q = int8 activation code) are exact; they are combined exactly as the single-column kernel does:
+// t_sb = fma(d_sb, float(I_sb), -s_sb); v = d_w * ((t0 + t1) + (t2 + t3)); blocks are added in groups of four,
+// (v0 + v1) + (v2 + v3), groups in ascending order. A column of this kernel is therefore bit-identical to the
+// single-column projection of the same activation vector.
+//
+// One CTA owns tiles of 128 rows over all of K. Per 128-weight block of the tile:
+//   producer warp   bulk-copies the rows' PTQ1_0 bytes and the activation image of 8 blocks into a ring stage
+//   4 decode warps  (lane = row) unpack 5 trits per byte with the multiply-by-3 chain on byte pairs held in the
+//                   16-bit halves of a register, and store the 128 codes as the A operand into tensor memory
+//   4 MMA threads   issue one tcgen05.mma.kind::i8 each (M=128, N=columns, K=32: one per sub-block), A from tensor
+//                   memory, B = the int8 codes in shared memory, D = int32 in tensor memory
+//   8 epilogue warps read D with tcgen05.ld and do the fp32 combination for their row and half of the columns
+// Every wait is bounded: on giving up the kernel records it in the error word and drains.
+#include "gemm_tc.cuh"
+
+#include <algorithm>
+
+namespace {
+
+using namespace bnk;
+
+#ifndef GEMM_BK
+#define GEMM_BK 8
+#endif
+constexpr int BK = GEMM_BK;                 // blocks per ring stage
+constexpr int ROWP = BK * 28 + 16;         // shared-memory pitch of a row's BK*28 bytes
+constexpr int WBYTES = 128 * ROWP;
+constexpr int TBYTES = BK * 7 * 128 * 4;     // one stage of repacked weights: [block][word][row] dwords
+constexpr int A_COL = 0;                   // tensor-memory columns: NA operand slots x 32, then ND accumulator slots x 4*NCP
+constexpr int DWS = 16;                    // ring of per-row block scales handed from the decode warps to the epilogue
+constexpr uint32_t MAGIC = 0x4B400000u;    // float 12582912.0: adding an int |i| < 2^22 to its bits gives the float 12582912 + i
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t *b, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+// Bounded wait. try_wait suspends the thread until the phase completes or the time hint (ns) runs out, so a waiting
+// warp does not take issue slots from the warps that are working; after ~0.5 s in total it gives up and records it.
+__device__ __forceinline__ bool mbar_wait(uint64_t *b, uint32_t parity, int *err, volatile int *abort_flag) {
+    const uint32_t addr = smem_u32(b);
+    for (int it = 0; it < (1 << 16); ++it) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(addr), "r"(parity), "r"(8000u) : "memory");
+        if (ok) return true;
+        if ((it & 63) == 63 && *abort_flag) return false;
+    }
+    if (err) atomicExch(err, 2);
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void bulk_copy(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[128 x N] (+)= A[128 x 32] (u8, tensor memory) x B[N x 32] (s8, shared memory descriptor)
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}\n"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// shared-memory operand descriptor: K-major, no swizzle; lbo = byte distance between the two 16-byte k-halves,
+// sbo = byte distance between groups of 8 rows
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    return uint64_t((saddr >> 4) & 0x3FFFu) | (uint64_t((lbo >> 4) & 0x3FFFu) << 16) | (uint64_t((sbo >> 4) & 0x3FFFu) << 32) |
+           (uint64_t(1) << 46);
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+                   "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+template <int N> __device__ __forceinline__ void tmem_fill(uint32_t taddr, uint32_t v);
+template <> __device__ __forceinline__ void tmem_fill<4>(uint32_t taddr, uint32_t v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %1, %1, %1};" ::"r"(taddr), "r"(v) : "memory");
+}
+template <> __device__ __forceinline__ void tmem_fill<8>(uint32_t taddr, uint32_t v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(v) : "memory");
+}
+template <int N> __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t *r);
+template <> __device__ __forceinline__ void tmem_ld<4>(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
+}
+template <> __device__ __forceinline__ void tmem_ld<8>(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr) : "memory");
+}
+
+// Four packed bytes (5 trits each) -> five dwords of codes: o[t*stride] = codes at level t of the four bytes, in byte
+// order. T_t = (b * 3^(t+1)) >> 8 is the running base-3 prefix of byte b, and trit_t + 1 = T_t - 3 * T_(t-1)
+// (the reference decoder's v = (v*3) & 0xFF; trit = (v*3) >> 8, unrolled). The even and odd bytes sit in the 16-bit
+// halves of two registers, so one multiply serves two bytes; PRMT gathers the four T bytes of a level, and because
+// every byte of T_t - 3 * T_(t-1) lies in 0..2 the subtraction can be done on the whole dword at once.
+__device__ __forceinline__ void decode4(uint32_t w, uint32_t *o, int stride) {
+    const uint32_t e = __byte_perm(w, 0u, 0x4240u), d = __byte_perm(w, 0u, 0x4341u);
+    const uint32_t t0 = __byte_perm(e * 3u, d * 3u, 0x7351u);
+    const uint32_t t1 = __byte_perm(e * 9u, d * 9u, 0x7351u);
+    const uint32_t t2 = __byte_perm(e * 27u, d * 27u, 0x7351u);
+    const uint32_t t3 = __byte_perm(e * 81u, d * 81u, 0x7351u);
+    const uint32_t t4 = __byte_perm(e * 243u, d * 243u, 0x7351u);
+    o[0] = t0;
+    o[stride] = t1 - 3u * t0;
+    o[2 * stride] = t2 - 3u * t1;
+    o[3 * stride] = t3 - 3u * t2;
+    o[4 * stride] = t4 - 3u * t3;
+}
+// one block's 28 bytes (7 dwords) -> 32 dwords of codes in element order
+__device__ __forceinline__ void decode_block(const uint32_t (&r)[7], uint32_t (&o)[32]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) decode4(r[i], o + i, 4);           // elements 16t + 4i .. : dword 4t + i
+    decode4(r[4], o + 20, 2);                                      // elements 80 + 8t + 0..3 : dword 20 + 2t
+    decode4(r[5], o + 21, 2);                                      // elements 80 + 8t + 4..7 : dword 21 + 2t
+    const uint32_t v = __byte_perm(r[6], 0u, 0x4140u);             // bytes 24, 25 (4 trits each) in the two halves
+    const uint32_t ta = __byte_perm(v * 3u, v * 9u, 0x7531u);      // [T0(24), T0(25), T1(24), T1(25)]
+    const uint32_t tb = __byte_perm(v * 27u, v * 81u, 0x7531u);    // [T2(24), T2(25), T3(24), T3(25)]
+    o[30] = ta - 3u * (ta << 16);                                  // elements 120..123
+    o[31] = tb - 3u * __byte_perm(ta, tb, 0x5432u);                // elements 124..127
+}
+
+// optional cycle accounting of CTA 0 (GemmArgs::prof != null): where each role's time goes
+#define PROF_T0() const long long prof_t0 = a.prof ? clock64() : 0
+#define PROF_ADD(slot) do { if (a.prof) prof[slot] += clock64() - prof_t0; } while (0)
+
+template <int NCP> struct Cfg {
+    static constexpr int BBYTES = BK * NCP * 160;
+    static constexpr int STAGE = WBYTES + BBYTES;
+    static constexpr int STAGES = BK == 8 ? (NCP == 32 ? 3 : 4) : 2;
+    static constexpr int EW = 8;                      // epilogue warps
+    static constexpr int NCW = NCP / (EW / 4);        // columns per epilogue warp
+    static constexpr int CH = 4;                      // columns per tensor-memory load (x 4 sub-blocks = 16 registers)
+    static constexpr int NCH = NCW / CH;
+    static constexpr int DW = 4;                      // decode warps (one per quarter of the rows)
+    static constexpr int NWARPS = DW + EW + 1 + 4;    // decode, epilogue, producer, 4 MMA issuers (one per sub-block)
+    // slots in flight: the hops decode -> MMA -> commit -> epilogue -> slot free each cost a few hundred cycles, so
+    // several blocks must be in flight to keep the decode and epilogue warps busy
+    // operand slot i and accumulator slot i belong to the same block, so one "done" barrier per slot (armed by the
+    // MMA issuers' commits) tells the epilogue that the accumulators are ready and the decode warps that the operand
+    // slot may be overwritten
+    static constexpr int NA = NCP == 8 ? 8 : (NCP == 16 ? 4 : 3);
+    static constexpr int ND = NA;
+    static constexpr int D_COL = NA * 32;
+    static constexpr int TMEM_COLS = 512;
+    static_assert(D_COL + ND * 4 * NCP <= 512 && NA + ND <= DWS, "tensor memory budget");
+    static constexpr size_t SMEM = size_t(STAGES) * STAGE + DWS * 128 * 4 + 512;
+};
+
+template <int NCP>
+__global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const GemmArgs a) {
+    using C = Cfg<NCP>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char *ring = smem;
+    float *dwv = reinterpret_cast<float *>(smem + size_t(C::STAGES) * C::STAGE);      // [DWS][128] block scales of the rows
+    uint64_t *bars = reinterpret_cast<uint64_t *>(dwv + DWS * 128);
+    uint64_t *full = bars, *empty = bars + 4, *afull = bars + 8, *dfull = bars + 24, *dempty = bars + 32;
+    uint64_t *aempty = dfull;                      // "done": all four sub-block MMAs of the slot's block have completed
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 40);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    constexpr int NA = C::NA, ND = C::ND, D_COL = C::D_COL, EW = C::EW, DW = C::DW;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nb = a.K / 128, nkc = nb / BK, ntiles = (a.M + 127) / 128;
+    const size_t rowbytes = size_t(nb) * 28;
+
+    if (tid == 0) {
+        for (int i = 0; i < C::STAGES; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, EW); }
+        for (int i = 0; i < NA; ++i) { mbar_init(afull + i, 4); mbar_init(dfull + i, 4); mbar_init(dempty + i, EW); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(uint32_t(C::TMEM_COLS)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tb = *tmem_slot;
+    // everything above overlaps the previous kernel's tail; its results (the activation image) are read below
+    pdl_sync();
+
+    int n_items = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) n_items += nkc;
+
+    if (warp == DW + EW) {
+        // ---- producer ----------------------------------------------------------------------------------
+        int s = 0, ph = 1;                         // a fresh barrier passes a wait on parity 1
+        for (int t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x)
+            for (int kc = 0; kc < nkc; ++kc) {
+                if (!mbar_wait(empty + s, ph, a.err, abort_flag)) break;
+                unsigned char *st = ring + size_t(s) * C::STAGE;
+                if (a.tiled) {                      // repacked weights: the stage is one contiguous piece
+                    if (lane == 0) {
+                        mbar_expect_tx(full + s, TBYTES + C::BBYTES);
+                        bulk_copy(st, a.W + (size_t(t) * nkc + kc) * TBYTES, TBYTES, full + s);
+                    }
+                } else {
+                    if (lane == 0) mbar_expect_tx(full + s, 128 * (BK * 28) + C::BBYTES);
+                    __syncwarp();
+#pragma unroll
+                    for (int r = lane; r < 128; r += 32) {
+                        const int grow = min(t * 128 + r, a.M - 1);
+                        bulk_copy(st + r * ROWP, a.W + size_t(grow) * rowbytes + size_t(kc) * (BK * 28), BK * 28, full + s);
+                    }
+                }
+                if (lane == 0) bulk_copy(st + WBYTES, a.image + size_t(kc) * C::BBYTES, C::BBYTES, full + s);
+                if (++s == C::STAGES) { s = 0; ph ^= 1; }
+            }
+    } else if (warp > DW + EW) {
+        // ---- MMA issue: thread sb of four issues the sub-block's MMA of every block (an issue costs the thread ~55
+        //      cycles whatever its size, so the four go out in parallel) --------------------------------------------
+        if (lane == 0) {
+            const int sb = warp - (DW + EW + 1);
+            // D s32, A u8, B s8, both K-major, N = NCP, M = 128
+            const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (uint32_t(NCP >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+            const uint32_t LBO = (NCP / 8) * 128, SBO = 128;
+            bool ok = true;
+            int s = 0, sph = 0, slot = 0, aph = 0, dph = 1;
+            long long prof[4] = {0, 0, 0, 0};
+            for (int it = 0; it < n_items && ok; ++it) {
+                { PROF_T0(); if (!mbar_wait(full + s, sph, a.err, abort_flag)) break; PROF_ADD(0); }
+                const uint32_t bbase = smem_u32(ring + size_t(s) * C::STAGE + WBYTES) + sb * (NCP * 32);
+                for (int j = 0; j < BK; ++j) {
+                    { PROF_T0(); if (!mbar_wait(afull + slot, aph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(1); }
+                    { PROF_T0(); if (!mbar_wait(dempty + slot, dph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(2); }
+                    tc_fence_after();
+                    tc_mma_i8(tb + D_COL + slot * 4 * NCP + sb * NCP, tb + A_COL + slot * 32 + sb * 8,
+                              smem_desc(bbase + j * (NCP * 160), LBO, SBO), idesc, 0u);
+                    tc_commit(dfull + slot);
+                    if (++slot == NA) { slot = 0; aph ^= 1; dph ^= 1; }
+                }
+                if (++s == C::STAGES) { s = 0; sph ^= 1; }
+            }
+            if (a.prof && blockIdx.x == 0 && sb == 0) for (int i = 0; i < 4; ++i) a.prof[4 + i] = prof[i];
+        }
+    } else if (warp < DW) {
+        // ---- decode ------------------------------------------------------------------------------------
+        const int q = warp & 3, row = q * 32 + lane;
+        const uint32_t lane_base = uint32_t(q * 32) << 16;
+        bool ok = true;
+        int pending = -1;                          // slot whose tensor-memory store is in flight
+        auto publish = [&]() {                     // the store of `pending` is complete: hand the slot to the MMA thread
+            if (pending < 0) return;
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(afull + pending);
+            pending = -1;
+        };
+        int s = 0, sph = 0, g = 0;
+        long long prof[4] = {0, 0, 0, 0};
+        for (int it = 0; it < n_items && ok; ++it) {
+            { PROF_T0(); if (!mbar_wait(full + s, sph, a.err, abort_flag)) break; PROF_ADD(0); }
+            const unsigned char *st = ring + size_t(s) * C::STAGE;
+#pragma unroll 1
+            for (int j = 0; j < BK; ++j, ++g) {
+                const int slot = g % NA;
+                uint32_t r[7];
+                if (a.tiled) {                      // [block][word][row]: the warp's rows are consecutive dwords
+                    const uint32_t *src = reinterpret_cast<const uint32_t *>(st) + j * 7 * 128 + row;
+#pragma unroll
+                    for (int i = 0; i < 7; ++i) r[i] = src[i * 128];
+                } else {
+                    const uint32_t *src = reinterpret_cast<const uint32_t *>(st + row * ROWP + j * 28);
+#pragma unroll
+                    for (int i = 0; i < 7; ++i) r[i] = src[i];
+                }
+                uint32_t o[32];
+                { PROF_T0(); decode_block(r, o); if (a.prof && o[31] == 0xFFFFFFFFu) prof[3]++; PROF_ADD(1); }
+                { PROF_T0(); publish(); PROF_ADD(2); }   // the previous block's store had this block's arithmetic to finish
+                { PROF_T0(); if (!mbar_wait(aempty + slot, ((g / NA) & 1) ^ 1, a.err, abort_flag)) { ok = false; break; } PROF_ADD(3); }
+                tc_fence_after();
+                const uint32_t ta = tb + lane_base + A_COL + slot * 32;
+                tmem_st16(ta, o);
+                tmem_st16(ta + 16, o + 16);
+                dwv[(g % DWS) * 128 + row] = half_bits_to_float(r[6] >> 16);
+                pending = slot;
+            }
+            if (++s == C::STAGES) { s = 0; sph ^= 1; }
+        }
+        publish();
+        if (a.prof && blockIdx.x == 0 && warp == 0 && lane == 0) for (int i = 0; i < 4; ++i) a.prof[i] = prof[i];
+    } else {
+        // ---- epilogue (warps DW .. DW+EW-1) ------------------------------------------------------------------
+        // unit = (block, chunk of CH columns). The tensor-memory load of the next unit is in flight while this one
+        // is combined. Two cursors walk the blocks in order: one for the loads, one for the arithmetic.
+        const int q = warp & 3, part = (warp - DW) >> 2, row = q * 32 + lane;
+        const uint32_t lane_base = uint32_t(q * 32) << 16;
+        const int c0 = part * C::NCW;
+        constexpr int NCH = C::NCH, NCW = C::NCW;
+        float acc[NCW], u[NCW], ve[NCW];
+#pragma unroll
+        for (int c = 0; c < NCW; ++c) { acc[c] = 0.0f; u[c] = 0.0f; ve[c] = 0.0f; }
+        const int n_blocks = n_items * BK;
+        bool ok = true;
+        long long prof[4] = {0, 0, 0, 0};
+        // load cursor
+        int lg = 0, lds = 0, ldph = 0, lj = 0, ls = 0, lsph = 0;
+        auto issue = [&](int chunk, uint32_t (&buf)[4][C::CH]) {
+            if (lg >= n_blocks || !ok) return;
+            if (chunk == 0) {
+                PROF_T0();
+                if (lj == 0 && !mbar_wait(full + ls, lsph, a.err, abort_flag)) { ok = false; return; }
+                if (!mbar_wait(dfull + lds, ldph, a.err, abort_flag)) { ok = false; return; }
+                tc_fence_after();
+                PROF_ADD(0);
+            }
+#pragma unroll
+            for (int sb = 0; sb < 4; ++sb)
+                tmem_ld<C::CH>(tb + lane_base + D_COL + lds * 4 * NCP + sb * NCP + c0 + chunk * C::CH, buf[sb]);
+            if (chunk == NCH - 1) {
+                ++lg;
+                if (++lds == ND) { lds = 0; ldph ^= 1; }
+                if (++lj == BK) { lj = 0; if (++ls == C::STAGES) { ls = 0; lsph ^= 1; } }
+            }
+        };
+        // arithmetic cursor
+        int cg = 0, cds = 0, cj = 0, cs = 0, cb = 0, ct = blockIdx.x;
+        auto finish = [&](int chunk) {              // the unit's columns are in registers; after the last chunk the slot is free
+            PROF_T0();
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            PROF_ADD(1);
+            if (chunk == NCH - 1) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dempty + cds);
+            }
+        };
+        // the unit's scale pairs (d, s) x 4 sub-blocks x CH columns and the rows' block scale: independent of the
+        // accumulators, so they are fetched before the wait for the tensor-memory load
+        struct Scales { float4 a[C::CH], b[C::CH]; float dw; };
+        auto load_scales = [&](int chunk, Scales &sc) {
+            const unsigned char *scales = ring + size_t(cs) * C::STAGE + WBYTES + cj * (NCP * 160) + NCP * 128 + (c0 + chunk * C::CH) * 32;
+#pragma unroll
+            for (int c = 0; c < C::CH; ++c) {
+                sc.a[c] = *reinterpret_cast<const float4 *>(scales + c * 32);
+                sc.b[c] = *reinterpret_cast<const float4 *>(scales + c * 32 + 16);
+            }
+            sc.dw = dwv[(cg % DWS) * 128 + row];
+        };
+        auto combine = [&](int chunk, uint32_t (&buf)[4][C::CH], const Scales &sc) {
+            PROF_T0();
+            const float dw = sc.dw;
+            const int bi = cb & 3;
+            float v[C::CH];
+#pragma unroll
+            for (int c = 0; c < C::CH; ++c) {       // straight-line: the columns' dependency chains interleave
+                const float4 s01 = sc.a[c], s23 = sc.b[c];
+                const float t0 = fmaf(s01.x, __fsub_rn(__uint_as_float(MAGIC + buf[0][c]), 12582912.0f), -s01.y);
+                const float t1 = fmaf(s01.z, __fsub_rn(__uint_as_float(MAGIC + buf[1][c]), 12582912.0f), -s01.w);
+                const float t2 = fmaf(s23.x, __fsub_rn(__uint_as_float(MAGIC + buf[2][c]), 12582912.0f), -s23.y);
+                const float t3 = fmaf(s23.z, __fsub_rn(__uint_as_float(MAGIC + buf[3][c]), 12582912.0f), -s23.w);
+                v[c] = __fmul_rn(dw, __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3)));
+            }
+            if (bi == 0 || bi == 2) {
+#pragma unroll
+                for (int c = 0; c < C::CH; ++c) ve[chunk * C::CH + c] = v[c];
+            } else if (bi == 1) {
+#pragma unroll
+                for (int c = 0; c < C::CH; ++c) u[chunk * C::CH + c] = __fadd_rn(ve[chunk * C::CH + c], v[c]);
+            } else {
+                const bool first = cb < 4;
+#pragma unroll
+                for (int c = 0; c < C::CH; ++c) {
+                    const int ci = chunk * C::CH + c;
+                    const float p = __fadd_rn(u[ci], __fadd_rn(ve[ci], v[c]));
+                    acc[ci] = first ? p : __fadd_rn(acc[ci], p);
+                }
+            }
+            if (chunk == NCH - 1) {
+                if (cb == nb - 1) {
+                    const int grow = ct * 128 + row;
+                    if (grow < a.M) {
+#pragma unroll
+                        for (int c = 0; c < NCW; ++c) {
+                            if (c0 + c >= a.ncol) continue;
+                            float r = acc[c];
+                            if (a.resid) r = __fadd_rn(r, a.resid[size_t(c0 + c) * a.resid_stride + grow]);
+                            a.out[size_t(c0 + c) * a.out_stride + grow] = r;
+                        }
+                    }
+                }
+                ++cg;
+                if (++cds == ND) cds = 0;
+                if (++cb == nb) { cb = 0; ct += gridDim.x; }
+                if (++cj == BK) {                   // the stage's scales and weights are not needed any more
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty + cs);
+                    cj = 0;
+                    if (++cs == C::STAGES) cs = 0;
+                }
+            }
+            PROF_ADD(2);
+        };
+        uint32_t buf0[4][C::CH], buf1[4][C::CH];
+        Scales sc;
+        issue(0, buf0);
+        if constexpr (NCH == 1) {
+            for (int g = 0; g < n_blocks && ok; g += 2) {
+                load_scales(0, sc); finish(0); issue(0, buf1); combine(0, buf0, sc);
+                if (g + 1 >= n_blocks || !ok) break;
+                load_scales(0, sc); finish(0); issue(0, buf0); combine(0, buf1, sc);
+            }
+        } else {                                    // an even number of chunks per block: the buffers alternate within a block
+            for (int g = 0; g < n_blocks && ok; ++g) {
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch) {
+                    load_scales(ch, sc);
+                    finish(ch);
+                    if (ch & 1) { issue((ch + 1) % NCH, buf0); combine(ch, buf1, sc); }
+                    else { issue((ch + 1) % NCH, buf1); combine(ch, buf0, sc); }
+                }
+            }
+        }
+        if (a.prof && blockIdx.x == 0 && warp == DW && lane == 0) for (int i = 0; i < 4; ++i) a.prof[8 + i] = prof[i];
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tb), "r"(uint32_t(C::TMEM_COLS)) : "memory");
+}
+
+// ---- activation image: [rms norm] -> signs -> Hadamard per hat_block -> q8_1 codes and scales -----------------
+// grid (K / chunk, padded columns), 512 threads; chunk = hat_block (or 1024 without rotation)
+__device__ __forceinline__ float block_tree_sum(float *p, int n) {
+    for (int s = n >> 1; s > 0; s >>= 1) {
+        __syncthreads();
+        if (int(threadIdx.x) < s) p[threadIdx.x] = __fadd_rn(p[threadIdx.x], p[threadIdx.x + s]);
+    }
+    __syncthreads();
+    return p[0];
+}
+
+__global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, int ncp) {
+    pdl_sync();
+    extern __shared__ float s[];                   // chunk floats
+    __shared__ float part[256];
+    const int c = blockIdx.y, tid = threadIdx.x;
+    const size_t base = size_t(blockIdx.x) * chunk;
+    const size_t blk_bytes = size_t(ncp) * 160;
+    if (c >= a.ncol) {                             // padding column: zero codes and scales
+        for (int e = tid * 16; e < chunk; e += 512 * 16) {
+            const size_t b = (base + e) / 128;
+            const int sb = (e & 127) >> 5, kh = (e >> 4) & 1;
+            *reinterpret_cast<uint4 *>(a.image + b * blk_bytes + ((sb * 2 + kh) * (ncp / 8) + c / 8) * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+        }
+        for (int e = tid * 32; e < chunk; e += 512 * 32) {
+            const size_t b = (base + e) / 128;
+            *reinterpret_cast<float2 *>(a.image + b * blk_bytes + size_t(ncp) * 128 + (c * 4 + ((e & 127) >> 5)) * 8) = make_float2(0.0f, 0.0f);
+        }
+        return;
+    }
+    const float *x = a.x + size_t(c) * a.x_stride;
+    float inv = 1.0f;
+    if (a.mode == PREP_NORM) {
+        // same partial sums as the stand-alone norm kernel: 256 lanes, each its consecutive run, then the tree
+        const int per = (a.K + 255) / 256;
+        if (tid < 256) {
+            float acc = 0.0f;
+            for (int i = 0; i < per; ++i) {
+                const int d = tid * per + i;
+                if (d < a.K) { const float v = x[d]; acc = __fadd_rn(acc, __fmul_rn(v, v)); }
+            }
+            part[tid] = acc;
+        }
+        const float ss = block_tree_sum(part, 256);
+        inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, float(a.K)), a.eps)));
+        if (a.inv_out && blockIdx.x == 0 && tid == 0) a.inv_out[size_t(c) * a.inv_stride] = inv;
+    }
+    for (int i = tid; i < chunk; i += 512) {
+        float v = x[base + i];
+        if (a.mode == PREP_NORM) v = __fmul_rn(__fmul_rn(v, inv), a.w[base + i]);
+        if (a.signs) v = __fmul_rn(v, float(a.signs[base + i]));
+        s[i] = v;
+    }
+    if (a.signs) {
+        const float hinv = 1.0f / sqrtf(float(chunk));
+        for (int h = 1; h < chunk; h <<= 1) {
+            __syncthreads();
+            for (int i = tid; i < (chunk >> 1); i += 512) {
+                const int j = ((i & ~(h - 1)) << 1) | (i & (h - 1));
+                const float p = s[j], r = s[j + h];
+                s[j] = __fadd_rn(p, r);
+                s[j + h] = __fsub_rn(p, r);
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < chunk; i += 512) s[i] = __fmul_rn(s[i], hinv);
+    }
+    __syncthreads();
+    // q8_1 per 32 values (a warp): d = amax/127 (0 below 1e-35), q = round-half-away(v/d), s = d * sum(q), both rounded to fp16
+    const int lane = tid & 31;
+    for (int e = tid; e < chunk; e += 512) {
+        const float v = s[e];
+        float amax = fabsf(v);
+#pragma unroll
+        for (int k = 16; k > 0; k >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, k));
+        const float d = amax > 1e-35f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+        const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+        float r = roundf(__fmul_rn(v, id));
+        r = fminf(fmaxf(r, -127.0f), 127.0f);
+        const int qi = int(r);
+        int sum = qi;
+#pragma unroll
+        for (int k = 16; k > 0; k >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, k);
+        const size_t b = (base + e) / 128;
+        const int sb = (e & 127) >> 5, kh = (e >> 4) & 1;
+        unsigned char *blk = a.image + b * blk_bytes;
+        blk[((sb * 2 + kh) * (ncp / 8) + c / 8) * 128 + (c & 7) * 16 + (e & 15)] = uint8_t(int8_t(qi));
+        if (lane == 0) {
+            const float df = half_bits_to_float(float_to_half_bits(d));
+            const float sf = half_bits_to_float(float_to_half_bits(__fmul_rn(d, float(sum))));
+            *reinterpret_cast<float2 *>(blk + size_t(ncp) * 128 + (c * 4 + sb) * 8) = make_float2(df, sf);
+        }
+    }
+}
+
+// native row-major PTQ1_0 -> per (tile of 128 rows, 8 blocks of K): [block][word 0..6][row] dwords; rows beyond M are zero
+__global__ void k_repack_tiles(const uint32_t *__restrict__ W, int M, int nb, uint32_t *__restrict__ out, size_t total) {
+    pdl_sync();
+    const int nkc = nb / BK;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+        const int row = int(i & 127);
+        size_t r = i >> 7;
+        const int k = int(r % 7); r /= 7;
+        const int j = int(r % BK); r /= BK;
+        const int kc = int(r % nkc);
+        const size_t t = r / nkc;
+        const size_t grow = t * 128 + row;
+        out[i] = grow < size_t(M) ? W[grow * (size_t(nb) * 7) + (size_t(kc) * BK + j) * 7 + k] : 0u;
+    }
+}
+
+template <int NCP>
+cudaError_t launch_t(cudaStream_t st, int sm_count, const GemmArgs &a, bool pdl) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(k_ptq_gemm_tc<NCP>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(Cfg<NCP>::SMEM));
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const int ntiles = (a.M + 127) / 128;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ntiles < sm_count ? ntiles : sm_count);
+    cfg.blockDim = dim3(Cfg<NCP>::NWARPS * 32);
+    cfg.dynamicSmemBytes = Cfg<NCP>::SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1 : 0;
+    BN_COUNT(1);
+    return cudaLaunchKernelEx(&cfg, k_ptq_gemm_tc<NCP>, a);
+}
+
+}  // namespace
+
+namespace bnk {
+
+bool gemm_supported(int M, int K, int ncol) {
+    return M >= 1 && K >= 1024 && K % 1024 == 0 && ncol >= 1 && ncol <= GEMM_MAX_COLS;
+}
+
+cudaError_t launch_gemm(cudaStream_t st, int sm_count, const GemmArgs &a, bool pdl) {
+    const int ncp = gemm_padded_cols(a.ncol);
+    if (ncp == 8) return launch_t<8>(st, sm_count, a, pdl);
+    if (ncp == 16) return launch_t<16>(st, sm_count, a, pdl);
+    return launch_t<32>(st, sm_count, a, pdl);
+}
+
+size_t gemm_tiled_bytes(int M, int K) { return size_t((M + 127) / 128) * (K / 128 / BK) * TBYTES; }
+void repack_tiles(cudaStream_t st, const uint32_t *W, int M, int K, uint32_t *out) {
+    const size_t total = gemm_tiled_bytes(M, K) / 4;
+    launch(k_repack_tiles, dim3(unsigned(std::min<size_t>((total + 255) / 256, 148 * 16))), dim3(256), 0, st, W, M, K / 128, out, total);
+}
+
+void prep_cols(cudaStream_t st, const PrepArgs &a) {
+    const int chunk = a.signs ? a.hat_block : 1024;
+    const int ncp = gemm_padded_cols(a.ncol);
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(k_prep_cols, cudaFuncAttributeMaxDynamicSharedMemorySize, 4096 * 4); attr = true; }
+    launch(k_prep_cols, dim3(a.K / chunk, ncp), dim3(512), size_t(chunk) * 4, st, a, chunk, ncp);
+}
+
+}  // namespace bnk

@@ -3,6 +3,7 @@
 #include "ops.cuh"
 
 #include "phase_gemv.cuh"
+#include "gemm_tc.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -60,6 +61,15 @@ struct bn_model {
         int idx;   // index among its kind
     };
     std::vector<Layer> layers;
+    // multi-sequence pass (bn_model_stage_batch): per-column arenas, shared activation images, tile-major weights
+    int ncols = 1;
+    uint8_t *IMG_H = nullptr, *IMG_F = nullptr;
+    uint8_t *tiled = nullptr;
+    struct TiledLayer { const uint8_t *in = nullptr, *out = nullptr, *ffn_in = nullptr, *ffn_down = nullptr; };
+    std::vector<TiledLayer> tl;
+    const uint8_t *t_head = nullptr;
+    std::map<long, cudaGraphExec_t> batch_graphs;   // key = stream0 * 64 + ncol
+    int batch_graph_launches = 0;
     const uint32_t *embd = nullptr, *out_w = nullptr;
     const float *out_norm = nullptr;
 };
@@ -274,6 +284,120 @@ void enqueue_token(bn_model *m, int stop_after, bool want_logits) {
     if (!m->phases_only) bnk::argmax_first(st, m->LOGITS, h.vocab, m->NEXT, m->AMV, m->AMI);
 }
 
+// ---- multi-sequence pass ---------------------------------------------------------------------------------
+// Tile-major copies of the local projection weights (one allocation). Projections that read the same input are
+// stacked into one matrix whatever their placement in memory: every part is a whole number of 128-row tiles.
+int build_batch_side(bn_model *m) {
+    const bn_hparams &h = m->hp;
+    const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D, IN = NH * D;
+    const int QD = h.n_head * h.head_dim, KD = h.n_kv * h.head_dim;
+    BN_REQUIRE(h.batch_cols <= bnk::GEMM_MAX_COLS, BN_ERR_ARG, "bn_model_finalize: batch_cols %d exceeds %d", h.batch_cols, bnk::GEMM_MAX_COLS);
+    BN_REQUIRE(h.hidden % 1024 == 0 && h.ffn % 1024 == 0, BN_ERR_ARG, "bn_model_finalize: the multi-sequence pass needs hidden and ffn to be multiples of 1024");
+    BN_REQUIRE(C % 128 == 0 && IN % 128 == 0 && (2 * QD) % 128 == 0 && KD % 128 == 0 && h.ffn % 128 == 0 && h.hidden % 128 == 0, BN_ERR_ARG,
+               "bn_model_finalize: the multi-sequence pass needs every projection height to be a multiple of 128");
+    struct Part { const uint32_t *w; int M; };
+    struct Group { std::vector<Part> parts; int K; const uint8_t **dst; };
+    std::vector<Group> groups;
+    m->tl.assign(h.n_layer, bn_model::TiledLayer());
+    for (int b = m->b0; b < m->b1; ++b) {
+        const bn_model::Layer &L = m->layers[b];
+        bn_model::TiledLayer &T = m->tl[b];
+        if (L.attn) {
+            groups.push_back({{{L.q_w, 2 * QD}, {L.k_w, KD}, {L.v_w, KD}}, h.hidden, &T.in});
+            groups.push_back({{{L.o_w, h.hidden}}, QD, &T.out});
+        } else {
+            groups.push_back({{{L.qkv, C}, {L.gate_w, IN}}, h.hidden, &T.in});
+            groups.push_back({{{L.ssm_out, h.hidden}}, IN, &T.out});
+        }
+        groups.push_back({{{L.ffn_gate, h.ffn}, {L.ffn_up, h.ffn}}, h.hidden, &T.ffn_in});
+        groups.push_back({{{L.ffn_down, h.hidden}}, h.ffn, &T.ffn_down});
+    }
+    if (m->b1 == h.n_layer) groups.push_back({{{m->out_w, h.vocab}}, h.hidden, &m->t_head});
+    size_t total = 0;
+    for (const Group &g : groups) for (const Part &p : g.parts) total += bnk::gemm_tiled_bytes(p.M, g.K);
+    BN_CUDA(cudaMalloc(&m->tiled, total));
+    size_t off = 0;
+    for (const Group &g : groups) {
+        *g.dst = m->tiled + off;
+        for (const Part &p : g.parts) {
+            bnk::repack_tiles(m->ctx->stream, p.w, p.M, g.K, reinterpret_cast<uint32_t *>(m->tiled + off));
+            off += bnk::gemm_tiled_bytes(p.M, g.K);
+        }
+    }
+    BN_CUDA(cudaMalloc(&m->IMG_H, bnk::gemm_image_bytes(h.hidden, h.batch_cols)));
+    BN_CUDA(cudaMalloc(&m->IMG_F, bnk::gemm_image_bytes(h.ffn, h.batch_cols)));
+    BN_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    return BN_OK;
+}
+
+struct ColInit { int tok[bnk::GEMM_MAX_COLS]; int pos[bnk::GEMM_MAX_COLS]; };
+__global__ void k_set_cols(int *tok, int *pos, size_t arena, int n, ColInit ci, const int *tok_src) {
+    const int c = threadIdx.x;
+    if (c >= n) return;
+    bnk::colp(tok, c * arena)[0] = tok_src ? tok_src[c] : ci.tok[c];
+    bnk::colp(pos, c * arena)[0] = ci.pos[c];
+}
+
+// the token schedule for ncol sequences at once; m->cur = first sequence
+void enqueue_batch(bn_model *m, int ncol) {
+    const bn_hparams &h = m->hp;
+    cudaStream_t st = m->ctx->stream;
+    const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D, IN = NH * D;
+    const int QD = h.n_head * h.head_dim, KD = h.n_kv * h.head_dim;
+    const size_t AS = m->arena_bytes / 4;       // column stride in floats
+    bnk::Cols cols;
+    cols.n = ncol; cols.arena = m->arena_bytes; cols.gdn = m->gdn_stream_stride * 4; cols.conv = m->conv_stream_stride * 4;
+    cols.kv = m->kv_layer_bytes * m->n_attn;
+    auto prep = [&](int mode, const float *x, const float *w, const int32_t *sg, int K, uint8_t *img, float *inv_out) {
+        bnk::PrepArgs a = {};
+        a.x = x; a.x_stride = AS; a.w = w; a.signs = sg; a.K = K; a.hat_block = h.hat_block; a.eps = h.rms_eps; a.ncol = ncol;
+        a.image = img; a.inv_out = inv_out; a.inv_stride = AS; a.mode = mode;
+        bnk::prep_cols(st, a);
+    };
+    auto gemm = [&](const uint8_t *Wt, int M, int K, const uint8_t *img, float *out, const float *resid) {
+        bnk::GemmArgs a = {};
+        a.W = Wt; a.M = M; a.K = K; a.tiled = 1; a.image = img; a.ncol = ncol; a.out = out; a.out_stride = AS;
+        a.resid = resid; a.resid_stride = AS; a.err = m->ctx->err_dev;
+        cudaError_t e = bnk::launch_gemm(st, m->ctx->sm_count, a, m->use_pdl);
+        if (e != cudaSuccess && m->launch_err == cudaSuccess) m->launch_err = e;
+    };
+    if (m->b0 == 0) {
+        bnk::embed_row(st, m->embd, h.hidden, m->TOK, m->X1, cols);
+        bnk::rotate_inv(st, m->X1, m->signs, h.hidden, h.hat_block, m->RES, cols);
+    }
+    for (int b = m->b0; b < m->b1; ++b) {
+        const bn_model::Layer &L = m->layers[b];
+        const bn_model::TiledLayer &T = m->tl[b];
+        if (L.attn) {
+            const bnk::AttnDims ad = attn_dims(m);
+            const bnk::KvLayer kv = kv_layer(m, L.idx);
+            prep(bnk::PREP_NORM, m->RES, L.attn_norm, m->signs, h.hidden, m->IMG_H, nullptr);
+            gemm(T.in, 2 * QD + 2 * KD, h.hidden, m->IMG_H, m->QKV, nullptr);
+            bnk::attn_prep(st, ad, m->QKV, m->KBUF, m->VBUF, L.q_norm, L.k_norm, m->POS, kv, m->Q16F, m->GATEB, cols);
+            bnk::attn_decode(st, ad, m->Q16F, m->GATEB, m->POS, kv, m->SCORE, m->P16F, m->ESUM, m->PVPART, m->pv_splits, nullptr, m->GOUT, true, cols);
+            prep(bnk::PREP_PLAIN, m->GOUT, nullptr, m->signs, QD, m->IMG_H, nullptr);
+            gemm(T.out, h.hidden, QD, m->IMG_H, m->RES, m->RES);
+        } else {
+            prep(bnk::PREP_NORM, m->RES, L.attn_norm, m->signs, h.hidden, m->IMG_H, m->G + 48);
+            gemm(T.in, C + IN, h.hidden, m->IMG_H, m->QKV, nullptr);
+            const bnk::GdnDims gd{NH, NQ, D};
+            bnk::gdn_core_fused(st, gd, h.hidden, m->QKV, L.conv_w, conv_of(m, 0, L.idx), conv_of(m, 1, L.idx), m->POS, m->RES, m->G + 48,
+                                L.attn_norm, L.alpha_w, L.beta_w, L.dt_bias, L.ssm_a, gdn_state_of(m, L.idx), m->Z, L.ssm_norm, h.rms_eps, m->X1, cols);
+            prep(bnk::PREP_PLAIN, m->X1, nullptr, m->signs, IN, m->IMG_H, nullptr);
+            gemm(T.out, h.hidden, IN, m->IMG_H, m->RES, m->RES);
+        }
+        prep(bnk::PREP_NORM, m->RES, L.post_norm, m->signs, h.hidden, m->IMG_H, nullptr);
+        gemm(T.ffn_in, 2 * h.ffn, h.hidden, m->IMG_H, m->FG, nullptr);
+        bnk::swiglu(st, m->FG, m->FU, h.ffn, m->FS, cols);
+        prep(bnk::PREP_PLAIN, m->FS, nullptr, m->signs + h.hidden, h.ffn, m->IMG_F, nullptr);
+        gemm(T.ffn_down, h.hidden, h.ffn, m->IMG_F, m->RES, m->RES);
+    }
+    if (m->b1 != h.n_layer) return;
+    prep(bnk::PREP_NORM, m->RES, m->out_norm, m->signs, h.hidden, m->IMG_H, nullptr);
+    gemm(m->t_head, h.vocab, h.hidden, m->IMG_H, m->LOGITS, nullptr);
+    bnk::argmax_first(st, m->LOGITS, h.vocab, m->NEXT, m->AMV, m->AMI, cols);
+}
+
 // feed the greedy pick back as the next input, on the device
 __global__ void k_advance(int *tok, int *pos, const int *next, int *hist, int *step) {
     bnk::pdl_sync();
@@ -417,8 +541,9 @@ int bn_model_finalize(bn_model *m) {
     slots.push_back({reinterpret_cast<void **>(&m->PACK_H), carve(bnk::act_pack_bytes(h.hidden))});
     slots.push_back({reinterpret_cast<void **>(&m->PACK_F), carve(bnk::act_pack_bytes(h.ffn))});
     m->arena_bytes = off;
+    m->ncols = h.batch_cols > 0 ? h.batch_cols : 1;
     BN_CUDA(cudaSetDevice(m->ctx->device));
-    BN_CUDA(cudaMalloc(&m->arena, m->arena_bytes));
+    BN_CUDA(cudaMalloc(&m->arena, m->arena_bytes * m->ncols));
     for (auto &s : slots) *s.p = m->arena + s.o;
     m->Z = m->QKV + C;               // [qkv | gate] of a GDN block, [q | k | v] of an attention block
     m->KBUF = m->QKV + 2 * QD;
@@ -447,6 +572,10 @@ int bn_model_finalize(bn_model *m) {
         m->kv_layer_bytes = o;
         BN_CUDA(cudaMalloc(&m->kv, m->kv_layer_bytes * m->n_attn * S));
     }
+    if (h.batch_cols > 0) {
+        rc = build_batch_side(m);
+        if (rc != BN_OK) return rc;
+    }
     m->finalized = true;
     return bn_model_reset(m);
 }
@@ -456,7 +585,7 @@ int bn_model_reset(bn_model *m) {
     const bn_hparams &h = m->hp;
     const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D;
     cudaStream_t st = m->ctx->stream;
-    BN_CUDA(cudaMemsetAsync(m->arena, 0, m->arena_bytes, st));
+    BN_CUDA(cudaMemsetAsync(m->arena, 0, m->arena_bytes * m->ncols, st));
     if (m->n_gdn) {
         const int S = h.n_streams > 0 ? h.n_streams : 1;
         BN_CUDA(cudaMemsetAsync(m->gdn_state, 0, m->gdn_stream_stride * S * 4, st));
@@ -476,6 +605,10 @@ void bn_model_destroy(bn_model *m) {
     if (m->kv) cudaFree(m->kv);
     if (m->token_graph) cudaGraphExecDestroy(m->token_graph);
     for (cudaGraphExec_t g : m->stage_graphs) if (g) cudaGraphExecDestroy(g);
+    for (auto &kv : m->batch_graphs) cudaGraphExecDestroy(kv.second);
+    if (m->tiled) cudaFree(m->tiled);
+    if (m->IMG_H) cudaFree(m->IMG_H);
+    if (m->IMG_F) cudaFree(m->IMG_F);
     delete m;
 }
 
@@ -597,6 +730,70 @@ int bn_model_stage(bn_model *m, int stream, int tok, int pos, const bn_buf *in, 
     if (e != cudaSuccess) return bn_cuda_fail(e, "stage schedule");
     if (last) BN_CUDA(cudaMemcpyAsync(bn_ptr<char>(out, out_off), m->NEXT, 4, cudaMemcpyDeviceToDevice, st));
     else BN_CUDA(cudaMemcpyAsync(bn_ptr<char>(out, out_off), m->RES, size_t(h.hidden) * 4, cudaMemcpyDeviceToDevice, st));
+    return BN_OK;
+}
+
+int bn_model_stage_batch(bn_model *m, int stream0, int ncol, const int *tok, const int *pos, const bn_buf *in, size_t in_off,
+                         bn_buf *out, size_t out_off) {
+    BN_REQUIRE(m && m->finalized && pos, BN_ERR_STATE, "bn_model_stage_batch: model not finalized or no positions");
+    const bn_hparams &h = m->hp;
+    const int S = h.n_streams > 0 ? h.n_streams : 1;
+    BN_REQUIRE(h.batch_cols > 0 && ncol >= 1 && ncol <= h.batch_cols, BN_ERR_ARG,
+               "bn_model_stage_batch: %d sequences per call, the model was created for at most %d (bn_hparams.batch_cols)", ncol, h.batch_cols);
+    BN_REQUIRE(stream0 >= 0 && stream0 + ncol <= S, BN_ERR_ARG, "bn_model_stage_batch: sequences %d..%d outside [0, %d)", stream0, stream0 + ncol - 1, S);
+    BN_REQUIRE(m->fused, BN_ERR_STATE, "bn_model_stage_batch: needs the fused layer kernels (shapes supported by the streamed projection kernel)");
+    const bool first = m->b0 == 0, last = m->b1 == h.n_layer;
+    cudaStream_t st = m->ctx->stream;
+    ColInit ci = {};
+    for (int c = 0; c < ncol; ++c) {
+        BN_REQUIRE(pos[c] >= 0 && pos[c] < h.cap, BN_ERR_BOUNDS, "bn_model_stage_batch: position %d does not fit the KV capacity %d", pos[c], h.cap);
+        ci.pos[c] = pos[c];
+        if (first && tok) {
+            BN_REQUIRE(tok[c] >= 0 && tok[c] < h.vocab, BN_ERR_ARG, "bn_model_stage_batch: token %d outside vocab %d", tok[c], h.vocab);
+            ci.tok[c] = tok[c];
+        }
+    }
+    if (first) { if (!tok) BN_RANGE(in, in_off, size_t(ncol) * 4, 4, "bn_model_stage_batch token input"); }
+    else BN_RANGE(in, in_off, size_t(ncol) * h.hidden * 4, 16, "bn_model_stage_batch hidden input");
+    BN_RANGE(out, out_off, last ? size_t(ncol) * 4 : size_t(ncol) * h.hidden * 4, 4, "bn_model_stage_batch output");
+    m->cur = stream0;
+    m->next_pos = pos[0] + 1;
+    k_set_cols<<<1, 32, 0, st>>>(m->TOK, m->POS, m->arena_bytes, ncol, ci, (first && !tok) ? bn_ptr<int>(in, in_off) : nullptr);
+    BN_COUNT(1);
+    if (!first)
+        BN_CUDA(cudaMemcpy2DAsync(m->RES, m->arena_bytes, bn_ptr<char>(in, in_off), size_t(h.hidden) * 4, size_t(h.hidden) * 4, ncol,
+                                  cudaMemcpyDeviceToDevice, st));
+    cudaError_t e = cudaSuccess;
+    if (getenv("BONSAI_NO_STAGE_GRAPH")) {
+        enqueue_batch(m, ncol);
+        e = cudaGetLastError();
+    } else {
+        const long key = long(stream0) * 64 + ncol;
+        auto it = m->batch_graphs.find(key);
+        if (it == m->batch_graphs.end()) {
+            cudaGraph_t g = nullptr;
+            cudaGraphExec_t ge = nullptr;
+            const unsigned long long before = g_bn_launches;
+            BN_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+            enqueue_batch(m, ncol);
+            e = cudaStreamEndCapture(st, &g);
+            if (e != cudaSuccess) return bn_cuda_fail(e, "cudaStreamEndCapture(stage batch)");
+            m->batch_graph_launches = int(g_bn_launches - before);
+            g_bn_launches = before;
+            e = cudaGraphInstantiate(&ge, g, 0);
+            cudaGraphDestroy(g);
+            if (e != cudaSuccess) return bn_cuda_fail(e, "cudaGraphInstantiate(stage batch)");
+            it = m->batch_graphs.emplace(key, ge).first;
+        }
+        e = cudaGraphLaunch(it->second, st);
+        BN_COUNT(m->batch_graph_launches);
+    }
+    if (e == cudaSuccess) e = m->launch_err;
+    m->launch_err = cudaSuccess;
+    if (e != cudaSuccess) return bn_cuda_fail(e, "stage batch schedule");
+    if (last) BN_CUDA(cudaMemcpy2DAsync(bn_ptr<char>(out, out_off), 4, m->NEXT, m->arena_bytes, 4, ncol, cudaMemcpyDeviceToDevice, st));
+    else BN_CUDA(cudaMemcpy2DAsync(bn_ptr<char>(out, out_off), size_t(h.hidden) * 4, m->RES, m->arena_bytes, size_t(h.hidden) * 4, ncol,
+                                   cudaMemcpyDeviceToDevice, st));
     return BN_OK;
 }
 

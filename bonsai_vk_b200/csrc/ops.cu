@@ -60,8 +60,9 @@ __global__ void __launch_bounds__(512) k_rotate_quant(const float *__restrict__ 
 }
 
 __global__ void __launch_bounds__(512) k_rotate_inv(const float *__restrict__ x, const int32_t *__restrict__ signs,
-                                                    int block, float inv, float *__restrict__ y) {
+                                                    int block, float inv, float *__restrict__ y, bnk::Cols cols) {
     bnk::pdl_sync();
+    { const size_t col = blockIdx.z; x = bnk::colp(x, col * cols.arena); y = bnk::colp(y, col * cols.arena); }
     extern __shared__ float s[];
     const size_t base = size_t(blockIdx.x) * block;
     for (int i = threadIdx.x; i < block; i += blockDim.x) s[i] = x[base + i];
@@ -71,8 +72,9 @@ __global__ void __launch_bounds__(512) k_rotate_inv(const float *__restrict__ x,
 
 // ---- embedding gather (reference addressing: runtime_vk/shaders/gather_rows.comp:12-16) ----------
 __global__ void k_embed_row(const uint32_t *__restrict__ W, int K, const int *__restrict__ tok_ptr,
-                            float *__restrict__ out) {
+                            float *__restrict__ out, bnk::Cols cols) {
     bnk::pdl_sync();
+    { const size_t col = blockIdx.z; tok_ptr = bnk::colp(tok_ptr, col * cols.arena); out = bnk::colp(out, col * cols.arena); }
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= K) return;
     const int tok = tok_ptr[0];
@@ -118,8 +120,9 @@ __global__ void k_add_inplace(float *__restrict__ res, const float *__restrict__
     if (i < n) res[i] = __fadd_rn(d[i], res[i]);
 }
 
-__global__ void k_swiglu(const float *__restrict__ a, const float *__restrict__ b, int n, float *__restrict__ y) {
+__global__ void k_swiglu(const float *__restrict__ a, const float *__restrict__ b, int n, float *__restrict__ y, bnk::Cols cols) {
     bnk::pdl_sync();
+    { const size_t col = blockIdx.z; a = bnk::colp(a, col * cols.arena); b = bnk::colp(b, col * cols.arena); y = bnk::colp(y, col * cols.arena); }
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) y[i] = __fmul_rn(silu_f(a[i]), b[i]);
 }
@@ -233,8 +236,9 @@ __global__ void __launch_bounds__(512) k_gdn_core(int heads, int qk_heads, int h
                                                   const float *__restrict__ beta_w, const float *__restrict__ dt_bias,
                                                   const float *__restrict__ ssm_a, float *__restrict__ state,
                                                   const float *__restrict__ z, const float *__restrict__ ssm_norm, float eps,
-                                                  float *__restrict__ y, float scale) {
+                                                  float *__restrict__ y, float scale, bnk::Cols cols) {
     bnk::pdl_sync();
+    { const size_t col = blockIdx.z; qkv = bnk::colp(qkv, col * cols.arena); hist0 = bnk::colp(hist0, col * cols.conv); hist1 = bnk::colp(hist1, col * cols.conv); pos_ptr = bnk::colp(pos_ptr, col * cols.arena); x = bnk::colp(x, col * cols.arena); inv_ptr = bnk::colp(inv_ptr, col * cols.arena); state = bnk::colp(state, col * cols.gdn); z = bnk::colp(z, col * cols.arena); y = bnk::colp(y, col * cols.arena); }
     __shared__ float sq[128], sk[128], sv[128], so[128], sgb[2];
     extern __shared__ float4 dyn[];                // [3][hidden/4]: normed residual, row h of ssm_alpha, row h of ssm_beta
     const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -385,8 +389,9 @@ __global__ void __launch_bounds__(256) k_attn_prep(bnk::AttnDims a, const float 
                                                    const float *__restrict__ kin, const float *__restrict__ vin,
                                                    const float *__restrict__ qn_w, const float *__restrict__ kn_w,
                                                    const int *__restrict__ pos_ptr, bnk::KvLayer kv,
-                                                   float *__restrict__ q16f, float *__restrict__ gate) {
+                                                   float *__restrict__ q16f, float *__restrict__ gate, bnk::Cols cols) {
     bnk::pdl_sync();
+    { const size_t col = blockIdx.z; qg = bnk::colp(qg, col * cols.arena); kin = bnk::colp(kin, col * cols.arena); vin = bnk::colp(vin, col * cols.arena); pos_ptr = bnk::colp(pos_ptr, col * cols.arena); kv.k_data = bnk::colp(kv.k_data, col * cols.kv); kv.k_scale = bnk::colp(kv.k_scale, col * cols.kv); kv.v_data = bnk::colp(kv.v_data, col * cols.kv); kv.v_scale = bnk::colp(kv.v_scale, col * cols.kv); q16f = bnk::colp(q16f, col * cols.arena); gate = bnk::colp(gate, col * cols.arena); }
     __shared__ float part[256];
     __shared__ float sx[256];
     const int d = threadIdx.x, hd = a.head_dim, w = blockIdx.x;
@@ -432,8 +437,9 @@ __global__ void __launch_bounds__(256) k_attn_prep(bnk::AttnDims a, const float 
 template <int GQA>
 __global__ void __launch_bounds__(256) k_attn_scores(bnk::AttnDims a, const float *__restrict__ q16f,
                                                      const int *__restrict__ pos_ptr, bnk::KvLayer kv,
-                                                     float *__restrict__ score) {
+                                                     float *__restrict__ score, bnk::Cols cols) {
     bnk::pdl_sync();
+    { const size_t col = blockIdx.z; q16f = bnk::colp(q16f, col * cols.arena); pos_ptr = bnk::colp(pos_ptr, col * cols.arena); kv.k_data = bnk::colp(kv.k_data, col * cols.kv); kv.k_scale = bnk::colp(kv.k_scale, col * cols.kv); kv.v_data = bnk::colp(kv.v_data, col * cols.kv); kv.v_scale = bnk::colp(kv.v_scale, col * cols.kv); score = bnk::colp(score, col * cols.arena); }
     const int kvh = blockIdx.y, lane = threadIdx.x & 31, hd = a.head_dim;
     const int nfill = pos_ptr[0] + 1;
     const int jb = (blockIdx.x * 8 + (threadIdx.x >> 5)) * 8;
@@ -491,8 +497,9 @@ __global__ void __launch_bounds__(256) k_attn_scores(bnk::AttnDims a, const floa
 constexpr int EXPSUM_PARTS = 8;
 __global__ void __launch_bounds__(1024) k_attn_expsum(bnk::AttnDims a, const int *__restrict__ pos_ptr,
                                                       const float *__restrict__ score, float scale,
-                                                      float *__restrict__ pe, float *__restrict__ partial) {
+                                                      float *__restrict__ pe, float *__restrict__ partial, bnk::Cols cols) {
     bnk::pdl_sync();
+    { const size_t col = blockIdx.z; pos_ptr = bnk::colp(pos_ptr, col * cols.arena); score = bnk::colp(score, col * cols.arena); pe = bnk::colp(pe, col * cols.arena); partial = bnk::colp(partial, col * cols.arena); }
     __shared__ float red[1024];
     const int h = blockIdx.x, c = blockIdx.y, t = threadIdx.x, nfill = pos_ptr[0] + 1;
     const float *sr = score + size_t(h) * a.cap;
@@ -516,8 +523,9 @@ __global__ void __launch_bounds__(1024) k_attn_expsum(bnk::AttnDims a, const int
 // probabilities: p = fp16(e / total), total = the fixed tree over the head's 1024 partial sums (recomputed by
 // every CTA of the head). grid (n_head, ceil(cap / 4096)), 1024 threads, 4 keys per thread.
 __global__ void __launch_bounds__(1024) k_attn_normalise(bnk::AttnDims a, const int *__restrict__ pos_ptr,
-                                                         const float *__restrict__ partial, float *__restrict__ pe) {
+                                                         const float *__restrict__ partial, float *__restrict__ pe, bnk::Cols cols) {
     bnk::pdl_sync();
+    { const size_t col = blockIdx.z; pos_ptr = bnk::colp(pos_ptr, col * cols.arena); partial = bnk::colp(partial, col * cols.arena); pe = bnk::colp(pe, col * cols.arena); }
     __shared__ float red[1024];
     const int h = blockIdx.x, t = threadIdx.x, nfill = pos_ptr[0] + 1;
     if (int(blockIdx.y) * 4096 >= nfill) return;
@@ -534,8 +542,9 @@ __global__ void __launch_bounds__(1024) k_attn_normalise(bnk::AttnDims a, const 
 template <int GQA>
 __global__ void __launch_bounds__(256) k_attn_pv(bnk::AttnDims a, const float *__restrict__ p16f,
                                                  const int *__restrict__ pos_ptr, bnk::KvLayer kv, int splits,
-                                                 float *__restrict__ part) {
+                                                 float *__restrict__ part, bnk::Cols cols) {
     bnk::pdl_sync();
+    { const size_t col = blockIdx.z; p16f = bnk::colp(p16f, col * cols.arena); pos_ptr = bnk::colp(pos_ptr, col * cols.arena); kv.k_data = bnk::colp(kv.k_data, col * cols.kv); kv.k_scale = bnk::colp(kv.k_scale, col * cols.kv); kv.v_data = bnk::colp(kv.v_data, col * cols.kv); kv.v_scale = bnk::colp(kv.v_scale, col * cols.kv); part = bnk::colp(part, col * cols.arena); }
     extern __shared__ float ps[];                     // [GQA][per]
     const int kvh = blockIdx.x, sp = blockIdx.y, d = threadIdx.x, hd = a.head_dim;
     const int nfill = pos_ptr[0] + 1;
@@ -570,8 +579,9 @@ __global__ void __launch_bounds__(256) k_attn_pv(bnk::AttnDims a, const float *_
 
 // combine the splits ascending, then the sigmoid gate
 __global__ void k_attn_combine(bnk::AttnDims a, const float *__restrict__ part, int splits, const int *pos_ptr,
-                               const float *__restrict__ gate, float *__restrict__ pregate, float *__restrict__ gated) {
+                               const float *__restrict__ gate, float *__restrict__ pregate, float *__restrict__ gated, bnk::Cols cols) {
     bnk::pdl_sync();
+    { const size_t col = blockIdx.z; part = bnk::colp(part, col * cols.arena); pos_ptr = bnk::colp(pos_ptr, col * cols.arena); gate = bnk::colp(gate, col * cols.arena); pregate = bnk::colp(pregate, col * cols.arena); gated = bnk::colp(gated, col * cols.arena); }
     const int i = blockIdx.x * blockDim.x + threadIdx.x, n = a.n_head * a.head_dim;
     if (i >= n) return;
     const int nfill = pos_ptr[0] + 1;
@@ -590,8 +600,9 @@ __global__ void k_attn_combine(bnk::AttnDims a, const float *__restrict__ part, 
 
 // ---- greedy pick: first maximum (Sampler::pick, runtime_vk/bonsai_forward.h:2568-2570) ----------
 __global__ void __launch_bounds__(1024) k_argmax_part(const float *__restrict__ x, int n, float *__restrict__ bv,
-                                                      int *__restrict__ bi) {
+                                                      int *__restrict__ bi, bnk::Cols cols) {
     bnk::pdl_sync();
+    { const size_t col = blockIdx.z; x = bnk::colp(x, col * cols.arena); bv = bnk::colp(bv, col * cols.arena); bi = bnk::colp(bi, col * cols.arena); }
     __shared__ float sv[1024];
     __shared__ int si[1024];
     const int t = threadIdx.x;
@@ -610,8 +621,9 @@ __global__ void __launch_bounds__(1024) k_argmax_part(const float *__restrict__ 
     }
     if (t == 0) { bv[blockIdx.x] = sv[0]; bi[blockIdx.x] = si[0]; }
 }
-__global__ void k_argmax_final(const float *__restrict__ bv, const int *__restrict__ bi, int nparts, int *out) {
+__global__ void k_argmax_final(const float *__restrict__ bv, const int *__restrict__ bi, int nparts, int *out, bnk::Cols cols) {
     bnk::pdl_sync();
+    { const size_t col = blockIdx.z; bv = bnk::colp(bv, col * cols.arena); bi = bnk::colp(bi, col * cols.arena); out = bnk::colp(out, col * cols.arena); }
     if (threadIdx.x != 0) return;
     float best = bv[0]; int idx = bi[0];
     for (int p = 1; p < nparts; ++p) if (bv[p] > best || (bv[p] == best && bi[p] < idx)) { best = bv[p]; idx = bi[p]; }
@@ -630,17 +642,19 @@ void rotate_quant(cudaStream_t st, const float *x, const int32_t *signs, int n, 
     uint32_t *q81 = pack, *table = pack ? pack + size_t(n / 128) * Q81_DWORDS : nullptr;
     launch(k_rotate_quant, dim3(n / block), dim3(512), size_t(block) * 4 + 512, st, x, signs, block, inv, y, q81, table); 
 }
-void rotate_inv(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y) {
-    launch(k_rotate_inv, dim3(n / block), dim3(512), size_t(block) * 4, st, x, signs, block, 1.0f / sqrtf(float(block)), y); 
+void rotate_inv(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y, Cols cols) {
+    launch(k_rotate_inv, dim3(n / block, 1, cols.z()), dim3(512), size_t(block) * 4, st, x, signs, block, 1.0f / sqrtf(float(block)), y, cols); 
 }
-void embed_row(cudaStream_t st, const uint32_t *W, int K, const int *tok_ptr, float *out) {
-    launch(k_embed_row, dim3((K + 255) / 256), dim3(256), 0, st, W, K, tok_ptr, out); 
+void embed_row(cudaStream_t st, const uint32_t *W, int K, const int *tok_ptr, float *out, Cols cols) {
+    launch(k_embed_row, dim3((K + 255) / 256, 1, cols.z()), dim3(256), 0, st, W, K, tok_ptr, out, cols); 
 }
 void rms_norm(cudaStream_t st, const float *x, const float *w, int rows, int cols, float eps, float *y) {
     launch(k_rms_norm, dim3(rows), dim3(256), 0, st, x, w, cols, eps, y); 
 }
 void add_inplace(cudaStream_t st, float *res, const float *d, int n) { launch(k_add_inplace, dim3((n + 255) / 256), dim3(256), 0, st, res, d, n);  }
-void swiglu(cudaStream_t st, const float *a, const float *b, int n, float *y) { launch(k_swiglu, dim3((n + 255) / 256), dim3(256), 0, st, a, b, n, y);  }
+void swiglu(cudaStream_t st, const float *a, const float *b, int n, float *y, Cols cols) {
+    launch(k_swiglu, dim3((n + 255) / 256, 1, cols.z()), dim3(256), 0, st, a, b, n, y, cols);
+}
 void gemv_f32_small(cudaStream_t st, const float *W, int M, int K, const float *x, float *out) {
     launch(k_gemv_f32_small, dim3((M + 7) / 8), dim3(256), 0, st, W, M, K, x, out); 
 }
@@ -662,35 +676,36 @@ void gdn_delta(cudaStream_t st, GdnDims d, const float *q, const float *k, const
 void gdn_core_fused(cudaStream_t st, GdnDims d, int hidden, const float *qkv, const float *conv_w, float *hist0,
                     float *hist1, const int *pos_ptr, const float *x, const float *inv_ptr, const float *norm_w, const float *alpha_w,
                     const float *beta_w, const float *dt_bias, const float *ssm_a, float *state, const float *z,
-                    const float *ssm_norm, float eps, float *y) {
+                    const float *ssm_norm, float eps, float *y, Cols cols) {
     static bool attr = false;
     if (!attr) { cudaFuncSetAttribute(k_gdn_core, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 16384 * 4); attr = true; }
-    launch(k_gdn_core, dim3(d.heads), dim3(512), size_t(hidden) * 12, st, d.heads, d.qk_heads, hidden, qkv, conv_w, hist0, hist1, pos_ptr, x, inv_ptr,
+    launch(k_gdn_core, dim3(d.heads, 1, cols.z()), dim3(512), size_t(hidden) * 12, st, d.heads, d.qk_heads, hidden, qkv, conv_w, hist0, hist1, pos_ptr, x, inv_ptr,
                                                          norm_w, alpha_w, beta_w, dt_bias, ssm_a, state, z, ssm_norm, eps, y,
-                                                         1.0f / sqrtf(float(d.dim))); 
+                                                         1.0f / sqrtf(float(d.dim)), cols); 
 }
 void gdn_out(cudaStream_t st, GdnDims d, const float *o, const float *z, const float *ssm_norm, float eps, float *y) {
     launch(k_gdn_out, dim3((d.heads + 7) / 8), dim3(256), 0, st, d.heads, d.qk_heads, o, z, ssm_norm, eps, y); 
 }
 void attn_prep(cudaStream_t st, AttnDims a, const float *qg, const float *kin, const float *vin, const float *qn_w,
-               const float *kn_w, const int *pos_ptr, KvLayer kv, float *q16f, float *gate) {
-    launch(k_attn_prep, dim3(a.n_head + a.n_kv), dim3(256), 0, st, a, qg, kin, vin, qn_w, kn_w, pos_ptr, kv, q16f, gate); 
+               const float *kn_w, const int *pos_ptr, KvLayer kv, float *q16f, float *gate, Cols cols) {
+    launch(k_attn_prep, dim3(a.n_head + a.n_kv, 1, cols.z()), dim3(256), 0, st, a, qg, kin, vin, qn_w, kn_w, pos_ptr, kv, q16f, gate, cols); 
 }
 void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *gate, const int *pos_ptr, KvLayer kv,
-                 float *score, float *p16f, float *esum, float *pv_part, int splits, float *pregate, float *gated, bool combine) {
+                 float *score, float *p16f, float *esum, float *pv_part, int splits, float *pregate, float *gated, bool combine,
+                 Cols cols) {
     // grids are sized for the cache capacity; warps beyond the filled prefix return at once
-    launch(k_attn_scores<4>, dim3((a.cap + 63) / 64, a.n_kv), dim3(256), 0, st, a, q16f, pos_ptr, kv, score);
-    launch(k_attn_expsum, dim3(a.n_head, EXPSUM_PARTS), dim3(1024), 0, st, a, pos_ptr, score, 1.0f / sqrtf(float(a.head_dim)), p16f, esum);
-    launch(k_attn_normalise, dim3(a.n_head, (a.cap + 4095) / 4096), dim3(1024), 0, st, a, pos_ptr, esum, p16f);
-    launch(k_attn_pv<4>, dim3(a.n_kv, splits), dim3(256), size_t(4) * ((a.cap + splits - 1) / splits) * 4, st, a, p16f, pos_ptr, kv, splits, pv_part);
+    launch(k_attn_scores<4>, dim3((a.cap + 63) / 64, a.n_kv, cols.z()), dim3(256), 0, st, a, q16f, pos_ptr, kv, score, cols);
+    launch(k_attn_expsum, dim3(a.n_head, EXPSUM_PARTS, cols.z()), dim3(1024), 0, st, a, pos_ptr, score, 1.0f / sqrtf(float(a.head_dim)), p16f, esum, cols);
+    launch(k_attn_normalise, dim3(a.n_head, (a.cap + 4095) / 4096, cols.z()), dim3(1024), 0, st, a, pos_ptr, esum, p16f, cols);
+    launch(k_attn_pv<4>, dim3(a.n_kv, splits, cols.z()), dim3(256), size_t(4) * ((a.cap + splits - 1) / splits) * 4, st, a, p16f, pos_ptr, kv, splits, pv_part, cols);
     if (!combine) return;
     const int n = a.n_head * a.head_dim;
-    launch(k_attn_combine, dim3((n + 255) / 256), dim3(256), 0, st, a, pv_part, splits, pos_ptr, gate, pregate, gated); 
+    launch(k_attn_combine, dim3((n + 255) / 256, 1, cols.z()), dim3(256), 0, st, a, pv_part, splits, pos_ptr, gate, pregate, gated, cols); 
 }
-void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx) {
+void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx, Cols cols) {
     const int parts = 64;
-    launch(k_argmax_part, dim3(parts), dim3(1024), 0, st, x, n, scratch_val, scratch_idx); 
-    launch(k_argmax_final, dim3(1), dim3(32), 0, st, scratch_val, scratch_idx, parts, out_idx); 
+    launch(k_argmax_part, dim3(parts, 1, cols.z()), dim3(1024), 0, st, x, n, scratch_val, scratch_idx, cols); 
+    launch(k_argmax_final, dim3(1, 1, cols.z()), dim3(32), 0, st, scratch_val, scratch_idx, parts, out_idx, cols); 
 }
 
 }  // namespace bnk

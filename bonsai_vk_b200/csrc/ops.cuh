@@ -2,6 +2,8 @@
 #pragma once
 #include "common.cuh"
 
+#include <type_traits>
+
 // All helpers enqueue on `st` and return cudaGetLastError() state through bn_launch_check by the caller.
 namespace bnk {
 
@@ -28,6 +30,20 @@ __device__ __forceinline__ void pdl_sync() {
 }
 #endif
 
+// Several sequences ("columns") in one launch: blockIdx.z is the column; its activations live at the column-0
+// pointer + col * arena bytes, its recurrent state, conv taps and KV cache at + col * the respective stream strides.
+// The default (no columns) leaves every pointer as it is.
+struct Cols {
+    int n = 0;
+    size_t arena = 0, gdn = 0, conv = 0, kv = 0;
+    unsigned z() const { return n > 0 ? unsigned(n) : 1u; }
+};
+#ifdef __CUDACC__
+template <class T> __device__ __forceinline__ T *colp(T *p, size_t bytes) {
+    return p ? reinterpret_cast<T *>(reinterpret_cast<char *>(const_cast<typename std::remove_const<T>::type *>(p)) + bytes) : p;
+}
+#endif
+
 constexpr int Q81_DWORDS = 36;
 constexpr int BF_WORDS = 512;
 inline size_t act_pack_bytes(int K) { return size_t(K / 128) * (Q81_DWORDS + BF_WORDS) * 4; }
@@ -41,13 +57,13 @@ void act_quant_q81(cudaStream_t st, const float *x, int K, uint32_t *pack);
 // y may be null when only the pack is wanted). n % block == 0, block = power of two in [128, 4096].
 void rotate_quant(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y, uint32_t *pack);
 // embedding side: y = s . H(x)
-void rotate_inv(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y);
+void rotate_inv(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y, Cols cols = {});
 // PTQ1_0 row gather: out[K] = dequantised row `tok` (tok read from tok_ptr[0])
-void embed_row(cudaStream_t st, const uint32_t *W, int K, const int *tok_ptr, float *out);
+void embed_row(cudaStream_t st, const uint32_t *W, int K, const int *tok_ptr, float *out, Cols cols = {});
 
 void rms_norm(cudaStream_t st, const float *x, const float *w, int rows, int cols, float eps, float *y);
 void add_inplace(cudaStream_t st, float *res, const float *d, int n);       // res = d + res
-void swiglu(cudaStream_t st, const float *a, const float *b, int n, float *y);
+void swiglu(cudaStream_t st, const float *a, const float *b, int n, float *y, Cols cols = {});
 void gemv_f32_small(cudaStream_t st, const float *W, int M, int K, const float *x, float *out);
 
 struct GdnDims { int heads, qk_heads, dim; };
@@ -63,7 +79,7 @@ void gdn_delta(cudaStream_t st, GdnDims d, const float *q, const float *k, const
 void gdn_core_fused(cudaStream_t st, GdnDims d, int hidden, const float *qkv, const float *conv_w, float *hist0,
                     float *hist1, const int *pos_ptr, const float *x, const float *inv_ptr, const float *norm_w, const float *alpha_w,
                     const float *beta_w, const float *dt_bias, const float *ssm_a, float *state, const float *z,
-                    const float *ssm_norm, float eps, float *y);
+                    const float *ssm_norm, float eps, float *y, Cols cols = {});
 // per-head RMS (no weight) * ssm_norm, swiglu(z, .), v-grouped permutation -> y[heads*dim]
 void gdn_out(cudaStream_t st, GdnDims d, const float *o, const float *z, const float *ssm_norm, float eps, float *y);
 
@@ -71,12 +87,12 @@ struct AttnDims { int n_head, n_kv, head_dim, n_rot, cap; float eps, rope_base; 
 struct KvLayer { void *k_data; uint16_t *k_scale; void *v_data; uint16_t *v_scale; };   // scales null in fp16 mode
 // norm + rope + fp16 rounding of q, gate split, K/V quantise + insert at *pos_ptr
 void attn_prep(cudaStream_t st, AttnDims a, const float *qg, const float *kin, const float *vin, const float *qn_w,
-               const float *kn_w, const int *pos_ptr, KvLayer kv, float *q16f, float *gate);
+               const float *kn_w, const int *pos_ptr, KvLayer kv, float *q16f, float *gate, Cols cols = {});
 // scores -> softmax (fp16-rounded probabilities) -> PV -> sigmoid gate. Scratch buffers sized by cap.
 void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *gate, const int *pos_ptr, KvLayer kv,
                  float *score /*[nh][cap]*/, float *p16f /*[nh][cap]*/, float *esum /*[nh][1024]*/,
                  float *pv_part /*[splits][nh][hd]*/, int splits,
-                 float *pregate /*[nh][hd] or null*/, float *gated, bool combine /*false: leave the split partials*/);
-void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx);
+                 float *pregate /*[nh][hd] or null*/, float *gated, bool combine /*false: leave the split partials*/, Cols cols = {});
+void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx, Cols cols = {});
 
 }  // namespace bnk

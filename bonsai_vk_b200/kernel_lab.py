@@ -3,6 +3,7 @@
 
   python -m bonsai_vk_b200.kernel_lab M K [ITER] [--nocheck]
   python -m bonsai_vk_b200.kernel_lab attn CTX [ITER]      one decode-attention layer (16/4 heads x 256, q8_0 K and V)
+  python -m bonsai_vk_b200.kernel_lab gemm M K NCOL [ITER]  the multi-column tensor-core projection (tcgen05), timed
 
 Prints max|err| and rel against the CPU checker (when oracle/ is built), then ms/op, Gop/s and GB/s of
 PTQ1_0 bytes from CUDA events. Timing rotates through enough copies of the matrix to exceed L2.
@@ -55,10 +56,71 @@ def attn_lab(argv):
     ctx.close()
 
 
+def gemm_lab(argv):
+    """NCOL activation columns against one M x K PTQ1_0 matrix; column 0 is checked against the single-column kernel."""
+    from bonsai_vk_b200 import Context, ptq
+    M, K, ncol = int(argv[0]), int(argv[1]), int(argv[2])
+    iters = int(argv[3]) if len(argv) > 3 and not argv[3].startswith("-") else 5
+    tiled = "--native" not in argv
+    ctx = Context(0)
+    rng = np.random.default_rng(3)
+    rows = min(M, 8192)
+    base = ptq.synth_matrix(rng, rows, K)
+    W = np.concatenate([base] * ((M + rows - 1) // rows), axis=0)[:M]
+    nbytes = M * (K // 128) * 28
+    ncopies = max(2, int(300e6 // nbytes) + 1)
+    wb = ctx.alloc(ncopies * nbytes)
+    for i in range(ncopies):
+        wb.upload(W, off=i * nbytes)
+    native = wb
+    if tiled:                       # the kernel's own tile-major copy of every rotation copy of the matrix
+        tbytes = int(ctx.lib.bn_gemm_tiled_bytes(M, K))
+        wt = ctx.alloc(ncopies * tbytes)
+        for i in range(ncopies):
+            one = ctx.gemm_repack(wb, M, K, w_off=i * nbytes)
+            wt.upload(one.download(np.uint8, tbytes), off=i * tbytes)
+            one.free()
+        wb, step = wt, tbytes
+    else:
+        step = nbytes
+    X = rng.standard_normal((ncol, K)).astype(np.float32)
+    xb = ctx.from_numpy(X)
+    image = ctx.alloc(ctx.gemm_image_bytes(K, ncol))
+    out = ctx.alloc(ncol * M * 4)
+    ctx.gemm_act_quant(xb, K, ncol, image)
+    ctx.gemm_q81(wb, M, K, image, ncol, out, tiled=tiled)
+    ctx.sync()
+    got = out.download(np.float32, ncol * M).reshape(ncol, M)
+    pack = ctx.alloc(ctx.act_pack_bytes(K))
+    ref = ctx.alloc(M * 4)
+    ctx.act_quant_q81(xb, K, pack)
+    ctx.gemv_q81(native, M, K, pack, ref)
+    ctx.sync()
+    same = np.array_equal(got[0].view(np.uint32), ref.download(np.float32, M).view(np.uint32))
+    print(f"column 0 vs single-column kernel: {'bit-identical' if same else 'DIFFERENT'}")
+    e0, e1 = ctx.event(), ctx.event()
+    for i in range(ncopies):
+        ctx.gemm_q81(wb, M, K, image, ncol, out, w_off=i * step, tiled=tiled)
+    ctx.record(e0)
+    for _ in range(iters):
+        for i in range(ncopies):
+            ctx.gemm_q81(wb, M, K, image, ncol, out, w_off=i * step, tiled=tiled)
+    ctx.record(e1)
+    import os
+    ms = ctx.elapsed_ms(e0, e1) / (iters * ncopies * max(1, int(os.environ.get("BONSAI_GEMM_REPS", "1"))))
+    ops = 2.0 * M * K * ncol
+    print(f"gemm {M}x{K} x {ncol} columns ({'tile-major' if tiled else 'native'} weights): {ms * 1000:.1f} us, {nbytes / ms / 1e6:.1f} GB/s of PTQ1_0 bytes, {ops / ms / 1e9:.2f} Top/s "
+          f"({ncopies} matrix copies = {ncopies * nbytes / 1e6:.0f} MB rotation)")
+    ctx.close()
+    return 0 if same else 1
+
+
 def main(argv):
     from bonsai_vk_b200 import Context, ptq
     if argv and argv[0] == "attn":
         return attn_lab(argv[1:])
+    if argv and argv[0] == "gemm":
+        return gemm_lab(argv[1:])
     M, K = int(argv[0]), int(argv[1])
     iters = int(argv[2]) if len(argv) > 2 and not argv[2].startswith("-") else 3
     check = "--nocheck" not in argv

@@ -21,7 +21,7 @@ class HParamsC(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "n_layer", "hidden", "ffn", "vocab", "n_head", "n_kv", "head_dim", "n_rot", "attn_interval",
         "gdn_heads", "gdn_qk_heads", "gdn_dim", "hat_block", "act_mode", "k_mode", "v_mode", "cap")] + [
-        ("rms_eps", C.c_float), ("rope_base", C.c_float)] + [(n, C.c_int32) for n in ("n_streams", "block_begin", "block_end")]
+        ("rms_eps", C.c_float), ("rope_base", C.c_float)] + [(n, C.c_int32) for n in ("n_streams", "block_begin", "block_end", "batch_cols")]
 
 
 class AttnDimsC(C.Structure):
@@ -66,6 +66,11 @@ def load_library() -> C.CDLL:
         "bn_act_quant_q81": (i32, [vp, vp, sz, i32, vp, sz]),
         "bn_gemv_q81": (i32, [vp, vp, sz, i32, i32, vp, sz, vp, sz, vp, sz]),
         "bn_gemv_q81_static": (i32, [vp, vp, sz, i32, i32, vp, sz, vp, sz]),
+        "bn_gemm_image_bytes": (sz, [i32, i32]),
+        "bn_gemm_act_quant": (i32, [vp, vp, sz, sz, i32, i32, vp, sz, i32, vp, sz]),
+        "bn_gemm_q81": (i32, [vp, vp, sz, i32, i32, i32, vp, sz, i32, vp, sz, sz]),
+        "bn_gemm_tiled_bytes": (sz, [i32, i32]),
+        "bn_gemm_repack": (i32, [vp, vp, sz, i32, i32, vp, sz]),
         "bn_attn_kv_bytes": (sz, [C.POINTER(AttnDimsC)]),
         "bn_attn_scratch_bytes": (sz, [C.POINTER(AttnDimsC)]),
         "bn_attn_insert": (i32, [vp, C.POINTER(AttnDimsC), vp, sz, vp, sz, vp, sz, i32, i32, vp, sz, vp, sz, vp, sz, vp, sz]),
@@ -80,6 +85,7 @@ def load_library() -> C.CDLL:
         "bn_model_read": (i32, [vp, i32, i32, vp, sz]),
         "bn_model_decode": (i32, [vp, i32, i32, i32, C.POINTER(i32)]),
         "bn_model_stage": (i32, [vp, i32, i32, i32, vp, sz, vp, sz]),
+        "bn_model_stage_batch": (i32, [vp, i32, i32, vp, vp, vp, sz, vp, sz]),
         "bn_model_fill_kv": (i32, [vp, i32, i32]),
         "bn_wrap": (i32, [vp, vp, sz, C.POINTER(vp)]),
         "bn_use_stream": (i32, [vp, vp]),
@@ -231,6 +237,34 @@ class Context:
         _check(self.lib.bn_gemv_q81_static(self.h, w.h, w_off, M, K, pack.h, pack_off, out.h, out_off), "bn_gemv_q81_static")
 
 
+def _gemm_methods():
+    def gemm_image_bytes(self, K: int, ncol: int) -> int:
+        return int(self.lib.bn_gemm_image_bytes(K, ncol))
+
+    def gemm_act_quant(self, x: Buffer, K: int, ncol: int, image: Buffer, signs: "Buffer | None" = None, hat_block: int = 0,
+                       x_stride: int = 0, x_off: int = 0, signs_off: int = 0):
+        """ncol fp32 vectors -> the activation image of the multi-column projection (optional rotation first)."""
+        _check(self.lib.bn_gemm_act_quant(self.h, x.h, x_off, x_stride or K, K, ncol, signs.h if signs is not None else None,
+                                          signs_off, hat_block, image.h, 0), "bn_gemm_act_quant")
+
+    def gemm_q81(self, w: Buffer, M: int, K: int, image: Buffer, ncol: int, out: Buffer, out_stride: int = 0, w_off: int = 0,
+                 tiled: bool = False):
+        _check(self.lib.bn_gemm_q81(self.h, w.h, w_off, 1 if tiled else 0, M, K, image.h, 0, ncol, out.h, 0, out_stride or M),
+               "bn_gemm_q81")
+
+    def gemm_repack(self, w: Buffer, M: int, K: int, w_off: int = 0) -> Buffer:
+        """The tile-major copy of a weight matrix for gemm_q81(tiled=True)."""
+        out = self.alloc(int(self.lib.bn_gemm_tiled_bytes(M, K)))
+        _check(self.lib.bn_gemm_repack(self.h, w.h, w_off, M, K, out.h, 0), "bn_gemm_repack")
+        return out
+
+    Context.gemm_image_bytes, Context.gemm_act_quant, Context.gemm_q81 = gemm_image_bytes, gemm_act_quant, gemm_q81
+    Context.gemm_repack = gemm_repack
+
+
+_gemm_methods()
+
+
 class Model:
     """Device-resident model: tensors registered by GGUF name (reference: engine_init + fwd_init)."""
 
@@ -282,6 +316,15 @@ class Model:
         """One pipeline stage for one token of one stream (enqueue only)."""
         _check(self.ctx.lib.bn_model_stage(self.h, stream, tok, pos, inp.h if inp is not None else None, in_off, out.h, out_off),
                "bn_model_stage")
+
+    def stage_batch(self, stream0: int, toks, pos, inp: "Buffer | None", out: "Buffer", in_off: int = 0, out_off: int = 0):
+        """One pipeline stage for len(pos) consecutive sequences at once (enqueue only). toks: token ids (first stage)
+        or None (ids or hidden states are read from inp)."""
+        n = len(pos)
+        pa = (C.c_int32 * n)(*[int(p) for p in pos])
+        ta = (C.c_int32 * n)(*[int(t) for t in toks]) if toks is not None else None
+        _check(self.ctx.lib.bn_model_stage_batch(self.h, stream0, n, ta, pa, inp.h if inp is not None else None, in_off, out.h, out_off),
+               "bn_model_stage_batch")
 
     def fill_kv(self, stream: int, n_positions: int):
         _check(self.ctx.lib.bn_model_fill_kv(self.h, stream, n_positions), "bn_model_fill_kv")

@@ -37,6 +37,7 @@ class HParams:
     n_streams: int = 1          # independent sequences resident on the device
     block_begin: int = 0        # pipeline stage: this device holds blocks [block_begin, block_end)
     block_end: int = 0          # 0 = n_layer
+    batch_cols: int = 0         # > 0: the multi-sequence pass (stage_batch) may take up to this many sequences per call
 
     def is_attn(self, b: int) -> bool:
         return b % self.attn_interval == self.attn_interval - 1

@@ -94,6 +94,27 @@ int bn_gemv_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const 
 int bn_gemv_q81_static(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const bn_buf *pack,
                        size_t pack_off, bn_buf *out, size_t out_off);
 
+/* ---- the same projection for several activation columns at once (prefill tokens, concurrent sequences) on the
+ *      tcgen05 tensor cores. Reference: the multi-column path of _mul_mat_vecq_ptq1_0.comp:204-347 (<= 8 columns;
+ *      beyond that the reference falls back to dequantise + f16 matmul, _ggml-vulkan.cpp:2195-2197, which has no
+ *      integer block dots). Every column of the result is bit-identical to bn_gemv_q81 on that column's vector. -----
+ * The activations are handed over as one "image" for all columns: int8 codes in the tensor-core operand layout plus
+ * the (d, s) scale pairs per 32 activations. bn_gemm_act_quant builds it from ncol fp32 vectors of K values
+ * (column c at x + c * x_stride floats): optional rotation y = H(s . x) per hat_block (signs NULL = none), then the
+ * q8_1 quantiser. K % 1024 == 0, 1 <= ncol <= 32. */
+size_t bn_gemm_image_bytes(int K, int ncol);
+int bn_gemm_act_quant(bn_ctx *ctx, const bn_buf *x, size_t x_off, size_t x_stride, int K, int ncol, const bn_buf *signs,
+                      size_t signs_off, int hat_block, bn_buf *image, size_t image_off);
+/* Optional second copy of a weight matrix for this kernel (reference: the engine also repacks its weights once at load,
+ * bonsai_weights.h:502-558): per tile of 128 rows and 8 blocks of K one contiguous piece, so that a pipeline stage is a
+ * single bulk copy. Same bytes, other order; rows beyond M are zero. */
+size_t bn_gemm_tiled_bytes(int M, int K);
+int bn_gemm_repack(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, bn_buf *tiled, size_t tiled_off);
+/* w_tiled = 0: w is the native row-major matrix; 1: w is the copy made by bn_gemm_repack.
+ * out: column c at out + c * out_stride floats, M values each */
+int bn_gemm_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int w_tiled, int M, int K, const bn_buf *image, size_t image_off,
+                int ncol, bn_buf *out, size_t out_off, size_t out_stride);
+
 /* ---- decode attention as stand-alone ops (reference: attn_block, runtime_vk/bonsai_forward.h:581-645; kernels
  *      attn_norm_rope2.comp, attn_qk_softmax*.comp, attn_pv_q8v*.comp; test harness align_attn.cpp) ------------
  * One layer's cache lives in a caller buffer of bn_attn_kv_bytes(); working memory of bn_attn_scratch_bytes(). */
@@ -133,6 +154,9 @@ typedef struct bn_hparams {
     int32_t n_streams;                        /* independent sequences, each with its own KV cache and recurrent state */
     int32_t block_begin, block_end;           /* this device holds blocks [begin, end); end 0 = n_layer. The embedding
                                                  belongs to the stage with block 0, the output head to the last one */
+    int32_t batch_cols;                       /* > 0: bn_model_stage_batch may run up to this many sequences per call
+                                                 (<= 32); costs one more activation arena per column and a tile-major
+                                                 copy of the local projection weights for the tensor-core kernel */
 } bn_hparams;
 
 enum bn_read_what {
@@ -159,6 +183,14 @@ int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *nex
  * (in, in_off). Other stages: (in, in_off) holds the `hidden` fp32 values from the previous stage. Output: the
  * hidden state at (out, out_off), or on the last stage the greedy pick as one int. Enqueues only - no host wait. */
 int bn_model_stage(bn_model *m, int stream, int tok, int pos, const bn_buf *in, size_t in_off, bn_buf *out, size_t out_off);
+/* The same stage for ncol consecutive sequences stream0 .. stream0+ncol-1 in one pass (the micro-batch of the layer
+ * pipeline): every projection reads its weights once for all of them (tcgen05 kernel, bn_gemm_q81), the other
+ * kernels run one grid slice per sequence. pos[c] is the position of sequence stream0+c. First stage: tok != NULL gives
+ * the token ids, tok == NULL reads ncol ints from (in, in_off). Other stages: (in, in_off) holds ncol x hidden fp32,
+ * sequence-major. Output: ncol x hidden fp32, or ncol ints (the greedy picks) on the last stage. Each sequence's result
+ * is bit-identical to what bn_model_stage gives for it alone. Needs bn_hparams.batch_cols >= ncol. Enqueues only. */
+int bn_model_stage_batch(bn_model *m, int stream0, int ncol, const int *tok, const int *pos, const bn_buf *in, size_t in_off,
+                         bn_buf *out, size_t out_off);
 /* timing fixture (reference: BONSAI_KVFILL, bonsai_forward.h:1338-1378): mark the first n_positions of a
  * stream's KV caches as filled with 1.0 so long-context steps can be timed without a long prefill */
 int bn_model_fill_kv(bn_model *m, int stream, int n_positions);

@@ -47,3 +47,64 @@ def test_two_stages_three_streams_match_whole_model(ctx):
     a.close(); b.close()
     for x in hid + tokb:
         x.free()
+
+
+def test_batched_stages_match_whole_model(ctx):
+    """The multi-sequence pass (tensor-core projections, one grid slice per sequence elsewhere): two stages, six
+    sequences run as micro-batches of 4 + 2 at different positions per sequence, against the whole model run one
+    sequence at a time. Streams AND final state must be identical: the batched pass computes every column in the
+    single-sequence operation order."""
+    from bonsai_vk_b200 import lib as L
+    hp = synth.tiny()
+    tensors, signs = synth.make_model(hp, seed=7)
+    S, T = 6, 9
+    first = [5, 77, 1234, 900, 3, 2000]
+    lag = [0, 1, 0, 2, 1, 0]                     # sequence s starts at step lag[s]: positions differ inside a micro-batch
+    whole = Model(ctx, hp, tensors, signs)
+    want, want_state = [], []
+    for s in range(S):
+        whole.reset()
+        tok, row = first[s], []
+        for pos in range(T - lag[s]):
+            tok = whole.token(tok, pos)
+            row.append(tok)
+        want.append(row)
+        want_state.append(whole.read(L.READ_GDN_STATE, np.float32, hp.gdn_heads * hp.gdn_dim ** 2, 0).copy())
+    whole.close()
+
+    a = Model(ctx, synth.tiny(n_streams=S, block_begin=0, block_end=2, batch_cols=4), tensors, signs)
+    b = Model(ctx, synth.tiny(n_streams=S, block_begin=2, block_end=4, batch_cols=4), tensors, signs)
+    hid, tokb = ctx.alloc(S * hp.hidden * 4), ctx.alloc(S * 4)
+    got = [[] for _ in range(S)]
+    cur = list(first)
+    groups = [(0, 4), (4, 2)]
+    for step in range(T):
+        for s0, n in groups:
+            live = [s for s in range(s0, s0 + n) if step >= lag[s]]
+            if not live:
+                continue
+            # a micro-batch is a run of consecutive sequences: here all of a group are live from step 2 on; before that
+            # the live ones are run in consecutive sub-runs
+            runs, run = [], [live[0]]
+            for s in live[1:]:
+                if s == run[-1] + 1:
+                    run.append(s)
+                else:
+                    runs.append(run); run = [s]
+            runs.append(run)
+            for run in runs:
+                r0, pos = run[0], [step - lag[s] for s in run]
+                a.stage_batch(r0, [cur[s] for s in run], pos, None, hid, out_off=r0 * hp.hidden * 4)
+                b.stage_batch(r0, None, pos, hid, tokb, in_off=r0 * hp.hidden * 4, out_off=r0 * 4)
+        ctx.sync()
+        picks = tokb.download(np.int32, S)
+        for s in range(S):
+            if step >= lag[s]:
+                cur[s] = int(picks[s])
+                got[s].append(cur[s])
+    assert got == want
+    # recurrent state of the first GDN layer (stage a holds it) of the sequence the last call started with
+    st4 = a.read(L.READ_GDN_STATE, np.float32, hp.gdn_heads * hp.gdn_dim ** 2, 0)
+    assert np.array_equal(st4.view(np.uint32), want_state[4].view(np.uint32))
+    a.close(); b.close()
+    hid.free(); tokb.free()
