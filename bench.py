@@ -89,23 +89,8 @@ class ClockSampler:
 
 
 def build_full_model(hp, seed=0):
-    """Seeded synthetic tensors of the 9B shape. Generating 8.9e9 trits in numpy takes minutes, so one
-    GDN block, one attention block and one FFN set are generated and reused for every block, and the two
-    vocab-sized tensors tile a 16384-row chunk. Timing depends on shapes and bytes, not on values."""
-    from bonsai_vk_b200 import ptq, synth
-    cache, tensors = {}, {}
-    for name, spec in synth.tensor_shapes(hp).items():
-        key = name.split(".", 2)[-1] if name.startswith("blk.") else name
-        if key in ("token_embd.weight", "output.weight"):
-            if "vocab" not in cache:
-                chunk = ptq.synth_matrix(np.random.default_rng(seed + 1), 16384, hp.hidden)
-                cache["vocab"] = np.concatenate([chunk] * ((hp.vocab + 16383) // 16384), axis=0)[:hp.vocab]
-            tensors[name] = cache["vocab"]
-            continue
-        if key not in cache:
-            cache[key] = synth.make_tensor(hp, seed, name, spec)
-        tensors[name] = cache[key]
-    return tensors, synth.make_signs(hp, seed)
+    from bonsai_vk_b200 import synth
+    return synth.make_model_repeated(hp, seed)
 
 
 def cpu_gemv_tokens_per_s(seconds=12.0, threads=None):
@@ -149,6 +134,11 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     fwd, back = dist.new_group(list(range(world))), dist.new_group(list(range(world)))
     S, CTX = 64, 8192
+    # micro-batch = sequences that move through the stages together (one pass of the tensor-core projection kernel
+    # reads the stage's weights once for all of them). Default: as many micro-batches as twice the stages.
+    MB = a.microbatch if a.microbatch > 0 else max(1, min(32, S // (2 * world)))
+    assert S % MB == 0, "the micro-batch size must divide 64"
+    U = S // MB
     b0, b1 = split_blocks(32, world)[rank]
     ctx = Context(local)
     # one explicit (non-default) stream for our kernels and, through torch, for the NCCL dependencies: the legacy
@@ -156,24 +146,28 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     work_stream = torch.cuda.Stream(device=local)
     torch.cuda.set_stream(work_stream)
     ctx.use_stream(work_stream.cuda_stream)
-    hp = synth.HParams(cap=CTX, n_streams=S, block_begin=b0, block_end=b1)
+    hp = synth.HParams(cap=CTX, n_streams=S, block_begin=b0, block_end=b1, batch_cols=MB if MB > 1 else 0)
     tensors, signs = build_full_model(hp)
     m = Model(ctx, hp, tensors, signs)
     del tensors
     total = 2 * (K + Wm) + 8
-    pos0 = [CTX - total - 1] * S
+    pos0 = [CTX - total - 1] * U
     dev = torch.device("cuda", local)
-    # Capture and instantiate every stream's stage graph now, before any NCCL kernel is in flight: a graph
+    # Capture and instantiate every micro-batch's stage graph now, before any NCCL kernel is in flight: a graph
     # instantiation may synchronise the device, and a device that is running a send/recv kernel which waits
     # for its peer must not be asked to do that.
-    scratch_in = ctx.wrap(torch.zeros(hp.hidden, dtype=torch.float32, device=dev).data_ptr(), hp.hidden * 4)
-    scratch_out = ctx.alloc(hp.hidden * 4)
-    for s in range(S):
-        m.stage(s, 1 if rank == 0 else 0, pos0[s], None if rank == 0 else scratch_in, scratch_out)
+    width = MB * (hp.hidden if rank > 0 else 1)
+    scratch_in = ctx.wrap(torch.zeros(MB * hp.hidden, dtype=torch.float32, device=dev).data_ptr(), MB * hp.hidden * 4)
+    scratch_out = ctx.alloc(MB * hp.hidden * 4)
+    for u in range(U):
+        if MB > 1:
+            m.stage_batch(u * MB, [1] * MB if rank == 0 else None, [pos0[u]] * MB, None if rank == 0 else scratch_in, scratch_out)
+        else:
+            m.stage(u, 1 if rank == 0 else 0, pos0[u], None if rank == 0 else scratch_in, scratch_out)
     torch.cuda.synchronize()
     m.reset()
     for s in range(S):
-        m.fill_kv(s, pos0[s])
+        m.fill_kv(s, pos0[0])
     torch.cuda.synchronize()
     wraps = {}
 
@@ -183,15 +177,21 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
             wraps[key] = ctx.wrap(key, t.numel() * t.element_size())
         return wraps[key]
 
-    def stage(s, step, pos, tok_first, tok_in, hin, out):
-        if rank == 0:
-            m.stage(s, tok_first if tok_first is not None else -1, pos, wrap(tok_in) if tok_in is not None else None, wrap(out))
+    def stage(u, step, pos, tok_first, tok_in, hin, out):
+        if MB > 1:
+            if rank == 0:
+                m.stage_batch(u * MB, tok_first, [pos] * MB, wrap(tok_in) if tok_in is not None else None, wrap(out))
+            else:
+                m.stage_batch(u * MB, None, [pos] * MB, wrap(hin), wrap(out))
+        elif rank == 0:
+            m.stage(u, tok_first if tok_first is not None else -1, pos, wrap(tok_in) if tok_in is not None else None, wrap(out))
         else:
-            m.stage(s, 0, pos, wrap(hin), wrap(out))
+            m.stage(u, 0, pos, wrap(hin), wrap(out))
 
-    pipe = Pipeline(dist, rank, world, S, stage, lambda: torch.zeros(hp.hidden, dtype=torch.float32, device=dev),
-                    lambda: torch.zeros(1, dtype=torch.int32, device=dev), fwd, back)
-    first = [int(t) for t in np.random.default_rng(42).integers(0, hp.vocab, size=S)]
+    pipe = Pipeline(dist, rank, world, U, stage, lambda: torch.zeros(MB * hp.hidden, dtype=torch.float32, device=dev),
+                    lambda: torch.zeros(MB, dtype=torch.int32, device=dev), fwd, back)
+    toks = [int(t) for t in np.random.default_rng(42).integers(0, hp.vocab, size=S)]
+    first = [toks[u * MB:(u + 1) * MB] for u in range(U)] if MB > 1 else toks
 
     def timed(n_steps, p0, collect):
         torch.cuda.synchronize(); dist.barrier()
@@ -218,19 +218,19 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     tok_s = S * K / (ms_dev / 1000.0)
     e2e = S * K / (ms_e2e / 1000.0)
     cfg = dict(base["config"], workload=f"config 4: 9B-shape synthetic model layer-pipelined over {world} GPUs "
-               f"({b1 - b0} blocks per stage), 64 concurrent sequences at context {CTX} (KV marked filled), greedy decode",
-               parallelism=f"pp{world}", streams=S, context=CTX)
+               f"({b1 - b0} blocks per stage), 64 concurrent sequences at context {CTX} (KV marked filled) in {U} micro-batches "
+               f"of {MB}, greedy decode", parallelism=f"pp{world}", streams=S, context=CTX, microbatch=MB)
     line = dict(base, metric="decode tok/s, 9B ternary (PTQ1_0), 64 streams pipelined", config=cfg, value=tok_s,
                 ms_per_step=ms_dev / K, clocks=clocks, gpu_launches=int(launches),
                 e2e={"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4 * S})
     if rank == 0:
         peak, which = peaks()
-        # per GPU and step: every sequence re-reads the stage's weights (no batched GEMM yet) plus its own state and KV
+        # per GPU and step: every micro-batch reads the stage's weights once; every sequence its own state and KV
         w_stage = (PTQ_BYTES_PER_TOKEN - 222_494_720) / world
-        per_gpu = S * (w_stage + (2 * 50_331_648 + 29_411_328) / world) + S * (8 / world) * CTX * 2176
+        per_gpu = U * w_stage + S * ((2 * 50_331_648 + 29_411_328) / world) + S * (8 / world) * CTX * 2176
         ach = per_gpu / (ms_dev / K / 1000.0) / 1e9
         line["roofline"] = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
-                            "peak_source": which, "kernel": "per-GPU stage bytes per step (weights re-read per sequence + state + KV)"}
+                            "peak_source": which, "kernel": "per-GPU stage bytes per step (weights once per micro-batch + per-sequence state + KV)"}
         print(json.dumps(line))
     m.close()
     ctx.close()
@@ -244,6 +244,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--prompt", type=int, default=16, help="prompt length in tokens (16 = the benchmark config)")
+    ap.add_argument("--microbatch", type=int, default=0, help="N > 1: sequences per micro-batch (0 = 64 / (2 x GPUs), 1 = one sequence per pass)")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

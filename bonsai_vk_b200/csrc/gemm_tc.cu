@@ -102,6 +102,15 @@ template <> __device__ __forceinline__ void tmem_ld<8>(uint32_t taddr, uint32_t 
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr) : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]) : "r"(taddr) : "memory");
+}
+
 // Four packed bytes (5 trits each) -> five dwords of codes: o[t*stride] = codes at level t of the four bytes, in byte
 // order. T_t = (b * 3^(t+1)) >> 8 is the running base-3 prefix of byte b, and trit_t + 1 = T_t - 3 * T_(t-1)
 // (the reference decoder's v = (v*3) & 0xFF; trit = (v*3) >> 8, unrolled). The even and odd bytes sit in the 16-bit
@@ -137,26 +146,25 @@ __device__ __forceinline__ void decode_block(const uint32_t (&r)[7], uint32_t (&
 #define PROF_T0() const long long prof_t0 = a.prof ? clock64() : 0
 #define PROF_ADD(slot) do { if (a.prof) prof[slot] += clock64() - prof_t0; } while (0)
 
+// NCP = 8 or 16 columns = NG groups of 8. The tensor-core instruction always has N = 8 (its issue cost does not
+// depend on N); per block there are 4 x NG of them, and each (row quarter, group) has its own epilogue warp that
+// fetches the group's 4 x 8 accumulators with one 32-column tensor-memory load.
 template <int NCP> struct Cfg {
+    static constexpr int NG = NCP / 8;
     static constexpr int BBYTES = BK * NCP * 160;
     static constexpr int STAGE = WBYTES + BBYTES;
-    static constexpr int STAGES = BK == 8 ? (NCP == 32 ? 3 : 4) : 2;
-    static constexpr int EW = 8;                      // epilogue warps
-    static constexpr int NCW = NCP / (EW / 4);        // columns per epilogue warp
-    static constexpr int CH = 4;                      // columns per tensor-memory load (x 4 sub-blocks = 16 registers)
-    static constexpr int NCH = NCW / CH;
+    static constexpr int STAGES = 4;
+    static constexpr int EW = 4 * NG;                 // epilogue warps
     static constexpr int DW = 4;                      // decode warps (one per quarter of the rows)
     static constexpr int NWARPS = DW + EW + 1 + 4;    // decode, epilogue, producer, 4 MMA issuers (one per sub-block)
-    // slots in flight: the hops decode -> MMA -> commit -> epilogue -> slot free each cost a few hundred cycles, so
-    // several blocks must be in flight to keep the decode and epilogue warps busy
     // operand slot i and accumulator slot i belong to the same block, so one "done" barrier per slot (armed by the
     // MMA issuers' commits) tells the epilogue that the accumulators are ready and the decode warps that the operand
-    // slot may be overwritten
-    static constexpr int NA = NCP == 8 ? 8 : (NCP == 16 ? 4 : 3);
-    static constexpr int ND = NA;
+    // slot may be overwritten. Several blocks are in flight: each hop (decode -> MMA -> commit -> epilogue -> slot
+    // free) costs a few hundred cycles.
+    static constexpr int NA = NG == 1 ? 8 : 5;
     static constexpr int D_COL = NA * 32;
     static constexpr int TMEM_COLS = 512;
-    static_assert(D_COL + ND * 4 * NCP <= 512 && NA + ND <= DWS, "tensor memory budget");
+    static_assert(D_COL + NA * NG * 32 <= 512 && 2 * NA <= DWS, "tensor memory budget");
     static constexpr size_t SMEM = size_t(STAGES) * STAGE + DWS * 128 * 4 + 512;
 };
 
@@ -171,7 +179,7 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
     uint64_t *aempty = dfull;                      // "done": all four sub-block MMAs of the slot's block have completed
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 40);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    constexpr int NA = C::NA, ND = C::ND, D_COL = C::D_COL, EW = C::EW, DW = C::DW;
+    constexpr int NA = C::NA, NG = C::NG, D_COL = C::D_COL, EW = C::EW, DW = C::DW;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nb = a.K / 128, nkc = nb / BK, ntiles = (a.M + 127) / 128;
@@ -226,21 +234,22 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
         //      cycles whatever its size, so the four go out in parallel) --------------------------------------------
         if (lane == 0) {
             const int sb = warp - (DW + EW + 1);
-            // D s32, A u8, B s8, both K-major, N = NCP, M = 128
-            const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (uint32_t(NCP >> 3) << 17) | (uint32_t(128 >> 4) << 24);
-            const uint32_t LBO = (NCP / 8) * 128, SBO = 128;
+            // D s32, A u8, B s8, both K-major, N = 8, M = 128
+            const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (uint32_t(8 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
             bool ok = true;
             int s = 0, sph = 0, slot = 0, aph = 0, dph = 1;
             long long prof[4] = {0, 0, 0, 0};
             for (int it = 0; it < n_items && ok; ++it) {
                 { PROF_T0(); if (!mbar_wait(full + s, sph, a.err, abort_flag)) break; PROF_ADD(0); }
-                const uint32_t bbase = smem_u32(ring + size_t(s) * C::STAGE + WBYTES) + sb * (NCP * 32);
+                const uint32_t bbase = smem_u32(ring + size_t(s) * C::STAGE + WBYTES) + sb * 256;
                 for (int j = 0; j < BK; ++j) {
                     { PROF_T0(); if (!mbar_wait(afull + slot, aph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(1); }
                     { PROF_T0(); if (!mbar_wait(dempty + slot, dph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(2); }
                     tc_fence_after();
-                    tc_mma_i8(tb + D_COL + slot * 4 * NCP + sb * NCP, tb + A_COL + slot * 32 + sb * 8,
-                              smem_desc(bbase + j * (NCP * 160), LBO, SBO), idesc, 0u);
+#pragma unroll
+                    for (int gi = 0; gi < NG; ++gi)
+                        tc_mma_i8(tb + D_COL + (slot * NG + gi) * 32 + sb * 8, tb + A_COL + slot * 32 + sb * 8,
+                                  smem_desc(bbase + j * (NCP * 160) + gi * 1024, 128, 128), idesc, 0u);
                     tc_commit(dfull + slot);
                     if (++slot == NA) { slot = 0; aph ^= 1; dph ^= 1; }
                 }
@@ -296,137 +305,78 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
         publish();
         if (a.prof && blockIdx.x == 0 && warp == 0 && lane == 0) for (int i = 0; i < 4; ++i) a.prof[i] = prof[i];
     } else {
-        // ---- epilogue (warps DW .. DW+EW-1) ------------------------------------------------------------------
-        // unit = (block, chunk of CH columns). The tensor-memory load of the next unit is in flight while this one
-        // is combined. Two cursors walk the blocks in order: one for the loads, one for the arithmetic.
-        const int q = warp & 3, part = (warp - DW) >> 2, row = q * 32 + lane;
+        // ---- epilogue (warps DW .. DW+EW-1): warp (quarter q, group gi) owns 32 rows x 8 columns -------------------
+        const int q = warp & 3, gi = (warp - DW) >> 2, row = q * 32 + lane;
         const uint32_t lane_base = uint32_t(q * 32) << 16;
-        const int c0 = part * C::NCW;
-        constexpr int NCH = C::NCH, NCW = C::NCW;
-        float acc[NCW], u[NCW], ve[NCW];
+        const int c0 = gi * 8;
+        float acc[8], u[8], ve[8];
 #pragma unroll
-        for (int c = 0; c < NCW; ++c) { acc[c] = 0.0f; u[c] = 0.0f; ve[c] = 0.0f; }
-        const int n_blocks = n_items * BK;
+        for (int c = 0; c < 8; ++c) { acc[c] = 0.0f; u[c] = 0.0f; ve[c] = 0.0f; }
         bool ok = true;
         long long prof[4] = {0, 0, 0, 0};
-        // load cursor
-        int lg = 0, lds = 0, ldph = 0, lj = 0, ls = 0, lsph = 0;
-        auto issue = [&](int chunk, uint32_t (&buf)[4][C::CH]) {
-            if (lg >= n_blocks || !ok) return;
-            if (chunk == 0) {
-                PROF_T0();
-                if (lj == 0 && !mbar_wait(full + ls, lsph, a.err, abort_flag)) { ok = false; return; }
-                if (!mbar_wait(dfull + lds, ldph, a.err, abort_flag)) { ok = false; return; }
-                tc_fence_after();
-                PROF_ADD(0);
-            }
+        int s = 0, sph = 0, slot = 0, dph = 0, g = 0;
+        for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x)
+            for (int kc = 0; kc < nkc && ok; ++kc) {
+                { PROF_T0(); if (!mbar_wait(full + s, sph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(0); }
+                const unsigned char *stage_scales = ring + size_t(s) * C::STAGE + WBYTES + NCP * 128 + c0 * 32;
+#pragma unroll 1
+                for (int j = 0; j < BK; ++j, ++g) {
+                    { PROF_T0(); if (!mbar_wait(dfull + slot, dph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(0); }
+                    tc_fence_after();
+                    uint32_t d[32];                         // [sub-block][column]
+                    tmem_ld32(tb + lane_base + D_COL + (slot * NG + gi) * 32, d);
+                    const float dw = dwv[(g % DWS) * 128 + row];
+                    const unsigned char *scales = stage_scales + j * (NCP * 160);
+                    { PROF_T0(); asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); PROF_ADD(1); }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(dempty + slot);      // the accumulators are in registers: the slot is free
+                    if (++slot == NA) { slot = 0; dph ^= 1; }
+                    PROF_T0();
+                    const int b = kc * BK + j, bi = b & 3;
+                    float v[8];
 #pragma unroll
-            for (int sb = 0; sb < 4; ++sb)
-                tmem_ld<C::CH>(tb + lane_base + D_COL + lds * 4 * NCP + sb * NCP + c0 + chunk * C::CH, buf[sb]);
-            if (chunk == NCH - 1) {
-                ++lg;
-                if (++lds == ND) { lds = 0; ldph ^= 1; }
-                if (++lj == BK) { lj = 0; if (++ls == C::STAGES) { ls = 0; lsph ^= 1; } }
-            }
-        };
-        // arithmetic cursor
-        int cg = 0, cds = 0, cj = 0, cs = 0, cb = 0, ct = blockIdx.x;
-        auto finish = [&](int chunk) {              // the unit's columns are in registers; after the last chunk the slot is free
-            PROF_T0();
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            PROF_ADD(1);
-            if (chunk == NCH - 1) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(dempty + cds);
-            }
-        };
-        // the unit's scale pairs (d, s) x 4 sub-blocks x CH columns and the rows' block scale: independent of the
-        // accumulators, so they are fetched before the wait for the tensor-memory load
-        struct Scales { float4 a[C::CH], b[C::CH]; float dw; };
-        auto load_scales = [&](int chunk, Scales &sc) {
-            const unsigned char *scales = ring + size_t(cs) * C::STAGE + WBYTES + cj * (NCP * 160) + NCP * 128 + (c0 + chunk * C::CH) * 32;
+                    for (int c = 0; c < 8; ++c) {           // straight-line: the columns' dependency chains interleave
+                        const float4 s01 = *reinterpret_cast<const float4 *>(scales + c * 32);
+                        const float4 s23 = *reinterpret_cast<const float4 *>(scales + c * 32 + 16);
+                        const float t0 = fmaf(s01.x, __fsub_rn(__uint_as_float(MAGIC + d[c]), 12582912.0f), -s01.y);
+                        const float t1 = fmaf(s01.z, __fsub_rn(__uint_as_float(MAGIC + d[8 + c]), 12582912.0f), -s01.w);
+                        const float t2 = fmaf(s23.x, __fsub_rn(__uint_as_float(MAGIC + d[16 + c]), 12582912.0f), -s23.y);
+                        const float t3 = fmaf(s23.z, __fsub_rn(__uint_as_float(MAGIC + d[24 + c]), 12582912.0f), -s23.w);
+                        v[c] = __fmul_rn(dw, __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3)));
+                    }
+                    if (bi == 0 || bi == 2) {
 #pragma unroll
-            for (int c = 0; c < C::CH; ++c) {
-                sc.a[c] = *reinterpret_cast<const float4 *>(scales + c * 32);
-                sc.b[c] = *reinterpret_cast<const float4 *>(scales + c * 32 + 16);
-            }
-            sc.dw = dwv[(cg % DWS) * 128 + row];
-        };
-        auto combine = [&](int chunk, uint32_t (&buf)[4][C::CH], const Scales &sc) {
-            PROF_T0();
-            const float dw = sc.dw;
-            const int bi = cb & 3;
-            float v[C::CH];
+                        for (int c = 0; c < 8; ++c) ve[c] = v[c];
+                    } else if (bi == 1) {
 #pragma unroll
-            for (int c = 0; c < C::CH; ++c) {       // straight-line: the columns' dependency chains interleave
-                const float4 s01 = sc.a[c], s23 = sc.b[c];
-                const float t0 = fmaf(s01.x, __fsub_rn(__uint_as_float(MAGIC + buf[0][c]), 12582912.0f), -s01.y);
-                const float t1 = fmaf(s01.z, __fsub_rn(__uint_as_float(MAGIC + buf[1][c]), 12582912.0f), -s01.w);
-                const float t2 = fmaf(s23.x, __fsub_rn(__uint_as_float(MAGIC + buf[2][c]), 12582912.0f), -s23.y);
-                const float t3 = fmaf(s23.z, __fsub_rn(__uint_as_float(MAGIC + buf[3][c]), 12582912.0f), -s23.w);
-                v[c] = __fmul_rn(dw, __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3)));
-            }
-            if (bi == 0 || bi == 2) {
+                        for (int c = 0; c < 8; ++c) u[c] = __fadd_rn(ve[c], v[c]);
+                    } else {
+                        const bool first = b < 4;
 #pragma unroll
-                for (int c = 0; c < C::CH; ++c) ve[chunk * C::CH + c] = v[c];
-            } else if (bi == 1) {
-#pragma unroll
-                for (int c = 0; c < C::CH; ++c) u[chunk * C::CH + c] = __fadd_rn(ve[chunk * C::CH + c], v[c]);
-            } else {
-                const bool first = cb < 4;
-#pragma unroll
-                for (int c = 0; c < C::CH; ++c) {
-                    const int ci = chunk * C::CH + c;
-                    const float p = __fadd_rn(u[ci], __fadd_rn(ve[ci], v[c]));
-                    acc[ci] = first ? p : __fadd_rn(acc[ci], p);
-                }
-            }
-            if (chunk == NCH - 1) {
-                if (cb == nb - 1) {
-                    const int grow = ct * 128 + row;
-                    if (grow < a.M) {
-#pragma unroll
-                        for (int c = 0; c < NCW; ++c) {
-                            if (c0 + c >= a.ncol) continue;
-                            float r = acc[c];
-                            if (a.resid) r = __fadd_rn(r, a.resid[size_t(c0 + c) * a.resid_stride + grow]);
-                            a.out[size_t(c0 + c) * a.out_stride + grow] = r;
+                        for (int c = 0; c < 8; ++c) {
+                            const float p = __fadd_rn(u[c], __fadd_rn(ve[c], v[c]));
+                            acc[c] = first ? p : __fadd_rn(acc[c], p);
                         }
                     }
-                }
-                ++cg;
-                if (++cds == ND) cds = 0;
-                if (++cb == nb) { cb = 0; ct += gridDim.x; }
-                if (++cj == BK) {                   // the stage's scales and weights are not needed any more
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(empty + cs);
-                    cj = 0;
-                    if (++cs == C::STAGES) cs = 0;
-                }
-            }
-            PROF_ADD(2);
-        };
-        uint32_t buf0[4][C::CH], buf1[4][C::CH];
-        Scales sc;
-        issue(0, buf0);
-        if constexpr (NCH == 1) {
-            for (int g = 0; g < n_blocks && ok; g += 2) {
-                load_scales(0, sc); finish(0); issue(0, buf1); combine(0, buf0, sc);
-                if (g + 1 >= n_blocks || !ok) break;
-                load_scales(0, sc); finish(0); issue(0, buf0); combine(0, buf1, sc);
-            }
-        } else {                                    // an even number of chunks per block: the buffers alternate within a block
-            for (int g = 0; g < n_blocks && ok; ++g) {
+                    if (b == nb - 1) {
+                        const int grow = t * 128 + row;
+                        if (grow < a.M) {
 #pragma unroll
-                for (int ch = 0; ch < NCH; ++ch) {
-                    load_scales(ch, sc);
-                    finish(ch);
-                    if (ch & 1) { issue((ch + 1) % NCH, buf0); combine(ch, buf1, sc); }
-                    else { issue((ch + 1) % NCH, buf1); combine(ch, buf0, sc); }
+                            for (int c = 0; c < 8; ++c) {
+                                if (c0 + c >= a.ncol) continue;
+                                float r = acc[c];
+                                if (a.resid) r = __fadd_rn(r, a.resid[size_t(c0 + c) * a.resid_stride + grow]);
+                                a.out[size_t(c0 + c) * a.out_stride + grow] = r;
+                            }
+                        }
+                    }
+                    PROF_ADD(2);
                 }
+                __syncwarp();
+                if (ok && lane == 0) mbar_arrive(empty + s);    // the stage's scales and weights are not needed any more
+                if (++s == C::STAGES) { s = 0; sph ^= 1; }
             }
-        }
         if (a.prof && blockIdx.x == 0 && warp == DW && lane == 0) for (int i = 0; i < 4; ++i) a.prof[8 + i] = prof[i];
     }
     tc_fence_before();
@@ -449,22 +399,26 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
     pdl_sync();
     extern __shared__ float s[];                   // chunk floats
     __shared__ float part[256];
-    const int c = blockIdx.y, tid = threadIdx.x;
+    // more than 16 columns are kept as two independent 16-column images, one after the other
+    const int cg = blockIdx.y, tid = threadIdx.x;
+    const int c = ncp == 32 ? (cg & 15) : cg;
     const size_t base = size_t(blockIdx.x) * chunk;
+    if (ncp == 32) ncp = 16;
     const size_t blk_bytes = size_t(ncp) * 160;
-    if (c >= a.ncol) {                             // padding column: zero codes and scales
+    unsigned char *image = a.image + (cg >> 4) * (size_t(a.K / 128) * 16 * 160) * (cg >= 16 ? 1 : 0);
+    if (cg >= a.ncol) {                             // padding column: zero codes and scales
         for (int e = tid * 16; e < chunk; e += 512 * 16) {
             const size_t b = (base + e) / 128;
             const int sb = (e & 127) >> 5, kh = (e >> 4) & 1;
-            *reinterpret_cast<uint4 *>(a.image + b * blk_bytes + ((sb * 2 + kh) * (ncp / 8) + c / 8) * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4 *>(image + b * blk_bytes + (c / 8) * 1024 + (sb * 2 + kh) * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
         }
         for (int e = tid * 32; e < chunk; e += 512 * 32) {
             const size_t b = (base + e) / 128;
-            *reinterpret_cast<float2 *>(a.image + b * blk_bytes + size_t(ncp) * 128 + (c * 4 + ((e & 127) >> 5)) * 8) = make_float2(0.0f, 0.0f);
+            *reinterpret_cast<float2 *>(image + b * blk_bytes + size_t(ncp) * 128 + (c * 4 + ((e & 127) >> 5)) * 8) = make_float2(0.0f, 0.0f);
         }
         return;
     }
-    const float *x = a.x + size_t(c) * a.x_stride;
+    const float *x = a.x + size_t(cg) * a.x_stride;
     float inv = 1.0f;
     if (a.mode == PREP_NORM) {
         // same partial sums as the stand-alone norm kernel: 256 lanes, each its consecutive run, then the tree
@@ -479,7 +433,7 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
         }
         const float ss = block_tree_sum(part, 256);
         inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, float(a.K)), a.eps)));
-        if (a.inv_out && blockIdx.x == 0 && tid == 0) a.inv_out[size_t(c) * a.inv_stride] = inv;
+        if (a.inv_out && blockIdx.x == 0 && tid == 0) a.inv_out[size_t(cg) * a.inv_stride] = inv;
     }
     for (int i = tid; i < chunk; i += 512) {
         float v = x[base + i];
@@ -519,8 +473,8 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
         for (int k = 16; k > 0; k >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, k);
         const size_t b = (base + e) / 128;
         const int sb = (e & 127) >> 5, kh = (e >> 4) & 1;
-        unsigned char *blk = a.image + b * blk_bytes;
-        blk[((sb * 2 + kh) * (ncp / 8) + c / 8) * 128 + (c & 7) * 16 + (e & 15)] = uint8_t(int8_t(qi));
+        unsigned char *blk = image + b * blk_bytes;
+        blk[(c / 8) * 1024 + (sb * 2 + kh) * 128 + (c & 7) * 16 + (e & 15)] = uint8_t(int8_t(qi));
         if (lane == 0) {
             const float df = half_bits_to_float(float_to_half_bits(d));
             const float sf = half_bits_to_float(float_to_half_bits(__fmul_rn(d, float(sum))));
@@ -580,7 +534,16 @@ cudaError_t launch_gemm(cudaStream_t st, int sm_count, const GemmArgs &a, bool p
     const int ncp = gemm_padded_cols(a.ncol);
     if (ncp == 8) return launch_t<8>(st, sm_count, a, pdl);
     if (ncp == 16) return launch_t<16>(st, sm_count, a, pdl);
-    return launch_t<32>(st, sm_count, a, pdl);
+    // 17..32 columns: two passes of 16 over their own images (the second pass finds the weights in L2 where they fit)
+    GemmArgs h = a;
+    h.ncol = 16;
+    cudaError_t e = launch_t<16>(st, sm_count, h, pdl);
+    if (e != cudaSuccess) return e;
+    h.ncol = a.ncol - 16;
+    h.image = a.image + size_t(a.K / 128) * 16 * 160;
+    h.out = a.out + 16 * a.out_stride;
+    if (a.resid) h.resid = a.resid + 16 * a.resid_stride;
+    return launch_t<16>(st, sm_count, h, pdl);
 }
 
 size_t gemm_tiled_bytes(int M, int K) { return size_t((M + 127) / 128) * (K / 128 / BK) * TBYTES; }

@@ -4,6 +4,8 @@
   python -m bonsai_vk_b200.kernel_lab M K [ITER] [--nocheck]
   python -m bonsai_vk_b200.kernel_lab attn CTX [ITER]      one decode-attention layer (16/4 heads x 256, q8_0 K and V)
   python -m bonsai_vk_b200.kernel_lab gemm M K NCOL [ITER]  the multi-column tensor-core projection (tcgen05), timed
+  python -m bonsai_vk_b200.kernel_lab stage NBLOCKS NCOL CTX [ITER]   one pipeline stage (first NBLOCKS blocks of the 9B
+                                            shape) for NCOL sequences per pass at context CTX, timed per pass
 
 Prints max|err| and rel against the CPU checker (when oracle/ is built), then ms/op, Gop/s and GB/s of
 PTQ1_0 bytes from CUDA events. Timing rotates through enough copies of the matrix to exceed L2.
@@ -115,8 +117,46 @@ def gemm_lab(argv):
     return 0 if same else 1
 
 
+def stage_lab(argv):
+    """One stage of the layer pipeline on one GPU: blocks [0, NBLOCKS) of the 9B shape, NCOL sequences per pass."""
+    from bonsai_vk_b200 import Context, Model, synth
+    nblocks, ncol, ctx_len = int(argv[0]), int(argv[1]), int(argv[2])
+    iters = int(argv[3]) if len(argv) > 3 else 5
+    ctx = Context(0)
+    hp = synth.HParams(cap=ctx_len + 64, n_streams=ncol, block_begin=0, block_end=nblocks, batch_cols=ncol if ncol > 1 else 0)
+    tensors, signs = synth.make_model_repeated(hp)
+    m = Model(ctx, hp, tensors, signs)
+    del tensors
+    out = ctx.alloc(ncol * hp.hidden * 4)
+    for s in range(ncol):
+        m.fill_kv(s, ctx_len)
+    pos = ctx_len
+
+    def one(p):
+        if ncol > 1:
+            m.stage_batch(0, [1 + c for c in range(ncol)], [p] * ncol, None, out)
+        else:
+            m.stage(0, 1, p, None, out)
+
+    for i in range(3):
+        one(pos + i)
+    ctx.sync()
+    e0, e1 = ctx.event(), ctx.event()
+    ctx.record(e0)
+    for i in range(iters):
+        one(pos + 3 + i)
+    ctx.record(e1)
+    ms = ctx.elapsed_ms(e0, e1) / iters
+    print(f"stage of {nblocks} blocks, {ncol} sequences per pass, context {ctx_len}: {ms:.3f} ms per pass, "
+          f"{ms / ncol * 1000:.1f} us per sequence, {ms / nblocks * 1000:.1f} us per block")
+    m.close()
+    ctx.close()
+
+
 def main(argv):
     from bonsai_vk_b200 import Context, ptq
+    if argv and argv[0] == "stage":
+        return stage_lab(argv[1:])
     if argv and argv[0] == "attn":
         return attn_lab(argv[1:])
     if argv and argv[0] == "gemm":

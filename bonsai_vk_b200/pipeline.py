@@ -63,7 +63,11 @@ class Pipeline:
       first stage : tok_first (int, step 0) or tok_in (tensor holding one int32, later steps) -> out (hidden)
       middle      : hidden_in -> out (hidden)
       last stage  : hidden_in -> out (tensor holding one int32: the pick)
-    new_hidden() / new_token() allocate the message tensors on the right device."""
+    new_hidden() / new_token() allocate the message tensors on the right device.
+
+    A "stream" may also be a micro-batch of several sequences that move through the stages together (the stage
+    function then runs them in one pass): the messages are [sequences x hidden] and [sequences] tensors, first_tokens[s]
+    is a list, and every sequence of the micro-batch is at position pos0[s] + step."""
 
     def __init__(self, dist, rank: int, world: int, n_streams: int, stage_fn: Callable, new_hidden: Callable,
                  new_token: Callable, fwd_group=None, back_group=None):
@@ -117,4 +121,7 @@ class Pipeline:
         for h in send_h + send_t:
             if h is not None:
                 h.wait()
-        return [[int(t.item()) for t in row] for row in self.picks] if (self.last and collect) else None
+        if not (self.last and collect):
+            return None
+        # one int per step for a single sequence, a list of ints per step for a micro-batch of sequences
+        return [[int(t.item()) if t.numel() == 1 else [int(v) for v in t.tolist()] for t in row] for row in self.picks]

@@ -130,3 +130,31 @@ def make_model(hp: HParams, seed: int = 0):
     streaming GGUF writer instead."""
     tensors = {n: make_tensor(hp, seed, n, s) for n, s in tensor_shapes(hp).items()}
     return tensors, make_signs(hp, seed)
+
+
+def make_model_repeated(hp: HParams, seed: int = 0):
+    """Seeded synthetic tensors of a large shape, quickly: generating 8.9e9 trits in numpy takes minutes, so one
+    GDN block, one attention block and one FFN set are generated and reused for every block, and the two
+    vocab-sized tensors tile a 16384-row chunk. Timing depends on shapes and bytes, not on values. Only the
+    tensors of the local blocks [block_begin, block_end) are produced."""
+    cache, tensors = {}, {}
+    b0, b1 = hp.block_begin, (hp.block_end or hp.n_layer)
+    for name, spec in tensor_shapes(hp).items():
+        if name.startswith("blk."):
+            if not (b0 <= int(name.split(".")[1]) < b1):
+                continue
+            key = name.split(".", 2)[-1]
+        else:
+            key = name
+            if (name == "token_embd.weight" and b0 != 0) or (name != "token_embd.weight" and b1 != hp.n_layer):
+                continue
+        if key in ("token_embd.weight", "output.weight"):
+            if "vocab" not in cache:
+                chunk = ptq.synth_matrix(np.random.default_rng(seed + 1), 16384, hp.hidden)
+                cache["vocab"] = np.concatenate([chunk] * ((hp.vocab + 16383) // 16384), axis=0)[:hp.vocab]
+            tensors[name] = cache["vocab"]
+            continue
+        if key not in cache:
+            cache[key] = make_tensor(hp, seed, name, spec)
+        tensors[name] = cache[key]
+    return tensors, make_signs(hp, seed)

@@ -35,13 +35,16 @@ def _gemm(ctx, W, M, K, X, signs=None, hat_block=0, out_stride=0, tiled=False):
 
 def _image_column(img, K, ncol, c):
     """q8_1 record of column c rebuilt from the image: (codes [K] int8, d [K/32] f32, s [K/32] f32)."""
-    ncp = 8 if ncol <= 8 else (16 if ncol <= 16 else 32)
     nb = K // 128
-    blocks = img.reshape(nb, ncp * 160)
+    ncp = 8 if ncol <= 8 else 16
+    if ncol > 16:                       # two 16-column images, one after the other
+        half = nb * 16 * 160
+        img, c = img[(c // 16) * half:(c // 16 + 1) * half], c % 16
+    blocks = img[:nb * ncp * 160].reshape(nb, ncp * 160)
     codes = np.empty((nb, 4, 2, 16), dtype=np.int8)
     for sb in range(4):
         for kh in range(2):
-            off = ((sb * 2 + kh) * (ncp // 8) + c // 8) * 128 + (c % 8) * 16
+            off = (c // 8) * 1024 + (sb * 2 + kh) * 128 + (c % 8) * 16
             codes[:, sb, kh, :] = blocks[:, off:off + 16].view(np.int8)
     ds = np.ascontiguousarray(blocks[:, ncp * 128 + c * 32: ncp * 128 + c * 32 + 32]).view(np.float32).reshape(nb, 4, 2)
     return codes.reshape(K), ds[:, :, 0].reshape(-1), ds[:, :, 1].reshape(-1)

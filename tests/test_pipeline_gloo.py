@@ -108,3 +108,69 @@ def test_message_schedule_on_gloo(world, tmp_path):
                 p.kill()
     assert all(p.returncode == 0 for p in procs), outs
     assert "PIPELINE_OK" in outs[-1]
+
+
+WORKER_MB = textwrap.dedent('''
+    import os, sys, torch, torch.distributed as dist
+    sys.path.insert(0, os.environ["BONSAI_ROOT"])
+    from bonsai_vk_b200.pipeline import Pipeline
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    fwd, back = dist.new_group(list(range(world))), dist.new_group(list(range(world)))
+    U, MB, T, H, V = 3, 4, 4, 8, 97          # 3 micro-batches of 4 sequences
+    def stage(u, step, pos, tok_first, tok_in, hin, out):
+        if rank == 0:
+            toks = tok_first if tok_first is not None else [int(v) for v in tok_in.tolist()]
+            h = torch.stack([torch.arange(H, dtype=torch.float32) * (t + 1) + pos + c for c, t in enumerate(toks)]).reshape(-1)
+        else:
+            h = hin.clone()
+        h = h * 1.5 + (rank + 1)
+        if rank == world - 1:
+            out.copy_((h.reshape(MB, H).sum(dim=1).to(torch.int64) % V).to(torch.int32))
+        else:
+            out.copy_(h)
+    p = Pipeline(dist, rank, world, U, stage, lambda: torch.zeros(MB * H), lambda: torch.zeros(MB, dtype=torch.int32), fwd, back)
+    first = [[3 + u * MB + c for c in range(MB)] for u in range(U)]
+    picks = p.run(first, [10 * u for u in range(U)], T)
+    if rank == world - 1:
+        want = []
+        for u in range(U):
+            toks, row = list(first[u]), []
+            for step in range(T):
+                nxt = []
+                for c, tok in enumerate(toks):
+                    h = torch.arange(H, dtype=torch.float32) * (tok + 1) + (10 * u + step) + c
+                    for r in range(world):
+                        h = h * 1.5 + (r + 1)
+                    nxt.append(int(h.sum().item()) % V)
+                toks = nxt
+                row.append(nxt)
+            want.append(row)
+        assert picks == want, (picks, want)
+        print("PIPELINE_OK")
+    dist.barrier()
+    dist.destroy_process_group()
+''')
+
+
+def test_micro_batched_schedule_on_gloo(tmp_path):
+    """The same ring with micro-batches of several sequences as the unit (vector messages)."""
+    world = 2
+    script = tmp_path / "worker_mb.py"
+    script.write_text(WORKER_MB)
+    with socket.socket() as sck:
+        sck.bind(("127.0.0.1", 0))
+        port = sck.getsockname()[1]
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   BONSAI_ROOT=ROOT)
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    try:
+        outs = [p.communicate(timeout=120)[0] for p in procs]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+    assert all(p.returncode == 0 for p in procs), outs
+    assert "PIPELINE_OK" in outs[-1]
