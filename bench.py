@@ -37,7 +37,7 @@ PTQ_BYTES_PER_TOKEN = 1_734_541_312                        # their PTQ1_0 bytes
 ALGO_BYTES_PER_TOKEN = 1_734_541_312 + 29_411_328 + 2 * 50_331_648 + 2 * 2_359_296 + 896   # + f32, GDN state r/w, conv
 
 
-NCU_TRAFFIC_RATIO = 1.019      # dram read+write / PTQ1_0 bytes of the launch (ncu, head projection 248320 x 4096)
+NCU_TRAFFIC_RATIO = 1.023      # dram read+write / PTQ1_0 bytes of the launch (ncu, head projection 248320 x 4096)
 
 
 def peaks():
@@ -337,7 +337,7 @@ def main():
         n_l = (ctx.launches - l1) // (reps + 1)
         ach = PTQ_BYTES_PER_TOKEN / (ms_g / 1000.0) / 1e9
         # DRAM bytes per algorithmic byte of k_phase_gemv, from the ncu capture summarised under profiles/
-        # (head projection: 226.7 MB moved for 222.5 MB of weights); the sweep's launches move the same ratio
+        # (head projection: 227.7 MB moved for 222.5 MB of weights); the sweep's launches move the same ratio
         line["roofline"] = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                             "traffic": NCU_TRAFFIC_RATIO * PTQ_BYTES_PER_TOKEN / n_l, "peak_source": which,
                             "kernel": f"k_phase_gemv: the {n_l} fused projection launches of one token (201 projections, "
