@@ -124,6 +124,42 @@ def cpu_gemv_tokens_per_s(seconds=12.0, threads=None):
                       f"{PTQ_WEIGHTS_PER_TOKEN} projection weights one token reads"}
 
 
+def streams64_one_gpu(ctx, tensors_again=None, steps=6, warm=2):
+    """Config 4's load on ONE GPU: all 32 blocks, 64 sequences at context 8192 (KV marked filled) as two passes of 32
+    sequences per decode step (tensor-core projection kernel: the weights are read once per pass)."""
+    from bonsai_vk_b200 import Model, synth
+    S, MB, CTX = 64, 32, 8192
+    hp = synth.HParams(cap=CTX, n_streams=S, batch_cols=MB)
+    tensors, signs = synth.make_model_repeated(hp)
+    m = Model(ctx, hp, tensors, signs)
+    del tensors
+    pos0 = CTX - (steps + warm) - 2
+    for s in range(S):
+        m.fill_kv(s, pos0)
+    toks = [ctx.alloc(MB * 4) for _ in range(S // MB)]
+    first = [int(t) for t in np.random.default_rng(7).integers(0, hp.vocab, size=S)]
+
+    def step(i):
+        for u in range(S // MB):
+            m.stage_batch(u * MB, first[u * MB:(u + 1) * MB] if i == 0 else None, [pos0 + i] * MB, None if i == 0 else toks[u], toks[u])
+
+    for i in range(warm):
+        step(i)
+    ctx.sync()
+    e0, e1 = ctx.event(), ctx.event()
+    l0 = ctx.launches
+    ctx.record(e0)
+    for i in range(warm, warm + steps):
+        step(i)
+    ctx.record(e1)
+    ms = ctx.elapsed_ms(e0, e1) / steps
+    launches = (ctx.launches - l0) // steps
+    m.close()
+    return {"value": S / (ms / 1000.0), "unit": "tok/s", "ms_per_step": ms, "streams": S, "context": CTX, "microbatch": MB,
+            "gpu_launches_per_step": int(launches),
+            "workload": "config 4 on one GPU: 64 sequences at context 8192, 2 passes of 32 sequences per decode step"}
+
+
 def pipeline_main(a, base, rank, world, local, K, Wm):
     """N > 1: layer pipeline, 64 streams, context 8192 (see the module docstring)."""
     import torch
@@ -135,8 +171,8 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     fwd, back = dist.new_group(list(range(world))), dist.new_group(list(range(world)))
     S, CTX = 64, 8192
     # micro-batch = sequences that move through the stages together (one pass of the tensor-core projection kernel
-    # reads the stage's weights once for all of them). Default: as many micro-batches as twice the stages.
-    MB = a.microbatch if a.microbatch > 0 else max(1, min(32, S // (2 * world)))
+    # reads the stage's weights once for all of them). Default: as many micro-batches as stages (32 / 16 / 8 sequences on 2 / 4 / 8 GPUs).
+    MB = a.microbatch if a.microbatch > 0 else max(1, min(32, S // world))
     assert S % MB == 0, "the micro-batch size must divide 64"
     U = S // MB
     b0, b1 = split_blocks(32, world)[rank]
@@ -244,7 +280,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--prompt", type=int, default=16, help="prompt length in tokens (16 = the benchmark config)")
-    ap.add_argument("--microbatch", type=int, default=0, help="N > 1: sequences per micro-batch (0 = 64 / (2 x GPUs), 1 = one sequence per pass)")
+    ap.add_argument("--microbatch", type=int, default=0, help="N > 1: sequences per micro-batch (0 = 64 / GPUs, at most 32; 1 = one sequence per pass)")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -349,8 +385,14 @@ def main():
                                             "frac_of_measured": ALGO_BYTES_PER_TOKEN / (ms_dev / K / 1000.0) / 1e9 / peak,
                                             "frac_of_8000": ALGO_BYTES_PER_TOKEN / (ms_dev / K / 1000.0) / 1e9 / 8000.0}}
         line["cpu_baseline"] = cpu_gemv_tokens_per_s(seconds=12.0)
-        print(json.dumps(line))
     m.close()
+    if rank == 0:
+        # the 64-sequence workload of config 4 on this one GPU (no pipeline): the base of the multi-GPU scaling
+        try:
+            line["streams64"] = streams64_one_gpu(ctx, tensors_again=None)
+        except Exception as exc:                       # the headline line must survive a failure of the extra measurement
+            line["streams64"] = {"error": str(exc)[:200]}
+        print(json.dumps(line))
     ctx.close()
     if dist is not None:
         dist.destroy_process_group()

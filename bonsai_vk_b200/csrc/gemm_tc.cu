@@ -44,16 +44,29 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *b) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t *b, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
 }
-// Bounded wait. try_wait suspends the thread until the phase completes or the time hint (ns) runs out, so a waiting
-// warp does not take issue slots from the warps that are working; after ~0.5 s in total it gives up and records it.
+// Bounded wait. try_wait suspends the thread until the phase completes or its time hint (ns) runs out; the retry loop
+// is four instructions, so a waiting warp takes few issue slots from the warps that are working. After 2^20 tries
+// (well over a second) it gives up: the error word is set and the abort flag drains every role of the CTA.
 __device__ __forceinline__ bool mbar_wait(uint64_t *b, uint32_t parity, int *err, volatile int *abort_flag) {
     const uint32_t addr = smem_u32(b);
-    for (int it = 0; it < (1 << 16); ++it) {
+    for (int round = 0; round < 1024; ++round) {
         uint32_t ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(ok) : "r"(addr), "r"(parity), "r"(8000u) : "memory");
+        asm volatile("{\n"
+                     ".reg .pred p, q;\n"
+                     ".reg .u32 n;\n"
+                     "mov.u32 n, 0;\n"
+                     "WAIT_LOOP:\n"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+                     "@p bra WAIT_DONE;\n"
+                     "add.u32 n, n, 1;\n"
+                     "setp.lt.u32 q, n, 1024;\n"
+                     "@q bra WAIT_LOOP;\n"
+                     "WAIT_DONE:\n"
+                     "selp.u32 %0, 1, 0, p;\n"
+                     "}\n"
+                     : "=r"(ok) : "r"(addr), "r"(parity), "r"(2000u) : "memory");
         if (ok) return true;
-        if ((it & 63) == 63 && *abort_flag) return false;
+        if (*abort_flag) return false;
     }
     if (err) atomicExch(err, 2);
     *abort_flag = 1;
@@ -154,7 +167,11 @@ template <int NCP> struct Cfg {
     static constexpr int BBYTES = BK * NCP * 160;
     static constexpr int STAGE = WBYTES + BBYTES;
     static constexpr int STAGES = 4;
-    static constexpr int EW = 4 * NG;                 // epilogue warps
+#ifndef GEMM_EW16
+#define GEMM_EW16 8
+#endif
+    static constexpr int EW = NG == 1 ? 4 : GEMM_EW16;   // epilogue warps: one per row quarter and GPW column groups
+    static constexpr int GPW = NG / (EW / 4);         // column groups per epilogue warp
     static constexpr int DW = 4;                      // decode warps (one per quarter of the rows)
     static constexpr int NWARPS = DW + EW + 1 + 4;    // decode, epilogue, producer, 4 MMA issuers (one per sub-block)
     // operand slot i and accumulator slot i belong to the same block, so one "done" barrier per slot (armed by the
@@ -306,12 +323,13 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
         if (a.prof && blockIdx.x == 0 && warp == 0 && lane == 0) for (int i = 0; i < 4; ++i) a.prof[i] = prof[i];
     } else {
         // ---- epilogue (warps DW .. DW+EW-1): warp (quarter q, group gi) owns 32 rows x 8 columns -------------------
-        const int q = warp & 3, gi = (warp - DW) >> 2, row = q * 32 + lane;
+        const int q = warp & 3, part = (warp - DW) >> 2, row = q * 32 + lane;
         const uint32_t lane_base = uint32_t(q * 32) << 16;
-        const int c0 = gi * 8;
-        float acc[8], u[8], ve[8];
+        constexpr int GPW = C::GPW, NCW = 8 * GPW;
+        const int c0 = part * NCW;
+        float acc[NCW], u[NCW], ve[NCW];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) { acc[c] = 0.0f; u[c] = 0.0f; ve[c] = 0.0f; }
+        for (int c = 0; c < NCW; ++c) { acc[c] = 0.0f; u[c] = 0.0f; ve[c] = 0.0f; }
         bool ok = true;
         long long prof[4] = {0, 0, 0, 0};
         int s = 0, sph = 0, slot = 0, dph = 0, g = 0;
@@ -323,47 +341,53 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
                 for (int j = 0; j < BK; ++j, ++g) {
                     { PROF_T0(); if (!mbar_wait(dfull + slot, dph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(0); }
                     tc_fence_after();
-                    uint32_t d[32];                         // [sub-block][column]
-                    tmem_ld32(tb + lane_base + D_COL + (slot * NG + gi) * 32, d);
                     const float dw = dwv[(g % DWS) * 128 + row];
                     const unsigned char *scales = stage_scales + j * (NCP * 160);
-                    { PROF_T0(); asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); PROF_ADD(1); }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(dempty + slot);      // the accumulators are in registers: the slot is free
-                    if (++slot == NA) { slot = 0; dph ^= 1; }
-                    PROF_T0();
                     const int b = kc * BK + j, bi = b & 3;
-                    float v[8];
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {           // straight-line: the columns' dependency chains interleave
-                        const float4 s01 = *reinterpret_cast<const float4 *>(scales + c * 32);
-                        const float4 s23 = *reinterpret_cast<const float4 *>(scales + c * 32 + 16);
-                        const float t0 = fmaf(s01.x, __fsub_rn(__uint_as_float(MAGIC + d[c]), 12582912.0f), -s01.y);
-                        const float t1 = fmaf(s01.z, __fsub_rn(__uint_as_float(MAGIC + d[8 + c]), 12582912.0f), -s01.w);
-                        const float t2 = fmaf(s23.x, __fsub_rn(__uint_as_float(MAGIC + d[16 + c]), 12582912.0f), -s23.y);
-                        const float t3 = fmaf(s23.z, __fsub_rn(__uint_as_float(MAGIC + d[24 + c]), 12582912.0f), -s23.w);
-                        v[c] = __fmul_rn(dw, __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3)));
-                    }
-                    if (bi == 0 || bi == 2) {
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) ve[c] = v[c];
-                    } else if (bi == 1) {
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) u[c] = __fadd_rn(ve[c], v[c]);
-                    } else {
-                        const bool first = b < 4;
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            const float p = __fadd_rn(u[c], __fadd_rn(ve[c], v[c]));
-                            acc[c] = first ? p : __fadd_rn(acc[c], p);
+                    for (int gw = 0; gw < GPW; ++gw) {
+                        uint32_t d[32];                     // [sub-block][column] of one group
+                        tmem_ld32(tb + lane_base + D_COL + (slot * NG + part * GPW + gw) * 32, d);
+                        { PROF_T0(); asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); PROF_ADD(1); }
+                        if (gw == GPW - 1) {                // all of this warp's accumulators are in registers: the slot is free
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(dempty + slot);
                         }
+                        PROF_T0();
+                        float v[8];
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {       // straight-line: the columns' dependency chains interleave
+                            const float4 s01 = *reinterpret_cast<const float4 *>(scales + (gw * 8 + c) * 32);
+                            const float4 s23 = *reinterpret_cast<const float4 *>(scales + (gw * 8 + c) * 32 + 16);
+                            const float t0 = fmaf(s01.x, __fsub_rn(__uint_as_float(MAGIC + d[c]), 12582912.0f), -s01.y);
+                            const float t1 = fmaf(s01.z, __fsub_rn(__uint_as_float(MAGIC + d[8 + c]), 12582912.0f), -s01.w);
+                            const float t2 = fmaf(s23.x, __fsub_rn(__uint_as_float(MAGIC + d[16 + c]), 12582912.0f), -s23.y);
+                            const float t3 = fmaf(s23.z, __fsub_rn(__uint_as_float(MAGIC + d[24 + c]), 12582912.0f), -s23.w);
+                            v[c] = __fmul_rn(dw, __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3)));
+                        }
+                        if (bi == 0 || bi == 2) {
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) ve[gw * 8 + c] = v[c];
+                        } else if (bi == 1) {
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) u[gw * 8 + c] = __fadd_rn(ve[gw * 8 + c], v[c]);
+                        } else {
+                            const bool first = b < 4;
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) {
+                                const float p = __fadd_rn(u[gw * 8 + c], __fadd_rn(ve[gw * 8 + c], v[c]));
+                                acc[gw * 8 + c] = first ? p : __fadd_rn(acc[gw * 8 + c], p);
+                            }
+                        }
+                        PROF_ADD(2);
                     }
+                    if (++slot == NA) { slot = 0; dph ^= 1; }
                     if (b == nb - 1) {
                         const int grow = t * 128 + row;
                         if (grow < a.M) {
 #pragma unroll
-                            for (int c = 0; c < 8; ++c) {
+                            for (int c = 0; c < NCW; ++c) {
                                 if (c0 + c >= a.ncol) continue;
                                 float r = acc[c];
                                 if (a.resid) r = __fadd_rn(r, a.resid[size_t(c0 + c) * a.resid_stride + grow]);
@@ -371,7 +395,6 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
                             }
                         }
                     }
-                    PROF_ADD(2);
                 }
                 __syncwarp();
                 if (ok && lane == 0) mbar_arrive(empty + s);    // the stage's scales and weights are not needed any more

@@ -556,14 +556,42 @@ __global__ void __launch_bounds__(256) k_attn_pv(bnk::AttnDims a, const float *_
     float acc[GQA];
 #pragma unroll
     for (int g = 0; g < GQA; ++g) acc[g] = 0.0f;
-    for (int jb = 0; jb < n; jb += 8) {
+    if (a.v_mode == 0) {
+        // q8_0 V: tiles of 32 keys x 256 bytes come in with 16-byte loads (the next tile is in flight while this one
+        // is consumed) and are walked from shared memory, key by key in ascending order as before
+        __shared__ uint4 vt[2][32 * 16];
+        __shared__ uint16_t vsc[2][32 * 8];
+        const int8_t *vd = reinterpret_cast<const int8_t *>(kv.v_data);
+        uint4 r0, r1;
+        uint16_t rs;
+        auto fetch = [&](int jb) {
+            const int k0 = min(jb + (d >> 4), n - 1), k1 = min(jb + 16 + (d >> 4), n - 1), ks = min(jb + (d >> 3), n - 1);
+            r0 = *reinterpret_cast<const uint4 *>(vd + (size_t(j0 + k0) * a.n_kv + kvh) * hd + (d & 15) * 16);
+            r1 = *reinterpret_cast<const uint4 *>(vd + (size_t(j0 + k1) * a.n_kv + kvh) * hd + (d & 15) * 16);
+            rs = kv.v_scale[(size_t(j0 + ks) * a.n_kv + kvh) * (hd / 32) + (d & 7)];
+        };
+        if (n > 0) fetch(0);
+        int buf = 0;
+        for (int jb = 0; jb < n; jb += 32, buf ^= 1) {
+            vt[buf][d] = r0; vt[buf][256 + d] = r1; vsc[buf][d] = rs;
+            __syncthreads();
+            if (jb + 32 < n) fetch(jb + 32);
+            const int8_t *tile = reinterpret_cast<const int8_t *>(vt[buf]);
+            const int lim = min(32, n - jb);
+            for (int u = 0; u < lim; ++u) {
+                const float v = __fmul_rn(half_bits_to_float(vsc[buf][u * 8 + (d >> 5)]), float(tile[u * 256 + d]));
+#pragma unroll
+                for (int g = 0; g < GQA; ++g) acc[g] = __fadd_rn(acc[g], __fmul_rn(ps[g * per + jb + u], v));
+            }
+        }
+    } else
+    for (int jb = 0; jb < n; jb += 8) {            // fp16 V
         float v[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const int jj = min(jb + u, n - 1);
             const size_t idx = (size_t(j0 + jj) * a.n_kv + kvh) * hd + d;
-            if (a.v_mode == 1) v[u] = __half2float(reinterpret_cast<const __half *>(kv.v_data)[idx]);
-            else v[u] = __fmul_rn(half_bits_to_float(kv.v_scale[idx / 32]), float(reinterpret_cast<const int8_t *>(kv.v_data)[idx]));
+            v[u] = __half2float(reinterpret_cast<const __half *>(kv.v_data)[idx]);
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
