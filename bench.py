@@ -8,7 +8,10 @@ One "step" is one decoded token (one pass of the whole-token schedule). Prints O
            the greedy pick is fed back without a host round trip), CUDA events on the launch stream.
   e2e    - the same metric through the per-token C-ABI call a host makes (bn_model_token): the token
            id and position go host->device and the pick comes device->host inside the timed region.
-  roofline / cpu_baseline - see DESIGN.md ("Measurement").
+  roofline - the token's fused projection launches (the dominant kernel) timed back to back with CUDA events:
+           algorithmic PTQ1_0 bytes / time, against the measured copy bandwidth of this GPU pool.
+  cpu_baseline - the reference's CPU arithmetic for the path, timed on the host cores on a bounded sample.
+  streams64 - (N=1 only) the 64-sequence workload of the multi-GPU configuration on this one GPU, the base of its scaling.
 --impl reference times the reference's own CPU arithmetic for the path (dequantise + fp64 dot,
 oracle/_ref when built, else the oracle port) on all host cores, in the same unit.
 N > 1 (torchrun, one rank per GPU): BASELINE config 4 - the model is layer-pipelined over the N GPUs
