@@ -458,25 +458,92 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
         inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, float(a.K)), a.eps)));
         if (a.inv_out && blockIdx.x == 0 && tid == 0) a.inv_out[size_t(cg) * a.inv_stride] = inv;
     }
-    for (int i = tid; i < chunk; i += 512) {
-        float v = x[base + i];
-        if (a.mode == PREP_NORM) v = __fmul_rn(__fmul_rn(v, inv), a.w[base + i]);
-        if (a.signs) v = __fmul_rn(v, float(a.signs[base + i]));
-        s[i] = v;
-    }
-    if (a.signs) {
-        const float hinv = 1.0f / sqrtf(float(chunk));
-        for (int h = 1; h < chunk; h <<= 1) {
-            __syncthreads();
-            for (int i = tid; i < (chunk >> 1); i += 512) {
-                const int j = ((i & ~(h - 1)) << 1) | (i & (h - 1));
-                const float p = s[j], r = s[j + h];
-                s[j] = __fadd_rn(p, r);
-                s[j + h] = __fsub_rn(p, r);
+    const int lane_id = tid & 31, warp_id = tid >> 5;
+    if (a.signs && chunk >= 256) {
+        // Sylvester butterflies (a+c, a-c), h ascending, as hat4096.comp:41-60: h = 1, 2, 4 inside a thread's 8
+        // consecutive elements, h = 8..128 across lanes; then through shared memory (h = 256..1024 inside a thread and
+        // h = 2048 between lanes l and l^16 when the chunk is 4096). Same pairs, same order: bit-identical to the plain loop.
+        if (tid < chunk / 8) {
+            const size_t tb = base + size_t(tid) * 8;
+            const float4 x0 = *reinterpret_cast<const float4 *>(x + tb), x1 = *reinterpret_cast<const float4 *>(x + tb + 4);
+            const int4 g0 = *reinterpret_cast<const int4 *>(a.signs + tb), g1 = *reinterpret_cast<const int4 *>(a.signs + tb + 4);
+            float v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            const int sg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            if (a.mode == PREP_NORM) {
+                const float4 n0 = *reinterpret_cast<const float4 *>(a.w + tb), n1 = *reinterpret_cast<const float4 *>(a.w + tb + 4);
+                const float ne[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+                for (int r = 0; r < 8; ++r) v[r] = __fmul_rn(__fmul_rn(v[r], inv), ne[r]);
             }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) v[r] = __fmul_rn(v[r], float(sg[r]));
+#pragma unroll
+            for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+                for (int r = 0; r < 8; ++r)
+                    if (!(r & h)) { const float p = v[r], q = v[r + h]; v[r] = __fadd_rn(p, q); v[r + h] = __fsub_rn(p, q); }
+#pragma unroll
+            for (int m2 = 1; m2 < 32; m2 <<= 1)
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const float pr = __shfl_xor_sync(0xFFFFFFFFu, v[r], m2);
+                    v[r] = (lane_id & m2) ? __fsub_rn(pr, v[r]) : __fadd_rn(v[r], pr);
+                }
+            float4 *dst = reinterpret_cast<float4 *>(s + tid * 8);
+            dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+            dst[1] = make_float4(v[4], v[5], v[6], v[7]);
         }
         __syncthreads();
-        for (int i = tid; i < chunk; i += 512) s[i] = __fmul_rn(s[i], hinv);
+        const float hinv = 1.0f / sqrtf(float(chunk));
+        if (chunk == 4096) {
+            const int i0 = (lane_id & 15) + 16 * warp_id + 2048 * (lane_id >> 4);
+            float u[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) u[r] = s[i0 + 256 * r];
+#pragma unroll
+            for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+                for (int r = 0; r < 8; ++r)
+                    if (!(r & h)) { const float p = u[r], q = u[r + h]; u[r] = __fadd_rn(p, q); u[r + h] = __fsub_rn(p, q); }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const float pr = __shfl_xor_sync(0xFFFFFFFFu, u[r], 16);
+                u[r] = (lane_id & 16) ? __fsub_rn(pr, u[r]) : __fadd_rn(u[r], pr);
+                s[i0 + 256 * r] = __fmul_rn(u[r], hinv);        // each thread rewrites only what it read
+            }
+        } else {
+            for (int h = 256; h < chunk; h <<= 1) {
+                for (int i = tid; i < (chunk >> 1); i += 512) {
+                    const int j = ((i & ~(h - 1)) << 1) | (i & (h - 1));
+                    const float p = s[j], r = s[j + h];
+                    s[j] = __fadd_rn(p, r);
+                    s[j + h] = __fsub_rn(p, r);
+                }
+                __syncthreads();
+            }
+            for (int i = tid; i < chunk; i += 512) s[i] = __fmul_rn(s[i], hinv);
+        }
+    } else {
+        for (int i = tid; i < chunk; i += 512) {
+            float v = x[base + i];
+            if (a.mode == PREP_NORM) v = __fmul_rn(__fmul_rn(v, inv), a.w[base + i]);
+            if (a.signs) v = __fmul_rn(v, float(a.signs[base + i]));
+            s[i] = v;
+        }
+        if (a.signs) {
+            const float hinv = 1.0f / sqrtf(float(chunk));
+            for (int h = 1; h < chunk; h <<= 1) {
+                __syncthreads();
+                for (int i = tid; i < (chunk >> 1); i += 512) {
+                    const int j = ((i & ~(h - 1)) << 1) | (i & (h - 1));
+                    const float p = s[j], r = s[j + h];
+                    s[j] = __fadd_rn(p, r);
+                    s[j + h] = __fsub_rn(p, r);
+                }
+            }
+            __syncthreads();
+            for (int i = tid; i < chunk; i += 512) s[i] = __fmul_rn(s[i], hinv);
+        }
     }
     __syncthreads();
     // q8_1 per 32 values (a warp): d = amax/127 (0 below 1e-35), q = round-half-away(v/d), s = d * sum(q), both rounded to fp16

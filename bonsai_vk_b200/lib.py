@@ -66,6 +66,8 @@ def load_library() -> C.CDLL:
         "bn_act_quant_q81": (i32, [vp, vp, sz, i32, vp, sz]),
         "bn_gemv_q81": (i32, [vp, vp, sz, i32, i32, vp, sz, vp, sz, vp, sz]),
         "bn_gemv_q81_static": (i32, [vp, vp, sz, i32, i32, vp, sz, vp, sz]),
+        "bn_gemv_f32act_splits": (i32, [i32, i32]),
+        "bn_gemv_f32act": (i32, [vp, vp, sz, i32, i32, vp, sz, i32, vp, sz]),
         "bn_gemm_image_bytes": (sz, [i32, i32]),
         "bn_gemm_act_quant": (i32, [vp, vp, sz, sz, i32, i32, vp, sz, i32, vp, sz]),
         "bn_gemm_q81": (i32, [vp, vp, sz, i32, i32, i32, vp, sz, i32, vp, sz, sz]),
@@ -258,6 +260,11 @@ def _gemm_methods():
         _check(self.lib.bn_gemm_repack(self.h, w.h, w_off, M, K, out.h, 0), "bn_gemm_repack")
         return out
 
+    def gemv_f32act(self, w: Buffer, M: int, K: int, x: Buffer, out: Buffer, n_splits: int = 0):
+        """The reference engine's fp32-activation projection (n_splits 0 = the reference's split rule)."""
+        _check(self.lib.bn_gemv_f32act(self.h, w.h, 0, M, K, x.h, 0, n_splits, out.h, 0), "bn_gemv_f32act")
+
+    Context.gemv_f32act = gemv_f32act
     Context.gemm_image_bytes, Context.gemm_act_quant, Context.gemm_q81 = gemm_image_bytes, gemm_act_quant, gemm_q81
     Context.gemm_repack = gemm_repack
 

@@ -94,6 +94,16 @@ int bn_gemv_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const 
 int bn_gemv_q81_static(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const bn_buf *pack,
                        size_t pack_off, bn_buf *out, size_t out_off);
 
+/* ---- PTQ1_0 x fp32 activations, the reference engine's own projection arithmetic (gemv_ptq,
+ *      runtime_vk/bonsai_forward.h:409-422 -> xsum.comp, gemv_ternary.comp:74-118, reduce.comp): out[r] =
+ *      sum_b d[r,b] * (sum c*x - xsum_b), c in {0,1,2}, four strided fma chains per 64-code half combined as
+ *      (a0+a1)+(a2+a3), blocks ascending, split-K partials added ascending. One fp32 fma per weight: a parity mode,
+ *      not the fast path. x: K fp32 (already rotated by the caller). n_splits: 1..16 dividing K/128, or 0 = the
+ *      reference's rule (pick_splits, bonsai_weights.h:581-588), which bn_gemv_f32act_splits also returns. ------------ */
+int bn_gemv_f32act_splits(int M, int K);
+int bn_gemv_f32act(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const bn_buf *x, size_t x_off, int n_splits,
+                   bn_buf *out, size_t out_off);
+
 /* ---- the same projection for several activation columns at once (prefill tokens, concurrent sequences) on the
  *      tcgen05 tensor cores. Reference: the multi-column path of _mul_mat_vecq_ptq1_0.comp:204-347 (<= 8 columns;
  *      beyond that the reference falls back to dequantise + f16 matmul, _ggml-vulkan.cpp:2195-2197, which has no

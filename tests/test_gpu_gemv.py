@@ -124,3 +124,36 @@ def test_gemv_q81_streamed_kernel(ctx, oracle, M, K):
         _, got, _ = _run(ctx, oracle, W, M, K, x, want_dots=False)
         assert _check_rows(got, exact) <= 1e-5
         assert np.array_equal(got.view(np.uint32), out.view(np.uint32))
+
+
+@pytest.mark.parametrize("M,K,splits", [(4096, 4096, 0), (1024, 4096, 4), (4096, 12288, 0), (100, 512, 1), (37, 640, 5), (300, 2048, 16)])
+def test_gemv_f32act_is_the_engine_arithmetic_bit_for_bit(ctx, oracle, M, K, splits):
+    """fp32-activation mode: the reference engine's own summation shape (four strided fma chains per 64-code half,
+    blocks ascending, split partials ascending) - the CPU checker's floats bit for bit."""
+    rng = np.random.default_rng(M + K)
+    W = ptq.synth_matrix(rng, M, K)
+    x = rng.standard_normal(K).astype(np.float32)
+    n = splits or int(ctx.lib.bn_gemv_f32act_splits(M, K))
+    wb, xb, out = ctx.from_numpy(W), ctx.from_numpy(x), ctx.alloc(M * 4)
+    ctx.gemv_f32act(wb, M, K, xb, out, n_splits=splits)
+    ctx.sync()
+    got = out.download(np.float32, M)
+    want, exact = oracle.gemv_f32act(W, M, K, x, n_splits=n)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # distance to the fp64 truth is a property of the engine's fp32 summation shape itself (measured 1.05e-5 of the
+    # floored magnitude at K = 12288 with 16 splits, 6e-6 at K = 4096), not of this kernel: it is bit-identical above
+    assert _check_rows(got, exact) <= (1e-5 if K <= 4096 else 2e-5)
+    for b in (wb, xb, out):
+        b.free()
+
+
+def test_gemv_f32act_split_rule_and_refusals(ctx):
+    from bonsai_vk_b200.lib import BonsaiError
+    f = ctx.lib.bn_gemv_f32act_splits
+    assert f(4096, 4096) == 16 and f(248320, 4096) == 1 and f(4096, 12288) == 16 and f(37, 640) == 1 and f(100, 512) == 4
+    buf = ctx.alloc(1 << 20)
+    with pytest.raises(BonsaiError):
+        ctx.gemv_f32act(buf, 64, 640, buf, buf, n_splits=4)      # 4 does not divide 5 blocks
+    with pytest.raises(BonsaiError):
+        ctx.gemv_f32act(buf, 64, 100, buf, buf)
+    buf.free()
