@@ -61,7 +61,8 @@ int bn_gemm_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int w_tiled, int M, 
     a.image = bn_ptr<uint8_t>(image, image_off); a.ncol = ncol;
     a.out = bn_ptr<float>(out, out_off); a.out_stride = out_stride;
     a.err = ctx->err_dev;
-    // profiling aid: BONSAI_GEMM_PROF=1 prints where the roles of CTA 0 spent their cycles (waiting vs working)
+    // profiling aid (library built with -DGEMM_PROF): BONSAI_GEMM_PROF=1 prints where the roles of CTA 0 spent their
+    // cycles (waiting vs working); without that build flag the counters stay zero
     static const bool want_prof = getenv("BONSAI_GEMM_PROF") != nullptr;
     long long *prof = nullptr;
     if (want_prof) {

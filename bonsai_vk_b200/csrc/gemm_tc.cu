@@ -11,13 +11,15 @@
 //   producer warp   bulk-copies the rows' PTQ1_0 bytes and the activation image of 8 blocks into a ring stage
 //   4 decode warps  (lane = row) unpack 5 trits per byte with the multiply-by-3 chain on byte pairs held in the
 //                   16-bit halves of a register, and store the 128 codes as the A operand into tensor memory
-//   4 MMA threads   issue one tcgen05.mma.kind::i8 each (M=128, N=columns, K=32: one per sub-block), A from tensor
+//   2 MMA threads   issue the tcgen05.mma.kind::i8 of two sub-blocks each (M=128, N=8, K=32 per sub-block and group of 8 columns), A from tensor
 //                   memory, B = the int8 codes in shared memory, D = int32 in tensor memory
 //   8 epilogue warps read D with tcgen05.ld and do the fp32 combination for their row and half of the columns
 // Every wait is bounded: on giving up the kernel records it in the error word and drains.
 #include "gemm_tc.cuh"
 
 #include <algorithm>
+
+#include <cuda_fp16.h>
 
 namespace {
 
@@ -31,6 +33,7 @@ constexpr int ROWP = BK * 28 + 16;         // shared-memory pitch of a row's BK*
 constexpr int WBYTES = 128 * ROWP;
 constexpr int TBYTES = BK * 7 * 128 * 4;     // one stage of repacked weights: [block][word][row] dwords
 constexpr int A_COL = 0;                   // tensor-memory columns: NA operand slots x 32, then ND accumulator slots x 4*NCP
+constexpr int IMG_COL = 144;               // image bytes per column and block: 128 int8 codes + 4 x (fp16 d, fp16 s)
 constexpr int DWS = 16;                    // ring of per-row block scales handed from the decode warps to the epilogue
 constexpr uint32_t MAGIC = 0x4B400000u;    // float 12582912.0: adding an int |i| < 2^22 to its bits gives the float 12582912 + i
 
@@ -98,23 +101,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r) {
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
                    "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
-template <int N> __device__ __forceinline__ void tmem_fill(uint32_t taddr, uint32_t v);
-template <> __device__ __forceinline__ void tmem_fill<4>(uint32_t taddr, uint32_t v) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %1, %1, %1};" ::"r"(taddr), "r"(v) : "memory");
-}
-template <> __device__ __forceinline__ void tmem_fill<8>(uint32_t taddr, uint32_t v) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(v) : "memory");
-}
-template <int N> __device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t *r);
-template <> __device__ __forceinline__ void tmem_ld<4>(uint32_t taddr, uint32_t *r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
-}
-template <> __device__ __forceinline__ void tmem_ld<8>(uint32_t taddr, uint32_t *r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr) : "memory");
-}
-
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
                  "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
@@ -155,16 +141,22 @@ __device__ __forceinline__ void decode_block(const uint32_t (&r)[7], uint32_t (&
     o[31] = tb - 3u * __byte_perm(ta, tb, 0x5432u);                // elements 124..127
 }
 
-// optional cycle accounting of CTA 0 (GemmArgs::prof != null): where each role's time goes
+// optional cycle accounting of CTA 0 (build with -DGEMM_PROF and pass GemmArgs::prof): where each role's time goes.
+// Compiled out by default: even the untaken branches cost a few percent in these short loops.
+#ifdef GEMM_PROF
 #define PROF_T0() const long long prof_t0 = a.prof ? clock64() : 0
 #define PROF_ADD(slot) do { if (a.prof) prof[slot] += clock64() - prof_t0; } while (0)
+#else
+#define PROF_T0() do { } while (0)
+#define PROF_ADD(slot) do { } while (0)
+#endif
 
 // NCP = 8 or 16 columns = NG groups of 8. The tensor-core instruction always has N = 8 (its issue cost does not
 // depend on N); per block there are 4 x NG of them, and each (row quarter, group) has its own epilogue warp that
 // fetches the group's 4 x 8 accumulators with one 32-column tensor-memory load.
 template <int NCP> struct Cfg {
     static constexpr int NG = NCP / 8;
-    static constexpr int BBYTES = BK * NCP * 160;
+    static constexpr int BBYTES = BK * NCP * IMG_COL;
     static constexpr int STAGE = WBYTES + BBYTES;
     static constexpr int STAGES = 4;
 #ifndef GEMM_EW16
@@ -173,7 +165,8 @@ template <int NCP> struct Cfg {
     static constexpr int EW = NG == 1 ? 4 : GEMM_EW16;   // epilogue warps: one per row quarter and GPW column groups
     static constexpr int GPW = NG / (EW / 4);         // column groups per epilogue warp
     static constexpr int DW = 4;                      // decode warps (one per quarter of the rows)
-    static constexpr int NWARPS = DW + EW + 1 + 4;    // decode, epilogue, producer, 4 MMA issuers (one per sub-block)
+    static constexpr int MW = 2;                      // MMA issuing threads (one warp each), two sub-blocks apiece
+    static constexpr int NWARPS = DW + EW + 1 + MW;   // decode, epilogue, producer, MMA issuers: at most 16 warps = 128 registers
     // operand slot i and accumulator slot i belong to the same block, so one "done" barrier per slot (armed by the
     // MMA issuers' commits) tells the epilogue that the accumulators are ready and the decode warps that the operand
     // slot may be overwritten. Several blocks are in flight: each hop (decode -> MMA -> commit -> epilogue -> slot
@@ -204,7 +197,7 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
 
     if (tid == 0) {
         for (int i = 0; i < C::STAGES; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, EW); }
-        for (int i = 0; i < NA; ++i) { mbar_init(afull + i, 4); mbar_init(dfull + i, 4); mbar_init(dempty + i, EW); }
+        for (int i = 0; i < NA; ++i) { mbar_init(afull + i, 4); mbar_init(dfull + i, C::MW); mbar_init(dempty + i, EW); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -247,10 +240,10 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
                 if (++s == C::STAGES) { s = 0; ph ^= 1; }
             }
     } else if (warp > DW + EW) {
-        // ---- MMA issue: thread sb of four issues the sub-block's MMA of every block (an issue costs the thread ~55
-        //      cycles whatever its size, so the four go out in parallel) --------------------------------------------
+        // ---- MMA issue: each of the two threads issues two sub-blocks' MMAs of every block (an issue costs the
+        //      thread ~55 cycles whatever its size; two threads keep that far below the other roles' time) --------
         if (lane == 0) {
-            const int sb = warp - (DW + EW + 1);
+            const int sb0 = 2 * (warp - (DW + EW + 1));
             // D s32, A u8, B s8, both K-major, N = 8, M = 128
             const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (uint32_t(8 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
             bool ok = true;
@@ -258,21 +251,23 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
             long long prof[4] = {0, 0, 0, 0};
             for (int it = 0; it < n_items && ok; ++it) {
                 { PROF_T0(); if (!mbar_wait(full + s, sph, a.err, abort_flag)) break; PROF_ADD(0); }
-                const uint32_t bbase = smem_u32(ring + size_t(s) * C::STAGE + WBYTES) + sb * 256;
+                const uint32_t bbase = smem_u32(ring + size_t(s) * C::STAGE + WBYTES);
                 for (int j = 0; j < BK; ++j) {
                     { PROF_T0(); if (!mbar_wait(afull + slot, aph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(1); }
                     { PROF_T0(); if (!mbar_wait(dempty + slot, dph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(2); }
                     tc_fence_after();
 #pragma unroll
-                    for (int gi = 0; gi < NG; ++gi)
-                        tc_mma_i8(tb + D_COL + (slot * NG + gi) * 32 + sb * 8, tb + A_COL + slot * 32 + sb * 8,
-                                  smem_desc(bbase + j * (NCP * 160) + gi * 1024, 128, 128), idesc, 0u);
+                    for (int k = 0; k < 2; ++k)
+#pragma unroll
+                        for (int gi = 0; gi < NG; ++gi)
+                            tc_mma_i8(tb + D_COL + (slot * NG + gi) * 32 + (sb0 + k) * 8, tb + A_COL + slot * 32 + (sb0 + k) * 8,
+                                      smem_desc(bbase + j * (NCP * IMG_COL) + gi * 1024 + (sb0 + k) * 256, 128, 128), idesc, 0u);
                     tc_commit(dfull + slot);
                     if (++slot == NA) { slot = 0; aph ^= 1; dph ^= 1; }
                 }
                 if (++s == C::STAGES) { s = 0; sph ^= 1; }
             }
-            if (a.prof && blockIdx.x == 0 && sb == 0) for (int i = 0; i < 4; ++i) a.prof[4 + i] = prof[i];
+            if (a.prof && blockIdx.x == 0 && sb0 == 0) for (int i = 0; i < 4; ++i) a.prof[4 + i] = prof[i];
         }
     } else if (warp < DW) {
         // ---- decode ------------------------------------------------------------------------------------
@@ -336,18 +331,26 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
         for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x)
             for (int kc = 0; kc < nkc && ok; ++kc) {
                 { PROF_T0(); if (!mbar_wait(full + s, sph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(0); }
-                const unsigned char *stage_scales = ring + size_t(s) * C::STAGE + WBYTES + NCP * 128 + c0 * 32;
+                const unsigned char *stage_scales = ring + size_t(s) * C::STAGE + WBYTES + NCP * 128 + c0 * 16;
 #pragma unroll 1
                 for (int j = 0; j < BK; ++j, ++g) {
+                    // the block's scales do not depend on the accumulators: fetched before the wait for them
+                    const unsigned char *scales = stage_scales + j * (NCP * IMG_COL);
+                    uint4 sc[NCW];                          // per column: (d, s) of the 4 sub-blocks as fp16 pairs
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) sc[c] = *reinterpret_cast<const uint4 *>(scales + c * 16);
                     { PROF_T0(); if (!mbar_wait(dfull + slot, dph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(0); }
                     tc_fence_after();
                     const float dw = dwv[(g % DWS) * 128 + row];
-                    const unsigned char *scales = stage_scales + j * (NCP * 160);
                     const int b = kc * BK + j, bi = b & 3;
 #pragma unroll
                     for (int gw = 0; gw < GPW; ++gw) {
                         uint32_t d[32];                     // [sub-block][column] of one group
                         tmem_ld32(tb + lane_base + D_COL + (slot * NG + part * GPW + gw) * 32, d);
+                        if (gw == 0) {                      // the rest of the scales travel while the accumulators do
+#pragma unroll
+                            for (int c = 4; c < NCW; ++c) sc[c] = *reinterpret_cast<const uint4 *>(scales + c * 16);
+                        }
                         { PROF_T0(); asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); PROF_ADD(1); }
                         if (gw == GPW - 1) {                // all of this warp's accumulators are in registers: the slot is free
                             tc_fence_before();
@@ -358,12 +361,15 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
                         float v[8];
 #pragma unroll
                         for (int c = 0; c < 8; ++c) {       // straight-line: the columns' dependency chains interleave
-                            const float4 s01 = *reinterpret_cast<const float4 *>(scales + (gw * 8 + c) * 32);
-                            const float4 s23 = *reinterpret_cast<const float4 *>(scales + (gw * 8 + c) * 32 + 16);
-                            const float t0 = fmaf(s01.x, __fsub_rn(__uint_as_float(MAGIC + d[c]), 12582912.0f), -s01.y);
-                            const float t1 = fmaf(s01.z, __fsub_rn(__uint_as_float(MAGIC + d[8 + c]), 12582912.0f), -s01.w);
-                            const float t2 = fmaf(s23.x, __fsub_rn(__uint_as_float(MAGIC + d[16 + c]), 12582912.0f), -s23.y);
-                            const float t3 = fmaf(s23.z, __fsub_rn(__uint_as_float(MAGIC + d[24 + c]), 12582912.0f), -s23.w);
+                            const uint4 q4 = sc[gw * 8 + c];
+                            const float2 p0 = __half22float2(*reinterpret_cast<const __half2 *>(&q4.x));
+                            const float2 p1 = __half22float2(*reinterpret_cast<const __half2 *>(&q4.y));
+                            const float2 p2 = __half22float2(*reinterpret_cast<const __half2 *>(&q4.z));
+                            const float2 p3 = __half22float2(*reinterpret_cast<const __half2 *>(&q4.w));
+                            const float t0 = fmaf(p0.x, __fsub_rn(__uint_as_float(MAGIC + d[c]), 12582912.0f), -p0.y);
+                            const float t1 = fmaf(p1.x, __fsub_rn(__uint_as_float(MAGIC + d[8 + c]), 12582912.0f), -p1.y);
+                            const float t2 = fmaf(p2.x, __fsub_rn(__uint_as_float(MAGIC + d[16 + c]), 12582912.0f), -p2.y);
+                            const float t3 = fmaf(p3.x, __fsub_rn(__uint_as_float(MAGIC + d[24 + c]), 12582912.0f), -p3.y);
                             v[c] = __fmul_rn(dw, __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3)));
                         }
                         if (bi == 0 || bi == 2) {
@@ -427,8 +433,8 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
     const int c = ncp == 32 ? (cg & 15) : cg;
     const size_t base = size_t(blockIdx.x) * chunk;
     if (ncp == 32) ncp = 16;
-    const size_t blk_bytes = size_t(ncp) * 160;
-    unsigned char *image = a.image + (cg >> 4) * (size_t(a.K / 128) * 16 * 160) * (cg >= 16 ? 1 : 0);
+    const size_t blk_bytes = size_t(ncp) * IMG_COL;
+    unsigned char *image = a.image + (cg >> 4) * (size_t(a.K / 128) * 16 * IMG_COL) * (cg >= 16 ? 1 : 0);
     if (cg >= a.ncol) {                             // padding column: zero codes and scales
         for (int e = tid * 16; e < chunk; e += 512 * 16) {
             const size_t b = (base + e) / 128;
@@ -437,7 +443,7 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
         }
         for (int e = tid * 32; e < chunk; e += 512 * 32) {
             const size_t b = (base + e) / 128;
-            *reinterpret_cast<float2 *>(image + b * blk_bytes + size_t(ncp) * 128 + (c * 4 + ((e & 127) >> 5)) * 8) = make_float2(0.0f, 0.0f);
+            *reinterpret_cast<uint32_t *>(image + b * blk_bytes + size_t(ncp) * 128 + (c * 4 + ((e & 127) >> 5)) * 4) = 0u;
         }
         return;
     }
@@ -565,11 +571,9 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
         const int sb = (e & 127) >> 5, kh = (e >> 4) & 1;
         unsigned char *blk = image + b * blk_bytes;
         blk[(c / 8) * 1024 + (sb * 2 + kh) * 128 + (c & 7) * 16 + (e & 15)] = uint8_t(int8_t(qi));
-        if (lane == 0) {
-            const float df = half_bits_to_float(float_to_half_bits(d));
-            const float sf = half_bits_to_float(float_to_half_bits(__fmul_rn(d, float(sum))));
-            *reinterpret_cast<float2 *>(blk + size_t(ncp) * 128 + (c * 4 + sb) * 8) = make_float2(df, sf);
-        }
+        if (lane == 0)      // (d, s) as the q8_1 record keeps them: two fp16 values
+            *reinterpret_cast<uint32_t *>(blk + size_t(ncp) * 128 + (c * 4 + sb) * 4) =
+                float_to_half_bits(d) | (float_to_half_bits(__fmul_rn(d, float(sum))) << 16);
     }
 }
 
@@ -630,7 +634,7 @@ cudaError_t launch_gemm(cudaStream_t st, int sm_count, const GemmArgs &a, bool p
     cudaError_t e = launch_t<16>(st, sm_count, h, pdl);
     if (e != cudaSuccess) return e;
     h.ncol = a.ncol - 16;
-    h.image = a.image + size_t(a.K / 128) * 16 * 160;
+    h.image = a.image + size_t(a.K / 128) * 16 * IMG_COL;
     h.out = a.out + 16 * a.out_stride;
     if (a.resid) h.resid = a.resid + 16 * a.resid_stride;
     return launch_t<16>(st, sm_count, h, pdl);
