@@ -178,7 +178,10 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     MB = a.microbatch if a.microbatch > 0 else max(1, min(32, S // world))
     assert S % MB == 0, "the micro-batch size must divide 64"
     U = S // MB
-    b0, b1 = split_blocks(32, world)[rank]
+    # "equal": the partition the benchmark configuration names (16 / 8 / 4 blocks per GPU). "bytes": the reference's own
+    # rule (fleet_split_schedule: ranges balanced by bytes read per token, the output head charged to the last stage)
+    bb = [48_923_392 if b % 4 != 3 else 45_910_016 for b in range(32)]
+    b0, b1 = split_blocks(32, world, a.balance, block_bytes=bb, head_bytes=222_494_720)[rank]
     ctx = Context(local)
     # one explicit (non-default) stream for our kernels and, through torch, for the NCCL dependencies: the legacy
     # default stream cannot be captured into the per-stream stage graphs
@@ -258,7 +261,7 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     e2e = S * K / (ms_e2e / 1000.0)
     cfg = dict(base["config"], workload=f"config 4: 9B-shape synthetic model layer-pipelined over {world} GPUs "
                f"({b1 - b0} blocks per stage), 64 concurrent sequences at context {CTX} (KV marked filled) in {U} micro-batches "
-               f"of {MB}, greedy decode", parallelism=f"pp{world}", streams=S, context=CTX, microbatch=MB)
+               f"of {MB}, greedy decode", parallelism=f"pp{world}", streams=S, context=CTX, microbatch=MB, balance=a.balance)
     line = dict(base, metric="decode tok/s, 9B ternary (PTQ1_0), 64 streams pipelined", config=cfg, value=tok_s,
                 ms_per_step=ms_dev / K, clocks=clocks, gpu_launches=int(launches),
                 e2e={"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4 * S})
@@ -283,6 +286,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--prompt", type=int, default=16, help="prompt length in tokens (16 = the benchmark config)")
+    ap.add_argument("--balance", default="equal", choices=["equal", "bytes"],
+                    help="N > 1: stage split - equal block counts (the benchmark configuration) or byte-balanced with the head on the last stage")
     ap.add_argument("--microbatch", type=int, default=0, help="N > 1: sequences per micro-batch (0 = 64 / GPUs, at most 32; 1 = one sequence per pass)")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
