@@ -33,7 +33,7 @@ constexpr int ROWP = BK * 28 + 16;         // shared-memory pitch of a row's BK*
 constexpr int WBYTES = 128 * ROWP;
 constexpr int TBYTES = BK * 7 * 128 * 4;     // one stage of repacked weights: [block][word][row] dwords
 constexpr int A_COL = 0;                   // tensor-memory columns: NA operand slots x 32, then ND accumulator slots x 4*NCP
-constexpr int IMG_COL = 144;               // image bytes per column and block: 128 int8 codes + 4 x (fp16 d, fp16 s)
+constexpr int IMG_COL = 160;               // image bytes per column and block: 128 int8 codes + 4 x (fp32 d, fp32 -s)
 constexpr int DWS = 16;                    // ring of per-row block scales handed from the decode warps to the epilogue
 constexpr uint32_t MAGIC = 0x4B400000u;    // float 12582912.0: adding an int |i| < 2^22 to its bits gives the float 12582912 + i
 
@@ -109,6 +109,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
                    "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
                    "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]) : "r"(taddr) : "memory");
 }
+
+// Packed fp32 pairs (two IEEE single operations per instruction, each lane rounded as the scalar instruction would)
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float a, float b) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ void unpk2(f32x2 v, float &a, float &b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { f32x2 d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) { f32x2 d; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { f32x2 d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
 
 // Four packed bytes (5 trits each) -> five dwords of codes: o[t*stride] = codes at level t of the four bytes, in byte
 // order. T_t = (b * 3^(t+1)) >> 8 is the running base-3 prefix of byte b, and trit_t + 1 = T_t - 3 * T_(t-1)
@@ -322,35 +331,36 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
         const uint32_t lane_base = uint32_t(q * 32) << 16;
         constexpr int GPW = C::GPW, NCW = 8 * GPW;
         const int c0 = part * NCW;
-        float acc[NCW], u[NCW], ve[NCW];
+        // running sums as column pairs (2p, 2p+1): the arithmetic below is done two columns at a time
+        constexpr int NPR = NCW / 2;
+        f32x2 acc[NPR], u[NPR], ve[NPR];
 #pragma unroll
-        for (int c = 0; c < NCW; ++c) { acc[c] = 0.0f; u[c] = 0.0f; ve[c] = 0.0f; }
+        for (int c = 0; c < NPR; ++c) { acc[c] = 0ull; u[c] = 0ull; ve[c] = 0ull; }
+        const f32x2 magic2 = pk2(12582912.0f, 12582912.0f);
         bool ok = true;
         long long prof[4] = {0, 0, 0, 0};
         int s = 0, sph = 0, slot = 0, dph = 0, g = 0;
         for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x)
             for (int kc = 0; kc < nkc && ok; ++kc) {
                 { PROF_T0(); if (!mbar_wait(full + s, sph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(0); }
-                const unsigned char *stage_scales = ring + size_t(s) * C::STAGE + WBYTES + NCP * 128 + c0 * 16;
+                const unsigned char *stage_scales = ring + size_t(s) * C::STAGE + WBYTES + NCP * 128 + (c0 / 8) * 256;
 #pragma unroll 1
                 for (int j = 0; j < BK; ++j, ++g) {
-                    // the block's scales do not depend on the accumulators: fetched before the wait for them
                     const unsigned char *scales = stage_scales + j * (NCP * IMG_COL);
-                    uint4 sc[NCW];                          // per column: (d, s) of the 4 sub-blocks as fp16 pairs
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) sc[c] = *reinterpret_cast<const uint4 *>(scales + c * 16);
                     { PROF_T0(); if (!mbar_wait(dfull + slot, dph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(0); }
                     tc_fence_after();
                     const float dw = dwv[(g % DWS) * 128 + row];
+                    const f32x2 dw2 = pk2(dw, dw);
                     const int b = kc * BK + j, bi = b & 3;
 #pragma unroll
                     for (int gw = 0; gw < GPW; ++gw) {
                         uint32_t d[32];                     // [sub-block][column] of one group
                         tmem_ld32(tb + lane_base + D_COL + (slot * NG + part * GPW + gw) * 32, d);
-                        if (gw == 0) {                      // the rest of the scales travel while the accumulators do
+                        // the group's scales, per sub-block and column pair one 16-byte entry (d, d', -s, -s'): they do not
+                        // depend on the accumulators and travel while those do
+                        ulonglong2 sc[16];
 #pragma unroll
-                            for (int c = 4; c < NCW; ++c) sc[c] = *reinterpret_cast<const uint4 *>(scales + c * 16);
-                        }
+                        for (int e = 0; e < 16; ++e) sc[e] = *reinterpret_cast<const ulonglong2 *>(scales + gw * 256 + e * 16);
                         { PROF_T0(); asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); PROF_ADD(1); }
                         if (gw == GPW - 1) {                // all of this warp's accumulators are in registers: the slot is free
                             tc_fence_before();
@@ -358,32 +368,29 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
                             if (lane == 0) mbar_arrive(dempty + slot);
                         }
                         PROF_T0();
-                        float v[8];
+                        f32x2 v[4];
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) {       // straight-line: the columns' dependency chains interleave
-                            const uint4 q4 = sc[gw * 8 + c];
-                            const float2 p0 = __half22float2(*reinterpret_cast<const __half2 *>(&q4.x));
-                            const float2 p1 = __half22float2(*reinterpret_cast<const __half2 *>(&q4.y));
-                            const float2 p2 = __half22float2(*reinterpret_cast<const __half2 *>(&q4.z));
-                            const float2 p3 = __half22float2(*reinterpret_cast<const __half2 *>(&q4.w));
-                            const float t0 = fmaf(p0.x, __fsub_rn(__uint_as_float(MAGIC + d[c]), 12582912.0f), -p0.y);
-                            const float t1 = fmaf(p1.x, __fsub_rn(__uint_as_float(MAGIC + d[8 + c]), 12582912.0f), -p1.y);
-                            const float t2 = fmaf(p2.x, __fsub_rn(__uint_as_float(MAGIC + d[16 + c]), 12582912.0f), -p2.y);
-                            const float t3 = fmaf(p3.x, __fsub_rn(__uint_as_float(MAGIC + d[24 + c]), 12582912.0f), -p3.y);
-                            v[c] = __fmul_rn(dw, __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3)));
+                        for (int p = 0; p < 4; ++p) {       // straight-line: the pairs' dependency chains interleave
+                            f32x2 tt[4];
+#pragma unroll
+                            for (int sb = 0; sb < 4; ++sb) {
+                                const f32x2 f = sub2(pk2(__uint_as_float(MAGIC + d[sb * 8 + 2 * p]), __uint_as_float(MAGIC + d[sb * 8 + 2 * p + 1])), magic2);
+                                tt[sb] = fma2(sc[sb * 4 + p].x, f, sc[sb * 4 + p].y);
+                            }
+                            v[p] = mul2(dw2, add2(add2(tt[0], tt[1]), add2(tt[2], tt[3])));
                         }
                         if (bi == 0 || bi == 2) {
 #pragma unroll
-                            for (int c = 0; c < 8; ++c) ve[gw * 8 + c] = v[c];
+                            for (int p = 0; p < 4; ++p) ve[gw * 4 + p] = v[p];
                         } else if (bi == 1) {
 #pragma unroll
-                            for (int c = 0; c < 8; ++c) u[gw * 8 + c] = __fadd_rn(ve[gw * 8 + c], v[c]);
+                            for (int p = 0; p < 4; ++p) u[gw * 4 + p] = add2(ve[gw * 4 + p], v[p]);
                         } else {
                             const bool first = b < 4;
 #pragma unroll
-                            for (int c = 0; c < 8; ++c) {
-                                const float p = __fadd_rn(u[gw * 8 + c], __fadd_rn(ve[gw * 8 + c], v[c]));
-                                acc[gw * 8 + c] = first ? p : __fadd_rn(acc[gw * 8 + c], p);
+                            for (int p = 0; p < 4; ++p) {
+                                const f32x2 q2 = add2(u[gw * 4 + p], add2(ve[gw * 4 + p], v[p]));
+                                acc[gw * 4 + p] = first ? q2 : add2(acc[gw * 4 + p], q2);
                             }
                         }
                         PROF_ADD(2);
@@ -395,7 +402,9 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
 #pragma unroll
                             for (int c = 0; c < NCW; ++c) {
                                 if (c0 + c >= a.ncol) continue;
-                                float r = acc[c];
+                                float lo, hi;
+                                unpk2(acc[c >> 1], lo, hi);
+                                float r = (c & 1) ? hi : lo;
                                 if (a.resid) r = __fadd_rn(r, a.resid[size_t(c0 + c) * a.resid_stride + grow]);
                                 a.out[size_t(c0 + c) * a.out_stride + grow] = r;
                             }
@@ -443,7 +452,8 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
         }
         for (int e = tid * 32; e < chunk; e += 512 * 32) {
             const size_t b = (base + e) / 128;
-            *reinterpret_cast<uint32_t *>(image + b * blk_bytes + size_t(ncp) * 128 + (c * 4 + ((e & 127) >> 5)) * 4) = 0u;
+            float *ent = reinterpret_cast<float *>(image + b * blk_bytes + size_t(ncp) * 128 + (c / 8) * 256 + ((((e & 127) >> 5) * 4) + ((c & 7) >> 1)) * 16);
+            ent[c & 1] = 0.0f; ent[2 + (c & 1)] = 0.0f;
         }
         return;
     }
@@ -571,9 +581,11 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
         const int sb = (e & 127) >> 5, kh = (e >> 4) & 1;
         unsigned char *blk = image + b * blk_bytes;
         blk[(c / 8) * 1024 + (sb * 2 + kh) * 128 + (c & 7) * 16 + (e & 15)] = uint8_t(int8_t(qi));
-        if (lane == 0)      // (d, s) as the q8_1 record keeps them: two fp16 values
-            *reinterpret_cast<uint32_t *>(blk + size_t(ncp) * 128 + (c * 4 + sb) * 4) =
-                float_to_half_bits(d) | (float_to_half_bits(__fmul_rn(d, float(sum))) << 16);
+        if (lane == 0) {    // (d, s) rounded to fp16 as the q8_1 record keeps them, stored as fp32 d and -s in the pair entry
+            float *ent = reinterpret_cast<float *>(blk + size_t(ncp) * 128 + (c / 8) * 256 + (sb * 4 + ((c & 7) >> 1)) * 16);
+            ent[c & 1] = half_bits_to_float(float_to_half_bits(d));
+            ent[2 + (c & 1)] = -half_bits_to_float(float_to_half_bits(__fmul_rn(d, float(sum))));
+        }
     }
 }
 

@@ -13,9 +13,11 @@ inline int gemm_padded_cols(int ncol) { return ncol <= 8 ? 8 : (ncol <= 16 ? 16 
 //   codes: column n, sub-block sb (32 activations), k-half kh (16 of them): int8 codes at
 //          (n/8) * 1024 + (sb*2 + kh) * 128 + (n%8) * 16   - per group of 8 columns the shared-memory operand layout
 //          of the instruction (8 x 16-byte core matrices, K-major, no swizzle), so a stage is one contiguous bulk copy
-//   scales: (fp16 d, fp16 s) of column n, sub-block sb at ncp*128 + (n*4 + sb) * 4 (as the q8_1 record keeps them)
+//   scales: per group of 8 columns 256 bytes at ncp*128 + (n/8)*256: entry (sb, column pair p) at (sb*4 + p) * 16 holds
+//           fp32 (d[2p], d[2p+1], -s[2p], -s[2p+1]) - the fp16 values of the q8_1 record, widened, s negated - so that the
+//           epilogue's packed two-column arithmetic reads its operands with one 16-byte load
 // 17..32 columns are two such 16-column images, one after the other.
-inline size_t gemm_image_block_bytes(int ncp) { return size_t(ncp) * 144; }
+inline size_t gemm_image_block_bytes(int ncp) { return size_t(ncp) * 160; }
 inline size_t gemm_image_bytes(int K, int ncol) { return size_t(K / 128) * gemm_image_block_bytes(gemm_padded_cols(ncol)); }
 
 enum PrepMode { PREP_PLAIN = 0, PREP_NORM = 1 };

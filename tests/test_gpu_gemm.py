@@ -38,16 +38,19 @@ def _image_column(img, K, ncol, c):
     nb = K // 128
     ncp = 8 if ncol <= 8 else 16
     if ncol > 16:                       # two 16-column images, one after the other
-        half = nb * 16 * 144
+        half = nb * 16 * 160
         img, c = img[(c // 16) * half:(c // 16 + 1) * half], c % 16
-    blocks = img[:nb * ncp * 144].reshape(nb, ncp * 144)
+    blocks = img[:nb * ncp * 160].reshape(nb, ncp * 160)
     codes = np.empty((nb, 4, 2, 16), dtype=np.int8)
     for sb in range(4):
         for kh in range(2):
             off = (c // 8) * 1024 + (sb * 2 + kh) * 128 + (c % 8) * 16
             codes[:, sb, kh, :] = blocks[:, off:off + 16].view(np.int8)
-    ds = np.ascontiguousarray(blocks[:, ncp * 128 + c * 16: ncp * 128 + c * 16 + 16]).view(np.float16).astype(np.float32).reshape(nb, 4, 2)
-    return codes.reshape(K), np.ascontiguousarray(ds[:, :, 0]).reshape(-1), np.ascontiguousarray(ds[:, :, 1]).reshape(-1)
+    # scales: per group of 8 columns 256 bytes; entry (sb, pair) = fp32 (d, d', -s, -s')
+    grp = np.ascontiguousarray(blocks[:, ncp * 128 + (c // 8) * 256: ncp * 128 + (c // 8) * 256 + 256]).view(np.float32).reshape(nb, 4, 4, 4)
+    d = np.ascontiguousarray(grp[:, :, (c % 8) // 2, c % 2]).reshape(-1)
+    s = -np.ascontiguousarray(grp[:, :, (c % 8) // 2, 2 + c % 2]).reshape(-1)
+    return codes.reshape(K), d, s + np.float32(0.0)
 
 
 def _oracle_record(xq, K):
