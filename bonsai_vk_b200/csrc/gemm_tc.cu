@@ -160,14 +160,14 @@ __device__ __forceinline__ void decode_block(const uint32_t (&r)[7], uint32_t (&
 #define PROF_ADD(slot) do { } while (0)
 #endif
 
-// NCP = 8 or 16 columns = NG groups of 8. The tensor-core instruction always has N = 8 (its issue cost does not
+// NCP = 8, 16 or 32 columns = NG groups of 8. The tensor-core instruction always has N = 8 (its issue cost does not
 // depend on N); per block there are 4 x NG of them, and each (row quarter, group) has its own epilogue warp that
 // fetches the group's 4 x 8 accumulators with one 32-column tensor-memory load.
 template <int NCP> struct Cfg {
     static constexpr int NG = NCP / 8;
     static constexpr int BBYTES = BK * NCP * IMG_COL;
     static constexpr int STAGE = WBYTES + BBYTES;
-    static constexpr int STAGES = 4;
+    static constexpr int STAGES = NG == 4 ? 3 : 4;
 #ifndef GEMM_EW16
 #define GEMM_EW16 8
 #endif
@@ -180,7 +180,7 @@ template <int NCP> struct Cfg {
     // MMA issuers' commits) tells the epilogue that the accumulators are ready and the decode warps that the operand
     // slot may be overwritten. Several blocks are in flight: each hop (decode -> MMA -> commit -> epilogue -> slot
     // free) costs a few hundred cycles.
-    static constexpr int NA = NG == 1 ? 8 : 5;
+    static constexpr int NA = NG == 1 ? 8 : (NG == 2 ? 5 : 3);
     static constexpr int D_COL = NA * 32;
     static constexpr int TMEM_COLS = 512;
     static_assert(D_COL + NA * NG * 32 <= 512 && 2 * NA <= DWS, "tensor memory budget");
@@ -437,13 +437,11 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
     pdl_sync();
     extern __shared__ float s[];                   // chunk floats
     __shared__ float part[256];
-    // more than 16 columns are kept as two independent 16-column images, one after the other
     const int cg = blockIdx.y, tid = threadIdx.x;
-    const int c = ncp == 32 ? (cg & 15) : cg;
+    const int c = cg;
     const size_t base = size_t(blockIdx.x) * chunk;
-    if (ncp == 32) ncp = 16;
     const size_t blk_bytes = size_t(ncp) * IMG_COL;
-    unsigned char *image = a.image + (cg >> 4) * (size_t(a.K / 128) * 16 * IMG_COL) * (cg >= 16 ? 1 : 0);
+    unsigned char *image = a.image;
     if (cg >= a.ncol) {                             // padding column: zero codes and scales
         for (int e = tid * 16; e < chunk; e += 512 * 16) {
             const size_t b = (base + e) / 128;
@@ -640,16 +638,7 @@ cudaError_t launch_gemm(cudaStream_t st, int sm_count, const GemmArgs &a, bool p
     const int ncp = gemm_padded_cols(a.ncol);
     if (ncp == 8) return launch_t<8>(st, sm_count, a, pdl);
     if (ncp == 16) return launch_t<16>(st, sm_count, a, pdl);
-    // 17..32 columns: two passes of 16 over their own images (the second pass finds the weights in L2 where they fit)
-    GemmArgs h = a;
-    h.ncol = 16;
-    cudaError_t e = launch_t<16>(st, sm_count, h, pdl);
-    if (e != cudaSuccess) return e;
-    h.ncol = a.ncol - 16;
-    h.image = a.image + size_t(a.K / 128) * 16 * IMG_COL;
-    h.out = a.out + 16 * a.out_stride;
-    if (a.resid) h.resid = a.resid + 16 * a.resid_stride;
-    return launch_t<16>(st, sm_count, h, pdl);
+    return launch_t<32>(st, sm_count, a, pdl);
 }
 
 size_t gemm_tiled_bytes(int M, int K) { return size_t((M + 127) / 128) * (K / 128 / BK) * TBYTES; }

@@ -9,14 +9,13 @@ namespace bnk {
 constexpr int GEMM_MAX_COLS = 32;
 // columns are padded to 8, 16 or 32 (the N of the tensor-core instruction)
 inline int gemm_padded_cols(int ncol) { return ncol <= 8 ? 8 : (ncol <= 16 ? 16 : 32); }
-// The "activation image" the kernel consumes, per 128 activations (one PTQ1_0 block) of up to 16 columns (ncp = 8 or 16):
+// The "activation image" the kernel consumes, per 128 activations (one PTQ1_0 block) of ncp = 8, 16 or 32 columns:
 //   codes: column n, sub-block sb (32 activations), k-half kh (16 of them): int8 codes at
 //          (n/8) * 1024 + (sb*2 + kh) * 128 + (n%8) * 16   - per group of 8 columns the shared-memory operand layout
 //          of the instruction (8 x 16-byte core matrices, K-major, no swizzle), so a stage is one contiguous bulk copy
 //   scales: per group of 8 columns 256 bytes at ncp*128 + (n/8)*256: entry (sb, column pair p) at (sb*4 + p) * 16 holds
 //           fp32 (d[2p], d[2p+1], -s[2p], -s[2p+1]) - the fp16 values of the q8_1 record, widened, s negated - so that the
 //           epilogue's packed two-column arithmetic reads its operands with one 16-byte load
-// 17..32 columns are two such 16-column images, one after the other.
 inline size_t gemm_image_block_bytes(int ncp) { return size_t(ncp) * 160; }
 inline size_t gemm_image_bytes(int K, int ncol) { return size_t(K / 128) * gemm_image_block_bytes(gemm_padded_cols(ncol)); }
 

@@ -36,10 +36,7 @@ def _gemm(ctx, W, M, K, X, signs=None, hat_block=0, out_stride=0, tiled=False):
 def _image_column(img, K, ncol, c):
     """q8_1 record of column c rebuilt from the image: (codes [K] int8, d [K/32] f32, s [K/32] f32)."""
     nb = K // 128
-    ncp = 8 if ncol <= 8 else 16
-    if ncol > 16:                       # two 16-column images, one after the other
-        half = nb * 16 * 160
-        img, c = img[(c // 16) * half:(c // 16 + 1) * half], c % 16
+    ncp = 8 if ncol <= 8 else (16 if ncol <= 16 else 32)
     blocks = img[:nb * ncp * 160].reshape(nb, ncp * 160)
     codes = np.empty((nb, 4, 2, 16), dtype=np.int8)
     for sb in range(4):
