@@ -179,7 +179,8 @@ int bn_sync(bn_ctx *ctx) {
     BN_CUDA(cudaMemcpy(&flag, ctx->err_dev, 4, cudaMemcpyDeviceToHost));
     if (flag) {
         cudaMemset(ctx->err_dev, 0, 4);
-        bn_set_error("a bounded device-side wait gave up (copy ring); results of the last kernels are invalid");
+        bn_set_error("a bounded device-side wait gave up (%s); results of the last kernels are invalid",
+                     flag == 2 ? "tensor-core projection pipeline" : "copy ring");
         return BN_ERR_TIMEOUT;
     }
     return BN_OK;

@@ -1,5 +1,6 @@
 // gemm_abi.cu - C entry points of the multi-column tensor-core projection (declared in include/bonsai_cuda.h).
 #include "gemm_tc.cuh"
+#include "phase_gemv.cuh"
 
 #include <cstdio>
 #include <cstdlib>
@@ -86,6 +87,15 @@ int bn_gemm_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int w_tiled, int M, 
                 h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[8], h[9], h[10]);
     }
     return bn_launch_check(ctx, "k_ptq_gemm_tc");
+}
+
+int bn_selftest_wait(bn_ctx *ctx, int which) {
+    BN_REQUIRE(ctx, BN_ERR_ARG, "bn_selftest_wait: null context");
+    BN_REQUIRE(which == 0 || which == 1, BN_ERR_ARG, "bn_selftest_wait: which=%d (0 = copy-ring wait, 1 = tensor-core pipeline wait)", which);
+    cudaError_t e = which == 0 ? bnk::launch_wait_selftest_ring(ctx->stream, ctx->err_dev)
+                               : bnk::launch_wait_selftest_tc(ctx->stream, ctx->err_dev);
+    if (e != cudaSuccess) return bn_cuda_fail(e, "bn_selftest_wait");
+    return BN_OK;
 }
 
 }  // extern "C"

@@ -50,9 +50,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *b, uint32_t bytes) {
 // Bounded wait. try_wait suspends the thread until the phase completes or its time hint (ns) runs out; the retry loop
 // is four instructions, so a waiting warp takes few issue slots from the warps that are working. After 2^20 tries
 // (well over a second) it gives up: the error word is set and the abort flag drains every role of the CTA.
-__device__ __forceinline__ bool mbar_wait(uint64_t *b, uint32_t parity, int *err, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *b, uint32_t parity, int *err, volatile int *abort_flag, int rounds = 1024) {
     const uint32_t addr = smem_u32(b);
-    for (int round = 0; round < 1024; ++round) {
+    for (int round = 0; round < rounds; ++round) {
         uint32_t ok;
         asm volatile("{\n"
                      ".reg .pred p, q;\n"
@@ -626,6 +626,20 @@ cudaError_t launch_t(cudaStream_t st, int sm_count, const GemmArgs &a, bool pdl)
     return cudaLaunchKernelEx(&cfg, k_ptq_gemm_tc<NCP>, a);
 }
 
+// A wait that nothing will ever satisfy, one round of tries (about 2 ms): exercises the give-up path of mbar_wait
+// (error word = 2, abort flag raised, kernel returns) without hanging anything.
+__global__ void k_wait_selftest_tc(int *err) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_word;
+    if (threadIdx.x == 0) {
+        abort_word = 0;
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait(&bar, 0, err, &abort_word, 1);
+}
+
 }  // namespace
 
 namespace bnk {
@@ -653,6 +667,12 @@ void prep_cols(cudaStream_t st, const PrepArgs &a) {
     static bool attr = false;
     if (!attr) { cudaFuncSetAttribute(k_prep_cols, cudaFuncAttributeMaxDynamicSharedMemorySize, 4096 * 4); attr = true; }
     launch(k_prep_cols, dim3(a.K / chunk, ncp), dim3(512), size_t(chunk) * 4, st, a, chunk, ncp);
+}
+
+cudaError_t launch_wait_selftest_tc(cudaStream_t st, int *err) {
+    BN_COUNT(1);
+    k_wait_selftest_tc<<<1, 32, 0, st>>>(err);
+    return cudaGetLastError();
 }
 
 }  // namespace bnk

@@ -48,5 +48,7 @@ bool gemm_supported(int M, int K, int ncol);
 size_t gemm_tiled_bytes(int M, int K);
 void repack_tiles(cudaStream_t st, const uint32_t *W, int M, int K, uint32_t *out);
 cudaError_t launch_gemm(cudaStream_t st, int sm_count, const GemmArgs &a, bool pdl);
+// one tiny kernel whose only wait can never complete and gives up after one round of tries: sets *err = 2 and returns
+cudaError_t launch_wait_selftest_tc(cudaStream_t st, int *err);
 
 }  // namespace bnk

@@ -61,9 +61,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *b, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
 }
 // bounded wait; on giving up records the fact and returns (no trap, no endless loop)
-__device__ __forceinline__ void mbar_wait(uint64_t *b, uint32_t parity, int *err) {
+__device__ __forceinline__ void mbar_wait(uint64_t *b, uint32_t parity, int *err, int limit = 1 << 22) {
     const uint32_t addr = smem_u32(b);
-    for (int it = 0; it < (1 << 22); ++it) {
+    for (int it = 0; it < limit; ++it) {
         uint32_t ok;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
                      : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
@@ -597,6 +597,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_phase_gemv(const PhaseArgs a) {
     STAMP(7);
 }
 
+// A wait that nothing will ever satisfy, with a short limit: the give-up path of mbar_wait (error word set, kernel
+// returns, context stays usable) can be exercised without hanging anything.
+__global__ void k_wait_selftest(int *err, int limit) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait(&bar, 0, err, limit);
+}
+
 }  // namespace
 
 namespace bnk {
@@ -635,6 +647,12 @@ cudaError_t launch_phase(cudaStream_t st, int sm_count, const PhaseArgs &a, bool
     cfg.numAttrs = pdl ? 1 : 0;
     BN_COUNT(1);
     return cudaLaunchKernelEx(&cfg, k_phase_gemv, a);
+}
+
+cudaError_t launch_wait_selftest_ring(cudaStream_t st, int *err) {
+    BN_COUNT(1);
+    k_wait_selftest<<<1, 32, 0, st>>>(err, 1 << 10);
+    return cudaGetLastError();
 }
 
 }  // namespace bnk

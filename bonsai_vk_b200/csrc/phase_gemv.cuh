@@ -45,5 +45,7 @@ size_t phase_smem_bytes(int hat_block);
 // launches with programmatic dependent launch when pdl is true
 cudaError_t launch_phase(cudaStream_t st, int sm_count, const PhaseArgs &a, bool pdl);
 bool phase_supported(int M, int K, int hat_block);
+// one tiny kernel whose only wait can never complete and gives up after ~1000 tries: sets *err = 1 and returns
+cudaError_t launch_wait_selftest_ring(cudaStream_t st, int *err);
 
 }  // namespace bnk

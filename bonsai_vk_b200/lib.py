@@ -55,6 +55,7 @@ def load_library() -> C.CDLL:
         "bn_download": (i32, [vp, vp, sz, vp, sz]),
         "bn_memset": (i32, [vp, vp, sz, i32, sz]),
         "bn_sync": (i32, [vp]),
+        "bn_selftest_wait": (i32, [vp, i32]),
         "bn_host_alloc": (i32, [sz, C.POINTER(vp)]),
         "bn_host_free": (i32, [vp]),
         "bn_event_create": (i32, [vp, C.POINTER(vp)]),
@@ -172,6 +173,11 @@ class Context:
 
     def sync(self):
         _check(self.lib.bn_sync(self.h), "bn_sync")
+
+    def selftest_wait(self, which: int):
+        """Queue a kernel whose bounded wait must give up (0: copy-ring wait, 1: tensor-core pipeline wait); the next
+        sync() then raises BonsaiError with code BN_ERR_TIMEOUT and the context stays usable."""
+        _check(self.lib.bn_selftest_wait(self.h, which), "bn_selftest_wait")
 
     def use_stream(self, cuda_stream: int):
         """Run this context's kernels on a stream owned by the caller (e.g. torch's current stream)."""

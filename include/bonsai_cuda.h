@@ -58,6 +58,12 @@ int bn_upload(bn_ctx *ctx, bn_buf *dst, size_t off, const void *src, size_t n);
 int bn_download(bn_ctx *ctx, const bn_buf *src, size_t off, void *dst, size_t n);
 int bn_memset(bn_ctx *ctx, bn_buf *dst, size_t off, int byte, size_t n);
 int bn_sync(bn_ctx *ctx);
+/* Failure detection without a fault: queues one tiny kernel whose only wait can never complete, with the wait's limit
+ * cut to a few milliseconds (which = 0: the copy-ring wait of the single-column projection; 1: the pipeline wait of the
+ * tensor-core projection). The kernel gives up, sets the context's error word and returns; the next bn_sync reports
+ * BN_ERR_TIMEOUT and clears the word, and the context stays usable. (The reference has no counterpart: its waits are
+ * Vulkan fences with an unbounded timeout, bonsai_weights.h:287.) */
+int bn_selftest_wait(bn_ctx *ctx, int which);
 
 /* page-locked host staging memory (reference: the mapped host_buf, bonsai_weights.h:199) */
 int bn_host_alloc(size_t bytes, void **out);
