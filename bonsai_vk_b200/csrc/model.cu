@@ -436,6 +436,9 @@ int bn_model_create(bn_ctx *ctx, const bn_hparams *hp, bn_model **out) {
     BN_REQUIRE(h.gdn_heads <= 64 && h.gdn_heads % h.gdn_qk_heads == 0, BN_ERR_ARG, "bn_model_create: bad gdn head counts");
     BN_REQUIRE(h.n_rot > 0 && h.n_rot <= h.head_dim && h.n_rot % 2 == 0, BN_ERR_ARG, "bn_model_create: bad rope dims");
     BN_REQUIRE(h.cap > 0 && h.cap % 2 == 0, BN_ERR_ARG, "bn_model_create: cap %d must be positive and even", h.cap);
+    BN_REQUIRE(h.attn_interval >= 1 || (h.attn_interval == 0 && h.n_layer <= 64), BN_ERR_ARG,
+               "bn_model_create: attn_interval %d must be >= 1, or 0 with an explicit layer mask over at most 64 blocks (have %d)",
+               h.attn_interval, h.n_layer);
     BN_REQUIRE(h.act_mode == 0, BN_ERR_ARG, "bn_model_create: only act_mode 0 (q8_1 activations) is built");
     BN_REQUIRE((h.k_mode | 1) == 1 && (h.v_mode | 1) == 1, BN_ERR_ARG, "bn_model_create: kv modes are 0 (q8_0) or 1 (fp16)");
     BN_REQUIRE(h.n_streams >= 0 && h.n_streams <= 1024, BN_ERR_ARG, "bn_model_create: n_streams %d out of range", h.n_streams);
@@ -481,7 +484,8 @@ int bn_model_finalize(bn_model *m) {
     for (int b = m->b0; b < m->b1 && rc == BN_OK; ++b) {
         bn_model::Layer &L = m->layers[b];
         const std::string B = "blk." + std::to_string(b) + ".";
-        L.attn = (b % h.attn_interval) == h.attn_interval - 1;
+        L.attn = h.attn_interval > 0 ? (b % h.attn_interval) == h.attn_interval - 1
+                                     : (((uint64_t(h.attn_mask_hi) << 32 | h.attn_mask_lo) >> b) & 1ull) != 0;
         L.attn_norm = tensor_ptr<float>(m, B + "attn_norm.weight", size_t(h.hidden) * 4, &rc);
         L.post_norm = tensor_ptr<float>(m, B + "post_attention_norm.weight", size_t(h.hidden) * 4, &rc);
         L.ffn_gate = tensor_ptr<uint32_t>(m, B + "ffn_gate.weight", ptq_bytes(h.ffn, h.hidden), &rc);

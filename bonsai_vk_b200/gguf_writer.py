@@ -33,8 +33,31 @@ def kv_arr_i32(k, a): return _kv(k, T_ARR, struct.pack("<IQ", T_I32, len(a)) + n
 def kv_arr_str(k, a): return _kv(k, T_ARR, struct.pack("<IQ", T_STR, len(a)) + b"".join(_s(x) for x in a))
 
 
-def metadata(hp: synth.HParams, signs: np.ndarray, hat_version: int = 1, names: list[str] | None = None) -> list[bytes]:
+def layer_type_kv(hp: synth.HParams, spelling: str) -> list[bytes]:
+    """The layer-typing keys in one of the spellings the loader accepts (reference contract: bonsai_model.h:432-468):
+    "interval" (full_attention_interval), "list" (string array, one token per block), "string" (one comma-separated
+    string), "numeric" (array of 0/1), "both" (interval and list), "none" (no key: the tensor table alone decides)."""
     A = ARCH + "."
+    tokens = ["full_attention" if hp.is_attn(b) else "linear_attention" for b in range(hp.n_layer)]
+    out = []
+    if spelling in ("interval", "both"):
+        out.append(kv_u32(A + "full_attention_interval", hp.attn_interval))
+    if spelling in ("list", "both"):
+        out.append(kv_arr_str(A + "attention.layer_types", tokens))
+    if spelling == "string":
+        out.append(kv_str(A + "layer_types", ", ".join(tokens)))
+    if spelling == "numeric":
+        out.append(kv_arr_i32(A + "layers.types", [1 if hp.is_attn(b) else 0 for b in range(hp.n_layer)]))
+    if spelling not in ("interval", "both", "list", "string", "numeric", "none"):
+        raise ValueError(f"unknown layer spelling {spelling}")
+    return out
+
+
+def metadata(hp: synth.HParams, signs: np.ndarray, hat_version: int = 1, names: list[str] | None = None,
+             layer_spelling: str | None = None, extra_kv: list[bytes] | None = None) -> list[bytes]:
+    A = ARCH + "."
+    if layer_spelling is None:
+        layer_spelling = "interval" if hp.attn_interval > 0 else "list"
     kv = [
         kv_str("general.architecture", ARCH),
         kv_u32("general.alignment", 32),
@@ -46,7 +69,8 @@ def metadata(hp: synth.HParams, signs: np.ndarray, hat_version: int = 1, names: 
         kv_u32(A + "attention.key_length", hp.head_dim),
         kv_u32(A + "attention.value_length", hp.head_dim),
         kv_u32(A + "rope.dimension_count", hp.n_rot),
-        kv_u32(A + "full_attention_interval", hp.attn_interval),
+        *layer_type_kv(hp, layer_spelling),
+        *(extra_kv or []),
         kv_u32(A + "ssm.conv_kernel", 4),
         kv_u32(A + "ssm.state_size", hp.gdn_dim),
         kv_u32(A + "ssm.group_count", hp.gdn_qk_heads),
@@ -69,14 +93,15 @@ def metadata(hp: synth.HParams, signs: np.ndarray, hat_version: int = 1, names: 
 
 
 def write(path: str, hp: synth.HParams, seed: int = 0, hat_version: int | None = 1, shuffle: bool = False,
-          override_dtype: dict[str, int] | None = None) -> dict:
+          override_dtype: dict[str, int] | None = None, layer_spelling: str | None = None,
+          extra_kv: list[bytes] | None = None) -> dict:
     """Write a synthetic model. Tensors are generated one at a time (the 9B shape never sits in memory whole).
     shuffle=True stores the tensors in name-sorted order (as real checkpoints do) instead of layer order.
     Returns {"tensors": n, "bytes": file size}."""
     shapes = synth.tensor_shapes(hp)
     names = sorted(shapes) if shuffle else list(shapes)
     signs = synth.make_signs(hp, seed)
-    kv = metadata(hp, signs, hat_version)
+    kv = metadata(hp, signs, hat_version, layer_spelling=layer_spelling, extra_kv=extra_kv)
     recs, off = [], 0
     for n in names:
         spec = shapes[n]

@@ -16,6 +16,7 @@
 #include <cstdio>
 #include <cstring>
 #include <map>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -137,6 +138,126 @@ inline bool gguf_load(const char *path, Gguf &g, std::string &why) {
     return true;
 }
 
+// ---- layer typing -------------------------------------------------------------------------------------------------
+// Which blocks are softmax-attention blocks and which are gated-delta-net blocks, from every spelling the reference
+// loader accepts (contract: bonsai_model.h:432-472): S1 an explicit per-layer list, S2 the interval key, S3 counts
+// (cross-check only), S4 the tensor table (always computed). Every spelling that answers must give the same mask.
+inline bool is_attn_block(const bn_hparams &h, int b) {
+    return h.attn_interval > 0 ? (b % h.attn_interval) == h.attn_interval - 1
+                               : (((uint64_t(h.attn_mask_hi) << 32 | h.attn_mask_lo) >> b) & 1ull) != 0;
+}
+// 1 = attention, 0 = recurrent, -1 = a kind this engine has no kernels for (refused, never remapped), -2 = unknown word
+inline int layer_token_kind(std::string t) {
+    while (!t.empty() && (t.back() == ' ' || t.back() == ',' || t.back() == ';')) t.pop_back();
+    while (!t.empty() && t.front() == ' ') t.erase(t.begin());
+    for (char &c : t) if (c >= 'A' && c <= 'Z') c = char(c - 'A' + 'a');
+    static const char *attn[] = {"full_attention", "attention", "attn", "full", "softmax", "self", "1"};
+    static const char *rec[] = {"ssm", "gdn", "gated_delta", "gated_delta_net", "linear_attention", "linear", "recurrent", "mamba", "none", "0"};
+    static const char *refused[] = {"sliding_attention", "sliding_window", "window", "windowed", "chunked", "moe", "hybrid"};
+    for (const char *w : attn) if (t == w) return 1;
+    for (const char *w : rec) if (t == w) return 0;
+    for (const char *w : refused) if (t == w) return -1;
+    return -2;
+}
+inline bool layer_mask_from_tokens(const std::vector<std::string> &tok, int n_layer, const std::string &key, uint64_t &mask, std::string &why) {
+    if (int(tok.size()) != n_layer) { why = key + " has " + std::to_string(tok.size()) + " entries, block_count is " + std::to_string(n_layer); return false; }
+    mask = 0;
+    for (int b = 0; b < n_layer; ++b) {
+        const int k = layer_token_kind(tok[b]);
+        if (k == -1) { why = key + ": block " + std::to_string(b) + " is '" + tok[b] + "', a layer kind this engine has no kernels for"; return false; }
+        if (k == -2) { why = key + ": block " + std::to_string(b) + " has the unknown layer type '" + tok[b] + "'"; return false; }
+        if (k == 1) mask |= 1ull << b;
+    }
+    return true;
+}
+// rc 0: h.attn_interval / h.attn_mask_* set. rc 2: refused, `why` says which spellings disagree or what is malformed.
+inline int resolve_layer_types(const Gguf &g, const std::string &arch, bn_hparams &h, std::string &why) {
+    const int n = h.n_layer;
+    if (n < 1 || n > 64) { why = "block_count " + std::to_string(n) + " is outside [1, 64] (the layer mask is 64 bits)"; return 2; }
+    const std::string prefixes[] = {arch + ".", "prism."};
+    struct Answer { std::string from; uint64_t mask; };
+    std::vector<Answer> answers;
+    // S1 explicit list
+    static const char *sufs[] = {"attention.layer_types", "layer_types", "layers.types"};
+    for (const std::string &P : prefixes) for (const char *s : sufs) {
+        const std::string key = P + s;
+        std::vector<std::string> tok;
+        bool have = false;
+        if (auto it = g.as.find(key); it != g.as.end()) { tok = it->second; have = true; }
+        else if (auto it2 = g.ai.find(key); it2 != g.ai.end()) { for (int64_t v : it2->second) tok.push_back(std::to_string(v)); have = true; }
+        else if (auto it3 = g.ks.find(key); it3 != g.ks.end()) {
+            std::string cur;
+            for (char c : it3->second + " ") {
+                if (c == ' ' || c == ',' || c == ';') { if (!cur.empty()) tok.push_back(cur); cur.clear(); } else cur.push_back(c);
+            }
+            have = true;
+        }
+        if (!have) continue;
+        uint64_t m = 0;
+        if (!layer_mask_from_tokens(tok, n, key, m, why)) return 2;
+        answers.push_back({key, m});
+    }
+    const bool have_list = !answers.empty();
+    // S2 interval
+    int interval = 0;
+    for (const std::string &P : prefixes) {
+        auto it = g.ki.find(P + "full_attention_interval");
+        if (it == g.ki.end()) continue;
+        if (it->second < 1) { why = P + "full_attention_interval = " + std::to_string(it->second) + ": must be >= 1 (a file whose layers are all attention says so with a layer list)"; return 2; }
+        if (interval && interval != int(it->second)) { why = "two full_attention_interval keys disagree"; return 2; }
+        interval = int(it->second);
+        uint64_t m = 0;
+        for (int b = 0; b < n; ++b) if ((b + 1) % interval == 0) m |= 1ull << b;
+        answers.push_back({P + "full_attention_interval", m});
+    }
+    const bool have_rule = have_list || interval > 0;
+    // S4 tensor table
+    {
+        std::set<std::string> names;
+        for (const Tensor &t : g.tensors) names.insert(t.name);
+        uint64_t m = 0;
+        for (int b = 0; b < n; ++b) {
+            const std::string B = "blk." + std::to_string(b) + ".";
+            const bool a = names.count(B + "attn_q.weight") || names.count(B + "attn_k.weight") || names.count(B + "attn_v.weight");
+            const bool r = names.count(B + "attn_qkv.weight") != 0;
+            if (a && r) { why = "block " + std::to_string(b) + " carries both attention (attn_q/k/v) and recurrent (attn_qkv) tensors"; return 2; }
+            if (!a && !r) { why = "block " + std::to_string(b) + " carries neither attn_q/k/v nor attn_qkv: it cannot be typed (a draft/MTP block has no path here)"; return 2; }
+            if (a) m |= 1ull << b;
+        }
+        answers.push_back({"the tensor table", m});
+    }
+    // S3 counts: cross-checks only
+    auto popcount = [](uint64_t v) { int c = 0; for (; v; v &= v - 1) ++c; return c; };
+    static const char *rec_counts[] = {"ssm_layer_count", "linear_attention_layer_count", "recurrent_layer_count", "gdn_layer_count"};
+    static const char *attn_counts[] = {"attn_layer_count", "full_attention_layer_count"};
+    for (const std::string &P : prefixes) {
+        for (int kind = 0; kind < 2; ++kind) {
+            const char *const *keys = kind ? attn_counts : rec_counts;
+            const int nkeys = kind ? 2 : 4;
+            for (int i = 0; i < nkeys; ++i) {
+                auto it = g.ki.find(P + keys[i]);
+                if (it == g.ki.end()) continue;
+                if (!have_rule) { why = P + keys[i] + " is present but neither a layer list nor full_attention_interval: a count cannot say where the layers are"; return 2; }
+                const int want = kind ? popcount(answers[0].mask) : n - popcount(answers[0].mask);
+                if (it->second != want) { why = P + keys[i] + " = " + std::to_string(it->second) + " but " + answers[0].from + " gives " + std::to_string(want); return 2; }
+            }
+        }
+    }
+    // agreement
+    for (size_t i = 1; i < answers.size(); ++i)
+        if (answers[i].mask != answers[0].mask) {
+            char buf[64];
+            snprintf(buf, sizeof buf, "%016llx vs %016llx", (unsigned long long)answers[0].mask, (unsigned long long)answers[i].mask);
+            why = "layer typing disagrees: " + answers[0].from + " and " + answers[i].from + " give different attention masks (" + buf + ")";
+            return 2;
+        }
+    const uint64_t mask = answers[0].mask;
+    h.attn_mask_lo = uint32_t(mask); h.attn_mask_hi = uint32_t(mask >> 32);
+    h.attn_interval = (interval > 0 && !have_list) ? interval : 0;
+    // an explicit list that happens to be an interval pattern stays a list: both forms give the same schedule
+    return 0;
+}
+
 struct Plan {
     bn_hparams hp = {};
     std::vector<int32_t> signs;
@@ -162,7 +283,7 @@ inline int plan_build(const Gguf &g, Plan &p, int cap, std::string &why) {
     if (!I("attention.value_length", vl)) return 2;
     if (vl != h.head_dim) { why = "attention.value_length differs from key_length"; return 2; }
     if (!I("rope.dimension_count", v)) return 2; h.n_rot = int(v);
-    if (!I("full_attention_interval", v)) return 2; h.attn_interval = int(v);
+    if (int rc = resolve_layer_types(g, arch_it->second, h, why)) return rc;
     if (!I("ssm.conv_kernel", v)) return 2; if (v != 4) { why = "ssm.conv_kernel must be 4"; return 2; }
     if (!I("ssm.state_size", v)) return 2; h.gdn_dim = int(v);
     if (!I("ssm.group_count", v)) return 2; h.gdn_qk_heads = int(v);

@@ -59,7 +59,7 @@ int lineage_gate(bh::Engine &e, const bh::Gguf &g, const char *path, const std::
         if (bn_model_token(ref.model, prompt[i], int(i), -1, nullptr)) { why = bn_last_error(); return -1; }
     const bn_hparams &h = e.plan.hp;
     int n_attn = 0, n_gdn = 0;
-    for (int b = 0; b < h.n_layer; ++b) (b % h.attn_interval == h.attn_interval - 1 ? n_attn : n_gdn)++;
+    for (int b = 0; b < h.n_layer; ++b) (bh::is_attn_block(h, b) ? n_attn : n_gdn)++;
     int mask = 0;
     std::vector<uint8_t> a, b;
     auto same = [&](int what, int index, size_t bytes, int bit) {
@@ -118,6 +118,9 @@ int main(int argc, char **argv) {
         printf("n_layer %d hidden %d ffn %d vocab %d heads %d/%d x %d rot %d interval %d gdn %d/%d x %d hat_block %d signs %zu\n", h.n_layer,
                h.hidden, h.ffn, h.vocab, h.n_head, h.n_kv, h.head_dim, h.n_rot, h.attn_interval, h.gdn_heads, h.gdn_qk_heads, h.gdn_dim,
                h.hat_block, e.plan.signs.size());
+        std::string kinds;
+        for (int b = 0; b < h.n_layer; ++b) kinds.push_back(bh::is_attn_block(h, b) ? 'A' : 'R');
+        printf("layer types %s (A = attention, R = gated delta net)\n", kinds.c_str());
         return 0;
     }
     if (mode != "run") return fail(2, "unknown mode " + mode);

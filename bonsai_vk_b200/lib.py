@@ -21,7 +21,8 @@ class HParamsC(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "n_layer", "hidden", "ffn", "vocab", "n_head", "n_kv", "head_dim", "n_rot", "attn_interval",
         "gdn_heads", "gdn_qk_heads", "gdn_dim", "hat_block", "act_mode", "k_mode", "v_mode", "cap")] + [
-        ("rms_eps", C.c_float), ("rope_base", C.c_float)] + [(n, C.c_int32) for n in ("n_streams", "block_begin", "block_end", "batch_cols")]
+        ("rms_eps", C.c_float), ("rope_base", C.c_float)] + [(n, C.c_int32) for n in ("n_streams", "block_begin", "block_end", "batch_cols")] + [
+        ("attn_mask_lo", C.c_uint32), ("attn_mask_hi", C.c_uint32)]
 
 
 class AttnDimsC(C.Structure):
@@ -286,6 +287,8 @@ class Model:
         lib = ctx.lib
         fields = {f[0] for f in HParamsC._fields_}
         hc = HParamsC(**{k: (float(v) if k in ("rms_eps", "rope_base") else int(v)) for k, v in hp.asdict().items() if k in fields})
+        mask = int(getattr(hp, "attn_mask", 0))
+        hc.attn_mask_lo, hc.attn_mask_hi = mask & 0xFFFFFFFF, mask >> 32
         h = C.c_void_p()
         _check(lib.bn_model_create(ctx.h, C.byref(hc), C.byref(h)), "bn_model_create")
         self.h = h

@@ -38,8 +38,11 @@ class HParams:
     block_begin: int = 0        # pipeline stage: this device holds blocks [block_begin, block_end)
     block_end: int = 0          # 0 = n_layer
     batch_cols: int = 0         # > 0: the multi-sequence pass (stage_batch) may take up to this many sequences per call
+    attn_mask: int = 0          # attn_interval == 0: explicit layer typing, bit b set = block b is an attention block
 
     def is_attn(self, b: int) -> bool:
+        if self.attn_interval == 0:
+            return bool((self.attn_mask >> b) & 1)
         return b % self.attn_interval == self.attn_interval - 1
 
     @property

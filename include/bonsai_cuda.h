@@ -159,7 +159,8 @@ typedef struct bn_model bn_model;
 typedef struct bn_hparams {
     int32_t n_layer, hidden, ffn, vocab;
     int32_t n_head, n_kv, head_dim, n_rot;    /* attention.head_count(_kv), key_length, rope.dimension_count */
-    int32_t attn_interval;                    /* full_attention_interval: block b is attention iff b % i == i-1 */
+    int32_t attn_interval;                    /* full_attention_interval: block b is attention iff b % i == i-1;
+                                                 0 = the explicit per-layer list in attn_mask_lo/hi is used instead */
     int32_t gdn_heads, gdn_qk_heads, gdn_dim; /* ssm.time_step_rank, ssm.group_count, ssm.state_size */
     int32_t hat_block;                        /* prism.hadamard.block_size */
     int32_t act_mode;                         /* 0 = q8_1 activations + integer dots */
@@ -173,6 +174,9 @@ typedef struct bn_hparams {
     int32_t batch_cols;                       /* > 0: bn_model_stage_batch may run up to this many sequences per call
                                                  (<= 32); costs one more activation arena per column and a tile-major
                                                  copy of the local projection weights for the tensor-core kernel */
+    /* explicit layer typing (reference: the resolved 64-bit mask of bonsai_model.h:470-472), read only when
+     * attn_interval == 0: block b (n_layer <= 64) is an attention block iff bit b is set, else a gated-delta-net block */
+    uint32_t attn_mask_lo, attn_mask_hi;
 } bn_hparams;
 
 enum bn_read_what {

@@ -31,7 +31,10 @@ struct HParams {
     int attn_order = 0;     // 0: the reference's serial order; 1: the CUDA kernels' order (same arithmetic,
     int pv_splits = 1;      //    sums regrouped as stated at attn_core_device_order)
     int threads = 8;        // row-parallel threads for the projections
-    bool is_attn(int b) const { return (b % attn_interval) == attn_interval - 1; }   // bonsai_model.h:136-138
+    unsigned long long attn_mask = 0;   // attn_interval == 0: the resolved explicit layer list, bit b = block b is attention
+    bool is_attn(int b) const {         // bonsai_model.h:136-148 (interval rule, or the per-layer list when the file has one)
+        return attn_interval > 0 ? (b % attn_interval) == attn_interval - 1 : ((attn_mask >> b) & 1ull) != 0;
+    }
     int qkv_dim() const { return 2 * gdn_qk_heads * gdn_dim + gdn_heads * gdn_dim; }  // 8192
     int inner() const { return gdn_heads * gdn_dim; }                                 // 4096
 };

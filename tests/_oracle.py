@@ -189,6 +189,8 @@ class OracleModel:
         # attn_order 1 = sums grouped as the CUDA kernels group them (pv split rule of bn_model_finalize)
         self.pv_splits = 256 if hp.cap >= 16384 else (64 if hp.cap >= 4096 else (8 if hp.cap >= 512 else 1))
         lib.bo_model_set_attn_order(self.m, attn_order, self.pv_splits)
+        mask = int(getattr(hp, "attn_mask", 0))
+        lib.bo_model_set_attn_mask(self.m, C.c_uint32(mask & 0xFFFFFFFF), C.c_uint32(mask >> 32))
         self.keep = {n: np.ascontiguousarray(t) for n, t in tensors.items()}
         for n, t in self.keep.items():
             lib.bo_model_set_tensor(self.m, n.encode(), _p(t))

@@ -127,3 +127,30 @@ def test_model_refuses_bad_calls(pair, ctx):
     del tensors["blk.0.ffn_up.weight"]
     with pytest.raises(BonsaiError, match="ffn_up"):
         Model(ctx, hp, tensors, signs)
+
+
+def test_explicit_layer_list_model(ctx):
+    """Layer kinds from an explicit per-layer list (attn_interval = 0, mask R A R R A A) instead of the interval rule:
+    logits and greedy stream against the oracle running the same list."""
+    hp = synth.tiny(n_layer=6, attn_interval=0, attn_mask=0b110010)
+    assert [hp.is_attn(b) for b in range(6)] == [False, True, False, False, True, True]
+    tensors, signs = synth.make_model(hp, seed=4)
+    gm, om = Model(ctx, hp, tensors, signs), OracleModel(hp, tensors, signs)
+    rng = np.random.default_rng(9)
+    gt = ot = None
+    worst = 0.0
+    for pos, t in enumerate(int(x) for x in rng.integers(0, hp.vocab, size=8)):
+        gt = gm.token(t, pos)
+        ol, _ = om.token(t, pos)
+        ot = om.argmax(ol)
+        worst = max(worst, _rel(gm.logits(), ol))
+    g_stream, o_stream = [], []
+    for i in range(16):
+        g_stream.append(gt); o_stream.append(ot)
+        gt = gm.token(gt, 8 + i)
+        ol, _ = om.token(ot, 8 + i)
+        ot = om.argmax(ol)
+    assert g_stream == o_stream
+    assert worst <= 1e-5
+    assert np.array_equal(gm.logits().view(np.uint32), ol.view(np.uint32)), "final logits are not bit-identical"
+    gm.close(); om.close()

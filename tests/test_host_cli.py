@@ -124,3 +124,30 @@ def test_run_matches_the_checker_and_passes_the_gate(exe, files):
     r2 = run(exe, files["sorted"], "run", "24", env=env)
     assert r2.returncode == 0, r2.stdout + r2.stderr
     assert _ids(r2.stdout) == want
+
+
+@pytest.mark.gpu
+def test_run_with_an_explicit_layer_list(exe, tmp_path):
+    """A file whose layer kinds come from `attention.layer_types` (an irregular pattern no interval can express):
+    loader -> decode gives the checker's token ids and the lineage gate passes."""
+    from tests._oracle import OracleModel
+
+    hp = synth.tiny(n_layer=6, attn_interval=0, attn_mask=0b110010)
+    p = str(tmp_path / "listed.gguf")
+    gguf_writer.write(p, hp, seed=3, shuffle=True)
+    tensors, signs = synth.make_model(hp, seed=3)
+    om = OracleModel(hp, tensors, signs)
+    prompt = [9, 1200, 33, 640]
+    want, logits = [], None
+    for pos, t in enumerate(prompt):
+        logits, _ = om.token(t, pos)
+    tok = om.argmax(logits)
+    for i in range(12):
+        want.append(tok)
+        logits, _ = om.token(tok, len(prompt) + i)
+        tok = om.argmax(logits)
+    om.close()
+    r = run(exe, p, "run", "12", env={"BONSAI_PROMPT_IDS": ",".join(map(str, prompt)), "BONSAI_CAP": "64", "BONSAI_QCHECK": "1"})
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "gate: PASS (bitmask 0 =" in r.stdout
+    assert _ids(r.stdout) == want

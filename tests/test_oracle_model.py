@@ -119,3 +119,18 @@ def test_attention_orders_agree():
         assert np.max(np.abs(outs[0] - outs[1]) / rms) <= 5e-4
         assert np.median(np.abs(outs[0] - outs[1]) / rms) <= 1e-5
         om.close()
+
+
+def test_explicit_layer_mask_equals_the_interval_rule():
+    """A per-layer list that spells the interval pattern must run the same schedule (bonsai_model.h:136-148, 470-472)."""
+    import dataclasses
+    hp = synth.tiny()                                           # interval 4 over 4 blocks: R R R A
+    tensors, signs = synth.make_model(hp, seed=2)
+    listed = dataclasses.replace(hp, attn_interval=0, attn_mask=0b1000)
+    assert [listed.is_attn(b) for b in range(4)] == [hp.is_attn(b) for b in range(4)]
+    a, b = OracleModel(hp, tensors, signs, threads=4), OracleModel(listed, tensors, signs, threads=4)
+    for pos, t in enumerate([5, 1000, 42]):
+        la, _ = a.token(t, pos)
+        lb, _ = b.token(t, pos)
+        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+    a.close(); b.close()
