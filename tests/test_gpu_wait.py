@@ -23,10 +23,12 @@ def test_bounded_wait_gives_up_and_context_survives(ctx, oracle, which, where):
     W = ptq.synth_matrix(rng, M, K)
     x = rng.standard_normal(K).astype(np.float32)
     xq = oracle.quantize_q8_1(x)
-    wb, xb, out = ctx.from_numpy(W), ctx.from_numpy(xq), ctx.alloc(M * 4)
-    ctx.gemv_q81(wb, M, K, xb, out)
+    wb, xb, out = ctx.from_numpy(W), ctx.from_numpy(x), ctx.alloc(M * 4)
+    pack = ctx.alloc(ctx.act_pack_bytes(K))
+    ctx.act_quant_q81(xb, K, pack)
+    ctx.gemv_q81(wb, M, K, pack, out)
     ctx.sync()
     ref, _, _ = oracle.gemv_q81(W, M, K, xq, want_dots=True)
     assert np.array_equal(out.download(np.float32, M).view(np.uint32), ref.view(np.uint32))
-    for b in (wb, xb, out):
+    for b in (wb, xb, pack, out):
         b.free()
