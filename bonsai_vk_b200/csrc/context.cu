@@ -155,6 +155,14 @@ int bn_upload(bn_ctx *ctx, bn_buf *dst, size_t off, const void *src, size_t n) {
     return BN_OK;
 }
 
+int bn_upload_async(bn_ctx *ctx, bn_buf *dst, size_t off, const void *src, size_t n) {
+    BN_REQUIRE(ctx && src, BN_ERR_ARG, "bn_upload_async: null argument");
+    BN_RANGE(dst, off, n, 1, "bn_upload_async");
+    if (n == 0) return BN_OK;
+    BN_CUDA(cudaMemcpyAsync(bn_ptr<char>(dst, off), src, n, cudaMemcpyHostToDevice, ctx->stream));
+    return BN_OK;
+}
+
 int bn_download(bn_ctx *ctx, const bn_buf *src, size_t off, void *dst, size_t n) {
     BN_REQUIRE(ctx && dst, BN_ERR_ARG, "bn_download: null argument");
     BN_RANGE(src, off, n, 1, "bn_download");

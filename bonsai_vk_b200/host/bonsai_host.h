@@ -352,22 +352,28 @@ inline int engine_load(Engine &e, const char *path, const Gguf &g, size_t chunk_
     if (bn_model_create(e.ctx, &e.plan.hp, &e.model)) { why = bn_last_error(); return 2; }
     FILE *f = fopen(path, "rb");
     if (!f) { why = "cannot reopen the GGUF"; return 3; }
-    void *stage = nullptr;
-    if (bn_host_alloc(chunk_bytes, &stage)) { why = bn_last_error(); fclose(f); return 3; }
+    // Two page-locked staging buffers: while the copy of one piece runs on the device's copy engine, the next piece
+    // is read from the file into the other buffer. bn_sync before a buffer is queued confirms that the copy queued one
+    // step earlier (out of the other buffer) is done, so a buffer is never overwritten while it is still being copied.
+    void *stage[2] = {nullptr, nullptr};
+    auto drop = [&]() { for (void *&s : stage) if (s) { bn_host_free(s); s = nullptr; } fclose(f); };
+    for (void *&s : stage) if (bn_host_alloc(chunk_bytes, &s)) { why = bn_last_error(); drop(); return 3; }
     uint64_t off = 0;
+    int cur = 0;
     for (const Tensor *tp : order) {
         const Tensor &t = *tp;
-        if (fseeko(f, off_t(g.data_start + t.off), SEEK_SET) != 0) { why = "seek failed for " + t.name; fclose(f); return 3; }
+        if (fseeko(f, off_t(g.data_start + t.off), SEEK_SET) != 0) { why = "seek failed for " + t.name; bn_sync(e.ctx); drop(); return 3; }
         for (uint64_t done = 0; done < t.bytes; done += chunk_bytes) {
             const size_t n = size_t(std::min<uint64_t>(chunk_bytes, t.bytes - done));
-            if (fread(stage, 1, n, f) != n) { why = "short read in " + t.name; fclose(f); return 3; }
-            if (bn_upload(e.ctx, e.weights, off + done, stage, n)) { why = bn_last_error(); fclose(f); return 3; }
+            if (fread(stage[cur], 1, n, f) != n) { why = "short read in " + t.name; bn_sync(e.ctx); drop(); return 3; }
+            if (bn_sync(e.ctx) || bn_upload_async(e.ctx, e.weights, off + done, stage[cur], n)) { why = bn_last_error(); bn_sync(e.ctx); drop(); return 3; }
+            cur ^= 1;
         }
-        if (bn_model_set_tensor(e.model, t.name.c_str(), e.weights, off, t.bytes)) { why = bn_last_error(); fclose(f); return 3; }
+        if (bn_model_set_tensor(e.model, t.name.c_str(), e.weights, off, t.bytes)) { why = bn_last_error(); bn_sync(e.ctx); drop(); return 3; }
         off += al(t.bytes);
     }
-    fclose(f);
-    bn_host_free(stage);
+    if (bn_sync(e.ctx)) { why = bn_last_error(); drop(); return 3; }
+    drop();
     if (bn_upload(e.ctx, e.weights, off, e.plan.signs.data(), e.plan.signs.size() * 4)) { why = bn_last_error(); return 3; }
     if (bn_model_set_signs(e.model, e.weights, off, int(e.plan.signs.size()))) { why = bn_last_error(); return 2; }
     if (bn_model_finalize(e.model)) { why = bn_last_error(); return 2; }

@@ -53,6 +53,7 @@ def load_library() -> C.CDLL:
         "bn_free": (i32, [vp, vp]),
         "bn_buf_size": (sz, [vp]),
         "bn_upload": (i32, [vp, vp, sz, vp, sz]),
+        "bn_upload_async": (i32, [vp, vp, sz, vp, sz]),
         "bn_download": (i32, [vp, vp, sz, vp, sz]),
         "bn_memset": (i32, [vp, vp, sz, i32, sz]),
         "bn_sync": (i32, [vp]),

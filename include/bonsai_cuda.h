@@ -55,6 +55,10 @@ int bn_alloc(bn_ctx *ctx, size_t bytes, bn_buf **out);
 int bn_free(bn_ctx *ctx, bn_buf *buf);
 size_t bn_buf_size(const bn_buf *buf);
 int bn_upload(bn_ctx *ctx, bn_buf *dst, size_t off, const void *src, size_t n);
+/* queued copy from page-locked memory (bn_host_alloc): returns at once; src must stay untouched until the next bn_sync.
+ * The loader overlaps reading the next piece of the file with this copy (reference: the staged upload loop of
+ * bonsai_weights.h:440-529, which waits for every batch). */
+int bn_upload_async(bn_ctx *ctx, bn_buf *dst, size_t off, const void *src, size_t n);
 int bn_download(bn_ctx *ctx, const bn_buf *src, size_t off, void *dst, size_t n);
 int bn_memset(bn_ctx *ctx, bn_buf *dst, size_t off, int byte, size_t n);
 int bn_sync(bn_ctx *ctx);
