@@ -6,6 +6,9 @@
   python -m bonsai_vk_b200.kernel_lab gemm M K NCOL [ITER]  the multi-column tensor-core projection (tcgen05), timed
   python -m bonsai_vk_b200.kernel_lab stage NBLOCKS NCOL CTX [ITER]   one pipeline stage (first NBLOCKS blocks of the 9B
                                             shape) for NCOL sequences per pass at context CTX, timed per pass
+  python -m bonsai_vk_b200.kernel_lab stamps [TOKENS]       where one B=1 token of the 9B shape spends its time: device time
+                                            stamps of CTA 0 of every fused projection launch (the reference's per-token
+                                            ledger idea, BONSAI_PROFILE, bonsai_forward.h:650-662)
 
 Prints max|err| and rel against the CPU checker (when oracle/ is built), then ms/op, Gop/s and GB/s of
 PTQ1_0 bytes from CUDA events. Timing rotates through enough copies of the matrix to exceed L2.
@@ -153,8 +156,42 @@ def stage_lab(argv):
     ctx.close()
 
 
+def stamps_lab(argv):
+    """Per-token ledger of the B=1 schedule from the projection kernels' own time stamps (ns, global timer)."""
+    from bonsai_vk_b200 import Context, Model, synth
+    reps = int(argv[0]) if argv else 5
+    ctx = Context(0)
+    hp = synth.HParams(cap=256)
+    tensors, signs = synth.make_model_repeated(hp)
+    m = Model(ctx, hp, tensors, signs)
+    del tensors
+    nxt = 0
+    for pos in range(20):                                   # warm-up: state, cache and clocks
+        nxt = m.token(int(nxt) % hp.vocab, pos)
+    names = ["launch -> first copies issued", "waiting for the previous grid", "norm", "signs + Hadamard (last block)", "q8_1 (last block)",
+             "operand registers", "main loop + epilogue", "gap after the previous launch's CTA 0", "in kernel"]
+    acc, span = None, 0.0
+    for rep in range(reps):
+        st = m.profile_token(int(nxt) % hp.vocab, 20 + rep).astype(np.int64)
+        nxt = 5
+        d = np.diff(st, axis=1)
+        gap = np.concatenate([[0], st[1:, 0] - st[:-1, 7]])
+        row = np.concatenate([d, gap[:, None], (st[:, 7] - st[:, 0])[:, None]], axis=1)
+        acc = row if acc is None else acc + row
+        span += (st[-1, 7] - st[0, 0]) / 1000.0
+    acc = acc / reps
+    print(f"{acc.shape[0]} projection launches per token, mean of {reps} tokens; first start -> last end {span / reps:.1f} us")
+    print(f"{'interval':40s} {'sum us':>9s} {'mean us':>8s}  first block's 4 launches (us)")
+    for k, name in enumerate(names):
+        first = " ".join(f"{acc[i, k] / 1000:6.2f}" for i in range(min(4, acc.shape[0])))
+        print(f"{name:40s} {acc[:, k].sum() / 1000:9.1f} {acc[:, k].mean() / 1000:8.2f}  {first}")
+    m.close()
+
+
 def main(argv):
     from bonsai_vk_b200 import Context, ptq
+    if argv and argv[0] == "stamps":
+        return stamps_lab(argv[1:])
     if argv and argv[0] == "stage":
         return stage_lab(argv[1:])
     if argv and argv[0] == "attn":
