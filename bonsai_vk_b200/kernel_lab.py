@@ -168,7 +168,7 @@ def stamps_lab(argv):
     nxt = 0
     for pos in range(20):                                   # warm-up: state, cache and clocks
         nxt = m.token(int(nxt) % hp.vocab, pos)
-    names = ["launch -> first copies issued", "waiting for the previous grid", "norm", "signs + Hadamard (last block)", "q8_1 (last block)",
+    names = ["launch -> first copies issued", "waiting for the previous grid", "norm", "signs + Hadamard (+ q8_1 of earlier blocks)", "q8_1 (last Hadamard block)",
              "operand registers", "main loop + epilogue", "gap after the previous launch's CTA 0", "in kernel"]
     acc, span = None, 0.0
     for rep in range(reps):
@@ -181,10 +181,10 @@ def stamps_lab(argv):
         span += (st[-1, 7] - st[0, 0]) / 1000.0
     acc = acc / reps
     print(f"{acc.shape[0]} projection launches per token, mean of {reps} tokens; first start -> last end {span / reps:.1f} us")
-    print(f"{'interval':40s} {'sum us':>9s} {'mean us':>8s}  first block's 4 launches (us)")
+    print(f"{'interval':44s} {'sum us':>9s} {'mean us':>8s}  first block's 4 launches (us)")
     for k, name in enumerate(names):
         first = " ".join(f"{acc[i, k] / 1000:6.2f}" for i in range(min(4, acc.shape[0])))
-        print(f"{name:40s} {acc[:, k].sum() / 1000:9.1f} {acc[:, k].mean() / 1000:8.2f}  {first}")
+        print(f"{name:44s} {acc[:, k].sum() / 1000:9.1f} {acc[:, k].mean() / 1000:8.2f}  {first}")
     m.close()
 
 
