@@ -228,7 +228,11 @@ __global__ void __launch_bounds__(256) k_gdn_delta(int heads, int qk_heads, cons
 // input. The conv history is double-buffered by position parity: the two v-heads that share a q/k head both
 // read its taps while one of them writes the shifted taps into the other buffer.
 // Arithmetic and its order are those of the stand-alone kernels above.
-__global__ void __launch_bounds__(512) k_gdn_core(int heads, int qk_heads, int hidden, const float *__restrict__ qkv,
+// MINB = CTAs per SM the register budget is set for: 1 for a single sequence (32 CTAs in all; the loads hoisted above
+// the dependency wait keep ~90 registers live, measured 4 % of a token faster than the 64-register build), 2 when many
+// sequences fill the GPU with CTAs (measured 3 % of a 32-sequence pass faster than one CTA per SM).
+template <int MINB>
+__global__ void __launch_bounds__(512, MINB) k_gdn_core(int heads, int qk_heads, int hidden, const float *__restrict__ qkv,
                                                   const float *__restrict__ conv_w, float *__restrict__ hist0,
                                                   float *__restrict__ hist1, const int *__restrict__ pos_ptr,
                                                   const float *__restrict__ x, const float *__restrict__ inv_ptr,
@@ -237,42 +241,58 @@ __global__ void __launch_bounds__(512) k_gdn_core(int heads, int qk_heads, int h
                                                   const float *__restrict__ ssm_a, float *__restrict__ state,
                                                   const float *__restrict__ z, const float *__restrict__ ssm_norm, float eps,
                                                   float *__restrict__ y, float scale, bnk::Cols cols) {
-    bnk::pdl_sync();
     { const size_t col = blockIdx.z; qkv = bnk::colp(qkv, col * cols.arena); hist0 = bnk::colp(hist0, col * cols.conv); hist1 = bnk::colp(hist1, col * cols.conv); pos_ptr = bnk::colp(pos_ptr, col * cols.arena); x = bnk::colp(x, col * cols.arena); inv_ptr = bnk::colp(inv_ptr, col * cols.arena); state = bnk::colp(state, col * cols.gdn); z = bnk::colp(z, col * cols.arena); y = bnk::colp(y, col * cols.arena); }
     __shared__ float sq[128], sk[128], sv[128], so[128], sgb[2];
     extern __shared__ float4 dyn[];                // [3][hidden/4]: normed residual, row h of ssm_alpha, row h of ssm_beta
     const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hq = h % qk_heads, n4 = hidden / 4;
+    // ---- before the dependency wait: everything that the preceding kernel (the qkv / gate projection) does not write.
+    // Constants, this layer's recurrent state and conv taps (last written one token ago) and the position (written at
+    // the end of the previous token) are requested while the projection's last CTAs are still running; every kernel of
+    // the schedule waits for its predecessor before it releases its successor, so all older kernels are complete here.
     const bool odd = pos_ptr[0] & 1;               // a token at position p reads taps from buffer p & 1, writes the other
     const float *hist_rd = odd ? hist1 : hist0;
     float *hist_wr = odd ? hist0 : hist1;
-    {   // everything the two dependent dot-product chains will touch goes to shared memory first, all loads in flight
+    float S[8][4];                                 // state rows of this warp (8 of the head's 128)
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        const float *Sr = state + (size_t(h) * 128 + warp * 8 + r) * 128;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[r][e] = Sr[lane + 32 * e];
+    }
+    const int cch = tid < 128 ? hq * 128 + tid : (tid < 256 ? qk_heads * 128 + hq * 128 + (tid - 128) : 2 * qk_heads * 128 + h * 128 + (tid - 256));
+    float tap0 = 0.0f, tap1 = 0.0f, tap2 = 0.0f, cw0 = 0.0f, cw1 = 0.0f, cw2 = 0.0f, cw3 = 0.0f;
+    if (tid < 384) {
+        const float *sr = hist_rd + 3 * size_t(cch);
+        const float *wc = conv_w + 4 * size_t(cch);
+        tap0 = sr[0]; tap1 = sr[1]; tap2 = sr[2];
+        cw0 = wc[0]; cw1 = wc[1]; cw2 = wc[2]; cw3 = wc[3];
+    }
+    {
+        const float4 *ra = reinterpret_cast<const float4 *>(alpha_w + size_t(h) * hidden), *rb = reinterpret_cast<const float4 *>(beta_w + size_t(h) * hidden);
+        for (int i = tid; i < n4; i += 512) { dyn[n4 + i] = ra[i]; dyn[2 * n4 + i] = rb[i]; }
+    }
+    bnk::pdl_sync();
+    {   // the normed residual goes to shared memory for the two dependent dot-product chains
         const float inv = inv_ptr[0];
         const float4 *xv = reinterpret_cast<const float4 *>(x), *nw = reinterpret_cast<const float4 *>(norm_w);
-        const float4 *ra = reinterpret_cast<const float4 *>(alpha_w + size_t(h) * hidden), *rb = reinterpret_cast<const float4 *>(beta_w + size_t(h) * hidden);
         for (int i = tid; i < n4; i += 512) {
             const float4 a4 = xv[i], w4 = nw[i];
             dyn[i] = make_float4(__fmul_rn(__fmul_rn(a4.x, inv), w4.x), __fmul_rn(__fmul_rn(a4.y, inv), w4.y),
                                  __fmul_rn(__fmul_rn(a4.z, inv), w4.z), __fmul_rn(__fmul_rn(a4.w, inv), w4.w));
-            dyn[n4 + i] = ra[i];
-            dyn[2 * n4 + i] = rb[i];
         }
     }
-    auto conv1 = [&](int c, bool store) -> float {
-        const float *sr = hist_rd + 3 * size_t(c);
-        const float *wc = conv_w + 4 * size_t(c);
-        const float s0 = sr[0], s1 = sr[1], s2 = sr[2], xn = qkv[c];
-        float acc = __fmul_rn(wc[0], s0);
-        acc = __fadd_rn(acc, __fmul_rn(wc[1], s1));
-        acc = __fadd_rn(acc, __fmul_rn(wc[2], s2));
-        acc = __fadd_rn(acc, __fmul_rn(wc[3], xn));
-        if (store) { float *sw = hist_wr + 3 * size_t(c); sw[0] = s1; sw[1] = s2; sw[2] = xn; }
-        return silu_f(acc);
-    };
     const bool own_qk = h < qk_heads;              // the first of the v-heads sharing q/k head hq writes its taps
-    if (tid < 128) sq[tid] = conv1(hq * 128 + tid, own_qk);
-    else if (tid < 256) sk[tid - 128] = conv1(qk_heads * 128 + hq * 128 + (tid - 128), own_qk);
-    else if (tid < 384) sv[tid - 256] = conv1(2 * qk_heads * 128 + h * 128 + (tid - 256), true);
+    if (tid < 384) {
+        const float xn = qkv[cch];
+        float acc = __fmul_rn(cw0, tap0);
+        acc = __fadd_rn(acc, __fmul_rn(cw1, tap1));
+        acc = __fadd_rn(acc, __fmul_rn(cw2, tap2));
+        acc = __fadd_rn(acc, __fmul_rn(cw3, xn));
+        if (tid >= 256 || own_qk) { float *sw = hist_wr + 3 * size_t(cch); sw[0] = tap1; sw[1] = tap2; sw[2] = xn; }
+        const float cv = silu_f(acc);
+        if (tid < 128) sq[tid] = cv; else if (tid < 256) sk[tid - 128] = cv; else sv[tid - 256] = cv;
+    }
     __syncthreads();
     if (warp >= 14) {
         // row h of ssm_alpha (warp 14) or ssm_beta (warp 15) times the normed residual: lane l takes float4 groups
@@ -292,14 +312,6 @@ __global__ void __launch_bounds__(512) k_gdn_core(int heads, int qk_heads, int h
                 sgb[0] = __fmul_rn(sp, ssm_a[h]);
             } else sgb[1] = sigmoid_f(acc);
         }
-    }
-    // state rows of this warp (8 of the head's 128), loaded while the two chains run
-    float S[8][4];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        const float *Sr = state + (size_t(h) * 128 + warp * 8 + r) * 128;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) S[r][e] = Sr[lane + 32 * e];
     }
     float qq[4], kk[4];
     {
@@ -706,8 +718,15 @@ void gdn_core_fused(cudaStream_t st, GdnDims d, int hidden, const float *qkv, co
                     const float *beta_w, const float *dt_bias, const float *ssm_a, float *state, const float *z,
                     const float *ssm_norm, float eps, float *y, Cols cols) {
     static bool attr = false;
-    if (!attr) { cudaFuncSetAttribute(k_gdn_core, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 16384 * 4); attr = true; }
-    launch(k_gdn_core, dim3(d.heads, 1, cols.z()), dim3(512), size_t(hidden) * 12, st, d.heads, d.qk_heads, hidden, qkv, conv_w, hist0, hist1, pos_ptr, x, inv_ptr,
+    if (!attr) {
+        cudaFuncSetAttribute(k_gdn_core<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 16384 * 4);
+        cudaFuncSetAttribute(k_gdn_core<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 16384 * 4);
+        attr = true;
+    }
+    if (cols.z() > 1) launch(k_gdn_core<2>, dim3(d.heads, 1, cols.z()), dim3(512), size_t(hidden) * 12, st, d.heads, d.qk_heads, hidden, qkv, conv_w, hist0, hist1, pos_ptr, x, inv_ptr,
+                                                         norm_w, alpha_w, beta_w, dt_bias, ssm_a, state, z, ssm_norm, eps, y,
+                                                         1.0f / sqrtf(float(d.dim)), cols);
+    else launch(k_gdn_core<1>, dim3(d.heads, 1, cols.z()), dim3(512), size_t(hidden) * 12, st, d.heads, d.qk_heads, hidden, qkv, conv_w, hist0, hist1, pos_ptr, x, inv_ptr,
                                                          norm_w, alpha_w, beta_w, dt_bias, ssm_a, state, z, ssm_norm, eps, y,
                                                          1.0f / sqrtf(float(d.dim)), cols); 
 }
