@@ -14,7 +14,7 @@ One "step" is one decoded token (one pass of the whole-token schedule). Prints O
   streams64 - (N=1 only) the 64-sequence workload of the multi-GPU configuration on this one GPU, the base of its scaling.
 --impl reference times the reference's own CPU arithmetic for the path (dequantise + fp64 dot,
 oracle/_ref when built, else the oracle port) on all host cores, in the same unit.
-N > 1 (torchrun, one rank per GPU): BASELINE config 4 - the model is layer-pipelined over the N GPUs
+N > 1 (torchrun, one rank per GPU): the 64-stream pipeline workload - the model is layer-pipelined over the N GPUs
 (contiguous block stages, hidden state handed off over NVLink with NCCL send/recv), 64 concurrent sequences at
 context 8192 are micro-batched through the stages; a step is one decode step of all 64 sequences and `value`
 is the aggregate tok/s. The KV caches are marked filled up to the start position (the reference's own
@@ -141,6 +141,8 @@ def streams64_one_gpu(ctx, tensors_again=None, steps=6, warm=2):
         m.fill_kv(s, pos0)
     toks = [ctx.alloc(MB * 4) for _ in range(S // MB)]
     first = [int(t) for t in np.random.default_rng(7).integers(0, hp.vocab, size=S)]
+    for u in range(S // MB):
+        m.stage_prepare(u * MB, MB)
 
     def step(i):
         for u in range(S // MB):
@@ -202,6 +204,7 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     scratch_in = ctx.wrap(torch.zeros(MB * hp.hidden, dtype=torch.float32, device=dev).data_ptr(), MB * hp.hidden * 4)
     scratch_out = ctx.alloc(MB * hp.hidden * 4)
     for u in range(U):
+        m.stage_prepare(u * MB if MB > 1 else u, MB if MB > 1 else 0)
         if MB > 1:
             m.stage_batch(u * MB, [1] * MB if rank == 0 else None, [pos0[u]] * MB, None if rank == 0 else scratch_in, scratch_out)
         else:

@@ -61,7 +61,10 @@ def build_host(force: bool = False) -> str:
 def build_oracle() -> None:
     """Compile the CPU checker under oracle/ (and the reference shim when the reference tree is
     present). Building the checker is not using it: only tests and the benchmark baselines load it."""
-    r = subprocess.run(["make", "-C", os.path.join(ROOT, "oracle")], capture_output=True, text=True)
+    # the reference tree: $BONSAI_REF, else a directory named "reference" beside this repository
+    ref = os.environ.get("BONSAI_REF") or os.path.join(os.path.dirname(ROOT), "reference")
+    cmd = ["make", "-C", os.path.join(ROOT, "oracle")] + ([f"REF={ref}"] if os.path.isdir(os.path.join(ref, "runtime_vk")) else [])
+    r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)
         raise RuntimeError("oracle build failed")

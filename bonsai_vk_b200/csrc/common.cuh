@@ -55,7 +55,10 @@ int bn_cuda_fail(cudaError_t e, const char *what);
 // range check of (buffer, offset, size); alignment in bytes
 static inline int bn_check_range(const bn_buf *b, size_t off, size_t n, size_t align, const char *what) {
     if (!b || !b->dptr) { bn_set_error("%s: null buffer", what); return BN_ERR_ARG; }
-    if (off % align) { bn_set_error("%s: offset %zu not %zu-byte aligned", what, off, align); return BN_ERR_ARG; }
+    if ((reinterpret_cast<uintptr_t>(b->dptr) + off) % align) {      // the address itself: a wrapped pointer may have any base
+        bn_set_error("%s: address (base + offset %zu) not %zu-byte aligned", what, off, align);
+        return BN_ERR_ARG;
+    }
     if (off > b->bytes || n > b->bytes - off) {
         bn_set_error("%s: range [%zu, +%zu) exceeds buffer of %zu bytes", what, off, n, b->bytes);
         return BN_ERR_BOUNDS;

@@ -56,6 +56,12 @@ int bn_init(int device, bn_ctx **out) {
         return BN_ERR_CUDA;
     }
     BN_REQUIRE(device >= 0 && device < n, BN_ERR_ARG, "bn_init: device %d out of range [0,%d)", device, n);
+    // one process drives one GPU (multi-GPU = one process per stage): kernel attributes and the launch counter are
+    // kept per process, so a second device in the same process is refused rather than half-supported
+    static int g_first_device = -1;
+    BN_REQUIRE(g_first_device < 0 || g_first_device == device, BN_ERR_STATE,
+               "bn_init: this process already drives device %d; use one process per GPU (asked for device %d)", g_first_device, device);
+    g_first_device = device;
     BN_CUDA(cudaSetDevice(device));
     cudaDeviceProp p;
     BN_CUDA(cudaGetDeviceProperties(&p, device));
@@ -187,8 +193,12 @@ int bn_sync(bn_ctx *ctx) {
     BN_CUDA(cudaMemcpy(&flag, ctx->err_dev, 4, cudaMemcpyDeviceToHost));
     if (flag) {
         cudaMemset(ctx->err_dev, 0, 4);
+        if (flag == 3) {
+            bn_set_error("a token id read from device memory was outside the vocabulary (id 0 was used in its place); results of that step are invalid");
+            return BN_ERR_ARG;
+        }
         bn_set_error("a bounded device-side wait gave up (%s); results of the last kernels are invalid",
-                     flag == 2 ? "tensor-core projection pipeline" : "copy ring");
+                     flag == 2 ? "tensor-core projection pipeline" : flag == 4 ? "grid barrier of the whole-token kernel" : "copy ring");
         return BN_ERR_TIMEOUT;
     }
     return BN_OK;

@@ -331,10 +331,17 @@ int build_batch_side(bn_model *m) {
 }
 
 struct ColInit { int tok[bnk::GEMM_MAX_COLS]; int pos[bnk::GEMM_MAX_COLS]; };
-__global__ void k_set_cols(int *tok, int *pos, size_t arena, int n, ColInit ci, const int *tok_src) {
+// A token id that arrives through device memory (the message from the last pipeline stage) is checked here, before any
+// kernel forms an address from it: outside [0, vocab) sets the context's error word (code 3) and id 0 is used instead.
+__device__ __forceinline__ int checked_tok(int t, int vocab, int *err) {
+    if (t >= 0 && t < vocab) return t;
+    atomicExch(err, 3);
+    return 0;
+}
+__global__ void k_set_cols(int *tok, int *pos, size_t arena, int n, ColInit ci, const int *tok_src, int vocab, int *err) {
     const int c = threadIdx.x;
     if (c >= n) return;
-    bnk::colp(tok, c * arena)[0] = tok_src ? tok_src[c] : ci.tok[c];
+    bnk::colp(tok, c * arena)[0] = tok_src ? checked_tok(tok_src[c], vocab, err) : ci.tok[c];
     bnk::colp(pos, c * arena)[0] = ci.pos[c];
 }
 
@@ -409,9 +416,9 @@ __global__ void k_advance(int *tok, int *pos, const int *next, int *hist, int *s
     step[0] = s + 1;
 }
 
-__global__ void k_set_tok_pos(int *tok, int *pos, int t, int p, const int *tok_src) {
+__global__ void k_set_tok_pos(int *tok, int *pos, int t, int p, const int *tok_src, int vocab, int *err) {
     bnk::pdl_sync();
-    if (threadIdx.x == 0) { tok[0] = tok_src ? tok_src[0] : t; pos[0] = p; }
+    if (threadIdx.x == 0) { tok[0] = tok_src ? checked_tok(tok_src[0], vocab, err) : t; pos[0] = p; }
 }
 __global__ void k_fill_u16(uint16_t *p, size_t n, uint16_t v) {
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) p[i] = v;
@@ -688,6 +695,41 @@ int bn_model_decode(bn_model *m, int first_tok, int pos0, int n_steps, int *out_
     return BN_OK;
 }
 
+int bn_model_stage_prepare(bn_model *m, int stream0, int ncol) {
+    BN_REQUIRE(m && m->finalized, BN_ERR_STATE, "bn_model_stage_prepare: model not finalized");
+    const bn_hparams &h = m->hp;
+    const int S = h.n_streams > 0 ? h.n_streams : 1;
+    BN_REQUIRE(ncol >= 0 && stream0 >= 0 && stream0 + (ncol > 0 ? ncol : 1) <= S, BN_ERR_ARG,
+               "bn_model_stage_prepare: sequences %d..%d outside [0, %d)", stream0, stream0 + (ncol > 0 ? ncol : 1) - 1, S);
+    cudaStream_t st = m->ctx->stream;
+    cudaGraph_t g = nullptr;
+    cudaGraphExec_t ge = nullptr;
+    m->cur = stream0;
+    if (ncol == 0) {
+        if (m->stage_graphs.empty()) m->stage_graphs.assign(S, nullptr);
+        if (m->stage_graphs[stream0]) return BN_OK;
+    } else {
+        BN_REQUIRE(h.batch_cols > 0 && ncol <= h.batch_cols, BN_ERR_ARG,
+                   "bn_model_stage_prepare: %d sequences per pass, the model was created for at most %d (bn_hparams.batch_cols)", ncol, h.batch_cols);
+        BN_REQUIRE(m->fused, BN_ERR_STATE, "bn_model_stage_prepare: the multi-sequence pass needs the fused layer kernels");
+        if (m->batch_graphs.count(long(stream0) * 64 + ncol)) return BN_OK;
+    }
+    const unsigned long long before = g_bn_launches;
+    BN_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    if (ncol == 0) enqueue_token(m, -1, true); else enqueue_batch(m, ncol);
+    cudaError_t e = cudaStreamEndCapture(st, &g);
+    if (e == cudaSuccess) e = m->launch_err;
+    m->launch_err = cudaSuccess;
+    if (e != cudaSuccess) return bn_cuda_fail(e, "cudaStreamEndCapture(stage)");
+    (ncol == 0 ? m->graph_launches : m->batch_graph_launches) = int(g_bn_launches - before);
+    g_bn_launches = before;               // captured, not launched
+    e = cudaGraphInstantiate(&ge, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return bn_cuda_fail(e, "cudaGraphInstantiate(stage)");
+    if (ncol == 0) m->stage_graphs[stream0] = ge; else m->batch_graphs.emplace(long(stream0) * 64 + ncol, ge);
+    return BN_OK;
+}
+
 int bn_model_stage(bn_model *m, int stream, int tok, int pos, const bn_buf *in, size_t in_off, bn_buf *out, size_t out_off) {
     BN_REQUIRE(m && m->finalized, BN_ERR_STATE, "bn_model_stage: model not finalized");
     const bn_hparams &h = m->hp;
@@ -703,7 +745,7 @@ int bn_model_stage(bn_model *m, int stream, int tok, int pos, const bn_buf *in, 
     BN_RANGE(out, out_off, last ? 4 : size_t(h.hidden) * 4, 4, "bn_model_stage output");
     m->cur = stream;
     m->next_pos = pos + 1;
-    k_set_tok_pos<<<1, 32, 0, st>>>(m->TOK, m->POS, tok, pos, (first && tok < 0) ? bn_ptr<int>(in, in_off) : nullptr);
+    k_set_tok_pos<<<1, 32, 0, st>>>(m->TOK, m->POS, tok, pos, (first && tok < 0) ? bn_ptr<int>(in, in_off) : nullptr, h.vocab, m->ctx->err_dev);
     BN_COUNT(1);
     if (!first) BN_CUDA(cudaMemcpyAsync(m->RES, bn_ptr<char>(in, in_off), size_t(h.hidden) * 4, cudaMemcpyDeviceToDevice, st));
     cudaError_t e = cudaSuccess;
@@ -711,21 +753,11 @@ int bn_model_stage(bn_model *m, int stream, int tok, int pos, const bn_buf *in, 
         enqueue_token(m, -1, true);
         e = cudaGetLastError();
     } else {
-        // the ~100 launches of a stage are replayed as one graph: the host only feeds copies and NCCL calls
-        if (m->stage_graphs.empty()) m->stage_graphs.assign(S, nullptr);
-        if (!m->stage_graphs[stream]) {
-            cudaGraph_t g = nullptr;
-            const unsigned long long before = g_bn_launches;
-            BN_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-            enqueue_token(m, -1, true);
-            e = cudaStreamEndCapture(st, &g);
-            if (e != cudaSuccess) return bn_cuda_fail(e, "cudaStreamEndCapture(stage)");
-            m->graph_launches = int(g_bn_launches - before);
-            g_bn_launches = before;
-            e = cudaGraphInstantiate(&m->stage_graphs[stream], g, 0);
-            cudaGraphDestroy(g);
-            if (e != cudaSuccess) return bn_cuda_fail(e, "cudaGraphInstantiate(stage)");
-        }
+        // the ~100 launches of a stage are replayed as one graph: the host only feeds copies and NCCL calls. The graph
+        // must exist already (bn_model_stage_prepare): building one here could synchronise a device whose stream holds a
+        // send/recv kernel that is waiting for its peer
+        BN_REQUIRE(stream < int(m->stage_graphs.size()) && m->stage_graphs[stream], BN_ERR_STATE,
+                   "bn_model_stage: sequence %d was not prepared; call bn_model_stage_prepare(model, %d, 0) first", stream, stream);
         e = cudaGraphLaunch(m->stage_graphs[stream], st);
         BN_COUNT(m->graph_launches);
     }
@@ -762,7 +794,7 @@ int bn_model_stage_batch(bn_model *m, int stream0, int ncol, const int *tok, con
     BN_RANGE(out, out_off, last ? size_t(ncol) * 4 : size_t(ncol) * h.hidden * 4, 4, "bn_model_stage_batch output");
     m->cur = stream0;
     m->next_pos = pos[0] + 1;
-    k_set_cols<<<1, 32, 0, st>>>(m->TOK, m->POS, m->arena_bytes, ncol, ci, (first && !tok) ? bn_ptr<int>(in, in_off) : nullptr);
+    k_set_cols<<<1, 32, 0, st>>>(m->TOK, m->POS, m->arena_bytes, ncol, ci, (first && !tok) ? bn_ptr<int>(in, in_off) : nullptr, h.vocab, m->ctx->err_dev);
     BN_COUNT(1);
     if (!first)
         BN_CUDA(cudaMemcpy2DAsync(m->RES, m->arena_bytes, bn_ptr<char>(in, in_off), size_t(h.hidden) * 4, size_t(h.hidden) * 4, ncol,
@@ -772,23 +804,10 @@ int bn_model_stage_batch(bn_model *m, int stream0, int ncol, const int *tok, con
         enqueue_batch(m, ncol);
         e = cudaGetLastError();
     } else {
-        const long key = long(stream0) * 64 + ncol;
-        auto it = m->batch_graphs.find(key);
-        if (it == m->batch_graphs.end()) {
-            cudaGraph_t g = nullptr;
-            cudaGraphExec_t ge = nullptr;
-            const unsigned long long before = g_bn_launches;
-            BN_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-            enqueue_batch(m, ncol);
-            e = cudaStreamEndCapture(st, &g);
-            if (e != cudaSuccess) return bn_cuda_fail(e, "cudaStreamEndCapture(stage batch)");
-            m->batch_graph_launches = int(g_bn_launches - before);
-            g_bn_launches = before;
-            e = cudaGraphInstantiate(&ge, g, 0);
-            cudaGraphDestroy(g);
-            if (e != cudaSuccess) return bn_cuda_fail(e, "cudaGraphInstantiate(stage batch)");
-            it = m->batch_graphs.emplace(key, ge).first;
-        }
+        auto it = m->batch_graphs.find(long(stream0) * 64 + ncol);
+        BN_REQUIRE(it != m->batch_graphs.end(), BN_ERR_STATE,
+                   "bn_model_stage_batch: sequences %d..%d were not prepared as one pass; call bn_model_stage_prepare(model, %d, %d) first",
+                   stream0, stream0 + ncol - 1, stream0, ncol);
         e = cudaGraphLaunch(it->second, st);
         BN_COUNT(m->batch_graph_launches);
     }

@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(256) k_attn_prep(bnk::AttnDims a, const float 
                                                    float *__restrict__ q16f, float *__restrict__ gate, bnk::Cols cols) {
     bnk::pdl_sync();
     { const size_t col = blockIdx.z; qg = bnk::colp(qg, col * cols.arena); kin = bnk::colp(kin, col * cols.arena); vin = bnk::colp(vin, col * cols.arena); pos_ptr = bnk::colp(pos_ptr, col * cols.arena); kv.k_data = bnk::colp(kv.k_data, col * cols.kv); kv.k_scale = bnk::colp(kv.k_scale, col * cols.kv); kv.v_data = bnk::colp(kv.v_data, col * cols.kv); kv.v_scale = bnk::colp(kv.v_scale, col * cols.kv); q16f = bnk::colp(q16f, col * cols.arena); gate = bnk::colp(gate, col * cols.arena); }
-    __shared__ float part[256];
+    __shared__ __align__(16) float part[256];
     __shared__ float sx[256];
     const int d = threadIdx.x, hd = a.head_dim, w = blockIdx.x;
     const bool is_q = w < a.n_head;
@@ -415,7 +415,22 @@ __global__ void __launch_bounds__(256) k_attn_prep(bnk::AttnDims a, const float 
     const float x = src[d];
     sx[d] = x;
     part[d] = __fmul_rn(x, x);
-    const float ss = block_tree_sum(part, 256);
+    __syncthreads();
+    // the 256 squares are added serially in ascending order, as the reference's CPU mirror adds them
+    // (attn_vk.h:102-108), so that the fp16 operands below are the mirror's bit for bit
+    __shared__ float ssum;
+    if (d == 0) {
+        float acc = 0.0f;
+        const float4 *p4 = reinterpret_cast<const float4 *>(part);
+#pragma unroll 8
+        for (int i = 0; i < 64; ++i) {
+            const float4 v = p4[i];
+            acc = __fadd_rn(acc, v.x); acc = __fadd_rn(acc, v.y); acc = __fadd_rn(acc, v.z); acc = __fadd_rn(acc, v.w);
+        }
+        ssum = acc;
+    }
+    __syncthreads();
+    const float ss = ssum;
     const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, float(hd)), a.eps)));
     float y = __fmul_rn(__fmul_rn(x, inv), nw[d]);
     if (d < a.n_rot) {

@@ -198,7 +198,10 @@ int bn_gemv_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, const 
     if (dots) BN_RANGE(dots, dots_off, size_t(M) * nb * 16, 4, "bn_gemv_q81 dots");
     int rc = bn_scratch_reserve(ctx, size_t(ngroups) * M * 4);
     if (rc != BN_OK) return rc;
-    if (!dots && bnk::phase_supported(M, K, 512) && (M + 15) / 16 <= BN_MAX_TILES) {
+    // the streamed kernel moves rows with bulk copies, which need a 16-byte aligned source; any other 4-byte aligned
+    // placement goes through the kernel that reads with plain 4-byte loads (same results)
+    const bool w16 = (reinterpret_cast<uintptr_t>(bn_ptr<uint8_t>(w, w_off)) & 15u) == 0;
+    if (!dots && w16 && bnk::phase_supported(M, K, 512) && (M + 15) / 16 <= BN_MAX_TILES) {
         // streamed kernel; the op-level call hands it a ready-made activation pack
         bnk::PhaseArgs a = {};
         a.W = bn_ptr<uint8_t>(w, w_off); a.M = M; a.K = K;
@@ -247,6 +250,11 @@ int bn_gemv_q81_static(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K,
     BN_RANGE(pack, pack_off, bn_act_pack_bytes(K), 16, "bn_gemv_q81_static pack");
     BN_RANGE(out, out_off, size_t(M) * 4, 4, "bn_gemv_q81_static out");
     if (!g_static_partials_ptr[ctx->device]) {
+        // first call on this device: the address lookup below is not allowed while the stream is recording a capture
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        BN_CUDA(cudaStreamIsCapturing(ctx->stream, &cs));
+        BN_REQUIRE(cs == cudaStreamCaptureStatusNone, BN_ERR_STATE,
+                   "bn_gemv_q81_static: the first call on a device looks up the built-in scratch array and must come before any stream capture");
         BN_CUDA(cudaSetDevice(ctx->device));
         float *p = nullptr;
         BN_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_partials));

@@ -89,6 +89,7 @@ def load_library() -> C.CDLL:
         "bn_model_token": (i32, [vp, i32, i32, i32, C.POINTER(i32)]),
         "bn_model_read": (i32, [vp, i32, i32, vp, sz]),
         "bn_model_decode": (i32, [vp, i32, i32, i32, C.POINTER(i32)]),
+        "bn_model_stage_prepare": (i32, [vp, i32, i32]),
         "bn_model_stage": (i32, [vp, i32, i32, i32, vp, sz, vp, sz]),
         "bn_model_stage_batch": (i32, [vp, i32, i32, vp, vp, vp, sz, vp, sz]),
         "bn_model_fill_kv": (i32, [vp, i32, i32]),
@@ -333,6 +334,11 @@ class Model:
         """One pipeline stage for one token of one stream (enqueue only)."""
         _check(self.ctx.lib.bn_model_stage(self.h, stream, tok, pos, inp.h if inp is not None else None, in_off, out.h, out_off),
                "bn_model_stage")
+
+    def stage_prepare(self, stream0: int, ncol: int = 0):
+        """Build the replayable schedule of stage() (ncol = 0) or of stage_batch() over ncol sequences from stream0. May
+        synchronise the device: call it before any NCCL traffic. Unprepared calls of stage / stage_batch are refused."""
+        _check(self.ctx.lib.bn_model_stage_prepare(self.h, stream0, ncol), "bn_model_stage_prepare")
 
     def stage_batch(self, stream0: int, toks, pos, inp: "Buffer | None", out: "Buffer", in_off: int = 0, out_off: int = 0):
         """One pipeline stage for len(pos) consecutive sequences at once (enqueue only). toks: token ids (first stage)

@@ -17,8 +17,9 @@
  * bn_buf handles plus byte offsets; every op checks offsets and sizes against the buffer before it
  * launches anything and refuses (negative return, message in bn_last_error) instead of faulting.
  * Every call returns 0 on success or a negative bn_err. Calls on one context must be serialised by
- * the caller (the reference engine is single-threaded, runtime_vk/bonsai_http.h:458). There is no
- * CPU fallback: without a CUDA device bn_init fails.
+ * the caller (the reference engine is single-threaded, runtime_vk/bonsai_http.h:458). One process drives
+ * one GPU: bn_init refuses a second device index in the same process (a multi-GPU host runs one process
+ * per pipeline stage). There is no CPU fallback: without a CUDA device bn_init fails.
  */
 #ifndef BONSAI_CUDA_H
 #define BONSAI_CUDA_H
@@ -201,18 +202,29 @@ void bn_model_destroy(bn_model *m);
  * (first maximum, as Sampler::pick with temp <= 0); >= 0 stops after that block (alignment harness,
  * reference: BONSAI_LADDER / stop_at_block). next_tok may be NULL (nothing is copied back then). */
 int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *next_tok);
+/* Builds the replayable schedule of a pipeline stage before any traffic flows (reference: the engine records its command
+ * buffers and refuses bad plans before the first dispatch, runtime_vk/bonsai_weights.h:349-353): ncol = 0 prepares
+ * bn_model_stage for sequence stream0, ncol >= 1 prepares bn_model_stage_batch for the pass over sequences
+ * stream0 .. stream0+ncol-1. This call may synchronise the device, so make it while no kernel that waits for a peer (an
+ * NCCL send/recv) is queued - in practice right after bn_model_finalize, once for every (stream0, ncol) the host will use.
+ * bn_model_stage and bn_model_stage_batch never build a schedule themselves: a pair that was not prepared is refused
+ * with BN_ERR_STATE. */
+int bn_model_stage_prepare(bn_model *m, int stream0, int ncol);
 /* One pipeline stage (reference: the contiguous layer ranges of fleet_split_schedule, runtime_vk/gpu_fleet.h:990,
  * and the per-hop 16 KiB hidden-state hand-off, gpu_fleet.h:97): run this device's blocks for one token of
  * sequence `stream` at position pos. First stage: tok >= 0 is the token id, tok < 0 reads it from the int at
  * (in, in_off). Other stages: (in, in_off) holds the `hidden` fp32 values from the previous stage. Output: the
- * hidden state at (out, out_off), or on the last stage the greedy pick as one int. Enqueues only - no host wait. */
+ * hidden state at (out, out_off), or on the last stage the greedy pick as one int. Enqueues only - no host wait.
+ * Needs bn_model_stage_prepare(m, stream, 0). A token id read from device memory that lies outside the vocabulary is
+ * replaced by 0 and reported by the next bn_sync (BN_ERR_ARG). */
 int bn_model_stage(bn_model *m, int stream, int tok, int pos, const bn_buf *in, size_t in_off, bn_buf *out, size_t out_off);
 /* The same stage for ncol consecutive sequences stream0 .. stream0+ncol-1 in one pass (the micro-batch of the layer
  * pipeline): every projection reads its weights once for all of them (tcgen05 kernel, bn_gemm_q81), the other
  * kernels run one grid slice per sequence. pos[c] is the position of sequence stream0+c. First stage: tok != NULL gives
  * the token ids, tok == NULL reads ncol ints from (in, in_off). Other stages: (in, in_off) holds ncol x hidden fp32,
  * sequence-major. Output: ncol x hidden fp32, or ncol ints (the greedy picks) on the last stage. Each sequence's result
- * is bit-identical to what bn_model_stage gives for it alone. Needs bn_hparams.batch_cols >= ncol. Enqueues only. */
+ * is bit-identical to what bn_model_stage gives for it alone. Needs bn_hparams.batch_cols >= ncol and
+ * bn_model_stage_prepare(m, stream0, ncol). Enqueues only. */
 int bn_model_stage_batch(bn_model *m, int stream0, int ncol, const int *tok, const int *pos, const bn_buf *in, size_t in_off,
                          bn_buf *out, size_t out_off);
 /* timing fixture (reference: BONSAI_KVFILL, bonsai_forward.h:1338-1378): mark the first n_positions of a

@@ -203,6 +203,32 @@ static inline void block_dots_def(const uint8_t *pb, const uint32_t *xq, int32_t
     }
 }
 
+// The same four numbers through a 256-entry table of each byte's five trits (built once from trit_of_byte):
+// the whole-token checker at the 9B shape evaluates 62 million row-blocks per token, which the per-element
+// walk above is too slow for. Integer arithmetic, so equality with block_dots_def is exact; the tests compare
+// the two on random and on edge-case blocks.
+struct TritTable {
+    int8_t t[256][8];
+    TritTable() { for (int b = 0; b < 256; ++b) for (int l = 0; l < 8; ++l) t[b][l] = l < 5 ? int8_t(trit_of_byte(uint32_t(b), l)) : 0; }
+};
+static inline const TritTable &trit_table() { static const TritTable tt; return tt; }
+static inline void block_trits_fast(const uint8_t *pb, int8_t *sym /*128, element order*/) {
+    const TritTable &tt = trit_table();
+    for (int by = 0; by < 16; ++by) { const int8_t *r = tt.t[pb[by]]; for (int l = 0; l < 5; ++l) sym[16 * l + by] = r[l]; }
+    for (int by = 16; by < 24; ++by) { const int8_t *r = tt.t[pb[by]]; for (int l = 0; l < 5; ++l) sym[80 + 8 * l + (by - 16)] = r[l]; }
+    for (int by = 24; by < 26; ++by) { const int8_t *r = tt.t[pb[by]]; for (int l = 0; l < 4; ++l) sym[120 + 2 * l + (by - 24)] = r[l]; }
+}
+static inline void block_dots_fast(const uint8_t *pb, const uint32_t *xq, int32_t I[4]) {
+    const int8_t *q = reinterpret_cast<const int8_t *>(xq + 4);
+    int8_t sym[128];
+    block_trits_fast(pb, sym);
+    for (int sb = 0; sb < 4; ++sb) {
+        int32_t acc = 0;
+        for (int i = 0; i < 32; ++i) acc += int32_t(sym[sb * 32 + i]) * int32_t(q[sb * 32 + i]);
+        I[sb] = acc;
+    }
+}
+
 // The same four numbers computed the way the shader's two lanes do (16-bit-lane multiply by 3,
 // residue left in place and cancelled by pre-masked activations, packed 4x8 dot products):
 // _mul_mat_vecq_ptq1_0.comp:66-82 (TRIT_LEVEL), :99-186 (single-column path). Returned per lane
@@ -266,7 +292,10 @@ static inline void block_dots_shader_lanes(const uint8_t *pb, const uint32_t *xq
 // When K/128 is not a multiple of 4 the last group is padded with v = +0.
 // exact[] (optional) receives the same formula evaluated in double: the reference value for the
 // "within 1e-5 relative" check.
-static inline void gemv_q81(const uint8_t *W, int M, int K, const uint32_t *xq, float *out,
+#if defined(__x86_64__) && defined(__GNUC__)
+__attribute__((target_clones("avx2", "default")))     // same C code, vectorised where the host has AVX2 (integer work: exact)
+#endif
+static void gemv_q81(const uint8_t *W, int M, int K, const uint32_t *xq, float *out,
                             double *exact, int32_t *dots /* [M][K/128][4] or null */) {
     const int nb = K / 128;
     std::vector<float> dsb(size_t(nb) * 4), ssb(size_t(nb) * 4);
@@ -282,7 +311,7 @@ static inline void gemv_q81(const uint8_t *W, int M, int K, const uint32_t *xq, 
         for (int b = 0; b < nb; ++b) {
             const uint8_t *pb = W + (size_t(r) * nb + b) * PTQ_BLOCK_BYTES;
             int32_t I[4];
-            block_dots_def(pb, xq + size_t(b) * Q81_X4_DWORDS, I);
+            block_dots_fast(pb, xq + size_t(b) * Q81_X4_DWORDS, I);     // == block_dots_def (tested)
             if (dots) std::memcpy(dots + (size_t(r) * nb + b) * 4, I, 16);
             float t[4]; double te = 0.0;
             for (int sb = 0; sb < 4; ++sb) {

@@ -203,10 +203,8 @@ static inline void gdn_mix(Model &m, int b, int gi, float *res) {
 // norm + NeoX rope on the first n_rot dims of one head row (attn_norm_rope2.comp:137-160)
 static inline void head_norm_rope(const HParams &h, const float *x, const float *w, int pos, float *y) {
     const int hd = h.head_dim;
-    float sq[256];
-    for (int d = 0; d < hd; ++d) sq[d] = x[d] * x[d];
-    for (int d = hd; d < 256; ++d) sq[d] = 0.0f;
-    const float ss = tree_sum(sq, 256);                 // reference: serial ascending; here the fixed tree
+    float ss = 0.0f;                                    // attn_vk.h:102-108: squares summed serially, ascending d
+    for (int d = 0; d < hd; ++d) ss = ss + x[d] * x[d];
     const float inv = 1.0f / std::sqrt(ss / float(hd) + h.rms_eps);
     for (int d = 0; d < hd; ++d) y[d] = (x[d] * inv) * w[d];
     const int half = h.n_rot / 2;

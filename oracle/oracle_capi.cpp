@@ -43,6 +43,7 @@ void bo_quantize_q8_1(const float *x, int K, uint32_t *out) { quantize_q8_1_x4(x
 void bo_quantize_q8_0(const float *x, int n, int8_t *codes, uint16_t *scales) { quantize_q8_0(x, n, codes, scales); }
 
 void bo_block_dots_def(const uint8_t *pb, const uint32_t *xq, int32_t *I) { block_dots_def(pb, xq, I); }
+void bo_block_dots_fast(const uint8_t *pb, const uint32_t *xq, int32_t *I) { block_dots_fast(pb, xq, I); }
 void bo_block_dots_shader(const uint8_t *pb, const uint32_t *xq, int32_t *I) { block_dots_shader_lanes(pb, xq, I); }
 
 void bo_gemv_q81(const uint8_t *W, int M, int K, const uint32_t *xq, float *out, double *exact,

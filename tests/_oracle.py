@@ -86,11 +86,12 @@ class Oracle:
         self.lib.bo_quantize_q8_0(_p(x), x.size, _p(codes), _p(scales))
         return codes, scales
 
-    def block_dots(self, block, xq_block, shader=False):
+    def block_dots(self, block, xq_block, shader=False, fast=False):
         b = np.ascontiguousarray(block, dtype=np.uint8)
         xq = np.ascontiguousarray(xq_block, dtype=np.uint32)
         out = np.empty(4, dtype=np.int32)
-        (self.lib.bo_block_dots_shader if shader else self.lib.bo_block_dots_def)(_p(b), _p(xq), _p(out))
+        fn = self.lib.bo_block_dots_fast if fast else (self.lib.bo_block_dots_shader if shader else self.lib.bo_block_dots_def)
+        fn(_p(b), _p(xq), _p(out))
         return out
 
     def gemv_q81(self, W, M, K, xq, want_dots=False, threads=8):

@@ -1,4 +1,4 @@
-"""BASELINE config 1 at its real shape: hidden 4096, FFN 12288 (gate/up/down as PTQ1_0), the input rotated by the
+"""The ternary SwiGLU FFN block at its real shape: hidden 4096, FFN 12288 (gate/up/down as PTQ1_0), the input rotated by the
 normalized Walsh-Hadamard transform at block 4096, the 12288-wide intermediate as 3 blocks of 4096 with its own sign
 vector; batch 1 (GEMV path) and 16 tokens (tensor-core GEMM path). The FFN is exercised inside a one-block model of
 the 9B's layer shape, so the recurrent mixer in front of it runs at its real shape too. Both paths must give the CPU
@@ -38,6 +38,7 @@ def test_ffn_block_batch1_and_16_tokens(ctx):
     hb = synth.HParams(n_layer=1, vocab=2048, cap=32, n_streams=16, batch_cols=16)
     mb = Model(ctx, hb, tensors, signs)
     out = ctx.alloc(16 * 4)
+    mb.stage_prepare(0, 16)
     mb.stage_batch(0, toks, [0] * 16, None, out)
     ctx.sync()
     picks = out.download(np.int32, 16)

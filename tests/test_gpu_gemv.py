@@ -157,3 +157,28 @@ def test_gemv_f32act_split_rule_and_refusals(ctx):
     with pytest.raises(BonsaiError):
         ctx.gemv_f32act(buf, 64, 100, buf, buf)
     buf.free()
+
+
+@pytest.mark.parametrize("w_off", [4, 8, 16])
+def test_gemv_q81_weights_at_any_4_byte_offset(ctx, oracle, w_off):
+    """The streamed kernel's bulk copies need a 16-byte aligned source. A matrix that starts at another 4-byte aligned
+    address (28-byte blocks allow it) must take the kernel that reads with plain loads - same floats, no device fault -
+    and an offset that is not a multiple of 4 is refused before anything is launched."""
+    from bonsai_vk_b200 import BonsaiError
+    M, K = 512, 4096
+    rng = np.random.default_rng(7 + w_off)
+    W = ptq.synth_matrix(rng, M, K)
+    x = rng.standard_normal(K).astype(np.float32)
+    raw = np.zeros(W.size + 64, dtype=np.uint8)
+    raw[w_off:w_off + W.size] = W.reshape(-1)
+    wb, xb = ctx.from_numpy(raw), ctx.from_numpy(x)
+    pack, out = ctx.alloc(ctx.act_pack_bytes(K)), ctx.alloc(M * 4)
+    ctx.act_quant_q81(xb, K, pack)
+    ctx.gemv_q81(wb, M, K, pack, out, w_off=w_off)
+    ctx.sync()
+    ref, _, _ = oracle.gemv_q81(W, M, K, oracle.quantize_q8_1(x))
+    assert np.array_equal(out.download(np.uint32, M), ref.view(np.uint32))
+    with pytest.raises(BonsaiError, match="aligned"):
+        ctx.gemv_q81(wb, M, K, pack, out, w_off=w_off + 1)
+    for b in (wb, xb, pack, out):
+        b.free()

@@ -32,6 +32,11 @@ def test_two_stages_three_streams_match_whole_model(ctx):
     b = Model(ctx, hp_b, tensors, signs)
     hid = [ctx.alloc(hp.hidden * 4) for _ in range(S)]
     tokb = [ctx.alloc(16) for _ in range(S)]
+    from bonsai_vk_b200 import BonsaiError
+    with pytest.raises(BonsaiError, match="not prepared"):          # a stage never builds its schedule on the fly
+        a.stage(0, first[0], 0, None, hid[0])
+    for s in range(S):
+        a.stage_prepare(s); b.stage_prepare(s)
     got = [[] for _ in range(S)]
     for pos in range(T):
         for s in range(S):                     # sequences interleaved, as the pipeline runs them
@@ -75,6 +80,13 @@ def test_batched_stages_match_whole_model(ctx):
     a = Model(ctx, synth.tiny(n_streams=S, block_begin=0, block_end=2, batch_cols=4), tensors, signs)
     b = Model(ctx, synth.tiny(n_streams=S, block_begin=2, block_end=4, batch_cols=4), tensors, signs)
     hid, tokb = ctx.alloc(S * hp.hidden * 4), ctx.alloc(S * 4)
+    from bonsai_vk_b200 import BonsaiError
+    with pytest.raises(BonsaiError, match="not prepared"):
+        a.stage_batch(0, first[:4], [0] * 4, None, hid)
+    for r0 in range(S):                          # every run of consecutive sequences the loop below may form
+        for n in range(1, 5):
+            if r0 + n <= S:
+                a.stage_prepare(r0, n); b.stage_prepare(r0, n)
     got = [[] for _ in range(S)]
     cur = list(first)
     groups = [(0, 4), (4, 2)]
@@ -108,3 +120,25 @@ def test_batched_stages_match_whole_model(ctx):
     assert np.array_equal(st4.view(np.uint32), want_state[4].view(np.uint32))
     a.close(); b.close()
     hid.free(); tokb.free()
+
+
+def test_token_id_from_device_memory_is_checked(ctx):
+    """The first stage reads the next token id from device memory (the message of the last stage). An id outside the
+    vocabulary must not be turned into an address: id 0 is used, the next sync reports it, and the context stays usable."""
+    from bonsai_vk_b200 import BonsaiError
+    hp = synth.tiny(n_streams=1, block_begin=0, block_end=2)
+    tensors, signs = synth.make_model(hp, seed=7)
+    a = Model(ctx, hp, tensors, signs)
+    a.stage_prepare(0)
+    hid, hid0 = ctx.alloc(hp.hidden * 4), ctx.alloc(hp.hidden * 4)
+    bad = ctx.from_numpy(np.array([hp.vocab + 12345, 0, 0, 0], dtype=np.int32))
+    a.stage(0, -1, 0, bad, hid)
+    with pytest.raises(BonsaiError, match="outside the vocabulary"):
+        ctx.sync()
+    a.reset()
+    a.stage(0, 0, 0, None, hid0)              # what the refused step computed instead: token id 0
+    ctx.sync()
+    assert np.array_equal(hid.download(np.uint32, hp.hidden), hid0.download(np.uint32, hp.hidden))
+    a.close()
+    for x in (hid, hid0, bad):
+        x.free()

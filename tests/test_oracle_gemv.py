@@ -110,3 +110,20 @@ def test_kernel_lab_case_scale_one(oracle):
     assert np.allclose(truth, want, rtol=0, atol=1e-9)
     out, _ = oracle.gemv_f32act(W, M, K, x)
     assert np.max(np.abs(out - truth)) < 1e-4      # the lab expects rel ~1e-6 on values of order 10
+
+
+def test_table_driven_block_dots_equal_the_definition(oracle):
+    """The whole-token checker evaluates the integer block dots through a 256-entry trit table; it must give the very
+    numbers of the per-element definition (sum trit_e * q_e with trit_of_byte, ptq_decode.h:34-45) on raw random bytes
+    (243..255 included), on every byte value in every position, and with extreme activation codes."""
+    rng = np.random.default_rng(11)
+    for _ in range(300):
+        blk = rng.integers(0, 256, size=28, dtype=np.uint8)
+        xq = np.zeros(36, dtype=np.uint32)
+        xq[4:] = rng.integers(-127, 128, size=128).astype(np.int8).view(np.uint32)
+        assert np.array_equal(oracle.block_dots(blk, xq), oracle.block_dots(blk, xq, fast=True))
+    xq = np.zeros(36, dtype=np.uint32)
+    xq[4:] = np.full(128, 127, dtype=np.int8).view(np.uint32)
+    for v in range(256):
+        blk = np.full(28, v, dtype=np.uint8)
+        assert np.array_equal(oracle.block_dots(blk, xq), oracle.block_dots(blk, xq, fast=True))

@@ -49,34 +49,41 @@ def test_rotation_order(oracle):
 
 def test_attention_vs_reference_mirror(oracle, ref):
     """fp16 K / fp16 V with fp16-rounded probabilities is the configuration attn_vk.h mirrors
-    (attn_forward<true>). The oracle's attention must agree with it to float rounding: the two differ
-    only in the summation order of the 256 squares of the head norm (tree here, serial there)."""
-    hp = synth.tiny(k_mode=1, v_mode=1, cap=32, n_layer=4)
+    (attn_forward<true>). In the reference's own order (attn_order 0: head-norm squares, softmax sum and PV all
+    serial ascending) the oracle must reproduce the mirror bit for bit: both fp16 matmul operands (q16 of every
+    token, the K arena), the pre-gate output and the gated output of the last token."""
+    hp = synth.tiny(k_mode=1, v_mode=1, cap=64, n_layer=4)
     tensors, signs = synth.make_model(hp, seed=3)
     om = OracleModel(hp, tensors, signs, attn_order=0)
-    rng = np.random.default_rng(9)
-    seq = 12
-    QD, KD, hd = hp.n_head * hp.head_dim, hp.n_kv * hp.head_dim, hp.head_dim
-    qg = rng.standard_normal((seq, hp.n_head, 2 * hd)).astype(np.float32)
-    kin = rng.standard_normal((seq, KD)).astype(np.float32)
-    vin = rng.standard_normal((seq, KD)).astype(np.float32)
-    pos = np.arange(seq, dtype=np.int32)
-    pre = np.empty(QD, dtype=np.float32); gated = np.empty(QD, dtype=np.float32)
     b = 3   # the attention block of the tiny model
-    oracle.lib.bo_attn_insert_and_attend(om.m, b, 0, seq, _p(pos), _p(qg), _p(kin), _p(vin), _p(pre), _p(gated))
-    # reference mirror takes q and gate de-interleaved
-    q_in = np.ascontiguousarray(qg[:, :, :hd]).reshape(seq, QD)
-    g_in = np.ascontiguousarray(qg[:, :, hd:]).reshape(seq, QD)
-    r_pre = np.empty((seq, QD), dtype=np.float32); r_gated = np.empty((seq, QD), dtype=np.float32)
+    QD, KD, hd = hp.n_head * hp.head_dim, hp.n_kv * hp.head_dim, hp.head_dim
     qn = np.ascontiguousarray(tensors[f"blk.{b}.attn_q_norm.weight"]); kn = np.ascontiguousarray(tensors[f"blk.{b}.attn_k_norm.weight"])
-    upos = pos.astype(np.uint32)
-    ref.ref_attn_forward(seq, hp.cap, hp.n_head, hp.n_kv, hd, hp.n_rot, C.c_float(hp.rms_eps), C.c_float(hp.rope_base),
-                         _p(q_in), _p(kin), _p(vin), _p(g_in), _p(qn), _p(kn), _p(upos), 1,
-                         _p(r_pre), _p(r_gated), None, None, None)
-    scale = np.sqrt(np.mean(r_pre[-1].astype(np.float64) ** 2))
-    assert np.max(np.abs(pre - r_pre[-1])) <= 2e-3 * scale      # fp16 operand rounding can flip on a 1-ulp norm change
-    assert np.median(np.abs(pre - r_pre[-1])) <= 1e-6 * scale
-    assert np.max(np.abs(gated - r_gated[-1])) <= 2e-3 * scale
+    for seed, seq in ((9, 12), (10, 48), (11, 64)):
+        rng = np.random.default_rng(seed)
+        qg = rng.standard_normal((seq, hp.n_head, 2 * hd)).astype(np.float32)
+        kin = rng.standard_normal((seq, KD)).astype(np.float32)
+        vin = rng.standard_normal((seq, KD)).astype(np.float32)
+        pos = np.arange(seq, dtype=np.int32)
+        om.reset()
+        q16 = np.empty((seq, QD), dtype=np.uint16)
+        oracle.lib.bo_attn_insert_q16(om.m, b, 0, seq, _p(pos), _p(qg), _p(kin), _p(vin), _p(q16))
+        k16 = om.kv(0)[0][0][: seq * KD].reshape(seq, KD)
+        om.reset()
+        pre = np.empty(QD, dtype=np.float32); gated = np.empty(QD, dtype=np.float32)
+        oracle.lib.bo_attn_insert_and_attend(om.m, b, 0, seq, _p(pos), _p(qg), _p(kin), _p(vin), _p(pre), _p(gated))
+        # the reference mirror takes q and gate de-interleaved
+        q_in = np.ascontiguousarray(qg[:, :, :hd]).reshape(seq, QD)
+        g_in = np.ascontiguousarray(qg[:, :, hd:]).reshape(seq, QD)
+        r_pre = np.empty((seq, QD), dtype=np.float32); r_gated = np.empty((seq, QD), dtype=np.float32)
+        r_q16 = np.empty((seq, QD // 2), dtype=np.uint32); r_kc = np.empty((hp.cap, KD // 2), dtype=np.uint32)
+        upos = pos.astype(np.uint32)
+        ref.ref_attn_forward(seq, hp.cap, hp.n_head, hp.n_kv, hd, hp.n_rot, C.c_float(hp.rms_eps), C.c_float(hp.rope_base),
+                             _p(q_in), _p(kin), _p(vin), _p(g_in), _p(qn), _p(kn), _p(upos), 1,
+                             _p(r_pre), _p(r_gated), None, _p(r_q16), _p(r_kc))
+        assert np.array_equal(r_q16.view(np.uint16).reshape(seq, QD), q16), "fp16 query operands differ from attn_vk.h"
+        assert np.array_equal(r_kc.view(np.uint16).reshape(hp.cap, KD)[:seq], k16), "fp16 K arena differs from attn_vk.h"
+        assert np.array_equal(pre.view(np.uint32), r_pre[-1].view(np.uint32)), "pre-gate output is not bit-identical to attn_vk.h"
+        assert np.array_equal(gated.view(np.uint32), r_gated[-1].view(np.uint32)), "gated output is not bit-identical to attn_vk.h"
     om.close()
 
 
@@ -96,8 +103,11 @@ def test_oracle_token_is_deterministic_and_state_carries():
 
 
 def test_attention_orders_agree():
-    """The reference's serial order and the regrouped order the CUDA kernels use are the same
-    arithmetic: per-head outputs agree within 1e-5 relative (contexts 40 and 1500, q8_0 cache)."""
+    """The reference's serial order (bit-identical to attn_vk.h, test above) against the regrouped order the CUDA
+    kernels use (same arithmetic, sums regrouped: see attn_core_device_order), q8_0 cache, contexts 40 and 1500.
+    The regrouped softmax sum can differ from the serial one in its last bit; a probability that then lands on the
+    other side of an fp16 rounding boundary moves by one fp16 ulp (2^-11 of itself). Measured here: worst element
+    1.0e-4 of the row RMS, worst row 3.3e-5 in the L2 sense, median element below 1e-6. The bounds state that."""
     for cap, seq, splits in ((64, 40, 1), (2048, 1500, 8)):
         hp = synth.tiny(cap=cap)
         tensors, signs = synth.make_model(hp, seed=4)
@@ -115,9 +125,11 @@ def test_attention_orders_agree():
             om.o.lib.bo_attn_insert_and_attend(om.m, 3, 0, seq, _p(pos), _p(qg), _p(kin), _p(vin), _p(pre), _p(gated))
             outs.append(pre.reshape(hp.n_head, hd).astype(np.float64))
         rms = np.sqrt(np.mean(outs[0] ** 2, axis=1, keepdims=True))
-        # a probability within float rounding of an fp16 tie may round the other way: bound by one fp16 ulp of it
-        assert np.max(np.abs(outs[0] - outs[1]) / rms) <= 5e-4
-        assert np.median(np.abs(outs[0] - outs[1]) / rms) <= 1e-5
+        elem = np.abs(outs[0] - outs[1]) / rms
+        row = np.sqrt(((outs[0] - outs[1]) ** 2).sum(axis=1)) / np.sqrt((outs[0] ** 2).sum(axis=1))
+        assert elem.max() <= 2e-4, f"worst element {elem.max():.2e} of the row RMS"
+        assert row.max() <= 5e-5, f"worst row {row.max():.2e} (L2 relative)"
+        assert np.median(elem) <= 1e-5
         om.close()
 
 
