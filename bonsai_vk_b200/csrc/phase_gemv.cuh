@@ -12,7 +12,16 @@ enum Prologue {
     PRO_NORM = 2,     // x = rms_norm(x0) * w                                   (pre_norm, bonsai_forward.h:480)
     PRO_SWIGLU = 3,   // x = silu(x0) * x1                                       (ffn_block :498)
     PRO_GDN_OUT = 4,  // x = permute(silu(z = x1) * (rms_head(o = x0) * w))      (gdn_block :559-567)
-    PRO_ATTN_OUT = 5  // x = (sum_s pv[s]) * sigmoid(gate = x1)                  (attn_pv_q8v.comp tail)
+    PRO_ATTN_OUT = 5, // x = (sum_s pv[s]) * sigmoid(gate = x1)                  (attn_pv_q8v.comp tail)
+    PRO_GDN_OUT_SZ = 6 // as PRO_GDN_OUT with x1 = silu(z) already applied by the producing phase's epilogue
+};
+
+enum Epilogue {
+    EPI_PLAIN = 0,     // out[row] = sum; optional resid_out = sum + resid_in
+    EPI_SWIGLU = 1,    // rows [0, M/2) are gate rows, [M/2, M) up rows: out2[r] = silu(gate_r) * up_r   (ffn_block :498);
+                       // needs K <= 4096 (one chunk) and M/2 a multiple of 16
+    EPI_SILU_FROM = 2, // out[row] = row >= epi_arg ? silu(sum) : sum   (the z rows of a gated-delta-net block, gdn_block :563)
+    EPI_ARGMAX = 3     // EPI_PLAIN + the CTA's first-maximum candidate (cand_val / cand_idx [cta])   (Sampler::pick, temp <= 0)
 };
 
 struct PhaseArgs {
@@ -22,8 +31,12 @@ struct PhaseArgs {
     float *out;              // [M] final sums (may be null when resid_out is set)
     const float *resid_in;   // optional [M]
     float *resid_out;        // optional [M]: resid_out = out + resid_in
-    float *part;             // [K/512][M] scratch
-    unsigned *counters;      // [ceil(M/16)] zero before launch; left zero
+    float *part;             // unused by the streamed kernel (kept for the op-level callers)
+    unsigned *counters;
+    int epi, epi_arg;        // Epilogue
+    float *out2;             // EPI_SWIGLU: [M/2]
+    float *cand_val;         // EPI_ARGMAX: per-CTA candidate
+    int *cand_idx;
     // prologue
     int pro;
     const float *x0, *x1, *w;

@@ -7,7 +7,7 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libbonsai_cuda.so")
+LIB_PATH = os.environ.get("BONSAI_CUDA_LIB") or os.path.join(HERE, "libbonsai_cuda.so")     # override: a differently built copy (experiments)
 
 _lib = None
 

@@ -152,3 +152,43 @@ def test_explicit_layer_list_model(ctx):
     assert worst <= 1e-5
     assert np.array_equal(gm.logits().view(np.uint32), ol.view(np.uint32)), "final logits are not bit-identical"
     gm.close(); om.close()
+
+
+def test_whole_token_kernel_matches_the_oracle(ctx):
+    """The one-launch-per-token kernel (opt-in, BONSAI_TOKEN_KERNEL=1: every phase of a token in one cooperative launch with
+    grid barriers, the weight ring fed by the compute warps themselves) runs the same arithmetic in the same order: prompt
+    logits, the greedy stream of a multi-token launch and the final logits must be the oracle's, bit for bit."""
+    import os
+    hp = synth.tiny()
+    tensors, signs = synth.make_model(hp, seed=3)
+    os.environ["BONSAI_TOKEN_KERNEL"] = "1"
+    try:
+        gm = Model(ctx, hp, tensors, signs)
+    finally:
+        del os.environ["BONSAI_TOKEN_KERNEL"]
+    om = OracleModel(hp, tensors, signs)
+    rng = np.random.default_rng(21)
+    gt = ot = None
+    for pos, t in enumerate(int(x) for x in rng.integers(0, hp.vocab, size=6)):
+        gt = gm.token(t, pos)
+        ol, ores = om.token(t, pos)
+        ot = om.argmax(ol)
+        assert np.array_equal(gm.logits().view(np.uint32), ol.view(np.uint32)), f"position {pos}: logits differ"
+        assert np.array_equal(gm.residual().view(np.uint32), ores.view(np.uint32))
+    assert gt == ot
+    g_stream = gm.decode(gt, 6, 24)                      # 24 tokens in ONE launch
+    o_stream, t = [], ot
+    for i in range(24):
+        ol, _ = om.token(t, 6 + i)
+        t = om.argmax(ol)
+        o_stream.append(t)
+    assert g_stream == o_stream
+    assert np.array_equal(gm.logits().view(np.uint32), ol.view(np.uint32)), "final logits are not bit-identical"
+    # the residual ladder through the phase-list prefix (stop after a block)
+    gm.reset(); om.reset()
+    for stop in range(hp.n_layer):
+        gm.token(5, 0, stop_after=stop, want_next=False)
+        _, ores = om.token(5, 0, stop_after=stop)
+        assert np.array_equal(gm.residual().view(np.uint32), ores.view(np.uint32)), f"stop after block {stop}"
+        gm.reset(); om.reset()
+    gm.close(); om.close()
