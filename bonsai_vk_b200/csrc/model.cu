@@ -213,7 +213,9 @@ void ffn_fused(bn_model *m, const bn_model::Layer &L) {
     if (adjacent(L.ffn_gate, ptq_bytes(h.ffn, h.hidden), L.ffn_up)) { a.M = 2 * h.ffn; a.out = m->FG; launch(m, a); }
     else { a.out = m->FG; launch(m, a); a.W = reinterpret_cast<const uint8_t *>(L.ffn_up); a.out = m->FU; launch(m, a); }
     bnk::PhaseArgs d = phase_base(m, L.ffn_down, h.hidden, h.ffn, m->signs + h.hidden);
-    // silu needs a double-precision exp per element: computed once by a small kernel, not by every CTA
+    // silu needs a double-precision exp per element: computed once by a small kernel, not by every CTA. (Measured: folding it
+    // into the gate / up projection's epilogue costs that launch 2.8 us and saves nothing - the small kernel overlaps the
+    // neighbouring launches under programmatic dependent launch.)
     if (!m->phases_only) bnk::swiglu(m->ctx->stream, m->FG, m->FU, h.ffn, m->FS);
     d.pro = bnk::PRO_PLAIN; d.x0 = m->FS;
     d.resid_in = m->RES; d.resid_out = m->RES;
@@ -234,8 +236,13 @@ void gdn_fused(bn_model *m, const bn_model::Layer &L) {
     if (!m->phases_only) {
         const bnk::GdnDims gd{NH, NQ, D};
         float *h0 = conv_of(m, 0, L.idx), *h1 = conv_of(m, 1, L.idx);
-        bnk::gdn_core_fused(m->ctx->stream, gd, h.hidden, m->QKV, L.conv_w, h0, h1, m->POS, m->RES, m->G + 48, L.attn_norm,
-                            L.alpha_w, L.beta_w, L.dt_bias, L.ssm_a, gdn_state_of(m, L.idx), m->Z, L.ssm_norm, h.rms_eps, m->X1);
+        // one sequence: heads x 4 CTAs in clusters of 4 (fills the GPU); several sequences: one CTA per head and sequence
+        if (D == 128 && getenv("BONSAI_GDN_ONE_CTA_PER_HEAD") == nullptr)
+            bnk::gdn_core_split(m->ctx->stream, gd, h.hidden, m->QKV, L.conv_w, h0, h1, m->POS, m->RES, m->G + 48, L.attn_norm, L.alpha_w,
+                                L.beta_w, L.dt_bias, L.ssm_a, gdn_state_of(m, L.idx), m->Z, L.ssm_norm, h.rms_eps, m->X1);
+        else
+            bnk::gdn_core_fused(m->ctx->stream, gd, h.hidden, m->QKV, L.conv_w, h0, h1, m->POS, m->RES, m->G + 48, L.attn_norm,
+                                L.alpha_w, L.beta_w, L.dt_bias, L.ssm_a, gdn_state_of(m, L.idx), m->Z, L.ssm_norm, h.rms_eps, m->X1);
     }
     bnk::PhaseArgs o = phase_base(m, L.ssm_out, h.hidden, IN, m->signs);
     o.pro = bnk::PRO_PLAIN; o.x0 = m->X1;

@@ -7,6 +7,8 @@
 #include "ops.cuh"
 #include "quant.cuh"
 
+#include <cooperative_groups.h>
+
 namespace {
 
 // ---- block-wide helpers ------------------------------------------------------------------------
@@ -354,6 +356,130 @@ __global__ void __launch_bounds__(512, MINB) k_gdn_core(int heads, int qk_heads,
             y[hd * 128 + d] = __fmul_rn(silu_f(z[h * 128 + d]), nrm);
         }
     }
+}
+
+// The same mixer core for one sequence, split four ways per value head so that a 148-SM GPU is filled (heads x 4 CTAs,
+// 128 at 32 heads): the 4 CTAs of a head form a thread-block cluster, each owns 32 of the head's 128 state rows, two per
+// warp. Everything that does not depend on the preceding projection is requested before the dependency wait: state rows,
+// conv taps and weights, the two small projections' weight rows (staged in shared memory by all threads). After the wait:
+// normed residual, the two dot products (warps 14 / 15), conv + silu, L2 norms, delta rule. The per-head output norm needs
+// all 128 outputs of the head: every CTA reads the other three quarters from their shared memory (distributed shared
+// memory) and evaluates the same 128-value tree as k_gdn_core, then finishes its own 32 values (ssm_norm, swiglu(z, .),
+// v-grouped permutation). Arithmetic and its order are those of k_gdn_core.
+__global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(512, 1)
+k_gdn_split(int heads, int qk_heads, int hidden, const float *__restrict__ qkv, const float *__restrict__ conv_w,
+            float *__restrict__ hist0, float *__restrict__ hist1, const int *__restrict__ pos_ptr, const float *__restrict__ x,
+            const float *__restrict__ inv_ptr, const float *__restrict__ norm_w, const float *__restrict__ alpha_w,
+            const float *__restrict__ beta_w, const float *__restrict__ dt_bias, const float *__restrict__ ssm_a,
+            float *__restrict__ state, const float *__restrict__ z, const float *__restrict__ ssm_norm, float eps,
+            float *__restrict__ y, float scale) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float sq[128], sk[128], sv[32], so[32], sgb[2];
+    extern __shared__ float4 dyn[];                // [3][hidden/4]: normed residual, row h of ssm_alpha, row h of ssm_beta
+    const int unit = blockIdx.x, h = unit >> 2, q4 = unit & 3, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hq = h % qk_heads, n4 = hidden / 4;
+    const bool odd = pos_ptr[0] & 1;               // a token at position p reads taps from buffer p & 1, writes the other
+    const float *hist_rd = odd ? hist1 : hist0;
+    float *hist_wr = odd ? hist0 : hist1;
+    float S[2][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const float *Sr = state + (size_t(h) * 128 + q4 * 32 + warp * 2 + r) * 128;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[r][e] = Sr[lane + 32 * e];
+    }
+    const int cch = tid < 128 ? hq * 128 + tid : (tid < 256 ? qk_heads * 128 + hq * 128 + (tid - 128) : 2 * qk_heads * 128 + h * 128 + q4 * 32 + (tid - 256));
+    float tap0 = 0.0f, tap1 = 0.0f, tap2 = 0.0f, cw0 = 0.0f, cw1 = 0.0f, cw2 = 0.0f, cw3 = 0.0f;
+    if (tid < 288) {
+        const float *sr = hist_rd + 3 * size_t(cch);
+        const float *wc = conv_w + 4 * size_t(cch);
+        tap0 = sr[0]; tap1 = sr[1]; tap2 = sr[2];
+        cw0 = wc[0]; cw1 = wc[1]; cw2 = wc[2]; cw3 = wc[3];
+    }
+    {
+        const float4 *ra = reinterpret_cast<const float4 *>(alpha_w + size_t(h) * hidden), *rb = reinterpret_cast<const float4 *>(beta_w + size_t(h) * hidden);
+        for (int i = tid; i < n4; i += 512) { dyn[n4 + i] = ra[i]; dyn[2 * n4 + i] = rb[i]; }
+    }
+    bnk::pdl_sync();
+    {
+        const float inv = inv_ptr[0];
+        const float4 *xv = reinterpret_cast<const float4 *>(x), *nw = reinterpret_cast<const float4 *>(norm_w);
+        for (int i = tid; i < n4; i += 512) {
+            const float4 a4 = xv[i], w4 = nw[i];
+            dyn[i] = make_float4(__fmul_rn(__fmul_rn(a4.x, inv), w4.x), __fmul_rn(__fmul_rn(a4.y, inv), w4.y),
+                                 __fmul_rn(__fmul_rn(a4.z, inv), w4.z), __fmul_rn(__fmul_rn(a4.w, inv), w4.w));
+        }
+    }
+    if (tid < 288) {
+        const float xn = qkv[cch];
+        float acc = __fmul_rn(cw0, tap0);
+        acc = __fadd_rn(acc, __fmul_rn(cw1, tap1));
+        acc = __fadd_rn(acc, __fmul_rn(cw2, tap2));
+        acc = __fadd_rn(acc, __fmul_rn(cw3, xn));
+        // one writer per channel: this CTA's own 32 value channels; the q / k channels by the first quarter of the first of
+        // the value heads that share them
+        if (tid >= 256 || (h < qk_heads && q4 == 0)) { float *sw = hist_wr + 3 * size_t(cch); sw[0] = tap1; sw[1] = tap2; sw[2] = xn; }
+        const float cv = silu_f(acc);
+        if (tid < 128) sq[tid] = cv; else if (tid < 256) sk[tid - 128] = cv; else sv[tid - 256] = cv;
+    }
+    __syncthreads();
+    if (warp >= 14) {
+        const float4 *wr = dyn + (warp == 14 ? n4 : 2 * n4);
+        float acc = 0.0f;
+        for (int i = lane; i < n4; i += 32) {
+            const float4 w4 = wr[i], a4 = dyn[i];
+            acc = fmaf(w4.x, a4.x, acc); acc = fmaf(w4.y, a4.y, acc); acc = fmaf(w4.z, a4.z, acc); acc = fmaf(w4.w, a4.w, acc);
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, s));
+        if (lane == 0) {
+            if (warp == 14) {
+                const float al = __fadd_rn(acc, dt_bias[h]);
+                const float sp = al > 20.0f ? al : log_f(__fadd_rn(1.0f, exp_f(al)));
+                sgb[0] = __fmul_rn(sp, ssm_a[h]);
+            } else sgb[1] = sigmoid_f(acc);
+        }
+    }
+    float qq[4], kk[4];
+    {
+        const float a0 = sq[lane], a1 = sq[lane + 32], a2 = sq[lane + 64], a3 = sq[lane + 96];
+        const float iq = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(warp_tree128(__fmul_rn(a0, a0), __fmul_rn(a1, a1), __fmul_rn(a2, a2), __fmul_rn(a3, a3)), 1e-12f)));
+        qq[0] = __fmul_rn(a0, iq); qq[1] = __fmul_rn(a1, iq); qq[2] = __fmul_rn(a2, iq); qq[3] = __fmul_rn(a3, iq);
+        const float b0 = sk[lane], b1 = sk[lane + 32], b2 = sk[lane + 64], b3 = sk[lane + 96];
+        const float ik = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(warp_tree128(__fmul_rn(b0, b0), __fmul_rn(b1, b1), __fmul_rn(b2, b2), __fmul_rn(b3, b3)), 1e-12f)));
+        kk[0] = __fmul_rn(b0, ik); kk[1] = __fmul_rn(b1, ik); kk[2] = __fmul_rn(b2, ik); kk[3] = __fmul_rn(b3, ik);
+    }
+    __syncthreads();
+    const float eg = exp_f(sgb[0]), bt = sgb[1];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int jl = warp * 2 + r, j = q4 * 32 + jl;
+        float *Sr = state + (size_t(h) * 128 + j) * 128;
+        float s[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[e] = __fmul_rn(S[r][e], eg);
+        const float pred = warp_tree128(__fmul_rn(s[0], kk[0]), __fmul_rn(s[1], kk[1]), __fmul_rn(s[2], kk[2]), __fmul_rn(s[3], kk[3]));
+        const float u = __fmul_rn(bt, __fsub_rn(sv[jl], pred));
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { s[e] = fmaf(kk[e], u, s[e]); Sr[lane + 32 * e] = s[e]; }
+        const float ov = warp_tree128(__fmul_rn(s[0], qq[0]), __fmul_rn(s[1], qq[1]), __fmul_rn(s[2], qq[2]), __fmul_rn(s[3], qq[3]));
+        if (lane == 0) so[jl] = __fmul_rn(ov, scale);
+    }
+    cluster.sync();                                 // the four quarters of the head's output are in the four CTAs' so[]
+    if (warp == 0) {
+        // per-head RMS over all 128 outputs: lane l holds elements l, l+32, l+64, l+96 = index l of quarters 0..3
+        float e[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) e[i] = cluster.map_shared_rank(so, i)[lane];
+        const float ss = warp_tree128(__fmul_rn(e[0], e[0]), __fmul_rn(e[1], e[1]), __fmul_rn(e[2], e[2]), __fmul_rn(e[3], e[3]));
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.0f), eps)));
+        const int sub = heads / qk_heads, hd = sub * (h % qk_heads) + h / qk_heads;
+        const int d = q4 * 32 + lane;               // this CTA finishes its own quarter
+        const float nrm = __fmul_rn(__fmul_rn(e[q4], inv), ssm_norm[d]);
+        y[hd * 128 + d] = __fmul_rn(silu_f(z[h * 128 + d]), nrm);
+    }
+    cluster.sync();                                 // nobody leaves while a neighbour may still read its shared memory
 }
 
 // per-head RMS (no weight; 128 squares, tree), * ssm_norm, swiglu(z, .), v-grouped permutation
@@ -744,6 +870,15 @@ void gdn_core_fused(cudaStream_t st, GdnDims d, int hidden, const float *qkv, co
     else launch(k_gdn_core<1>, dim3(d.heads, 1, cols.z()), dim3(512), size_t(hidden) * 12, st, d.heads, d.qk_heads, hidden, qkv, conv_w, hist0, hist1, pos_ptr, x, inv_ptr,
                                                          norm_w, alpha_w, beta_w, dt_bias, ssm_a, state, z, ssm_norm, eps, y,
                                                          1.0f / sqrtf(float(d.dim)), cols); 
+}
+void gdn_core_split(cudaStream_t st, GdnDims d, int hidden, const float *qkv, const float *conv_w, float *hist0, float *hist1,
+                    const int *pos_ptr, const float *x, const float *inv_ptr, const float *norm_w, const float *alpha_w,
+                    const float *beta_w, const float *dt_bias, const float *ssm_a, float *state, const float *z,
+                    const float *ssm_norm, float eps, float *y) {
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(k_gdn_split, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 16384 * 4); attr = true; }
+    launch(k_gdn_split, dim3(d.heads * 4), dim3(512), size_t(hidden) * 12, st, d.heads, d.qk_heads, hidden, qkv, conv_w, hist0, hist1, pos_ptr, x,
+           inv_ptr, norm_w, alpha_w, beta_w, dt_bias, ssm_a, state, z, ssm_norm, eps, y, 1.0f / sqrtf(float(d.dim)));
 }
 void gdn_out(cudaStream_t st, GdnDims d, const float *o, const float *z, const float *ssm_norm, float eps, float *y) {
     launch(k_gdn_out, dim3((d.heads + 7) / 8), dim3(256), 0, st, d.heads, d.qk_heads, o, z, ssm_norm, eps, y); 

@@ -80,6 +80,12 @@ void gdn_core_fused(cudaStream_t st, GdnDims d, int hidden, const float *qkv, co
                     float *hist1, const int *pos_ptr, const float *x, const float *inv_ptr, const float *norm_w, const float *alpha_w,
                     const float *beta_w, const float *dt_bias, const float *ssm_a, float *state, const float *z,
                     const float *ssm_norm, float eps, float *y, Cols cols = {});
+// the same fused mixer for one sequence on heads x 4 CTAs (clusters of 4, 32 state rows per CTA, the head norm through
+// distributed shared memory): same arguments and results as gdn_core_fused
+void gdn_core_split(cudaStream_t st, GdnDims d, int hidden, const float *qkv, const float *conv_w, float *hist0, float *hist1,
+                    const int *pos_ptr, const float *x, const float *inv_ptr, const float *norm_w, const float *alpha_w,
+                    const float *beta_w, const float *dt_bias, const float *ssm_a, float *state, const float *z,
+                    const float *ssm_norm, float eps, float *y);
 // per-head RMS (no weight) * ssm_norm, swiglu(z, .), v-grouped permutation -> y[heads*dim]
 void gdn_out(cudaStream_t st, GdnDims d, const float *o, const float *z, const float *ssm_norm, float eps, float *y);
 

@@ -454,6 +454,23 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
 #pragma unroll
                         for (int r = 0; r < 8; ++r) v[r] = __fmul_rn(xv[r], float(sg[r]));
                     }
+                } else if (a.pro == PRO_GDN_OUT || a.pro == PRO_GDN_OUT_SZ) {
+                    // 8 consecutive values lie in one destination head: one source head, three 32-byte loads
+                    const int hd = tb >> 7, d0 = tb & 127, sub = a.gdn_heads / a.gdn_qk_heads;
+                    const int hs = hd / sub + a.gdn_qk_heads * (hd % sub);
+                    const float hi = hinv[1 + hs];
+                    const float4 o0 = ldf4<CG>(a.x0 + hs * 128 + d0), o1 = ldf4<CG>(a.x0 + hs * 128 + d0 + 4);
+                    const float4 z0 = ldf4<CG>(a.x1 + hs * 128 + d0), z1 = ldf4<CG>(a.x1 + hs * 128 + d0 + 4);
+                    const float4 n0 = *reinterpret_cast<const float4 *>(a.w + d0), n1 = *reinterpret_cast<const float4 *>(a.w + d0 + 4);
+                    const float ov[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+                    const float zv[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+                    const float nv[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        const float nrm = __fmul_rn(__fmul_rn(ov[r], hi), nv[r]);
+                        const float zz = a.pro == PRO_GDN_OUT ? silu_f(zv[r]) : zv[r];
+                        v[r] = __fmul_rn(__fmul_rn(zz, nrm), float(sg[r]));
+                    }
                 } else {
 #pragma unroll
                     for (int r = 0; r < 8; ++r) v[r] = __fmul_rn(input(tb + r), float(sg[r]));

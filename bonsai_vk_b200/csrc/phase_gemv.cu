@@ -7,6 +7,7 @@ namespace {
 using namespace bnk;
 using namespace bnk::phase;
 
+template <int EPI>
 __global__ void __launch_bounds__(NTHREADS, 1) k_phase_gemv(const PhaseArgs a) {
     const Smem s = carve(dyn_smem());
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, cta = blockIdx.x;
@@ -42,7 +43,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_phase_gemv(const PhaseArgs a) {
     prologue<false>(a, s, pl, cta);
     BN_STAMP(5);
     NoFeed nofeed;
-    main_loop<EPI_PLAIN>(a, w, s, 0u, cta, nofeed);
+    main_loop<EPI>(a, w, s, 0u, cta, nofeed);
 }
 
 // A wait that nothing will ever satisfy, with a short limit: the give-up path of mbar_wait (error word set, kernel
@@ -74,15 +75,19 @@ bool phase_supported(int M, int K, int hat_block) {
 cudaError_t launch_phase(cudaStream_t st, int sm_count, const PhaseArgs &a, bool pdl) {
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(k_phase_gemv, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             int(phase_smem_bytes(4096)));
+        const int bytes = int(phase_smem_bytes(4096));
+        cudaError_t e = cudaFuncSetAttribute(k_phase_gemv<EPI_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(k_phase_gemv<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(k_phase_gemv<EPI_SILU_FROM>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
     const int ntiles = (a.M + 15) / 16, nchunks = (a.K / 128 + phase::MAXCH - 1) / phase::MAXCH;
     int grid = ntiles < sm_count ? ntiles : sm_count;
+    if (a.epi == EPI_SWIGLU && grid > ntiles / 2) grid = ntiles / 2;              // whole gate / up pairs per CTA
     // multi-chunk projections keep per-tile running sums in shared memory: at most 64 tiles per CTA
-    while (nchunks > 1 && (ntiles + grid - 1) / grid > 64) ++grid;
+    while ((nchunks > 1 || a.epi != EPI_PLAIN) && (ntiles + grid - 1) / grid > 64 - 2) ++grid;
+    if (a.epi != EPI_PLAIN && (nchunks > 1 || a.epi == EPI_ARGMAX)) return cudaErrorInvalidValue;   // one chunk of K; the pick runs in the whole-token kernel only
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(phase::NTHREADS);
@@ -94,7 +99,9 @@ cudaError_t launch_phase(cudaStream_t st, int sm_count, const PhaseArgs &a, bool
     cfg.attrs = at;
     cfg.numAttrs = pdl ? 1 : 0;
     BN_COUNT(1);
-    return cudaLaunchKernelEx(&cfg, k_phase_gemv, a);
+    if (a.epi == EPI_SWIGLU) return cudaLaunchKernelEx(&cfg, k_phase_gemv<EPI_SWIGLU>, a);
+    if (a.epi == EPI_SILU_FROM) return cudaLaunchKernelEx(&cfg, k_phase_gemv<EPI_SILU_FROM>, a);
+    return cudaLaunchKernelEx(&cfg, k_phase_gemv<EPI_PLAIN>, a);
 }
 
 cudaError_t launch_wait_selftest_ring(cudaStream_t st, int *err) {
