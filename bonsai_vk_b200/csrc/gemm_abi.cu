@@ -62,6 +62,11 @@ int bn_gemm_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int w_tiled, int M, 
     a.image = bn_ptr<uint8_t>(image, image_off); a.ncol = ncol;
     a.out = bn_ptr<float>(out, out_off); a.out_stride = out_stride;
     a.err = ctx->err_dev;
+    if (bnk::gemm_wants_split(ctx->sm_count, M, K, ncol)) {
+        int rc = bn_scratch_reserve(ctx, bnk::gemm_group_floats(M, K, ncol) * 4);
+        if (rc != BN_OK) return rc;
+        a.groups = ctx->scratch;
+    }
     // profiling aid (library built with -DGEMM_PROF): BONSAI_GEMM_PROF=1 prints where the roles of CTA 0 spent their
     // cycles (waiting vs working); without that build flag the counters stay zero
     static const bool want_prof = getenv("BONSAI_GEMM_PROF") != nullptr;

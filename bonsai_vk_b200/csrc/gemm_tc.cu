@@ -18,6 +18,7 @@
 #include "gemm_tc.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 #include <cuda_fp16.h>
 
@@ -167,7 +168,13 @@ template <int NCP> struct Cfg {
     static constexpr int NG = NCP / 8;
     static constexpr int BBYTES = BK * NCP * IMG_COL;
     static constexpr int STAGE = WBYTES + BBYTES;
-    static constexpr int STAGES = NG == 4 ? 3 : 4;
+#ifndef GEMM_CTAS8
+#define GEMM_CTAS8 2
+#endif
+    // 8 columns: the decode warps are the bottleneck (the epilogue has little to do), so TWO CTAs share an SM - twice the
+    // decode warps per SM - each with half the ring and half the tensor memory
+    static constexpr int CTAS = NG == 1 ? GEMM_CTAS8 : 1;
+    static constexpr int STAGES = NG == 4 ? 3 : (NG == 1 && CTAS == 2 ? 2 : 4);
 #ifndef GEMM_EW16
 #define GEMM_EW16 8
 #endif
@@ -180,15 +187,15 @@ template <int NCP> struct Cfg {
     // MMA issuers' commits) tells the epilogue that the accumulators are ready and the decode warps that the operand
     // slot may be overwritten. Several blocks are in flight: each hop (decode -> MMA -> commit -> epilogue -> slot
     // free) costs a few hundred cycles.
-    static constexpr int NA = NG == 1 ? 8 : (NG == 2 ? 5 : 3);
+    static constexpr int NA = NG == 1 ? (CTAS == 2 ? 4 : 8) : (NG == 2 ? 5 : 3);
     static constexpr int D_COL = NA * 32;
-    static constexpr int TMEM_COLS = 512;
-    static_assert(D_COL + NA * NG * 32 <= 512 && 2 * NA <= DWS, "tensor memory budget");
+    static constexpr int TMEM_COLS = 512 / CTAS;
+    static_assert(D_COL + NA * NG * 32 <= TMEM_COLS && 2 * NA <= DWS, "tensor memory budget");
     static constexpr size_t SMEM = size_t(STAGES) * STAGE + DWS * 128 * 4 + 512;
 };
 
 template <int NCP>
-__global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const GemmArgs a) {
+__global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, Cfg<NCP>::CTAS) k_ptq_gemm_tc(const GemmArgs a) {
     using C = Cfg<NCP>;
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char *ring = smem;
@@ -221,14 +228,18 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
     // everything above overlaps the previous kernel's tail; its results (the activation image) are read below
     pdl_sync();
 
+    // work items: a tile over all of K, or (split) a single ring stage of a tile
+    const bool split = a.groups != nullptr;
+    const int nwork = split ? ntiles * nkc : ntiles;
     int n_items = 0;
-    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) n_items += nkc;
+    for (int t = blockIdx.x; t < nwork; t += gridDim.x) n_items += split ? 1 : nkc;
 
     if (warp == DW + EW) {
         // ---- producer ----------------------------------------------------------------------------------
         int s = 0, ph = 1;                         // a fresh barrier passes a wait on parity 1
-        for (int t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x)
-            for (int kc = 0; kc < nkc; ++kc) {
+        for (int tt = blockIdx.x; tt < nwork && !*abort_flag; tt += gridDim.x) {
+            const int t = split ? tt / nkc : tt, kc0 = split ? tt - t * nkc : 0, kc1 = split ? kc0 + 1 : nkc;
+            for (int kc = kc0; kc < kc1; ++kc) {
                 if (!mbar_wait(empty + s, ph, a.err, abort_flag)) break;
                 unsigned char *st = ring + size_t(s) * C::STAGE;
                 if (a.tiled) {                      // repacked weights: the stage is one contiguous piece
@@ -248,6 +259,7 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
                 if (lane == 0) bulk_copy(st + WBYTES, a.image + size_t(kc) * C::BBYTES, C::BBYTES, full + s);
                 if (++s == C::STAGES) { s = 0; ph ^= 1; }
             }
+        }
     } else if (warp > DW + EW) {
         // ---- MMA issue: each of the two threads issues two sub-blocks' MMAs of every block (an issue costs the
         //      thread ~55 cycles whatever its size; two threads keep that far below the other roles' time) --------
@@ -340,8 +352,9 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
         bool ok = true;
         long long prof[4] = {0, 0, 0, 0};
         int s = 0, sph = 0, slot = 0, dph = 0, g = 0;
-        for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x)
-            for (int kc = 0; kc < nkc && ok; ++kc) {
+        for (int tt = blockIdx.x; tt < nwork && ok; tt += gridDim.x) {
+            const int t = split ? tt / nkc : tt, kc0 = split ? tt - t * nkc : 0, kc1 = split ? kc0 + 1 : nkc;
+            for (int kc = kc0; kc < kc1 && ok; ++kc) {
                 { PROF_T0(); if (!mbar_wait(full + s, sph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(0); }
                 const unsigned char *stage_scales = ring + size_t(s) * C::STAGE + WBYTES + NCP * 128 + (c0 / 8) * 256;
 #pragma unroll 1
@@ -385,6 +398,21 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
                         } else if (bi == 1) {
 #pragma unroll
                             for (int p = 0; p < 4; ++p) u[gw * 4 + p] = add2(ve[gw * 4 + p], v[p]);
+                        } else if (split) {
+                            // the group sum p_g itself goes to memory; the groups are added in order by gemm_sum_groups
+                            const int grow = t * 128 + row;
+#pragma unroll
+                            for (int p = 0; p < 4; ++p) {
+                                const f32x2 q2 = add2(u[gw * 4 + p], add2(ve[gw * 4 + p], v[p]));
+                                float lo, hi;
+                                unpk2(q2, lo, hi);
+                                const int c = c0 + gw * 8 + 2 * p;
+                                if (grow < a.M) {
+                                    float *gp = a.groups + (size_t(b >> 2) * NCP + c) * size_t(a.M) + grow;
+                                    if (c < a.ncol) gp[0] = lo;
+                                    if (c + 1 < a.ncol) gp[a.M] = hi;
+                                }
+                            }
                         } else {
                             const bool first = b < 4;
 #pragma unroll
@@ -396,7 +424,7 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
                         PROF_ADD(2);
                     }
                     if (++slot == NA) { slot = 0; dph ^= 1; }
-                    if (b == nb - 1) {
+                    if (!split && b == nb - 1) {
                         const int grow = t * 128 + row;
                         if (grow < a.M) {
 #pragma unroll
@@ -415,6 +443,7 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, 1) k_ptq_gemm_tc(const 
                 if (ok && lane == 0) mbar_arrive(empty + s);    // the stage's scales and weights are not needed any more
                 if (++s == C::STAGES) { s = 0; sph ^= 1; }
             }
+        }
         if (a.prof && blockIdx.x == 0 && warp == DW && lane == 0) for (int i = 0; i < 4; ++i) a.prof[8 + i] = prof[i];
     }
     tc_fence_before();
@@ -603,6 +632,18 @@ __global__ void k_repack_tiles(const uint32_t *__restrict__ W, int M, int nb, ui
     }
 }
 
+// out[c][row] = groups[0][c][row] + groups[1][c][row] + ... (ascending), + residual: the tail of a split projection
+__global__ void k_gemm_sum_groups(const float *__restrict__ groups, int ngroups, int ncp, int M, int ncol, float *__restrict__ out,
+                                  size_t out_stride, const float *__restrict__ resid, size_t resid_stride) {
+    pdl_sync();
+    const int row = blockIdx.x * blockDim.x + threadIdx.x, c = blockIdx.y;
+    if (row >= M || c >= ncol) return;
+    float s = groups[size_t(c) * M + row];
+    for (int g = 1; g < ngroups; ++g) s = __fadd_rn(s, groups[(size_t(g) * ncp + c) * M + row]);
+    if (resid) s = __fadd_rn(s, resid[size_t(c) * resid_stride + row]);
+    out[size_t(c) * out_stride + row] = s;
+}
+
 template <int NCP>
 cudaError_t launch_t(cudaStream_t st, int sm_count, const GemmArgs &a, bool pdl) {
     static bool attr_set = false;
@@ -611,9 +652,9 @@ cudaError_t launch_t(cudaStream_t st, int sm_count, const GemmArgs &a, bool pdl)
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    const int ntiles = (a.M + 127) / 128;
+    const int ntiles = (a.M + 127) / 128, nwork = a.groups ? ntiles * (a.K / 128 / BK) : ntiles, cap = sm_count * Cfg<NCP>::CTAS;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ntiles < sm_count ? ntiles : sm_count);
+    cfg.gridDim = dim3(nwork < cap ? nwork : cap);
     cfg.blockDim = dim3(Cfg<NCP>::NWARPS * 32);
     cfg.dynamicSmemBytes = Cfg<NCP>::SMEM;
     cfg.stream = st;
@@ -623,7 +664,11 @@ cudaError_t launch_t(cudaStream_t st, int sm_count, const GemmArgs &a, bool pdl)
     cfg.attrs = at;
     cfg.numAttrs = pdl ? 1 : 0;
     BN_COUNT(1);
-    return cudaLaunchKernelEx(&cfg, k_ptq_gemm_tc<NCP>, a);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, k_ptq_gemm_tc<NCP>, a);
+    if (e != cudaSuccess || !a.groups) return e;
+    launch(k_gemm_sum_groups, dim3((a.M + 255) / 256, a.ncol), dim3(256), 0, st, static_cast<const float *>(a.groups), a.K / 512, NCP, a.M, a.ncol,
+           a.out, a.out_stride, a.resid, a.resid_stride);
+    return cudaGetLastError();
 }
 
 // A wait that nothing will ever satisfy, one round of tries (about 2 ms): exercises the give-up path of mbar_wait
@@ -647,6 +692,13 @@ namespace bnk {
 bool gemm_supported(int M, int K, int ncol) {
     return M >= 1 && K >= 1024 && K % 1024 == 0 && ncol >= 1 && ncol <= GEMM_MAX_COLS;
 }
+
+bool gemm_wants_split(int sm_count, int M, int K, int ncol) {
+    // fewer row tiles than half of what the GPU can hold at once: split over K
+    const int ntiles = (M + 127) / 128, cap = sm_count * (gemm_padded_cols(ncol) == 8 ? GEMM_CTAS8 : 1);
+    return K >= 2048 && 2 * ntiles <= cap && getenv("BONSAI_GEMM_NO_SPLIT") == nullptr;
+}
+size_t gemm_group_floats(int M, int K, int ncol) { return size_t(K / 512) * gemm_padded_cols(ncol) * size_t(M); }
 
 cudaError_t launch_gemm(cudaStream_t st, int sm_count, const GemmArgs &a, bool pdl) {
     const int ncp = gemm_padded_cols(a.ncol);

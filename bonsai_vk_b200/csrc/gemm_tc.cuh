@@ -40,6 +40,11 @@ struct GemmArgs {
     float *out; size_t out_stride;        // column c writes out + c * out_stride (floats)
     const float *resid; size_t resid_stride;   // optional: out = acc + resid (may alias out)
     int *err;                             // device error word (bounded waits)
+    // split over K for matrices with few row tiles (M = 4096 has 32 tiles of 128 rows - a fifth of the GPU): every ring stage
+    // (8 blocks of K = two groups of 4 blocks) becomes a work item of its own and the kernel writes the two group sums
+    // p_g of every (row, column) to groups[(g * padded columns + column) * M + row]; gemm_sum_groups then adds the
+    // groups in ascending order (+ residual), which is the order the unsplit kernel and the single-column kernel use
+    float *groups;                        // null = no split
     long long *prof;                      // optional: 12 cycle counters of CTA 0 (decode 0-3, MMA thread 4-7, epilogue 8-11)
 };
 bool gemm_supported(int M, int K, int ncol);
@@ -48,6 +53,9 @@ bool gemm_supported(int M, int K, int ncol);
 size_t gemm_tiled_bytes(int M, int K);
 void repack_tiles(cudaStream_t st, const uint32_t *W, int M, int K, uint32_t *out);
 cudaError_t launch_gemm(cudaStream_t st, int sm_count, const GemmArgs &a, bool pdl);
+// whether launch_gemm would like to split this shape over K, and the scratch floats it then needs (a.groups)
+bool gemm_wants_split(int sm_count, int M, int K, int ncol);
+size_t gemm_group_floats(int M, int K, int ncol);
 // one tiny kernel whose only wait can never complete and gives up after one round of tries: sets *err = 2 and returns
 cudaError_t launch_wait_selftest_tc(cudaStream_t st, int *err);
 

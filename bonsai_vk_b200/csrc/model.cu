@@ -66,6 +66,7 @@ struct bn_model {
     // multi-sequence pass (bn_model_stage_batch): per-column arenas, shared activation images, tile-major weights
     int ncols = 1;
     uint8_t *IMG_H = nullptr, *IMG_F = nullptr;
+    float *GROUPS = nullptr;              // group sums of the projections that are split over K (gemm_tc.cuh)
     uint8_t *tiled = nullptr;
     struct TiledLayer { const uint8_t *in = nullptr, *out = nullptr, *ffn_in = nullptr, *ffn_down = nullptr; };
     std::vector<TiledLayer> tl;
@@ -461,6 +462,16 @@ int build_batch_side(bn_model *m) {
     }
     BN_CUDA(cudaMalloc(&m->IMG_H, bnk::gemm_image_bytes(h.hidden, h.batch_cols)));
     BN_CUDA(cudaMalloc(&m->IMG_F, bnk::gemm_image_bytes(h.ffn, h.batch_cols)));
+    {
+        size_t need = 0;
+        for (const Group &g : groups) {
+            int M = 0;
+            for (const Part &p : g.parts) M += p.M;
+            if (bnk::gemm_wants_split(m->ctx->sm_count, M, g.K, 1) || bnk::gemm_wants_split(m->ctx->sm_count, M, g.K, h.batch_cols))
+                need = std::max(need, bnk::gemm_group_floats(M, g.K, h.batch_cols));
+        }
+        if (need) BN_CUDA(cudaMalloc(&m->GROUPS, need * 4));
+    }
     BN_CUDA(cudaStreamSynchronize(m->ctx->stream));
     return BN_OK;
 }
@@ -500,6 +511,7 @@ void enqueue_batch(bn_model *m, int ncol) {
         bnk::GemmArgs a = {};
         a.W = Wt; a.M = M; a.K = K; a.tiled = 1; a.image = img; a.ncol = ncol; a.out = out; a.out_stride = AS;
         a.resid = resid; a.resid_stride = AS; a.err = m->ctx->err_dev;
+        if (m->GROUPS && bnk::gemm_wants_split(m->ctx->sm_count, M, K, ncol)) a.groups = m->GROUPS;
         cudaError_t e = bnk::launch_gemm(st, m->ctx->sm_count, a, m->use_pdl);
         if (e != cudaSuccess && m->launch_err == cudaSuccess) m->launch_err = e;
     };
@@ -767,6 +779,7 @@ void bn_model_destroy(bn_model *m) {
     if (m->tok_stamps) cudaFree(m->tok_stamps);
     if (m->IMG_H) cudaFree(m->IMG_H);
     if (m->IMG_F) cudaFree(m->IMG_F);
+    if (m->GROUPS) cudaFree(m->GROUPS);
     delete m;
 }
 
