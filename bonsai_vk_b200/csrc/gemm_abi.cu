@@ -72,8 +72,8 @@ int bn_gemm_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int w_tiled, int M, 
     static const bool want_prof = getenv("BONSAI_GEMM_PROF") != nullptr;
     long long *prof = nullptr;
     if (want_prof) {
-        BN_CUDA(cudaMalloc(&prof, 12 * sizeof(long long)));
-        BN_CUDA(cudaMemsetAsync(prof, 0, 12 * sizeof(long long), ctx->stream));
+        BN_CUDA(cudaMalloc(&prof, 128 * sizeof(long long)));
+        BN_CUDA(cudaMemsetAsync(prof, 0, 128 * sizeof(long long), ctx->stream));
         a.prof = prof;
     }
     cudaError_t e = bnk::launch_gemm(ctx->stream, ctx->sm_count, a, false);
@@ -83,13 +83,23 @@ int bn_gemm_q81(bn_ctx *ctx, const bn_buf *w, size_t w_off, int w_tiled, int M, 
     static const int reps = getenv("BONSAI_GEMM_REPS") ? atoi(getenv("BONSAI_GEMM_REPS")) : 1;
     for (int r = 1; r < reps; ++r) bnk::launch_gemm(ctx->stream, ctx->sm_count, a, false);
     if (want_prof) {
-        long long h[12];
+        long long h[128];
         BN_CUDA(cudaStreamSynchronize(ctx->stream));
         BN_CUDA(cudaMemcpy(h, prof, sizeof h, cudaMemcpyDeviceToHost));
         cudaFree(prof);
         fprintf(stderr, "gemm prof (cycles, CTA 0): decode[wait full %lld, unpack %lld, publish %lld, wait slot %lld] "
-                        "mma[wait full %lld, wait A %lld, wait D %lld] epilogue[wait D %lld, wait ld %lld, combine %lld]\n",
-                h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[8], h[9], h[10]);
+                        "mma[wait full %lld, wait A %lld, wait D %lld] epilogue[wait D %lld, wait ld %lld, combine %lld]; CTA 0 set-up %lld ns, "
+                        "whole CTA %lld ns; last CTA after set-up %lld ns\n",
+                h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[8], h[9], h[10], h[12], h[14], h[13]);
+        if (getenv("BONSAI_GEMM_PROF_EVENTS")) {
+            static const char *names[7] = {"decode start", "decode stored", "mma has A", "mma has D", "mma committed", "epilogue has D", "epilogue done"};
+            long long t0 = h[16];
+            for (int ev = 0; ev < 7; ++ev) {
+                fprintf(stderr, "%-16s", names[ev]);
+                for (int g = 0; g < 16; ++g) fprintf(stderr, " %6lld", h[16 + ev * 16 + g] - t0);
+                fprintf(stderr, "\n");
+            }
+        }
     }
     return bn_launch_check(ctx, "k_ptq_gemm_tc");
 }

@@ -60,7 +60,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *b, uint32_t parity, int *err
                      ".reg .u32 n;\n"
                      "mov.u32 n, 0;\n"
                      "WAIT_LOOP:\n"
-                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+                                          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
                      "@p bra WAIT_DONE;\n"
                      "add.u32 n, n, 1;\n"
                      "setp.lt.u32 q, n, 1024;\n"
@@ -111,6 +111,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
                    "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]) : "r"(taddr) : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
+}
+
 // Packed fp32 pairs (two IEEE single operations per instruction, each lane rounded as the scalar instruction would)
 typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 pk2(float a, float b) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
@@ -154,10 +162,13 @@ __device__ __forceinline__ void decode_block(const uint32_t (&r)[7], uint32_t (&
 // optional cycle accounting of CTA 0 (build with -DGEMM_PROF and pass GemmArgs::prof): where each role's time goes.
 // Compiled out by default: even the untaken branches cost a few percent in these short loops.
 #ifdef GEMM_PROF
+// per-block event times of CTA 0 for blocks 8..23: a.prof[16 + ev * 16 + (g - 8)]
+#define PROF_EV(ev, g, cond) do { if (a.prof && blockIdx.x == 0 && (cond) && (g) >= 8 && (g) < 24) a.prof[16 + (ev) * 16 + ((g) - 8)] = clock64(); } while (0)
 #define PROF_T0() const long long prof_t0 = a.prof ? clock64() : 0
 #define PROF_ADD(slot) do { if (a.prof) prof[slot] += clock64() - prof_t0; } while (0)
 #else
 #define PROF_T0() do { } while (0)
+#define PROF_EV(ev, g, cond) do { } while (0)
 #define PROF_ADD(slot) do { } while (0)
 #endif
 
@@ -168,29 +179,39 @@ template <int NCP> struct Cfg {
     static constexpr int NG = NCP / 8;
     static constexpr int BBYTES = BK * NCP * IMG_COL;
     static constexpr int STAGE = WBYTES + BBYTES;
-#ifndef GEMM_CTAS8
-#define GEMM_CTAS8 2
+    static constexpr int CTAS = 1;                    // CTAs per SM (two were tried at 8 columns: the halved register file slowed the epilogue 3x)
+    static constexpr int STAGES = NG == 4 ? 3 : 4;
+    // Hand-offs between the roles cost each role a barrier round trip, so at 8 columns - where a block is little work -
+    // NB = 4 blocks (one group of the summation order) travel per hand-off; the wider passes keep one block per hand-off
+    // because a block's accumulators already take 64 / 128 tensor-memory columns there.
+#ifndef GEMM_NB8
+#define GEMM_NB8 4
 #endif
-    // 8 columns: the decode warps are the bottleneck (the epilogue has little to do), so TWO CTAs share an SM - twice the
-    // decode warps per SM - each with half the ring and half the tensor memory
-    static constexpr int CTAS = NG == 1 ? GEMM_CTAS8 : 1;
-    static constexpr int STAGES = NG == 4 ? 3 : (NG == 1 && CTAS == 2 ? 2 : 4);
-#ifndef GEMM_EW16
-#define GEMM_EW16 8
+    static constexpr int NB = NG == 1 ? GEMM_NB8 : 1;
+    // epilogue warps: one per row quarter and CPW columns. 8 columns: two warps per quarter, four columns each.
+    static constexpr int EW = 8;
+    static constexpr int CPW = NCP / (EW / 4);        // columns per epilogue warp
+    static constexpr int GPW = CPW >= 8 ? CPW / 8 : 1;   // column groups an epilogue warp visits
+    static constexpr int PPG = CPW >= 8 ? 4 : CPW / 2;   // column pairs it takes from each
+#ifndef GEMM_DW8
+#define GEMM_DW8 4
 #endif
-    static constexpr int EW = NG == 1 ? 4 : GEMM_EW16;   // epilogue warps: one per row quarter and GPW column groups
-    static constexpr int GPW = NG / (EW / 4);         // column groups per epilogue warp
-    static constexpr int DW = 4;                      // decode warps (one per quarter of the rows)
-    static constexpr int MW = 2;                      // MMA issuing threads (one warp each), two sub-blocks apiece
+    // decode warps: one per quarter of the rows (GEMM_DW8 = 8: two sets of four that take the slots in turn at 8 columns;
+    // measured no faster, because the tensor-core instructions themselves bound the 8-column pass)
+    static constexpr int DW = NG == 1 ? GEMM_DW8 : 4;
+#ifndef GEMM_MW
+#define GEMM_MW 2
+#endif
+    static constexpr int MW = GEMM_MW;                // MMA issuing threads (one warp each), 4 / MW sub-blocks apiece
     static constexpr int NWARPS = DW + EW + 1 + MW;   // decode, epilogue, producer, MMA issuers: at most 16 warps = 128 registers
-    // operand slot i and accumulator slot i belong to the same block, so one "done" barrier per slot (armed by the
+    // operand slot i and accumulator slot i belong to the same NB blocks, so one "done" barrier per slot (armed by the
     // MMA issuers' commits) tells the epilogue that the accumulators are ready and the decode warps that the operand
-    // slot may be overwritten. Several blocks are in flight: each hop (decode -> MMA -> commit -> epilogue -> slot
+    // slot may be overwritten. Several slots are in flight: each hop (decode -> MMA -> commit -> epilogue -> slot
     // free) costs a few hundred cycles.
-    static constexpr int NA = NG == 1 ? (CTAS == 2 ? 4 : 8) : (NG == 2 ? 5 : 3);
-    static constexpr int D_COL = NA * 32;
+    static constexpr int NA = NG == 1 ? 8 / NB : (NG == 2 ? 5 : 3);
+    static constexpr int D_COL = NA * NB * 32;
     static constexpr int TMEM_COLS = 512 / CTAS;
-    static_assert(D_COL + NA * NG * 32 <= TMEM_COLS && 2 * NA <= DWS, "tensor memory budget");
+    static_assert(D_COL + NA * NB * NG * 32 <= TMEM_COLS && 2 * NA * NB <= DWS && BK % (NB * (DW / 4)) == 0 && NA % (DW / 4) == 0, "tensor memory budget");
     static constexpr size_t SMEM = size_t(STAGES) * STAGE + DWS * 128 * 4 + 512;
 };
 
@@ -205,9 +226,13 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, Cfg<NCP>::CTAS) k_ptq_g
     uint64_t *aempty = dfull;                      // "done": all four sub-block MMAs of the slot's block have completed
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 40);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    constexpr int NA = C::NA, NG = C::NG, D_COL = C::D_COL, EW = C::EW, DW = C::DW;
+    constexpr int NA = C::NA, NB = C::NB, NG = C::NG, D_COL = C::D_COL, EW = C::EW, DW = C::DW;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef GEMM_PROF
+    unsigned long long prof_entry = 0;
+    if (a.prof && tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_entry));
+#endif
     const int nb = a.K / 128, nkc = nb / BK, ntiles = (a.M + 127) / 128;
     const size_t rowbytes = size_t(nb) * 28;
 
@@ -225,6 +250,9 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, Cfg<NCP>::CTAS) k_ptq_g
     __syncthreads();
     tc_fence_after();
     const uint32_t tb = *tmem_slot;
+#ifdef GEMM_PROF
+    if (a.prof && tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.prof[blockIdx.x == 0 ? 12 : 13] = (long long)(blockIdx.x == 0 ? t - prof_entry : t); }
+#endif
     // everything above overlaps the previous kernel's tail; its results (the activation image) are read below
     pdl_sync();
 
@@ -264,26 +292,32 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, Cfg<NCP>::CTAS) k_ptq_g
         // ---- MMA issue: each of the two threads issues two sub-blocks' MMAs of every block (an issue costs the
         //      thread ~55 cycles whatever its size; two threads keep that far below the other roles' time) --------
         if (lane == 0) {
-            const int sb0 = 2 * (warp - (DW + EW + 1));
-            // D s32, A u8, B s8, both K-major, N = 8, M = 128
-            const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (uint32_t(8 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+            constexpr int SPT = 4 / C::MW;          // sub-blocks per issuing thread
+            const int sb0 = SPT * (warp - (DW + EW + 1));
+            // D s32, A u8, B s8, both K-major, M = 128, N = all the pass's columns: one instruction per 32-weight sub-block.
+            // (An instruction costs the tensor core about 190 cycles here whatever N is - measured with N = 8 - so the column
+            // groups share one; a block's accumulators are laid out [sub-block][column].)
+            const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | (uint32_t(NCP >> 3) << 17) | (uint32_t(128 >> 4) << 24);
             bool ok = true;
             int s = 0, sph = 0, slot = 0, aph = 0, dph = 1;
             long long prof[4] = {0, 0, 0, 0};
             for (int it = 0; it < n_items && ok; ++it) {
                 { PROF_T0(); if (!mbar_wait(full + s, sph, a.err, abort_flag)) break; PROF_ADD(0); }
                 const uint32_t bbase = smem_u32(ring + size_t(s) * C::STAGE + WBYTES);
-                for (int j = 0; j < BK; ++j) {
+                for (int jt = 0; jt < BK / NB; ++jt) {
                     { PROF_T0(); if (!mbar_wait(afull + slot, aph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(1); }
+                    PROF_EV(2, it * BK + jt * NB, sb0 == 0);
                     { PROF_T0(); if (!mbar_wait(dempty + slot, dph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(2); }
+                    PROF_EV(3, it * BK + jt * NB, sb0 == 0);
                     tc_fence_after();
 #pragma unroll
-                    for (int k = 0; k < 2; ++k)
+                    for (int jb = 0; jb < NB; ++jb)
 #pragma unroll
-                        for (int gi = 0; gi < NG; ++gi)
-                            tc_mma_i8(tb + D_COL + (slot * NG + gi) * 32 + (sb0 + k) * 8, tb + A_COL + slot * 32 + (sb0 + k) * 8,
-                                      smem_desc(bbase + j * (NCP * IMG_COL) + gi * 1024 + (sb0 + k) * 256, 128, 128), idesc, 0u);
+                        for (int k = 0; k < SPT; ++k)
+                            tc_mma_i8(tb + D_COL + (slot * NB + jb) * NG * 32 + (sb0 + k) * NCP, tb + A_COL + (slot * NB + jb) * 32 + (sb0 + k) * 8,
+                                      smem_desc(bbase + (jt * NB + jb) * (NCP * IMG_COL) + (sb0 + k) * 256, 128, 1024), idesc, 0u);
                     tc_commit(dfull + slot);
+                    PROF_EV(4, it * BK + jt * NB, sb0 == 0);
                     if (++slot == NA) { slot = 0; aph ^= 1; dph ^= 1; }
                 }
                 if (++s == C::STAGES) { s = 0; sph ^= 1; }
@@ -304,14 +338,19 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, Cfg<NCP>::CTAS) k_ptq_g
             if (lane == 0) mbar_arrive(afull + pending);
             pending = -1;
         };
-        int s = 0, sph = 0, g = 0;
+        // DSETS sets of four decode warps take the slots (NB blocks each) in turn
+        constexpr int DSETS = DW / 4;
+        const int set = warp >> 2;
+        int s = 0, sph = 0;
         long long prof[4] = {0, 0, 0, 0};
         for (int it = 0; it < n_items && ok; ++it) {
             { PROF_T0(); if (!mbar_wait(full + s, sph, a.err, abort_flag)) break; PROF_ADD(0); }
             const unsigned char *st = ring + size_t(s) * C::STAGE;
 #pragma unroll 1
-            for (int j = 0; j < BK; ++j, ++g) {
-                const int slot = g % NA;
+            for (int j = 0; j < BK; ++j) {
+                const int g = it * BK + j, bt = g / NB, jb = g % NB, slot = bt % NA;
+                if (DSETS > 1 && bt % DSETS != set) continue;
+                PROF_EV(0, g, (warp & 3) == 0 && lane == 0);
                 uint32_t r[7];
                 if (a.tiled) {                      // [block][word][row]: the warp's rows are consecutive dwords
                     const uint32_t *src = reinterpret_cast<const uint32_t *>(st) + j * 7 * 128 + row;
@@ -324,14 +363,20 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, Cfg<NCP>::CTAS) k_ptq_g
                 }
                 uint32_t o[32];
                 { PROF_T0(); decode_block(r, o); if (a.prof && o[31] == 0xFFFFFFFFu) prof[3]++; PROF_ADD(1); }
-                { PROF_T0(); publish(); PROF_ADD(2); }   // the previous block's store had this block's arithmetic to finish
-                { PROF_T0(); if (!mbar_wait(aempty + slot, ((g / NA) & 1) ^ 1, a.err, abort_flag)) { ok = false; break; } PROF_ADD(3); }
-                tc_fence_after();
-                const uint32_t ta = tb + lane_base + A_COL + slot * 32;
+                if (jb == 0) {
+                    { PROF_T0(); publish(); PROF_ADD(2); }   // the previous slot's stores had this block's arithmetic to finish
+                    { PROF_T0(); if (!mbar_wait(aempty + slot, ((bt / NA) & 1) ^ 1, a.err, abort_flag)) { ok = false; break; } PROF_ADD(3); }
+                    tc_fence_after();
+                }
+                const uint32_t ta = tb + lane_base + A_COL + (slot * NB + jb) * 32;
                 tmem_st16(ta, o);
                 tmem_st16(ta + 16, o + 16);
+                PROF_EV(1, g, (warp & 3) == 0 && lane == 0);
                 dwv[(g % DWS) * 128 + row] = half_bits_to_float(r[6] >> 16);
-                pending = slot;
+                if (jb == NB - 1) {
+                    pending = slot;
+                    if (DSETS > 1) publish();       // this set's next slot is DSETS slots away: hand over now
+                }
             }
             if (++s == C::STAGES) { s = 0; sph ^= 1; }
         }
@@ -341,8 +386,8 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, Cfg<NCP>::CTAS) k_ptq_g
         // ---- epilogue (warps DW .. DW+EW-1): warp (quarter q, group gi) owns 32 rows x 8 columns -------------------
         const int q = warp & 3, part = (warp - DW) >> 2, row = q * 32 + lane;
         const uint32_t lane_base = uint32_t(q * 32) << 16;
-        constexpr int GPW = C::GPW, NCW = 8 * GPW;
-        const int c0 = part * NCW;
+        constexpr int GPW = C::GPW, PPG = C::PPG, NCW = C::CPW;
+        const int c0 = part * NCW, g0 = c0 / 8, p0 = (c0 % 8) / 2;
         // running sums as column pairs (2p, 2p+1): the arithmetic below is done two columns at a time
         constexpr int NPR = NCW / 2;
         f32x2 acc[NPR], u[NPR], ve[NPR];
@@ -351,62 +396,75 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, Cfg<NCP>::CTAS) k_ptq_g
         const f32x2 magic2 = pk2(12582912.0f, 12582912.0f);
         bool ok = true;
         long long prof[4] = {0, 0, 0, 0};
-        int s = 0, sph = 0, slot = 0, dph = 0, g = 0;
+        int s = 0, sph = 0, g = 0;
         for (int tt = blockIdx.x; tt < nwork && ok; tt += gridDim.x) {
             const int t = split ? tt / nkc : tt, kc0 = split ? tt - t * nkc : 0, kc1 = split ? kc0 + 1 : nkc;
             for (int kc = kc0; kc < kc1 && ok; ++kc) {
                 { PROF_T0(); if (!mbar_wait(full + s, sph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(0); }
-                const unsigned char *stage_scales = ring + size_t(s) * C::STAGE + WBYTES + NCP * 128 + (c0 / 8) * 256;
+                const unsigned char *stage_scales = ring + size_t(s) * C::STAGE + WBYTES + NCP * 128 + g0 * 256;
 #pragma unroll 1
                 for (int j = 0; j < BK; ++j, ++g) {
                     const unsigned char *scales = stage_scales + j * (NCP * IMG_COL);
-                    { PROF_T0(); if (!mbar_wait(dfull + slot, dph, a.err, abort_flag)) { ok = false; break; } PROF_ADD(0); }
-                    tc_fence_after();
+                    const int bt = g / NB, jb = g % NB, slot = bt % NA;
+                    if (jb == 0) {
+                        { PROF_T0(); if (!mbar_wait(dfull + slot, (bt / NA) & 1, a.err, abort_flag)) { ok = false; break; } PROF_ADD(0); }
+                        PROF_EV(5, g, warp == DW && lane == 0);
+                        tc_fence_after();
+                    }
                     const float dw = dwv[(g % DWS) * 128 + row];
                     const f32x2 dw2 = pk2(dw, dw);
                     const int b = kc * BK + j, bi = b & 3;
 #pragma unroll
                     for (int gw = 0; gw < GPW; ++gw) {
-                        uint32_t d[32];                     // [sub-block][column] of one group
-                        tmem_ld32(tb + lane_base + D_COL + (slot * NG + part * GPW + gw) * 32, d);
+                        constexpr int DS = 2 * PPG;         // this warp's columns per sub-block
+                        uint32_t d[4 * DS];                 // [sub-block][column] of one group (or of this warp's half of it)
+                        const uint32_t dsrc = tb + lane_base + D_COL + (slot * NB + jb) * NG * 32 + (g0 + gw) * 8;   // [sub-block][column]
+#pragma unroll
+                        for (int sb = 0; sb < 4; ++sb) {
+                            if (PPG == 4) tmem_ld8(dsrc + sb * NCP, d + sb * DS);
+                            else tmem_ld4(dsrc + sb * NCP + 2 * p0, d + sb * DS);
+                        }
                         // the group's scales, per sub-block and column pair one 16-byte entry (d, d', -s, -s'): they do not
                         // depend on the accumulators and travel while those do
-                        ulonglong2 sc[16];
+                        ulonglong2 sc[4 * PPG];
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) sc[e] = *reinterpret_cast<const ulonglong2 *>(scales + gw * 256 + e * 16);
+                        for (int sb = 0; sb < 4; ++sb)
+#pragma unroll
+                            for (int p = 0; p < PPG; ++p) sc[sb * PPG + p] = *reinterpret_cast<const ulonglong2 *>(scales + gw * 256 + (sb * 4 + p0 + p) * 16);
                         { PROF_T0(); asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); PROF_ADD(1); }
-                        if (gw == GPW - 1) {                // all of this warp's accumulators are in registers: the slot is free
+                        if (gw == GPW - 1 && jb == NB - 1) {   // all of this warp's accumulators of the slot are in registers: it is free
                             tc_fence_before();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(dempty + slot);
                         }
                         PROF_T0();
-                        f32x2 v[4];
+                        f32x2 v[PPG];
 #pragma unroll
-                        for (int p = 0; p < 4; ++p) {       // straight-line: the pairs' dependency chains interleave
+                        for (int p = 0; p < PPG; ++p) {     // straight-line: the pairs' dependency chains interleave
                             f32x2 tt[4];
 #pragma unroll
                             for (int sb = 0; sb < 4; ++sb) {
-                                const f32x2 f = sub2(pk2(__uint_as_float(MAGIC + d[sb * 8 + 2 * p]), __uint_as_float(MAGIC + d[sb * 8 + 2 * p + 1])), magic2);
-                                tt[sb] = fma2(sc[sb * 4 + p].x, f, sc[sb * 4 + p].y);
+                                const int dc = sb * DS + 2 * p;
+                                const f32x2 f = sub2(pk2(__uint_as_float(MAGIC + d[dc]), __uint_as_float(MAGIC + d[dc + 1])), magic2);
+                                tt[sb] = fma2(sc[sb * PPG + p].x, f, sc[sb * PPG + p].y);
                             }
                             v[p] = mul2(dw2, add2(add2(tt[0], tt[1]), add2(tt[2], tt[3])));
                         }
                         if (bi == 0 || bi == 2) {
 #pragma unroll
-                            for (int p = 0; p < 4; ++p) ve[gw * 4 + p] = v[p];
+                            for (int p = 0; p < PPG; ++p) ve[gw * PPG + p] = v[p];
                         } else if (bi == 1) {
 #pragma unroll
-                            for (int p = 0; p < 4; ++p) u[gw * 4 + p] = add2(ve[gw * 4 + p], v[p]);
+                            for (int p = 0; p < PPG; ++p) u[gw * PPG + p] = add2(ve[gw * PPG + p], v[p]);
                         } else if (split) {
                             // the group sum p_g itself goes to memory; the groups are added in order by gemm_sum_groups
                             const int grow = t * 128 + row;
 #pragma unroll
-                            for (int p = 0; p < 4; ++p) {
-                                const f32x2 q2 = add2(u[gw * 4 + p], add2(ve[gw * 4 + p], v[p]));
+                            for (int p = 0; p < PPG; ++p) {
+                                const f32x2 q2 = add2(u[gw * PPG + p], add2(ve[gw * PPG + p], v[p]));
                                 float lo, hi;
                                 unpk2(q2, lo, hi);
-                                const int c = c0 + gw * 8 + 2 * p;
+                                const int c = (g0 + gw) * 8 + 2 * (p0 + p);
                                 if (grow < a.M) {
                                     float *gp = a.groups + (size_t(b >> 2) * NCP + c) * size_t(a.M) + grow;
                                     if (c < a.ncol) gp[0] = lo;
@@ -416,14 +474,14 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, Cfg<NCP>::CTAS) k_ptq_g
                         } else {
                             const bool first = b < 4;
 #pragma unroll
-                            for (int p = 0; p < 4; ++p) {
-                                const f32x2 q2 = add2(u[gw * 4 + p], add2(ve[gw * 4 + p], v[p]));
-                                acc[gw * 4 + p] = first ? q2 : add2(acc[gw * 4 + p], q2);
+                            for (int p = 0; p < PPG; ++p) {
+                                const f32x2 q2 = add2(u[gw * PPG + p], add2(ve[gw * PPG + p], v[p]));
+                                acc[gw * PPG + p] = first ? q2 : add2(acc[gw * PPG + p], q2);
                             }
                         }
                         PROF_ADD(2);
                     }
-                    if (++slot == NA) { slot = 0; dph ^= 1; }
+                    PROF_EV(6, g, warp == DW && lane == 0);
                     if (!split && b == nb - 1) {
                         const int grow = t * 128 + row;
                         if (grow < a.M) {
@@ -448,6 +506,9 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, Cfg<NCP>::CTAS) k_ptq_g
     }
     tc_fence_before();
     __syncthreads();
+#ifdef GEMM_PROF
+    if (a.prof && tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); a.prof[blockIdx.x == 0 ? 14 : 13] = (long long)(blockIdx.x == 0 ? t - prof_entry : t - (unsigned long long)a.prof[13]); }
+#endif
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tb), "r"(uint32_t(C::TMEM_COLS)) : "memory");
 }
 
@@ -695,7 +756,7 @@ bool gemm_supported(int M, int K, int ncol) {
 
 bool gemm_wants_split(int sm_count, int M, int K, int ncol) {
     // fewer row tiles than half of what the GPU can hold at once: split over K
-    const int ntiles = (M + 127) / 128, cap = sm_count * (gemm_padded_cols(ncol) == 8 ? GEMM_CTAS8 : 1);
+    const int ntiles = (M + 127) / 128, cap = sm_count * (gemm_padded_cols(ncol) == 8 ? Cfg<8>::CTAS : 1);
     return K >= 2048 && 2 * ntiles <= cap && getenv("BONSAI_GEMM_NO_SPLIT") == nullptr;
 }
 size_t gemm_group_floats(int M, int K, int ncol) { return size_t(K / 512) * gemm_padded_cols(ncol) * size_t(M); }
