@@ -27,7 +27,7 @@ Scr scratch_layout(const bn_attn_dims &d) {
     Scr s;
     s.pos = al(size_t(d.cap) * 4); s.q16f = al(QD * 4); s.gate = al(QD * 4);
     s.score = al(size_t(d.n_head) * d.cap * 4); s.pe = al(size_t(d.n_head) * d.cap * 4);
-    s.esum = al(size_t(d.n_head) * 1024 * 4); s.pv = al(size_t(splits_for(d.cap)) * QD * 4);
+    s.esum = al(size_t(d.n_head) * 1026 * 4); s.pv = al(size_t(splits_for(d.cap)) * QD * 4);
     s.bytes = o;
     return s;
 }

@@ -687,7 +687,7 @@ int bn_model_finalize(bn_model *m) {
     F(m->Q16F, QD); F(m->GATEB, QD); F(m->GOUT, QD);
     F(m->FG, 2 * size_t(h.ffn)); F(m->FS, h.ffn); F(m->D, h.hidden); F(m->LOGITS, h.vocab);
     F(m->ALPHA, 64); F(m->BETA, 64); F(m->G, 64); F(m->BT, 64);
-    F(m->SCORE, size_t(h.n_head) * h.cap); F(m->P16F, size_t(h.n_head) * h.cap); F(m->ESUM, size_t(h.n_head) * 1024);
+    F(m->SCORE, size_t(h.n_head) * h.cap); F(m->P16F, size_t(h.n_head) * h.cap); F(m->ESUM, size_t(h.n_head) * 1026);
     F(m->PVPART, size_t(m->pv_splits) * QD); F(m->AMV, 64);
     F(m->GEMV_SCRATCH, size_t(maxG) * std::max(maxM, 1));
     slots.push_back({reinterpret_cast<void **>(&m->AMI), carve(64 * 4)});

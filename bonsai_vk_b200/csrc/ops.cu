@@ -584,69 +584,114 @@ __global__ void __launch_bounds__(256) k_attn_prep(bnk::AttnDims a, const float 
     else q80_store(v, lane, reinterpret_cast<int8_t *>(kv.v_data) + row + blk * 32, kv.v_scale + row / 32 + blk);
 }
 
+// ---- packed fp32 pairs: two IEEE single operations per instruction, each half rounded as the scalar instruction ----
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float a, float b) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ void unpk2(f32x2 v, float &a, float &b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { f32x2 d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) { f32x2 d; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { f32x2 d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+// int8 code -> float without the conversion unit: the word's bytes are biased by 128 (one xor for four codes), a byte
+// is dropped into the mantissa of 2^23 and 2^23 + 128 is subtracted: exact for every code
+constexpr float CODE_MAGIC = 8388736.0f;       // 2^23 + 128
+__device__ __forceinline__ float code_f(uint32_t biased_word, int byte) {
+    const uint32_t sel = byte == 0 ? 0x7440u : (byte == 1 ? 0x7441u : (byte == 2 ? 0x7442u : 0x7443u));
+    return __uint_as_float(__byte_perm(biased_word, 0x4B000000u, sel));   // 2^23 + (code + 128), magic still to subtract
+}
+
 // scores: each warp takes 8 consecutive keys of one kv head; the gqa query heads of that kv head share every K row
-// (merge idea: attn_qk_softmax_gqa.glslh:15-24) and stay in registers. Per key: lane l covers dims 8l..8l+7 with
-// an fmaf chain, then a 32-lane xor tree. The 8 K rows are requested before any of them is used.
-template <int GQA>
+// (merge idea: attn_qk_softmax_gqa.glslh:15-24). Per key and head: lane l covers dims 8l..8l+7 with an fmaf chain,
+// then the 32 lane sums meet in the xor-butterfly tree (16, 8, 4, 2, 1). Two keys travel in the halves of packed
+// registers (the duplicated query values are loop constants), and the 32 trees of a warp (8 keys x 4 heads) run as
+// one transposed butterfly - every lane ends up with one total - which forms the same pair sums in the same order.
+template <int GQA, int KMODE>
 __global__ void __launch_bounds__(256) k_attn_scores(bnk::AttnDims a, const float *__restrict__ q16f,
                                                      const int *__restrict__ pos_ptr, bnk::KvLayer kv,
-                                                     float *__restrict__ score, bnk::Cols cols) {
+                                                     float *__restrict__ score, unsigned *__restrict__ counters, bnk::Cols cols) {
+    static_assert(GQA == 4, "the transposed reduction is laid out for 8 keys x 4 heads");
     bnk::pdl_sync();
-    { const size_t col = blockIdx.z; q16f = bnk::colp(q16f, col * cols.arena); pos_ptr = bnk::colp(pos_ptr, col * cols.arena); kv.k_data = bnk::colp(kv.k_data, col * cols.kv); kv.k_scale = bnk::colp(kv.k_scale, col * cols.kv); kv.v_data = bnk::colp(kv.v_data, col * cols.kv); kv.v_scale = bnk::colp(kv.v_scale, col * cols.kv); score = bnk::colp(score, col * cols.arena); }
+    { const size_t col = blockIdx.z; q16f = bnk::colp(q16f, col * cols.arena); pos_ptr = bnk::colp(pos_ptr, col * cols.arena); kv.k_data = bnk::colp(kv.k_data, col * cols.kv); kv.k_scale = bnk::colp(kv.k_scale, col * cols.kv); score = bnk::colp(score, col * cols.arena); counters = bnk::colp(counters, col * cols.arena); }
     const int kvh = blockIdx.y, lane = threadIdx.x & 31, hd = a.head_dim;
+    // arrival counters of the softmax-sum kernel that follows: zero before it starts
+    if (blockIdx.x == 0 && kvh == 0 && int(threadIdx.x) < a.n_head) counters[threadIdx.x] = 0u;
     const int nfill = pos_ptr[0] + 1;
     const int jb = (blockIdx.x * 8 + (threadIdx.x >> 5)) * 8;
     if (jb >= nfill) return;
-    float q[GQA][8];
+    f32x2 qd[GQA][8];                            // (q, q): both keys of a pair meet the same query value
 #pragma unroll
     for (int g = 0; g < GQA; ++g) {
         const float4 *qv = reinterpret_cast<const float4 *>(q16f + size_t(kvh * GQA + g) * hd + lane * 8);
         const float4 q0 = qv[0], q1 = qv[1];
-        q[g][0] = q0.x; q[g][1] = q0.y; q[g][2] = q0.z; q[g][3] = q0.w; q[g][4] = q1.x; q[g][5] = q1.y; q[g][6] = q1.z; q[g][7] = q1.w;
+        const float qe[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) qd[g][e] = pk2(qe[e], qe[e]);
     }
-    uint4 raw16[8];
-    uint2 raw8[8];
+    uint4 raw16[KMODE == 1 ? 8 : 1];
+    uint2 raw8[KMODE == 1 ? 1 : 8];
     float sc[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
         const int j = min(jb + u, nfill - 1);
         const size_t row = (size_t(j) * a.n_kv + kvh) * hd;
-        if (a.k_mode == 1) raw16[u] = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(kv.k_data) + row + lane * 8);
+        if (KMODE == 1) raw16[u] = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(kv.k_data) + row + lane * 8);
         else {
             raw8[u] = *reinterpret_cast<const uint2 *>(reinterpret_cast<const int8_t *>(kv.k_data) + row + lane * 8);
             sc[u] = half_bits_to_float(kv.k_scale[row / 32 + (lane >> 2)]);
         }
     }
+    float v[32];                                 // v[4u + g]: this lane's part of (key jb+u, head g)
+    const f32x2 magic2 = pk2(CODE_MAGIC, CODE_MAGIC);
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-        const int j = jb + u;
-        float kf[8];
-        if (a.k_mode == 1) {
-            const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw16[u]);
+    for (int up = 0; up < 4; ++up) {             // keys jb+2up, jb+2up+1
+        f32x2 kf[8];
+        if (KMODE == 1) {
+            const __half2 *ha = reinterpret_cast<const __half2 *>(&raw16[2 * up]), *hb = reinterpret_cast<const __half2 *>(&raw16[2 * up + 1]);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h2[e]); kf[2 * e] = f.x; kf[2 * e + 1] = f.y; }
+            for (int e = 0; e < 4; ++e) {
+                const float2 fa = __half22float2(ha[e]), fb = __half22float2(hb[e]);
+                kf[2 * e] = pk2(fa.x, fb.x); kf[2 * e + 1] = pk2(fa.y, fb.y);
+            }
         } else {
-            const int8_t *c = reinterpret_cast<const int8_t *>(&raw8[u]);
+            const uint32_t a0 = raw8[2 * up].x ^ 0x80808080u, a1 = raw8[2 * up].y ^ 0x80808080u;
+            const uint32_t b0 = raw8[2 * up + 1].x ^ 0x80808080u, b1 = raw8[2 * up + 1].y ^ 0x80808080u;
+            const f32x2 sc2 = pk2(sc[2 * up], sc[2 * up + 1]);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) kf[e] = __fmul_rn(sc[u], float(c[e]));
+            for (int e = 0; e < 8; ++e) {
+                const f32x2 c = sub2(pk2(code_f(e < 4 ? a0 : a1, e & 3), code_f(e < 4 ? b0 : b1, e & 3)), magic2);
+                kf[e] = mul2(sc2, c);
+            }
         }
 #pragma unroll
         for (int g = 0; g < GQA; ++g) {
-            float acc = 0.0f;
+            f32x2 acc = 0ull;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc = fmaf(q[g][e], kf[e], acc);
-#pragma unroll
-            for (int s = 16; s > 0; s >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, s));
-            if (lane == 0 && j < nfill) score[size_t(kvh * GQA + g) * a.cap + j] = acc;
+            for (int e = 0; e < 8; ++e) acc = fma2(qd[g][e], kf[e], acc);
+            unpk2(acc, v[8 * up + g], v[8 * up + 4 + g]);
         }
     }
+    // transposed butterfly: at distance `off` a lane keeps the half of its values that its bit selects and adds the
+    // partner's copy of the same values; lane l ends with the total of value l
+#pragma unroll
+    for (int off = 16, n = 32; off >= 1; off >>= 1, n >>= 1) {
+        const bool upper = lane & off;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+            const float send = upper ? v[i] : v[i + n / 2];
+            const float keep = upper ? v[i + n / 2] : v[i];
+            v[i] = __fadd_rn(keep, __shfl_xor_sync(0xFFFFFFFFu, send, off));
+        }
+    }
+    const int u = lane >> 2, g = lane & 3, j = jb + u;
+    if (j < nfill) score[size_t(kvh * GQA + g) * a.cap + j] = v[0];
 }
 
 // Softmax numerators and their sum, spread over EXPSUM_PARTS CTAs per head with the summation order of one
 // 1024-thread CTA: "virtual thread" vt adds the keys vt, vt+1024, ... ascending, and the 1024 partial sums are
-// later combined by the fixed tree (attn_qk_softmax.comp / attn_vk.h:175-190 in the regrouped order the CPU
+// then combined by the fixed tree (attn_qk_softmax.comp / attn_vk.h:175-190 in the regrouped order the CPU
 // checker also carries). Every CTA recomputes the row maximum (a maximum does not depend on order); the
-// exponentials of one virtual thread are evaluated by 8 real threads, then its owner adds them in order.
+// exponentials of one virtual thread are evaluated by 8 real threads, then its owner adds them in order. The CTA of
+// a head that finishes last (arrival counter, no waiting) runs the tree and leaves the head's total.
 constexpr int EXPSUM_PARTS = 8;
 __global__ void __launch_bounds__(1024) k_attn_expsum(bnk::AttnDims a, const int *__restrict__ pos_ptr,
                                                       const float *__restrict__ score, float scale,
@@ -654,7 +699,10 @@ __global__ void __launch_bounds__(1024) k_attn_expsum(bnk::AttnDims a, const int
     bnk::pdl_sync();
     { const size_t col = blockIdx.z; pos_ptr = bnk::colp(pos_ptr, col * cols.arena); score = bnk::colp(score, col * cols.arena); pe = bnk::colp(pe, col * cols.arena); partial = bnk::colp(partial, col * cols.arena); }
     __shared__ float red[1024];
+    __shared__ unsigned arrived;
     const int h = blockIdx.x, c = blockIdx.y, t = threadIdx.x, nfill = pos_ptr[0] + 1;
+    float *total = partial + size_t(a.n_head) * 1024;
+    unsigned *counters = reinterpret_cast<unsigned *>(total + a.n_head);
     const float *sr = score + size_t(h) * a.cap;
     float mx = -INFINITY;
     for (int j = t; j < nfill; j += 1024) mx = fmaxf(mx, __fmul_rn(sr[j], scale));
@@ -670,41 +718,38 @@ __global__ void __launch_bounds__(1024) k_attn_expsum(bnk::AttnDims a, const int
         float sum = 0.0f;
         for (int j = vt; j < nfill; j += 1024) sum = __fadd_rn(sum, pr[j]);
         partial[size_t(h) * 1024 + vt] = sum;
+        __threadfence();
     }
-}
-
-// probabilities: p = fp16(e / total), total = the fixed tree over the head's 1024 partial sums (recomputed by
-// every CTA of the head). grid (n_head, ceil(cap / 4096)), 1024 threads, 4 keys per thread.
-__global__ void __launch_bounds__(1024) k_attn_normalise(bnk::AttnDims a, const int *__restrict__ pos_ptr,
-                                                         const float *__restrict__ partial, float *__restrict__ pe, bnk::Cols cols) {
-    bnk::pdl_sync();
-    { const size_t col = blockIdx.z; pos_ptr = bnk::colp(pos_ptr, col * cols.arena); partial = bnk::colp(partial, col * cols.arena); pe = bnk::colp(pe, col * cols.arena); }
-    __shared__ float red[1024];
-    const int h = blockIdx.x, t = threadIdx.x, nfill = pos_ptr[0] + 1;
-    if (int(blockIdx.y) * 4096 >= nfill) return;
-    red[t] = partial[size_t(h) * 1024 + t];
+    __syncthreads();
+    if (t == 0) arrived = atomicAdd(counters + h, 1u);
+    __syncthreads();
+    if (arrived != EXPSUM_PARTS - 1) return;
+    __threadfence();
+    red[t] = __ldcg(partial + size_t(h) * 1024 + t);
     const float tot = block_tree_sum(red, 1024);
-    float *pr = pe + size_t(h) * a.cap;
-    for (int j = blockIdx.y * 4096 + t; j < min(nfill, (int(blockIdx.y) + 1) * 4096); j += 1024)
-        pr[j] = __half2float(__float2half_rn(__fdiv_rn(pr[j], tot)));
+    if (t == 0) total[h] = tot;
 }
 
-// PV: grid (n_kv, splits); thread d = output dim; keys of the split ascending; acc = acc + p*v
+// PV: grid (n_kv, splits); thread d = output dim; keys of the split ascending; acc = acc + p*v with p = fp16(e / total)
+// formed while the split's numerators are staged in shared memory
 // (no fused multiply-add, runtime_vk/shaders/attn_pv_q8v.comp:85-112). The split's probabilities are staged in
 // shared memory and the V bytes of 8 keys are requested before the 8 dependent adds run.
 template <int GQA>
-__global__ void __launch_bounds__(256) k_attn_pv(bnk::AttnDims a, const float *__restrict__ p16f,
+__global__ void __launch_bounds__(256) k_attn_pv(bnk::AttnDims a, const float *__restrict__ p16f, const float *__restrict__ total,
                                                  const int *__restrict__ pos_ptr, bnk::KvLayer kv, int splits,
                                                  float *__restrict__ part, bnk::Cols cols) {
     bnk::pdl_sync();
-    { const size_t col = blockIdx.z; p16f = bnk::colp(p16f, col * cols.arena); pos_ptr = bnk::colp(pos_ptr, col * cols.arena); kv.k_data = bnk::colp(kv.k_data, col * cols.kv); kv.k_scale = bnk::colp(kv.k_scale, col * cols.kv); kv.v_data = bnk::colp(kv.v_data, col * cols.kv); kv.v_scale = bnk::colp(kv.v_scale, col * cols.kv); part = bnk::colp(part, col * cols.arena); }
+    { const size_t col = blockIdx.z; p16f = bnk::colp(p16f, col * cols.arena); total = bnk::colp(total, col * cols.arena); pos_ptr = bnk::colp(pos_ptr, col * cols.arena); kv.k_data = bnk::colp(kv.k_data, col * cols.kv); kv.k_scale = bnk::colp(kv.k_scale, col * cols.kv); kv.v_data = bnk::colp(kv.v_data, col * cols.kv); kv.v_scale = bnk::colp(kv.v_scale, col * cols.kv); part = bnk::colp(part, col * cols.arena); }
     extern __shared__ float ps[];                     // [GQA][per]
     const int kvh = blockIdx.x, sp = blockIdx.y, d = threadIdx.x, hd = a.head_dim;
     const int nfill = pos_ptr[0] + 1;
     const int per = (nfill + splits - 1) / splits;
     const int j0 = sp * per, j1 = min(nfill, j0 + per);
     const int n = max(0, j1 - j0);
-    for (int i = d; i < GQA * n; i += 256) { const int g = i / n, jj = i - g * n; ps[g * per + jj] = p16f[size_t(kvh * GQA + g) * a.cap + j0 + jj]; }
+    for (int i = d; i < GQA * n; i += 256) {
+        const int g = i / n, jj = i - g * n;
+        ps[g * per + jj] = __half2float(__float2half_rn(__fdiv_rn(p16f[size_t(kvh * GQA + g) * a.cap + j0 + jj], total[kvh * GQA + g])));
+    }
     __syncthreads();
     float acc[GQA];
 #pragma unroll
@@ -768,12 +813,12 @@ __global__ void k_attn_combine(bnk::AttnDims a, const float *__restrict__ part, 
     const int nfill = pos_ptr[0] + 1;
     const int per = (nfill + splits - 1) / splits;
     float acc = part[i];
-    for (int sb = 1; sb < splits; sb += 16) {          // 16 partials in flight, added in ascending order
-        float v[16];
+    for (int sb = 1; sb < splits; sb += 64) {          // 64 partials in flight, added in ascending order
+        float v[64];
 #pragma unroll
-        for (int u = 0; u < 16; ++u) v[u] = (sb + u < splits && (sb + u) * per < nfill) ? part[size_t(sb + u) * n + i] : 0.0f;
+        for (int u = 0; u < 64; ++u) v[u] = (sb + u < splits && (sb + u) * per < nfill) ? part[size_t(sb + u) * n + i] : 0.0f;
 #pragma unroll
-        for (int u = 0; u < 16; ++u) if (sb + u < splits && (sb + u) * per < nfill) acc = __fadd_rn(acc, v[u]);
+        for (int u = 0; u < 64; ++u) if (sb + u < splits && (sb + u) * per < nfill) acc = __fadd_rn(acc, v[u]);
     }
     if (pregate) pregate[i] = acc;
     gated[i] = __fmul_rn(acc, __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_f(-gate[i]))));
@@ -890,11 +935,15 @@ void attn_prep(cudaStream_t st, AttnDims a, const float *qg, const float *kin, c
 void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *gate, const int *pos_ptr, KvLayer kv,
                  float *score, float *p16f, float *esum, float *pv_part, int splits, float *pregate, float *gated, bool combine,
                  Cols cols) {
-    // grids are sized for the cache capacity; warps beyond the filled prefix return at once
-    launch(k_attn_scores<4>, dim3((a.cap + 63) / 64, a.n_kv, cols.z()), dim3(256), 0, st, a, q16f, pos_ptr, kv, score, cols);
+    // grids are sized for the cache capacity; warps beyond the filled prefix return at once.
+    // esum: [n_head][1024] partial sums, then n_head totals, then n_head arrival counters
+    float *total = esum + size_t(a.n_head) * 1024;
+    unsigned *counters = reinterpret_cast<unsigned *>(total + a.n_head);
+    const dim3 sg((a.cap + 63) / 64, a.n_kv, cols.z());
+    if (a.k_mode == 1) launch(k_attn_scores<4, 1>, sg, dim3(256), 0, st, a, q16f, pos_ptr, kv, score, counters, cols);
+    else launch(k_attn_scores<4, 0>, sg, dim3(256), 0, st, a, q16f, pos_ptr, kv, score, counters, cols);
     launch(k_attn_expsum, dim3(a.n_head, EXPSUM_PARTS, cols.z()), dim3(1024), 0, st, a, pos_ptr, score, 1.0f / sqrtf(float(a.head_dim)), p16f, esum, cols);
-    launch(k_attn_normalise, dim3(a.n_head, (a.cap + 4095) / 4096, cols.z()), dim3(1024), 0, st, a, pos_ptr, esum, p16f, cols);
-    launch(k_attn_pv<4>, dim3(a.n_kv, splits, cols.z()), dim3(256), size_t(4) * ((a.cap + splits - 1) / splits) * 4, st, a, p16f, pos_ptr, kv, splits, pv_part, cols);
+    launch(k_attn_pv<4>, dim3(a.n_kv, splits, cols.z()), dim3(256), size_t(4) * ((a.cap + splits - 1) / splits) * 4, st, a, static_cast<const float *>(p16f), static_cast<const float *>(total), pos_ptr, kv, splits, pv_part, cols);
     if (!combine) return;
     const int n = a.n_head * a.head_dim;
     launch(k_attn_combine, dim3((n + 255) / 256, 1, cols.z()), dim3(256), 0, st, a, pv_part, splits, pos_ptr, gate, pregate, gated, cols); 

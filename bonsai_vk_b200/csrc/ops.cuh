@@ -96,7 +96,7 @@ void attn_prep(cudaStream_t st, AttnDims a, const float *qg, const float *kin, c
                const float *kn_w, const int *pos_ptr, KvLayer kv, float *q16f, float *gate, Cols cols = {});
 // scores -> softmax (fp16-rounded probabilities) -> PV -> sigmoid gate. Scratch buffers sized by cap.
 void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *gate, const int *pos_ptr, KvLayer kv,
-                 float *score /*[nh][cap]*/, float *p16f /*[nh][cap]*/, float *esum /*[nh][1024]*/,
+                 float *score /*[nh][cap]*/, float *p16f /*[nh][cap]*/, float *esum /*[nh][1024] partial sums + [nh] totals + [nh] counters*/,
                  float *pv_part /*[splits][nh][hd]*/, int splits,
                  float *pregate /*[nh][hd] or null*/, float *gated, bool combine /*false: leave the split partials*/, Cols cols = {});
 void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx, Cols cols = {});
