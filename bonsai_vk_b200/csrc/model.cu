@@ -71,6 +71,9 @@ struct bn_model {
     struct TiledLayer { const uint8_t *in = nullptr, *out = nullptr, *ffn_in = nullptr, *ffn_down = nullptr; };
     std::vector<TiledLayer> tl;
     const uint8_t *t_head = nullptr;
+    int head_r0 = 0, head_r1 = 0;         // rows of the output head this model holds for the multi-sequence pass
+    bool head_sharded = false;            // bn_model_set_head_rows: the head runs through bn_model_head_batch, not in the last stage
+    float *CAND = nullptr;                // [batch_cols][2] candidates of a head shard
     std::map<long, cudaGraphExec_t> batch_graphs;   // key = stream0 * 64 + ncol
     int batch_graph_launches = 0;
     const uint32_t *embd = nullptr, *out_w = nullptr;
@@ -448,7 +451,8 @@ int build_batch_side(bn_model *m) {
         groups.push_back({{{L.ffn_gate, h.ffn}, {L.ffn_up, h.ffn}}, h.hidden, &T.ffn_in});
         groups.push_back({{{L.ffn_down, h.hidden}}, h.ffn, &T.ffn_down});
     }
-    if (m->b1 == h.n_layer) groups.push_back({{{m->out_w, h.vocab}}, h.hidden, &m->t_head});
+    if (m->head_sharded) groups.push_back({{{m->out_w + size_t(m->head_r0) * (h.hidden / 128) * 7, m->head_r1 - m->head_r0}}, h.hidden, &m->t_head});
+    else if (m->b1 == h.n_layer) { groups.push_back({{{m->out_w, h.vocab}}, h.hidden, &m->t_head}); m->head_r0 = 0; m->head_r1 = h.vocab; }
     size_t total = 0;
     for (const Group &g : groups) for (const Part &p : g.parts) total += bnk::gemm_tiled_bytes(p.M, g.K);
     BN_CUDA(cudaMalloc(&m->tiled, total));
@@ -472,6 +476,7 @@ int build_batch_side(bn_model *m) {
         }
         if (need) BN_CUDA(cudaMalloc(&m->GROUPS, need * 4));
     }
+    if (m->head_sharded) BN_CUDA(cudaMalloc(&m->CAND, size_t(h.batch_cols) * 8));
     BN_CUDA(cudaStreamSynchronize(m->ctx->stream));
     return BN_OK;
 }
@@ -546,7 +551,7 @@ void enqueue_batch(bn_model *m, int ncol) {
         prep(bnk::PREP_PLAIN, m->FS, nullptr, m->signs + h.hidden, h.ffn, m->IMG_F, nullptr);
         gemm(T.ffn_down, h.hidden, h.ffn, m->IMG_F, m->RES, m->RES);
     }
-    if (m->b1 != h.n_layer) return;
+    if (m->b1 != h.n_layer || m->head_sharded) return;
     prep(bnk::PREP_NORM, m->RES, m->out_norm, m->signs, h.hidden, m->IMG_H, nullptr);
     gemm(m->t_head, h.vocab, h.hidden, m->IMG_H, m->LOGITS, nullptr);
     bnk::argmax_first(st, m->LOGITS, h.vocab, m->NEXT, m->AMV, m->AMI, cols);
@@ -667,7 +672,7 @@ int bn_model_finalize(bn_model *m) {
         }
     }
     if (rc == BN_OK && m->b0 == 0) m->embd = tensor_ptr<uint32_t>(m, "token_embd.weight", ptq_bytes(h.vocab, h.hidden), &rc);
-    if (rc == BN_OK && m->b1 == h.n_layer) {
+    if (rc == BN_OK && (m->b1 == h.n_layer || m->head_sharded)) {
         m->out_w = tensor_ptr<uint32_t>(m, "output.weight", ptq_bytes(h.vocab, h.hidden), &rc);
         if (rc == BN_OK) m->out_norm = tensor_ptr<float>(m, "output_norm.weight", size_t(h.hidden) * 4, &rc);
     }
@@ -780,6 +785,7 @@ void bn_model_destroy(bn_model *m) {
     if (m->IMG_H) cudaFree(m->IMG_H);
     if (m->IMG_F) cudaFree(m->IMG_F);
     if (m->GROUPS) cudaFree(m->GROUPS);
+    if (m->CAND) cudaFree(m->CAND);
     delete m;
 }
 
@@ -914,6 +920,7 @@ int bn_model_stage_prepare(bn_model *m, int stream0, int ncol) {
 
 int bn_model_stage(bn_model *m, int stream, int tok, int pos, const bn_buf *in, size_t in_off, bn_buf *out, size_t out_off) {
     BN_REQUIRE(m && m->finalized, BN_ERR_STATE, "bn_model_stage: model not finalized");
+    BN_REQUIRE(!m->head_sharded, BN_ERR_STATE, "bn_model_stage: a model with a sharded output head runs through bn_model_stage_batch and bn_model_head_batch");
     const bn_hparams &h = m->hp;
     const int S = h.n_streams > 0 ? h.n_streams : 1;
     BN_REQUIRE(stream >= 0 && stream < S, BN_ERR_ARG, "bn_model_stage: stream %d outside [0, %d)", stream, S);
@@ -960,7 +967,7 @@ int bn_model_stage_batch(bn_model *m, int stream0, int ncol, const int *tok, con
                "bn_model_stage_batch: %d sequences per call, the model was created for at most %d (bn_hparams.batch_cols)", ncol, h.batch_cols);
     BN_REQUIRE(stream0 >= 0 && stream0 + ncol <= S, BN_ERR_ARG, "bn_model_stage_batch: sequences %d..%d outside [0, %d)", stream0, stream0 + ncol - 1, S);
     BN_REQUIRE(m->fused, BN_ERR_STATE, "bn_model_stage_batch: needs the fused layer kernels (shapes supported by the streamed projection kernel)");
-    const bool first = m->b0 == 0, last = m->b1 == h.n_layer;
+    const bool first = m->b0 == 0, last = m->b1 == h.n_layer && !m->head_sharded;
     cudaStream_t st = m->ctx->stream;
     ColInit ci = {};
     for (int c = 0; c < ncol; ++c) {
@@ -1000,6 +1007,51 @@ int bn_model_stage_batch(bn_model *m, int stream0, int ncol, const int *tok, con
     else BN_CUDA(cudaMemcpy2DAsync(bn_ptr<char>(out, out_off), size_t(h.hidden) * 4, m->RES, m->arena_bytes, size_t(h.hidden) * 4, ncol,
                                    cudaMemcpyDeviceToDevice, st));
     return BN_OK;
+}
+
+int bn_model_set_head_rows(bn_model *m, int row_begin, int row_end) {
+    BN_REQUIRE(m && !m->finalized, BN_ERR_STATE, "bn_model_set_head_rows: call before bn_model_finalize");
+    const bn_hparams &h = m->hp;
+    BN_REQUIRE(h.batch_cols > 0, BN_ERR_ARG, "bn_model_set_head_rows: the sharded output head belongs to the multi-sequence pass (bn_hparams.batch_cols > 0)");
+    BN_REQUIRE(row_begin >= 0 && row_begin < row_end && row_end <= h.vocab && row_begin % 128 == 0 && (row_end % 128 == 0 || row_end == h.vocab),
+               BN_ERR_ARG, "bn_model_set_head_rows: rows [%d, %d) must lie in [0, %d) on 128-row boundaries", row_begin, row_end, h.vocab);
+    m->head_r0 = row_begin; m->head_r1 = row_end; m->head_sharded = true;
+    return BN_OK;
+}
+
+int bn_model_head_batch(bn_model *m, int ncol, const bn_buf *in, size_t in_off, bn_buf *out, size_t out_off) {
+    BN_REQUIRE(m && m->finalized && m->head_sharded, BN_ERR_STATE, "bn_model_head_batch: needs a finalized model with bn_model_set_head_rows");
+    const bn_hparams &h = m->hp;
+    BN_REQUIRE(ncol >= 1 && ncol <= h.batch_cols, BN_ERR_ARG, "bn_model_head_batch: %d sequences, the model was created for at most %d", ncol, h.batch_cols);
+    BN_RANGE(in, in_off, size_t(ncol) * h.hidden * 4, 16, "bn_model_head_batch hidden input");
+    BN_RANGE(out, out_off, size_t(ncol) * 8, 8, "bn_model_head_batch candidate output");
+    cudaStream_t st = m->ctx->stream;
+    BN_CUDA(cudaMemcpy2DAsync(m->RES, m->arena_bytes, bn_ptr<char>(in, in_off), size_t(h.hidden) * 4, size_t(h.hidden) * 4, ncol, cudaMemcpyDeviceToDevice, st));
+    const size_t AS = m->arena_bytes / 4;
+    bnk::Cols cols;
+    cols.n = ncol; cols.arena = m->arena_bytes; cols.gdn = 0; cols.conv = 0; cols.kv = 0;
+    bnk::PrepArgs p = {};
+    p.x = m->RES; p.x_stride = AS; p.w = m->out_norm; p.signs = m->signs; p.K = h.hidden; p.hat_block = h.hat_block; p.eps = h.rms_eps; p.ncol = ncol;
+    p.image = m->IMG_H; p.inv_stride = AS; p.mode = bnk::PREP_NORM;
+    bnk::prep_cols(st, p);
+    const int rows = m->head_r1 - m->head_r0;
+    bnk::GemmArgs a = {};
+    a.W = m->t_head; a.M = rows; a.K = h.hidden; a.tiled = 1; a.image = m->IMG_H; a.ncol = ncol; a.out = m->LOGITS; a.out_stride = AS; a.err = m->ctx->err_dev;
+    if (m->GROUPS && bnk::gemm_wants_split(m->ctx->sm_count, rows, h.hidden, ncol)) a.groups = m->GROUPS;
+    cudaError_t e = bnk::launch_gemm(st, m->ctx->sm_count, a, m->use_pdl);
+    if (e != cudaSuccess) return bn_cuda_fail(e, "bn_model_head_batch");
+    bnk::argmax_first(st, m->LOGITS, rows, m->NEXT, m->AMV, m->AMI, cols, m->CAND, m->head_r0);
+    BN_CUDA(cudaMemcpyAsync(bn_ptr<char>(out, out_off), m->CAND, size_t(ncol) * 8, cudaMemcpyDeviceToDevice, st));
+    return bn_launch_check(m->ctx, "bn_model_head_batch");
+}
+
+int bn_model_pick_batch(bn_model *m, int ncol, int n_shards, const bn_buf *cands, size_t cands_off, bn_buf *out, size_t out_off) {
+    BN_REQUIRE(m && m->finalized, BN_ERR_STATE, "bn_model_pick_batch: model not finalized");
+    BN_REQUIRE(ncol >= 1 && ncol <= 32 && n_shards >= 1 && n_shards <= 64, BN_ERR_ARG, "bn_model_pick_batch: %d sequences x %d shards out of range", ncol, n_shards);
+    BN_RANGE(cands, cands_off, size_t(n_shards) * ncol * 8, 8, "bn_model_pick_batch candidates");
+    BN_RANGE(out, out_off, size_t(ncol) * 4, 4, "bn_model_pick_batch output");
+    bnk::pick_shards(m->ctx->stream, bn_ptr<float>(cands, cands_off), n_shards, ncol, bn_ptr<int>(out, out_off));
+    return bn_launch_check(m->ctx, "bn_model_pick_batch");
 }
 
 int bn_model_fill_kv(bn_model *m, int stream, int n_positions) {

@@ -847,7 +847,10 @@ __global__ void __launch_bounds__(1024) k_argmax_part(const float *__restrict__ 
     }
     if (t == 0) { bv[blockIdx.x] = sv[0]; bi[blockIdx.x] = si[0]; }
 }
-__global__ void k_argmax_final(const float *__restrict__ bv, const int *__restrict__ bi, int nparts, int *out, bnk::Cols cols) {
+// cand != null (the rows are one shard of the output head, starting at row0): the column's candidate (value, global
+// row or 0x7FFFFFFF when no row qualified) also goes to cand[2 * column], for the pick over all shards
+__global__ void k_argmax_final(const float *__restrict__ bv, const int *__restrict__ bi, int nparts, int *out, bnk::Cols cols,
+                               float *__restrict__ cand, int row0) {
     bnk::pdl_sync();
     { const size_t col = blockIdx.z; bv = bnk::colp(bv, col * cols.arena); bi = bnk::colp(bi, col * cols.arena); out = bnk::colp(out, col * cols.arena); }
     if (threadIdx.x != 0) return;
@@ -855,6 +858,23 @@ __global__ void k_argmax_final(const float *__restrict__ bv, const int *__restri
     for (int p = 1; p < nparts; ++p) if (bv[p] > best || (bv[p] == best && bi[p] < idx)) { best = bv[p]; idx = bi[p]; }
     // a row of NaN or -inf never satisfies v > best: fall back to index 0 as the scalar loop does
     out[0] = idx == 0x7FFFFFFF ? 0 : idx;
+    if (cand) {
+        cand[2 * blockIdx.z] = best;
+        reinterpret_cast<int *>(cand)[2 * blockIdx.z + 1] = idx == 0x7FFFFFFF ? idx : idx + row0;
+    }
+}
+// the pick over the shards' candidates: first maximum, shards in ascending row order. One thread per column.
+__global__ void k_pick_shards(const float *__restrict__ cands, int n_shards, int ncol, int *__restrict__ out) {
+    bnk::pdl_sync();
+    const int c = threadIdx.x;
+    if (c >= ncol) return;
+    float best = -INFINITY; int idx = 0x7FFFFFFF;
+    for (int s = 0; s < n_shards; ++s) {
+        const float v = cands[(size_t(s) * ncol + c) * 2];
+        const int i = reinterpret_cast<const int *>(cands)[(size_t(s) * ncol + c) * 2 + 1];
+        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    }
+    out[c] = idx == 0x7FFFFFFF ? 0 : idx;
 }
 
 }  // namespace
@@ -948,10 +968,13 @@ void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *ga
     const int n = a.n_head * a.head_dim;
     launch(k_attn_combine, dim3((n + 255) / 256, 1, cols.z()), dim3(256), 0, st, a, pv_part, splits, pos_ptr, gate, pregate, gated, cols); 
 }
-void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx, Cols cols) {
+void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx, Cols cols, float *cand, int row0) {
     const int parts = 64;
     launch(k_argmax_part, dim3(parts, 1, cols.z()), dim3(1024), 0, st, x, n, scratch_val, scratch_idx, cols); 
-    launch(k_argmax_final, dim3(1, 1, cols.z()), dim3(32), 0, st, scratch_val, scratch_idx, parts, out_idx, cols); 
+    launch(k_argmax_final, dim3(1, 1, cols.z()), dim3(32), 0, st, scratch_val, scratch_idx, parts, out_idx, cols, cand, row0);
+}
+void pick_shards(cudaStream_t st, const float *cands, int n_shards, int ncol, int *out) {
+    launch(k_pick_shards, dim3(1), dim3(32), 0, st, cands, n_shards, ncol, out);
 }
 
 }  // namespace bnk

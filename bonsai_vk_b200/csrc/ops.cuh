@@ -99,6 +99,10 @@ void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *ga
                  float *score /*[nh][cap]*/, float *p16f /*[nh][cap]*/, float *esum /*[nh][1024] partial sums + [nh] totals + [nh] counters*/,
                  float *pv_part /*[splits][nh][hd]*/, int splits,
                  float *pregate /*[nh][hd] or null*/, float *gated, bool combine /*false: leave the split partials*/, Cols cols = {});
-void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx, Cols cols = {});
+// cand (optional): per column (value, row0 + index) of the maximum, for an output head whose rows are sharded
+void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *scratch_val, int *scratch_idx, Cols cols = {},
+                  float *cand = nullptr, int row0 = 0);
+// first maximum over n_shards x ncol candidates (value, row), shards in ascending row order
+void pick_shards(cudaStream_t st, const float *cands, int n_shards, int ncol, int *out);
 
 }  // namespace bnk

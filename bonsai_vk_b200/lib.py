@@ -92,6 +92,9 @@ def load_library() -> C.CDLL:
         "bn_model_stage_prepare": (i32, [vp, i32, i32]),
         "bn_model_stage": (i32, [vp, i32, i32, i32, vp, sz, vp, sz]),
         "bn_model_stage_batch": (i32, [vp, i32, i32, vp, vp, vp, sz, vp, sz]),
+        "bn_model_set_head_rows": (i32, [vp, i32, i32]),
+        "bn_model_head_batch": (i32, [vp, i32, vp, sz, vp, sz]),
+        "bn_model_pick_batch": (i32, [vp, i32, i32, vp, sz, vp, sz]),
         "bn_model_fill_kv": (i32, [vp, i32, i32]),
         "bn_wrap": (i32, [vp, vp, sz, C.POINTER(vp)]),
         "bn_use_stream": (i32, [vp, vp]),
@@ -284,8 +287,11 @@ _gemm_methods()
 class Model:
     """Device-resident model: tensors registered by GGUF name (reference: engine_init + fwd_init)."""
 
-    def __init__(self, ctx: Context, hp, tensors: dict, signs: np.ndarray):
+    def __init__(self, ctx: Context, hp, tensors: dict, signs: np.ndarray, head_rows=None):
+        """head_rows = (row_begin, row_end): this model holds that slice of the output head for the multi-sequence pass
+        (bn_model_set_head_rows); its last stage then returns hidden states and head_batch / pick_batch make the pick."""
         self.ctx, self.hp = ctx, hp
+        self.head_rows = head_rows
         lib = ctx.lib
         fields = {f[0] for f in HParamsC._fields_}
         hc = HParamsC(**{k: (float(v) if k in ("rms_eps", "rope_base") else int(v)) for k, v in hp.asdict().items() if k in fields})
@@ -305,7 +311,7 @@ class Model:
                 return b0 <= int(name.split(".")[1]) < b1
             if name == "token_embd.weight":
                 return b0 == 0
-            return b1 == hp.n_layer           # output.weight, output_norm.weight
+            return b1 == hp.n_layer or head_rows is not None     # output.weight, output_norm.weight
 
         tensors = {n: t for n, t in tensors.items() if local(n)}
         total = sum(al(np.asarray(t).nbytes) for t in tensors.values()) + al(signs.nbytes)
@@ -319,6 +325,8 @@ class Model:
         sg = np.ascontiguousarray(signs, dtype=np.int32)
         self.weights.upload(sg, off)
         _check(lib.bn_model_set_signs(self.h, self.weights.h, off, sg.size), "bn_model_set_signs")
+        if head_rows is not None:
+            _check(lib.bn_model_set_head_rows(self.h, int(head_rows[0]), int(head_rows[1])), "bn_model_set_head_rows")
         _check(lib.bn_model_finalize(self.h), "bn_model_finalize")
 
     def reset(self):
@@ -348,6 +356,14 @@ class Model:
         ta = (C.c_int32 * n)(*[int(t) for t in toks]) if toks is not None else None
         _check(self.ctx.lib.bn_model_stage_batch(self.h, stream0, n, ta, pa, inp.h if inp is not None else None, in_off, out.h, out_off),
                "bn_model_stage_batch")
+
+    def head_batch(self, ncol: int, inp: "Buffer", out: "Buffer", in_off: int = 0, out_off: int = 0):
+        """This model's shard of the output head for ncol sequences: final hidden states in, (value, row) candidates out."""
+        _check(self.ctx.lib.bn_model_head_batch(self.h, ncol, inp.h, in_off, out.h, out_off), "bn_model_head_batch")
+
+    def pick_batch(self, ncol: int, n_shards: int, cands: "Buffer", out: "Buffer", cands_off: int = 0, out_off: int = 0):
+        """First maximum over the shards' candidates (shards in ascending row order): ncol token ids."""
+        _check(self.ctx.lib.bn_model_pick_batch(self.h, ncol, n_shards, cands.h, cands_off, out.h, out_off), "bn_model_pick_batch")
 
     def fill_kv(self, stream: int, n_positions: int):
         _check(self.ctx.lib.bn_model_fill_kv(self.h, stream, n_positions), "bn_model_fill_kv")

@@ -227,6 +227,23 @@ int bn_model_stage(bn_model *m, int stream, int tok, int pos, const bn_buf *in, 
  * bn_model_stage_prepare(m, stream0, ncol). Enqueues only. */
 int bn_model_stage_batch(bn_model *m, int stream0, int ncol, const int *tok, const int *pos, const bn_buf *in, size_t in_off,
                          bn_buf *out, size_t out_off);
+
+/* Output head sharded by rows over the stages of a pipeline (the reference charges the head's bytes to the last GPU of
+ * its byte-balanced split, runtime_vk/gpu_fleet.h:1013-1020; here every stage takes an equal slice of the rows instead,
+ * so the last stage is no longer the long one). Call before bn_model_finalize: this model keeps rows
+ * [row_begin, row_end) of output.weight (128-row boundaries; row_end may be the vocabulary size) for the multi-sequence
+ * pass and needs output.weight and output_norm.weight whatever its block range. Its last stage then returns the
+ * hidden state from bn_model_stage_batch like every other stage, and bn_model_stage refuses. */
+int bn_model_set_head_rows(bn_model *m, int row_begin, int row_end);
+/* One shard of the head for ncol sequences: (in, in_off) holds the final hidden state, ncol x hidden fp32; output norm,
+ * rotation, this model's rows of the head and the first maximum over them. Writes ncol candidates to (out, out_off):
+ * 8 bytes each, fp32 value then int32 row in the whole vocabulary (0x7FFFFFFF when no row of the shard qualified).
+ * Enqueues only. */
+int bn_model_head_batch(bn_model *m, int ncol, const bn_buf *in, size_t in_off, bn_buf *out, size_t out_off);
+/* The pick over all shards: (cands, cands_off) holds n_shards x ncol candidates, shards in ascending row order; the
+ * first maximum of every sequence (Sampler::pick's rule, runtime_vk/bonsai_forward.h:2568-2570: greater value, then
+ * lower row) goes to (out, out_off) as ncol int32 token ids - the same ids the unsharded head gives. Enqueues only. */
+int bn_model_pick_batch(bn_model *m, int ncol, int n_shards, const bn_buf *cands, size_t cands_off, bn_buf *out, size_t out_off);
 /* timing fixture (reference: BONSAI_KVFILL, bonsai_forward.h:1338-1378): mark the first n_positions of a
  * stream's KV caches as filled with 1.0 so long-context steps can be timed without a long prefill */
 int bn_model_fill_kv(bn_model *m, int stream, int n_positions);

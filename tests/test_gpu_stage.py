@@ -142,3 +142,53 @@ def test_token_id_from_device_memory_is_checked(ctx):
     a.close()
     for x in (hid, hid0, bad):
         x.free()
+
+
+def test_output_head_sharded_over_the_stages(ctx):
+    """Two stages, each holding half of the output head's rows: the last stage hands the final hidden state to both,
+    every stage gives its shard's (value, row) candidates, and the pick over the shards must be the token the whole
+    model picks (first maximum). Four sequences in one pass, eight steps; also the refusals around the mode."""
+    from bonsai_vk_b200 import BonsaiError
+    hp = synth.tiny()
+    tensors, signs = synth.make_model(hp, seed=11)
+    S, T = 4, 8
+    first = [9, 1500, 321, 77]
+    whole = Model(ctx, hp, tensors, signs)
+    want = []
+    for s in range(S):
+        whole.reset()
+        tok, row = first[s], []
+        for pos in range(T):
+            tok = whole.token(tok, pos)
+            row.append(tok)
+        want.append(row)
+    whole.close()
+    half = hp.vocab // 2
+    assert half % 128 == 0
+    a = Model(ctx, synth.tiny(n_streams=S, block_begin=0, block_end=2, batch_cols=4), tensors, signs, head_rows=(0, half))
+    b = Model(ctx, synth.tiny(n_streams=S, block_begin=2, block_end=4, batch_cols=4), tensors, signs, head_rows=(half, hp.vocab))
+    with pytest.raises(BonsaiError, match="128-row"):
+        Model(ctx, synth.tiny(n_streams=S, batch_cols=4), tensors, signs, head_rows=(64, hp.vocab))
+    a.stage_prepare(0, S); b.stage_prepare(0, S)
+    hid, fin = ctx.alloc(S * hp.hidden * 4), ctx.alloc(S * hp.hidden * 4)
+    cands, tokb = ctx.alloc(2 * S * 8), ctx.alloc(S * 4)
+    with pytest.raises(BonsaiError, match="sharded output head"):
+        a.stage(0, 1, 0, None, hid)
+    got = [[] for _ in range(S)]
+    for step in range(T):
+        a.stage_batch(0, first if step == 0 else None, [step] * S, None if step == 0 else tokb, hid)
+        b.stage_batch(0, None, [step] * S, hid, fin)          # last stage: hidden state out, not picks
+        a.head_batch(S, fin, cands, out_off=0)
+        b.head_batch(S, fin, cands, out_off=S * 8)
+        a.pick_batch(S, 2, cands, tokb)
+        ctx.sync()
+        picks = tokb.download(np.int32, S)
+        for s in range(S):
+            got[s].append(int(picks[s]))
+    assert got == want
+    # the candidates of the last step: each shard's row lies in its own range, and one of them is the pick
+    c = cands.download(np.int32, 2 * S * 2).reshape(2, S, 2)
+    assert np.all((c[0, :, 1] >= 0) & (c[0, :, 1] < half)) and np.all((c[1, :, 1] >= half) & (c[1, :, 1] < hp.vocab))
+    a.close(); b.close()
+    for x in (hid, fin, cands, tokb):
+        x.free()
