@@ -170,11 +170,12 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     import torch
     import torch.distributed as dist
     from bonsai_vk_b200 import Context, Model, synth
-    from bonsai_vk_b200.pipeline import Pipeline, split_blocks
+    from bonsai_vk_b200.pipeline import Pipeline, ShardedHeadPipeline, split_blocks, split_head_rows
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     fwd, back = dist.new_group(list(range(world))), dist.new_group(list(range(world)))
     S, CTX = 64, 8192
+    sharded = a.head == "sharded"
     # micro-batch = sequences that move through the stages together (one pass of the tensor-core projection kernel
     # reads the stage's weights once for all of them). Default: as many micro-batches as stages (32 / 16 / 8 sequences on 2 / 4 / 8 GPUs).
     MB = a.microbatch if a.microbatch > 0 else max(1, min(32, S // world))
@@ -185,6 +186,13 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     bb = [48_923_392 if b % 4 != 3 else 45_910_016 for b in range(32)]
     b0, b1 = split_blocks(32, world, a.balance, block_bytes=bb, head_bytes=222_494_720)[rank]
     ctx = Context(local)
+    # the same load on ONE GPU, measured by rank 0 on this box before the pipeline starts: the base of the scaling figure
+    # (the N = 1 headline line of this file is a different metric, single-sequence decode)
+    base1 = None
+    if rank == 0 and not a.no_base:
+        base1 = streams64_one_gpu(ctx)
+        ctx.sync()
+    dist.barrier()
     # one explicit (non-default) stream for our kernels and, through torch, for the NCCL dependencies: the legacy
     # default stream cannot be captured into the per-stream stage graphs
     work_stream = torch.cuda.Stream(device=local)
@@ -192,7 +200,7 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     ctx.use_stream(work_stream.cuda_stream)
     hp = synth.HParams(cap=CTX, n_streams=S, block_begin=b0, block_end=b1, batch_cols=MB if MB > 1 else 0)
     tensors, signs = build_full_model(hp)
-    m = Model(ctx, hp, tensors, signs)
+    m = Model(ctx, hp, tensors, signs, head_rows=split_head_rows(hp.vocab, world)[rank] if sharded else None)
     del tensors
     total = 2 * (K + Wm) + 8
     pos0 = [CTX - total - 1] * U
@@ -209,6 +217,11 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
             m.stage_batch(u * MB, [1] * MB if rank == 0 else None, [pos0[u]] * MB, None if rank == 0 else scratch_in, scratch_out)
         else:
             m.stage(u, 1 if rank == 0 else 0, pos0[u], None if rank == 0 else scratch_in, scratch_out)
+    if sharded:                  # first use of the head kernels, also before any NCCL kernel is in flight
+        warm_c, warm_t = ctx.alloc(world * MB * 8), ctx.alloc(MB * 4)
+        warm_c.memset(0)
+        m.head_batch(MB, scratch_out, warm_c)
+        m.pick_batch(MB, world, warm_c, warm_t)
     torch.cuda.synchronize()
     m.reset()
     for s in range(S):
@@ -233,8 +246,22 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
         else:
             m.stage(u, 0, pos, wrap(hin), wrap(out))
 
-    pipe = Pipeline(dist, rank, world, U, stage, lambda: torch.zeros(MB * hp.hidden, dtype=torch.float32, device=dev),
-                    lambda: torch.zeros(MB, dtype=torch.int32, device=dev), fwd, back)
+    if sharded:
+        assert MB > 1, "the sharded head belongs to the multi-sequence pass"
+
+        def head_fn(u, hfin, cand):
+            m.head_batch(MB, wrap(hfin), wrap(cand))
+
+        def pick_fn(u, allc, tok):
+            m.pick_batch(MB, world, wrap(allc), wrap(tok))
+
+        pipe = ShardedHeadPipeline(dist, rank, world, U, stage, head_fn, pick_fn,
+                                   lambda: torch.zeros(MB * hp.hidden, dtype=torch.float32, device=dev),
+                                   lambda: torch.zeros(MB, dtype=torch.int32, device=dev),
+                                   lambda n: torch.zeros(n * MB * 2, dtype=torch.float32, device=dev), fwd, back)
+    else:
+        pipe = Pipeline(dist, rank, world, U, stage, lambda: torch.zeros(MB * hp.hidden, dtype=torch.float32, device=dev),
+                        lambda: torch.zeros(MB, dtype=torch.int32, device=dev), fwd, back)
     toks = [int(t) for t in np.random.default_rng(42).integers(0, hp.vocab, size=S)]
     first = [toks[u * MB:(u + 1) * MB] for u in range(U)] if MB > 1 else toks
 
@@ -264,11 +291,16 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     e2e = S * K / (ms_e2e / 1000.0)
     cfg = dict(base["config"], workload=f"config 4: 9B-shape synthetic model layer-pipelined over {world} GPUs "
                f"({b1 - b0} blocks per stage), 64 concurrent sequences at context {CTX} (KV marked filled) in {U} micro-batches "
-               f"of {MB}, greedy decode", parallelism=f"pp{world}", streams=S, context=CTX, microbatch=MB, balance=a.balance)
+               f"of {MB}, greedy decode; output head " + ("sharded by rows over the stages" if sharded else "on the last stage"),
+               parallelism=f"pp{world}", streams=S, context=CTX, microbatch=MB, balance=a.balance, head=a.head)
     line = dict(base, metric="decode tok/s, 9B ternary (PTQ1_0), 64 streams pipelined", config=cfg, value=tok_s,
                 ms_per_step=ms_dev / K, clocks=clocks, gpu_launches=int(launches),
                 e2e={"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4 * S})
     if rank == 0:
+        if base1 is not None:
+            # the driver's own efficiency divides by the N = 1 headline (another metric); this is the like-for-like figure
+            line["scaling_base"] = base1
+            line["scaling_efficiency_vs_base"] = tok_s / (world * base1["value"])
         peak, which = peaks()
         # per GPU and step: every micro-batch reads the stage's weights once; every sequence its own state and KV
         w_stage = (PTQ_BYTES_PER_TOKEN - 222_494_720) / world
@@ -291,6 +323,9 @@ def main():
     ap.add_argument("--prompt", type=int, default=16, help="prompt length in tokens (16 = the benchmark config)")
     ap.add_argument("--balance", default="equal", choices=["equal", "bytes"],
                     help="N > 1: stage split - equal block counts (the benchmark configuration) or byte-balanced with the head on the last stage")
+    ap.add_argument("--head", default="sharded", choices=["sharded", "last"],
+                    help="N > 1: output head sharded by rows over all stages (default) or whole on the last stage")
+    ap.add_argument("--no-base", dest="no_base", action="store_true", help="N > 1: skip the one-GPU 64-stream base measurement")
     ap.add_argument("--microbatch", type=int, default=0, help="N > 1: sequences per micro-batch (0 = 64 / GPUs, at most 32; 1 = one sequence per pass)")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

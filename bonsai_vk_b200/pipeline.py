@@ -125,3 +125,101 @@ class Pipeline:
             return None
         # one int per step for a single sequence, a list of ints per step for a micro-batch of sequences
         return [[int(t.item()) if t.numel() == 1 else [int(v) for v in t.tolist()] for t in row] for row in self.picks]
+
+
+def split_head_rows(vocab: int, world: int, tile: int = 128) -> List[Tuple[int, int]]:
+    """Row ranges of the output head per stage for the sharded head: whole 128-row tiles, as equal as they come,
+    ascending with the stage number (the pick over the shards relies on that order for ties)."""
+    tiles = (vocab + tile - 1) // tile
+    if world < 1 or world > tiles:
+        raise ValueError(f"cannot split {tiles} head tiles over {world} stages")
+    base, extra = divmod(tiles, world)
+    out, t = [], 0
+    for r in range(world):
+        n = base + (1 if r < extra else 0)
+        out.append((t * tile, min(vocab, (t + n) * tile)))
+        t += n
+    return out
+
+
+class ShardedHeadPipeline:
+    """The same ring of stages with the output head spread over all of them (the reference charges the whole head to the
+    last GPU of its split, runtime_vk/gpu_fleet.h:1013-1020, which makes that stage the long one at 4 blocks per GPU).
+
+    Every stage, the last included, hands on a hidden state. For unit (micro-batch) instance m = step * units + u:
+      1. the last stage broadcasts the final hidden state of m to every rank        (collective on `head_group`)
+      2. every rank runs its rows of the head on it: head_fn(u, hidden, cand_out)   -> (value, row) per sequence
+      3. the candidates are gathered on every rank                                   (collective on `head_group`)
+      4. rank 0 picks: pick_fn(u, all_cands, tok_out) - the token that enters its stage for u at the next step.
+    A rank does the head work of instance m right after its own stage work of instance m + lag, lag = min(world - 1 - rank,
+    units - 1): that is the moment the last stage finishes m when every stage takes the same time, so nobody waits long,
+    rank 0 has the token before it needs it (units >= 1 suffices), and because the lag does not grow with the rank every
+    rank reaches collective m without needing anything a later collective would provide - the schedule cannot deadlock
+    even on a backend whose collectives block the host.
+
+    stage_fn(u, step, pos, tok_first, tok_in, hidden_in, hidden_out); picks are collected on rank 0."""
+
+    def __init__(self, dist, rank: int, world: int, n_units: int, stage_fn: Callable, head_fn: Callable, pick_fn: Callable,
+                 new_hidden: Callable, new_token: Callable, new_cand: Callable, fwd_group=None, head_group=None):
+        self.dist, self.rank, self.world, self.U = dist, rank, world, n_units
+        self.stage_fn, self.head_fn, self.pick_fn = stage_fn, head_fn, pick_fn
+        self.first, self.last = rank == 0, rank == world - 1
+        self.fwd, self.head = fwd_group, head_group
+        self.lag = min(world - 1 - rank, n_units - 1)
+        self.h_in = [new_hidden() for _ in range(n_units)] if not self.first else None
+        self.h_out = [new_hidden() for _ in range(n_units)] if not self.last else None
+        self.h_fin = [new_hidden() for _ in range(n_units)]
+        self.cand = [new_cand(1) for _ in range(n_units)]
+        self.cands_all = [new_cand(world) for _ in range(n_units)]
+        self.t_in = [new_token() for _ in range(n_units)] if self.first else None
+        self.picks: List[list] = [[] for _ in range(n_units)]
+
+    def _head_work(self, m: int, collect: bool):
+        d, u, P = self.dist, m % self.U, self.world
+        if P > 1:
+            d.broadcast(self.h_fin[u], src=P - 1, group=self.head, async_op=True).wait()
+        self.head_fn(u, self.h_fin[u], self.cand[u])
+        if P > 1:
+            rows = list(self.cands_all[u].view(P, -1).unbind(0))
+            d.all_gather(rows, self.cand[u].view(-1), group=self.head, async_op=True).wait()
+        else:
+            self.cands_all[u].copy_(self.cand[u])
+        if self.first:
+            self.pick_fn(u, self.cands_all[u], self.t_in[u])
+            if collect:
+                self.picks[u].append(self.t_in[u].clone())
+
+    def run(self, first_tokens, pos0, n_steps: int, collect: bool = True):
+        d, U, P = self.dist, self.U, self.world
+        N = n_steps * U
+        send_h = [None] * U
+        for n in range(N):
+            step, u = divmod(n, U)
+            pos = pos0[u] + step
+            tok_in, hin = None, None
+            if self.first:
+                if step > 0:
+                    tok_in = self.t_in[u]
+            else:
+                d.irecv(self.h_in[u], src=self.rank - 1, group=self.fwd).wait()
+                hin = self.h_in[u]
+            if self.last:
+                out = self.h_fin[u]
+            else:
+                if send_h[u] is not None:
+                    send_h[u].wait()            # the previous message of this unit has left the buffer
+                    send_h[u] = None
+                out = self.h_out[u]
+            self.stage_fn(u, step, pos, first_tokens[u] if (self.first and step == 0) else None, tok_in, hin, out)
+            if not self.last:
+                send_h[u] = d.isend(out, dst=self.rank + 1, group=self.fwd)
+            if n - self.lag >= 0:
+                self._head_work(n - self.lag, collect)
+        for m in range(max(0, N - self.lag), N):
+            self._head_work(m, collect)
+        for h in send_h:
+            if h is not None:
+                h.wait()
+        if not (self.first and collect):
+            return None
+        return [[int(t.item()) if t.numel() == 1 else [int(v) for v in t.tolist()] for t in row] for row in self.picks]

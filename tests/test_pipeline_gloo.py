@@ -174,3 +174,97 @@ def test_micro_batched_schedule_on_gloo(tmp_path):
                 p.kill()
     assert all(p.returncode == 0 for p in procs), outs
     assert "PIPELINE_OK" in outs[-1]
+
+
+def test_head_rows_split():
+    from bonsai_vk_b200.pipeline import split_head_rows
+    r = split_head_rows(248320, 8)
+    assert r[0][0] == 0 and r[-1][1] == 248320 and all(r[i][1] == r[i + 1][0] for i in range(7))
+    assert all(a % 128 == 0 for a, _ in r) and max(b - a for a, b in r) - min(b - a for a, b in r) <= 128
+    assert split_head_rows(2048, 1) == [(0, 2048)]
+    assert split_head_rows(1000, 2) == [(0, 512), (512, 1000)]
+    with pytest.raises(ValueError):
+        split_head_rows(256, 3)
+
+
+WORKER_SH = textwrap.dedent('''
+    import os, sys, torch, torch.distributed as dist
+    sys.path.insert(0, os.environ["BONSAI_ROOT"])
+    from bonsai_vk_b200.pipeline import ShardedHeadPipeline
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    fwd, head = dist.new_group(list(range(world))), dist.new_group(list(range(world)))
+    U, MB, T, H, V = int(os.environ["UNITS"]), 2, 5, 8, 96
+    rows = V // world                      # rank r holds "head rows" [r * rows, (r + 1) * rows)
+    def logits(h):                         # a stand-in head: V rows from one hidden vector
+        return torch.stack([(h * ((v % 7) + 1)).sum() % 11 for v in range(V)])
+    def stage(u, step, pos, tok_first, tok_in, hin, out):
+        if rank == 0:
+            toks = tok_first if tok_first is not None else [int(v) for v in tok_in.tolist()]
+            h = torch.stack([torch.arange(H, dtype=torch.float32) * (t + 1) + pos + c for c, t in enumerate(toks)]).reshape(-1)
+        else:
+            h = hin.clone()
+        out.copy_(h * 1.5 + (rank + 1))
+    def head_fn(u, hfin, cand):
+        for c in range(MB):
+            lg = logits(hfin.view(MB, H)[c])[rank * rows:(rank + 1) * rows]
+            i = int(torch.argmax(lg))                     # first maximum within the shard
+            cand.view(MB, 2)[c, 0] = lg[i]
+            cand.view(MB, 2)[c, 1] = float(rank * rows + i)
+    def pick_fn(u, allc, tok):
+        a = allc.view(world, MB, 2)
+        for c in range(MB):
+            best, idx = -1e30, 2 ** 31 - 1
+            for s in range(world):
+                v, i = float(a[s, c, 0]), int(a[s, c, 1])
+                if v > best or (v == best and i < idx):
+                    best, idx = v, i
+            tok[c] = idx
+    p = ShardedHeadPipeline(dist, rank, world, U, stage, head_fn, pick_fn, lambda: torch.zeros(MB * H),
+                            lambda: torch.zeros(MB, dtype=torch.int32), lambda n: torch.zeros(n * MB * 2), fwd, head)
+    first = [[3 + u * MB + c for c in range(MB)] for u in range(U)]
+    picks = p.run(first, [10 * u for u in range(U)], T)
+    if rank == 0:
+        want = []
+        for u in range(U):
+            toks, row = list(first[u]), []
+            for step in range(T):
+                nxt = []
+                for c, tok in enumerate(toks):
+                    h = torch.arange(H, dtype=torch.float32) * (tok + 1) + (10 * u + step) + c
+                    for r in range(world):
+                        h = h * 1.5 + (r + 1)
+                    nxt.append(int(torch.argmax(logits(h))))
+                toks = nxt
+                row.append(nxt)
+            want.append(row)
+        assert picks == want, (picks, want)
+        print("PIPELINE_OK")
+    dist.barrier()
+    dist.destroy_process_group()
+''')
+
+
+@pytest.mark.parametrize("world,units", [(2, 2), (3, 3), (3, 5), (3, 1)])
+def test_sharded_head_schedule_on_gloo(world, units, tmp_path):
+    """The ring with the output head spread over the stages: broadcast of the final hidden state, per-rank candidates,
+    gather, pick on rank 0 - as gloo ranks with blocking collectives (the schedule must not deadlock), with as many
+    units as stages, more, and fewer."""
+    script = tmp_path / "worker_sh.py"
+    script.write_text(WORKER_SH)
+    with socket.socket() as sck:
+        sck.bind(("127.0.0.1", 0))
+        port = sck.getsockname()[1]
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   BONSAI_ROOT=ROOT, UNITS=str(units))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    try:
+        outs = [p.communicate(timeout=180)[0] for p in procs]
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+    assert all(p.returncode == 0 for p in procs), outs
+    assert "PIPELINE_OK" in outs[0]
