@@ -91,9 +91,9 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-def build_full_model(hp, seed=0):
+def build_full_model(hp, seed=0, head_everywhere=False):
     from bonsai_vk_b200 import synth
-    return synth.make_model_repeated(hp, seed)
+    return synth.make_model_repeated(hp, seed, head_everywhere)
 
 
 def cpu_gemv_tokens_per_s(seconds=12.0, threads=None):
@@ -199,7 +199,7 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     torch.cuda.set_stream(work_stream)
     ctx.use_stream(work_stream.cuda_stream)
     hp = synth.HParams(cap=CTX, n_streams=S, block_begin=b0, block_end=b1, batch_cols=MB if MB > 1 else 0)
-    tensors, signs = build_full_model(hp)
+    tensors, signs = build_full_model(hp, head_everywhere=sharded)
     m = Model(ctx, hp, tensors, signs, head_rows=split_head_rows(hp.vocab, world)[rank] if sharded else None)
     del tensors
     total = 2 * (K + Wm) + 8

@@ -135,11 +135,12 @@ def make_model(hp: HParams, seed: int = 0):
     return tensors, make_signs(hp, seed)
 
 
-def make_model_repeated(hp: HParams, seed: int = 0):
+def make_model_repeated(hp: HParams, seed: int = 0, head_everywhere: bool = False):
     """Seeded synthetic tensors of a large shape, quickly: generating 8.9e9 trits in numpy takes minutes, so one
     GDN block, one attention block and one FFN set are generated and reused for every block, and the two
     vocab-sized tensors tile a 16384-row chunk. Timing depends on shapes and bytes, not on values. Only the
-    tensors of the local blocks [block_begin, block_end) are produced."""
+    tensors of the local blocks [block_begin, block_end) are produced (head_everywhere: the output head and its norm
+    too, whatever the block range - every stage holds a slice of a sharded head)."""
     cache, tensors = {}, {}
     b0, b1 = hp.block_begin, (hp.block_end or hp.n_layer)
     for name, spec in tensor_shapes(hp).items():
@@ -149,7 +150,7 @@ def make_model_repeated(hp: HParams, seed: int = 0):
             key = name.split(".", 2)[-1]
         else:
             key = name
-            if (name == "token_embd.weight" and b0 != 0) or (name != "token_embd.weight" and b1 != hp.n_layer):
+            if (name == "token_embd.weight" and b0 != 0) or (name != "token_embd.weight" and b1 != hp.n_layer and not head_everywhere):
                 continue
         if key in ("token_embd.weight", "output.weight"):
             if "vocab" not in cache:
