@@ -53,8 +53,42 @@ def layer_type_kv(hp: synth.HParams, spelling: str) -> list[bytes]:
     return out
 
 
+def byte_image() -> list[str]:
+    """The printable stand-in of every byte that byte-level BPE vocabularies use (the GPT-2 table): bytes 33..126,
+    161..172 and 174..255 stand for themselves, the others are moved to code points 256, 257, ... in byte order."""
+    keep = list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256))
+    out, extra = {}, 0
+    for b in range(256):
+        if b in keep:
+            out[b] = chr(b)
+        else:
+            out[b] = chr(256 + extra)
+            extra += 1
+    return [out[b] for b in range(256)]
+
+
+def toy_tokenizer(vocab: int, words=("hello", "world", "the")) -> tuple[list[str], list[str]]:
+    """A small byte-level BPE vocabulary for tests: ids 0..255 are the single bytes (so any text can be encoded),
+    then the merge products that build each of `words` left to right, then fillers. Returns (tokens, merges)."""
+    img = byte_image()
+    tokens = list(img)
+    merges = []
+    for w in words:
+        cur = img[ord(w[0])]
+        for ch in w[1:]:
+            nxt = img[ord(ch)]
+            if f"{cur} {nxt}" not in merges:
+                merges.append(f"{cur} {nxt}")
+            cur = cur + nxt
+            if cur not in tokens:
+                tokens.append(cur)
+    assert len(tokens) <= vocab
+    tokens += [f"<filler{i}>" for i in range(len(tokens), vocab)]
+    return tokens, merges
+
+
 def metadata(hp: synth.HParams, signs: np.ndarray, hat_version: int = 1, names: list[str] | None = None,
-             layer_spelling: str | None = None, extra_kv: list[bytes] | None = None) -> list[bytes]:
+             layer_spelling: str | None = None, extra_kv: list[bytes] | None = None, tokenizer=None) -> list[bytes]:
     A = ARCH + "."
     if layer_spelling is None:
         layer_spelling = "interval" if hp.attn_interval > 0 else "list"
@@ -78,8 +112,10 @@ def metadata(hp: synth.HParams, signs: np.ndarray, hat_version: int = 1, names: 
         kv_u32(A + "ssm.inner_size", hp.gdn_heads * hp.gdn_dim),
         kv_f32(A + "attention.layer_norm_rms_epsilon", hp.rms_eps),
         kv_f32(A + "rope.freq_base", hp.rope_base),
-        kv_arr_str("tokenizer.ggml.tokens", [f"<{i}>" for i in range(hp.vocab)]),
+        kv_arr_str("tokenizer.ggml.tokens", tokenizer[0] if tokenizer else [f"<{i}>" for i in range(hp.vocab)]),
     ]
+    if tokenizer:
+        kv += [kv_str("tokenizer.ggml.model", "gpt2"), kv_arr_str("tokenizer.ggml.merges", tokenizer[1])]
     if hat_version is not None:
         kv.append(kv_u32("prism.hadamard.version", hat_version))
         kv += [
@@ -94,14 +130,14 @@ def metadata(hp: synth.HParams, signs: np.ndarray, hat_version: int = 1, names: 
 
 def write(path: str, hp: synth.HParams, seed: int = 0, hat_version: int | None = 1, shuffle: bool = False,
           override_dtype: dict[str, int] | None = None, layer_spelling: str | None = None,
-          extra_kv: list[bytes] | None = None) -> dict:
+          extra_kv: list[bytes] | None = None, tokenizer=None) -> dict:
     """Write a synthetic model. Tensors are generated one at a time (the 9B shape never sits in memory whole).
     shuffle=True stores the tensors in name-sorted order (as real checkpoints do) instead of layer order.
     Returns {"tensors": n, "bytes": file size}."""
     shapes = synth.tensor_shapes(hp)
     names = sorted(shapes) if shuffle else list(shapes)
     signs = synth.make_signs(hp, seed)
-    kv = metadata(hp, signs, hat_version, layer_spelling=layer_spelling, extra_kv=extra_kv)
+    kv = metadata(hp, signs, hat_version, layer_spelling=layer_spelling, extra_kv=extra_kv, tokenizer=tokenizer)
     recs, off = [], 0
     for n in names:
         spec = shapes[n]

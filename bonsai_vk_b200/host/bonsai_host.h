@@ -59,22 +59,27 @@ private:
     bool ok_ = true;
 };
 
-inline bool read_scalar(Reader &r, uint32_t ty, int64_t &iv, double &fv, std::string &sv) {
-    switch (ty) {
-        case 0: iv = r.get<uint8_t>(); break;
-        case 1: iv = r.get<int8_t>(); break;
-        case 2: iv = r.get<uint16_t>(); break;
-        case 3: iv = r.get<int16_t>(); break;
-        case 4: iv = r.get<uint32_t>(); break;
-        case 5: iv = r.get<int32_t>(); break;
-        case 6: fv = r.get<float>(); break;
-        case 7: iv = r.get<uint8_t>(); break;
-        case 8: sv = r.str(); break;
-        case 10: iv = int64_t(r.get<uint64_t>()); break;
-        case 11: iv = r.get<int64_t>(); break;
-        case 12: fv = r.get<double>(); break;
-        default: return false;
-    }
+// One GGUF metadata value. The fixed-width kinds are described by a table (bytes, signed, floating) and read in one
+// place; strings are length-prefixed. Type numbers are the GGUF specification's (0..12, 9 = array).
+struct Value { int64_t i = 0; double f = 0; std::string s; bool is_float = false, is_string = false; };
+inline bool read_value(Reader &r, uint32_t ty, Value &v) {
+    struct Kind { int bytes; bool sign, flt; };
+    static const Kind kinds[13] = {{1, false, false}, {1, true, false}, {2, false, false}, {2, true, false}, {4, false, false}, {4, true, false},
+                                   {4, true, true}, {1, false, false}, {0, false, false}, {-1, false, false}, {8, false, false}, {8, true, false},
+                                   {8, true, true}};
+    if (ty > 12 || kinds[ty].bytes < 0) return false;
+    v = Value();
+    if (ty == 8) { v.s = r.str(); v.is_string = true; return r.ok(); }
+    const Kind k = kinds[ty];
+    uint64_t raw = 0;
+    for (int b = 0; b < k.bytes; ++b) raw |= uint64_t(r.get<uint8_t>()) << (8 * b);      // little endian
+    if (k.flt) {
+        v.is_float = true;
+        if (k.bytes == 4) { uint32_t w = uint32_t(raw); float x; memcpy(&x, &w, 4); v.f = x; } else memcpy(&v.f, &raw, 8);
+    } else if (k.sign && k.bytes < 8) {
+        const int sh = 64 - 8 * k.bytes;
+        v.i = int64_t(raw << sh) >> sh;
+    } else v.i = int64_t(raw);
     return r.ok();
 }
 
@@ -93,48 +98,70 @@ inline uint64_t tensor_bytes(const Tensor &t, std::string &why) {
 inline bool gguf_load(const char *path, Gguf &g, std::string &why) {
     FILE *f = fopen(path, "rb");
     if (!f) { why = std::string("cannot open ") + path; return false; }
+    struct Closer { FILE *f; ~Closer() { fclose(f); } } closer{f};
+    fseek(f, 0, SEEK_END);
+    const uint64_t file_size = uint64_t(ftell(f));
+    fseek(f, 0, SEEK_SET);
     Reader r(f);
     char magic[4] = {};
-    if (fread(magic, 1, 4, f) != 4 || memcmp(magic, "GGUF", 4) != 0) { why = std::string(path) + " is not a GGUF file"; fclose(f); return false; }
+    if (fread(magic, 1, 4, f) != 4 || memcmp(magic, "GGUF", 4) != 0) { why = std::string(path) + " is not a GGUF file"; return false; }
     g.version = r.get<uint32_t>();
     const uint64_t n_tensors = r.get<uint64_t>(), n_kv = r.get<uint64_t>();
-    if (!r.ok() || n_tensors > (1u << 20) || n_kv > (1u << 20)) { why = "truncated or implausible GGUF header"; fclose(f); return false; }
+    if (!r.ok() || n_tensors > (1u << 20) || n_kv > (1u << 20)) { why = "truncated or implausible GGUF header"; return false; }
+    // metadata: scalars by kind into ki / kf / ks, arrays into ai / as. An array cannot hold more elements than the file
+    // has bytes left: a corrupt count is refused before anything is allocated for it.
     for (uint64_t i = 0; i < n_kv; ++i) {
         const std::string key = r.str();
         const uint32_t ty = r.get<uint32_t>();
+        if (!r.ok()) { why = "truncated GGUF metadata"; return false; }
         if (ty == 9) {
             const uint32_t et = r.get<uint32_t>();
             const uint64_t n = r.get<uint64_t>();
-            if (et == 8) { auto &v = g.as[key]; v.resize(n); for (auto &s : v) s = r.str(); }
-            else {
-                auto &v = g.ai[key]; v.resize(n);
-                for (auto &x : v) { int64_t iv = 0; double fv = 0; std::string sv; if (!read_scalar(r, et, iv, fv, sv)) { why = "bad array element type in " + key; fclose(f); return false; } x = (et == 6 || et == 12) ? int64_t(fv) : iv; }
+            if (!r.ok() || n > file_size - std::min<uint64_t>(file_size, uint64_t(ftell(f)))) { why = "array " + key + " is longer than the file"; return false; }
+            if (et == 8) {
+                std::vector<std::string> &dst = g.as[key];
+                dst.reserve(n);
+                for (uint64_t k = 0; k < n && r.ok(); ++k) dst.push_back(r.str());
+            } else {
+                std::vector<int64_t> &dst = g.ai[key];
+                dst.reserve(n);
+                Value v;
+                for (uint64_t k = 0; k < n; ++k) {
+                    if (!read_value(r, et, v) || v.is_string) { why = "bad array element type in " + key; return false; }
+                    dst.push_back(v.is_float ? int64_t(v.f) : v.i);
+                }
             }
         } else {
-            int64_t iv = 0; double fv = 0; std::string sv;
-            if (!read_scalar(r, ty, iv, fv, sv)) { why = "bad value type for key " + key; fclose(f); return false; }
-            if (ty == 8) g.ks[key] = sv; else if (ty == 6 || ty == 12) g.kf[key] = fv; else g.ki[key] = iv;
+            Value v;
+            if (!read_value(r, ty, v)) { why = "bad value type for key " + key; return false; }
+            if (v.is_string) g.ks[key] = v.s; else if (v.is_float) g.kf[key] = v.f; else g.ki[key] = v.i;
         }
-        if (!r.ok()) { why = "truncated GGUF metadata at key " + key; fclose(f); return false; }
+        if (!r.ok()) { why = "truncated GGUF metadata at key " + key; return false; }
     }
+    g.tensors.reserve(n_tensors);
     for (uint64_t i = 0; i < n_tensors; ++i) {
         Tensor t;
         t.name = r.str();
         t.n_dims = r.get<uint32_t>();
-        if (t.n_dims > 4) { why = "tensor " + t.name + " has more than 4 dims"; fclose(f); return false; }
+        if (!r.ok() || t.n_dims > 4) { why = "tensor table: entry " + std::to_string(i) + " (" + t.name + ") is truncated or has more than 4 dims"; return false; }
         for (uint32_t k = 0; k < t.n_dims; ++k) t.d[k] = r.get<uint64_t>();
         t.dtype = r.get<uint32_t>();
         t.off = r.get<uint64_t>();
-        if (!r.ok()) { why = "truncated GGUF tensor table"; fclose(f); return false; }
+        if (!r.ok()) { why = "truncated GGUF tensor table"; return false; }
         t.bytes = tensor_bytes(t, why);
-        if (!t.bytes) { fclose(f); return false; }
+        if (!t.bytes) return false;
         g.tensors.push_back(t);
     }
-    auto it = g.ki.find("general.alignment");
-    if (it != g.ki.end() && it->second > 0) g.alignment = uint32_t(it->second);
-    const uint64_t pos = uint64_t(ftell(f));
-    g.data_start = (pos + g.alignment - 1) / g.alignment * g.alignment;
-    fclose(f);
+    const auto al = g.ki.find("general.alignment");
+    if (al != g.ki.end() && al->second > 0) g.alignment = uint32_t(al->second);
+    const uint64_t table_end = uint64_t(ftell(f));
+    g.data_start = (table_end + g.alignment - 1) / g.alignment * g.alignment;
+    // every tensor's bytes must lie inside the file (a truncated download otherwise shows up as a short read mid-load)
+    for (const Tensor &t : g.tensors)
+        if (t.off > file_size || t.bytes > file_size - t.off || g.data_start > file_size - t.off - t.bytes) {
+            why = "tensor " + t.name + " lies outside the file (" + std::to_string(file_size) + " bytes): truncated GGUF";
+            return false;
+        }
     return true;
 }
 

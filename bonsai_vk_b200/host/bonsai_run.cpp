@@ -1,15 +1,20 @@
 // bonsai_run - command-line host for the decode path on one B200.
 //
-//   bonsai_run <model.gguf> info                 metadata, contract and tensor census; no GPU work
-//   bonsai_run <model.gguf> run [n_gen]          prefill BONSAI_PROMPT_IDS, then n_gen greedy tokens (default 48)
+//   bonsai_run run [model.gguf] [chunk_MiB=32] [n_tokens=24] [-- "prompt"]     the reference's own grammar
+//                                                (bonsai_vk.exe run ..., runtime_vk/bonsai_forward.h:3086-3093)
+//   bonsai_run info [model.gguf]                 metadata, contract and tensor census; no GPU work
+//   bonsai_run <model.gguf> info | run [n_gen]   the earlier spelling, kept
+//
+// chunk_MiB is the size of the pinned staging buffers of the loader (the reference's upload chunk). The prompt is
+// taken as token ids from BONSAI_PROMPT_IDS: the tokenizer and the chat template stay on the reference's side of
+// the boundary (its Bpe / chat::render feed ids into bn_model_token unchanged), so a text prompt given after "--" or
+// in BONSAI_PROMPT is refused with that explanation unless BONSAI_PROMPT_IDS accompanies it.
 //
 // Behaviour mirrors the reference engine's `run` mode (runtime_vk/bonsai_forward.h:2645-3000 fwd_run,
 // :3240-3300 fwd_main): hyper-parameters only from GGUF metadata, the rotation gate before any GPU work
 // (exit 6), capacity checks (exit 4), context-fit guard (exit 7), the bitwise lineage gate behind
 // BONSAI_QCHECK=1 (exit 6, "REFUSING TO GENERATE"), and the same report lines
 // ("... generated tokens in ... ms  ->  ... tok/s", "steady-state: ... ms/token", "gate: PASS (bitmask 0 = ...)").
-// The tokenizer and chat template stay on the host side of the boundary and are not part of this tool: the
-// prompt is given as token ids.
 //
 // Environment: BONSAI_PROMPT_IDS (comma separated ids; default "1,2,3,4,5,6,7,8"), BONSAI_CAP (KV capacity in
 // positions, even; default 4096), BONSAI_QCHECK=1 (run the gate after the prefill), BONSAI_DEVICE (CUDA ordinal),
@@ -19,6 +24,7 @@
 #include <chrono>
 #include <cmath>
 #include <cstdlib>
+#include <cstring>
 
 namespace {
 
@@ -93,12 +99,21 @@ int lineage_gate(bh::Engine &e, const bh::Gguf &g, const char *path, const std::
 }  // namespace
 
 int main(int argc, char **argv) {
-    if (argc < 3) {
-        fprintf(stderr, "usage: %s <model.gguf> info | run [n_gen]\n", argv[0]);
+    if (argc < 2) {
+        fprintf(stderr, "usage: %s run [model.gguf] [chunk_MiB] [n_tokens] [-- \"prompt\"] | info [model.gguf] | <model.gguf> info | <model.gguf> run [n_gen]\n", argv[0]);
         return 2;
     }
-    const char *path = argv[1];
-    const std::string mode = argv[2];
+    // everything after "--" is the prompt text and not a positional argument
+    int npos = argc;
+    std::string text_prompt;
+    for (int i = 1; i < argc; ++i) if (!strcmp(argv[i], "--")) { npos = i; if (i + 1 < argc) text_prompt = argv[i + 1]; break; }
+    if (const char *p = getenv("BONSAI_PROMPT")) text_prompt = p;
+    const bool ref_grammar = !strcmp(argv[1], "run") || !strcmp(argv[1], "info");
+    const char *path = ref_grammar ? (npos > 2 ? argv[2] : "models/Ternary-Bonsai-2-9B-PTQ1_0.gguf") : argv[1];
+    if (!ref_grammar && npos < 3) { fprintf(stderr, "usage: %s <model.gguf> info | run [n_gen]\n", argv[0]); return 2; }
+    const std::string mode = ref_grammar ? argv[1] : argv[2];
+    const long chunk_mib = ref_grammar && npos > 3 ? atol(argv[3]) : (ref_grammar ? 32 : 64);
+    const int n_default = ref_grammar ? (npos > 4 ? atoi(argv[4]) : 24) : (npos > 3 ? atoi(argv[3]) : 48);
     std::string why;
     bh::Gguf g;
     double t0 = now_ms();
@@ -126,9 +141,12 @@ int main(int argc, char **argv) {
     if (mode != "run") return fail(2, "unknown mode " + mode);
     if (prc) return fail(prc, why);                       // rotation gate and contract: before any GPU work
     if (cap <= 0 || (cap & 1)) return fail(4, "BONSAI_CAP must be a positive even number of positions");
-    const int n_gen = argc > 3 ? atoi(argv[3]) : 48;
-    if (n_gen < 1) return fail(2, "n_gen must be >= 1");
+    const int n_gen = n_default;
+    if (n_gen < 1) return fail(2, "n_tokens must be >= 1");
+    if (chunk_mib < 1 || chunk_mib > 4096) return fail(2, "chunk_MiB must be between 1 and 4096");
     const char *ids_s = getenv("BONSAI_PROMPT_IDS");
+    if (!ids_s && !text_prompt.empty())
+        return fail(2, "a text prompt needs the tokenizer, which stays on the host side of the boundary: pass the prompt's token ids in BONSAI_PROMPT_IDS");
     const std::vector<int> prompt = parse_ids(ids_s ? ids_s : "1,2,3,4,5,6,7,8");
     if (prompt.empty()) return fail(2, "BONSAI_PROMPT_IDS holds no token id");
     for (int id : prompt) if (id < 0 || id >= e.plan.hp.vocab) return fail(2, "prompt id " + std::to_string(id) + " is outside the vocabulary");
@@ -137,7 +155,7 @@ int main(int argc, char **argv) {
 
     const char *dev_s = getenv("BONSAI_DEVICE");
     if (bn_init(dev_s ? atoi(dev_s) : 0, &e.ctx)) return fail(3, bn_last_error());
-    int rc = bh::engine_load(e, path, g, 64u << 20, why);
+    int rc = bh::engine_load(e, path, g, size_t(chunk_mib) << 20, why);
     if (rc) return fail(rc, why);
     e.load_ms = now_ms() - t0;
     printf("loaded %zu tensors (%.3f GB) in %.1f ms\n", g.tensors.size(), (b_ptq + b_f32) / 1e9, e.load_ms);

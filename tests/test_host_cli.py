@@ -151,3 +151,82 @@ def test_run_with_an_explicit_layer_list(exe, tmp_path):
     assert r.returncode == 0, r.stdout + r.stderr
     assert "gate: PASS (bitmask 0 =" in r.stdout
     assert _ids(r.stdout) == want
+
+
+def test_truncated_and_corrupt_files_are_refused_with_exit_3(exe, files, tmp_path):
+    """A file cut inside the tensor data, an array count larger than the file, and a tensor offset past the end:
+    each is refused by the reader (exit 3) before any load starts."""
+    whole = open(files["ok"], "rb").read()
+    cut = tmp_path / "cut_data.gguf"
+    cut.write_bytes(whole[: len(whole) - 100_000])
+    r = run(exe, str(cut), "info")
+    assert r.returncode == 3 and "lies outside the file" in r.stderr, r.stderr
+    # the sign array's count field blown up
+    key = b"prism.hadamard.sign_values"
+    at = whole.index(key) + len(key) + 4 + 4          # key, value type (array), element type
+    big = bytearray(whole)
+    big[at:at + 8] = struct.pack("<Q", 1 << 40)
+    huge = tmp_path / "huge_array.gguf"
+    huge.write_bytes(bytes(big))
+    r = run(exe, str(huge), "info")
+    assert r.returncode == 3 and "longer than the file" in r.stderr, r.stderr
+
+
+def test_reference_run_grammar(exe, files):
+    """`run [gguf] [chunk_MiB] [n] [-- "prompt"]` (runtime_vk/bonsai_forward.h:3086-3093): positional arguments are
+    parsed in the reference's order; the checks that need no GPU answer with the same exit codes as the other spelling."""
+    r = run(exe, "info", files["ok"])
+    assert r.returncode == 0 and "layer types" in r.stdout
+    r = run(exe, "run", files["ok"], "32", "100", env={"BONSAI_CAP": "64"})
+    assert r.returncode == 7 and "generation (100)" in r.stderr
+    r = run(exe, "run", files["norot"], "32", "4")
+    assert r.returncode == 6
+    r = run(exe, "run", files["ok"], "0", "4", env={"BONSAI_CAP": "64"})
+    assert r.returncode == 2 and "chunk_MiB" in r.stderr
+    # a text prompt without ids is refused with the explanation of the seam; with ids it is accepted (and then stops at the GPU)
+    r = run(exe, "run", files["ok"], "32", "4", "--", "hello world", env={"BONSAI_CAP": "64"})
+    assert r.returncode == 2 and "BONSAI_PROMPT_IDS" in r.stderr
+    r = run(exe, "run", files["ok"], "32", "4", env={"BONSAI_CAP": "64", "BONSAI_PROMPT": "hello"})
+    assert r.returncode == 2 and "BONSAI_PROMPT_IDS" in r.stderr
+
+
+REF_BIND = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "ref_bind_run")
+
+
+@pytest.fixture(scope="module")
+def tok_file(tmp_path_factory):
+    d = tmp_path_factory.mktemp("gguf_tok")
+    hp = synth.tiny()
+    p = str(d / "tok.gguf")
+    gguf_writer.write(p, hp, seed=1, tokenizer=gguf_writer.toy_tokenizer(hp.vocab))
+    return p
+
+
+@pytest.mark.skipif(not os.path.exists(REF_BIND), reason="oracle/_ref/ref_bind_run is built only where the reference tree is present")
+def test_reference_headers_read_our_file_and_tokenise(tok_file):
+    """The reference's own gguf_load + model_plan_build (+ contract) + Bpe, compiled unmodified into ref_bind_run, accept
+    the synthetic file and tokenise a text prompt; without a GPU the run then stops at bn_init (exit 3)."""
+    r = subprocess.run([REF_BIND, tok_file, "4", "--", "hello world"], capture_output=True, text=True, timeout=120,
+                       env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    m = re.search(r"^prompt ids:(.*)$", r.stdout, re.M)
+    assert m, r.stdout + r.stderr
+    ids = [int(x) for x in m.group(1).split()]
+    toks, _ = gguf_writer.toy_tokenizer(synth.tiny().vocab)
+    img = gguf_writer.byte_image()
+    # "hello" is one merged token; " world": the space byte's stand-in, then the merged "world"
+    assert ids == [toks.index("hello"), toks.index(img[32]), toks.index("world")], ids
+    assert r.returncode == 3
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not os.path.exists(REF_BIND), reason="oracle/_ref/ref_bind_run is built only where the reference tree is present")
+def test_reference_host_and_our_host_generate_the_same_ids(exe, tok_file):
+    """Text prompt -> the reference's tokenizer -> ids -> bn_model_* (ref_bind_run), against bonsai_run fed the same ids
+    through BONSAI_PROMPT_IDS with the reference's run grammar: identical generated ids."""
+    r = subprocess.run([REF_BIND, tok_file, "12", "--", "hello world the"], capture_output=True, text=True, timeout=300,
+                       env=dict(os.environ, BONSAI_CAP="64"))
+    assert r.returncode == 0, r.stdout + r.stderr
+    prompt = re.search(r"^prompt ids:(.*)$", r.stdout, re.M).group(1).split()
+    r2 = run(exe, "run", tok_file, "32", "12", "--", "hello world the", env={"BONSAI_CAP": "64", "BONSAI_PROMPT_IDS": ",".join(prompt)})
+    assert r2.returncode == 0, r2.stdout + r2.stderr
+    assert _ids(r2.stdout) == _ids(r.stdout)
