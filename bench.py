@@ -255,10 +255,19 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
         def pick_fn(u, allc, tok):
             m.pick_batch(MB, world, wrap(allc), wrap(tok))
 
+        # BONSAI_PIPE_MARKS=1: CUDA events at the phase boundaries of every slot; per-phase device time is printed per rank
+        marks = [] if os.environ.get("BONSAI_PIPE_MARKS") else None
+
+        def mark(name):
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev, time.perf_counter()))
+
         pipe = ShardedHeadPipeline(dist, rank, world, U, stage, head_fn, pick_fn,
                                    lambda: torch.zeros(MB * hp.hidden, dtype=torch.float32, device=dev),
                                    lambda: torch.zeros(MB, dtype=torch.int32, device=dev),
-                                   lambda n: torch.zeros(n * MB * 2, dtype=torch.float32, device=dev), fwd, back)
+                                   lambda n: torch.zeros(n * MB * 2, dtype=torch.float32, device=dev), fwd, back, mark=mark)
     else:
         pipe = Pipeline(dist, rank, world, U, stage, lambda: torch.zeros(MB * hp.hidden, dtype=torch.float32, device=dev),
                         lambda: torch.zeros(MB, dtype=torch.int32, device=dev), fwd, back)
@@ -282,7 +291,20 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     timed(Wm, pos0, False)
     sampler.mark()
     p1 = [p + Wm for p in pos0]
+    if sharded and marks is not None:
+        marks.clear()
     ms_dev, launches = timed(K, p1, False)
+    if sharded and marks is not None:
+        import collections
+        acc, host = collections.defaultdict(float), collections.defaultdict(float)
+        for (n0, e0, h0), (n1, e1, h1) in zip(marks, marks[1:]):
+            acc[n1] += e0.elapsed_time(e1)
+            host[n1] += (h1 - h0) * 1e3
+        slots = max(1, sum(1 for n, _, _ in marks if n == "stage"))
+        print(f"[rank {rank}] per slot, device ms up to each mark: " + ", ".join(f"{k} {v / slots:.3f}" for k, v in acc.items())
+              + " | host ms: " + ", ".join(f"{k} {v / slots:.3f}" for k, v in host.items()), file=sys.stderr, flush=True)
+        marks.clear()
+        marks = None
     clocks = sampler.stop()
     p2 = [p + K for p in p1]
     t0 = time.perf_counter()

@@ -162,8 +162,9 @@ class ShardedHeadPipeline:
     stage_fn(u, step, pos, tok_first, tok_in, hidden_in, hidden_out); picks are collected on rank 0."""
 
     def __init__(self, dist, rank: int, world: int, n_units: int, stage_fn: Callable, head_fn: Callable, pick_fn: Callable,
-                 new_hidden: Callable, new_token: Callable, new_cand: Callable, fwd_group=None, head_group=None):
+                 new_hidden: Callable, new_token: Callable, new_cand: Callable, fwd_group=None, head_group=None, mark: Callable = None):
         self.dist, self.rank, self.world, self.U = dist, rank, world, n_units
+        self.mark = mark or (lambda name: None)        # profiling aid: called at the phase boundaries of every slot
         self.stage_fn, self.head_fn, self.pick_fn = stage_fn, head_fn, pick_fn
         self.first, self.last = rank == 0, rank == world - 1
         self.fwd, self.head = fwd_group, head_group
@@ -178,16 +179,21 @@ class ShardedHeadPipeline:
 
     def _head_work(self, m: int, collect: bool):
         d, u, P = self.dist, m % self.U, self.world
+        self.mark("slot")
         if P > 1:
             d.broadcast(self.h_fin[u], src=P - 1, group=self.head, async_op=True).wait()
+        self.mark("bcast")
         self.head_fn(u, self.h_fin[u], self.cand[u])
+        self.mark("head")
         if P > 1:
             rows = list(self.cands_all[u].view(P, -1).unbind(0))
             d.all_gather(rows, self.cand[u].view(-1), group=self.head, async_op=True).wait()
         else:
             self.cands_all[u].copy_(self.cand[u])
+        self.mark("gather")
         if self.first:
             self.pick_fn(u, self.cands_all[u], self.t_in[u])
+            self.mark("pick")
             if collect:
                 self.picks[u].append(self.t_in[u].clone())
 
@@ -214,7 +220,9 @@ class ShardedHeadPipeline:
                     send_h[u].wait()            # the previous message of this unit has left the buffer
                     send_h[u] = None
                 out = self.h_out[u]
+            self.mark("recv")
             self.stage_fn(u, step, pos, first_tokens[u] if (self.first and step == 0) else None, tok_in, hin, out)
+            self.mark("stage")
             if not self.last:
                 send_h[u] = d.isend(out, dst=self.rank + 1, group=self.fwd)
         for m in range(max(0, N - self.lag), N):
