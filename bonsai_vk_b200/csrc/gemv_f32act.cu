@@ -84,6 +84,20 @@ __global__ void k_reduce_splits(const float *__restrict__ part, int M, int n_spl
 
 }  // namespace
 
+namespace bnk {
+size_t gemv_f32act_scratch_floats(int M, int K, int n_splits) { return ((size_t(K / 128) + 63) & ~size_t(63)) + size_t(n_splits) * M; }
+// block sums of x, the split partial dot products, then the splits added in order (the reference's two dispatches)
+void gemv_f32act(cudaStream_t st, const uint8_t *W, int M, int K, const float *x, int n_splits, float *out, float *scratch) {
+    const int nb = K / 128;
+    const size_t xs_floats = (size_t(nb) + 63) & ~size_t(63);
+    float *xsum = scratch, *part = scratch + xs_floats;
+    k_xsum<<<(nb + 7) / 8, 256, 0, st>>>(x, nb, xsum);
+    k_gemv_f32act<<<dim3((M + 7) / 8, n_splits), 256, 0, st>>>(W, M, nb, nb / n_splits, x, xsum, part);
+    k_reduce_splits<<<(M + 255) / 256, 256, 0, st>>>(part, M, n_splits, out);
+    BN_COUNT(3);
+}
+}  // namespace bnk
+
 extern "C" {
 
 // the reference's split rule (pick_splits, runtime_vk/bonsai_weights.h:581-588)
@@ -106,16 +120,9 @@ int bn_gemv_f32act(bn_ctx *ctx, const bn_buf *w, size_t w_off, int M, int K, con
     BN_RANGE(w, w_off, size_t(M) * nb * 28, 4, "bn_gemv_f32act W");
     BN_RANGE(x, x_off, size_t(K) * 4, 16, "bn_gemv_f32act x");
     BN_RANGE(out, out_off, size_t(M) * 4, 4, "bn_gemv_f32act out");
-    const size_t xs_floats = (size_t(nb) + 63) & ~size_t(63);
-    int rc = bn_scratch_reserve(ctx, (xs_floats + size_t(n_splits) * M) * 4);
+    int rc = bn_scratch_reserve(ctx, bnk::gemv_f32act_scratch_floats(M, K, n_splits) * 4);
     if (rc != BN_OK) return rc;
-    float *xsum = ctx->scratch, *part = ctx->scratch + xs_floats;
-    cudaStream_t st = ctx->stream;
-    k_xsum<<<(nb + 7) / 8, 256, 0, st>>>(bn_ptr<float>(x, x_off), nb, xsum);
-    k_gemv_f32act<<<dim3((M + 7) / 8, n_splits), 256, 0, st>>>(bn_ptr<uint8_t>(w, w_off), M, nb, nb / n_splits, bn_ptr<float>(x, x_off),
-                                                                xsum, part);
-    k_reduce_splits<<<(M + 255) / 256, 256, 0, st>>>(part, M, n_splits, bn_ptr<float>(out, out_off));
-    BN_COUNT(3);
+    bnk::gemv_f32act(ctx->stream, bn_ptr<uint8_t>(w, w_off), M, K, bn_ptr<float>(x, x_off), n_splits, bn_ptr<float>(out, out_off), ctx->scratch);
     return bn_launch_check(ctx, "k_gemv_f32act");
 }
 

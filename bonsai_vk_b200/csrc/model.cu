@@ -27,6 +27,7 @@ struct bn_model {
     size_t arena_bytes = 0;
     float *RES, *AN, *X1, *X2, *QKV, *Z, *CONV, *L2, *O, *KBUF, *VBUF, *Q16F, *GATEB, *GOUT, *FG, *FU, *FS, *D, *LOGITS;
     float *ALPHA, *BETA, *G, *BT, *SCORE, *P16F, *ESUM, *PVPART, *AMV;
+    float *XROT = nullptr, *F32ACT = nullptr;   // act_mode 1: the rotated fp32 input of a projection and the split partial sums
     int *AMI, *TOK, *POS, *NEXT, *HIST, *STEP;
     cudaGraphExec_t token_graph = nullptr;   // one whole token + advance, captured on first use
     std::vector<cudaGraphExec_t> stage_graphs;   // pipeline stage: one captured schedule per stream (its state pointers are baked in)
@@ -128,19 +129,30 @@ bnk::KvLayer kv_layer(const bn_model *m, int li) {
 }
 
 // ---- stand-alone kernel path (one kernel per reference dispatch; kept as the A/B control) ------------
-void rot_project(bn_model *m, const float *x, const int32_t *sg, int K, uint32_t *pack, const uint32_t *W, int M, float *out) {
+// The stand-alone lineage's projection in the model's activation mode (gemv_ptq, runtime_vk/bonsai_forward.h:409-422):
+// act_mode 0 = q8_1 codes x trits with integer block dots, act_mode 1 = the reference engine's own arithmetic, the
+// rotated fp32 vector against the dequantised trits with its split rule (gemv_ternary.comp:74-93).
+void rotate_in(bn_model *m, const float *x, const int32_t *sg, int K, uint32_t *pack) {
+    bnk::rotate_quant(m->ctx->stream, x, sg, K, m->hp.hat_block, m->hp.act_mode == 1 ? m->XROT : nullptr, pack);
+}
+void project(bn_model *m, const uint32_t *W, int M, int K, const uint32_t *pack, float *out) {
     cudaStream_t st = m->ctx->stream;
-    bnk::rotate_quant(st, x, sg, K, m->hp.hat_block, nullptr, pack);
-    bnk::gemv_q81(st, m->ctx->sm_count, W, M, K, pack, out, m->GEMV_SCRATCH, nullptr);
+    if (m->hp.act_mode == 1)
+        bnk::gemv_f32act(st, reinterpret_cast<const uint8_t *>(W), M, K, m->XROT, bn_gemv_f32act_splits(M, K), out, m->F32ACT);
+    else bnk::gemv_q81(st, m->ctx->sm_count, W, M, K, pack, out, m->GEMV_SCRATCH, nullptr);
+}
+void rot_project(bn_model *m, const float *x, const int32_t *sg, int K, uint32_t *pack, const uint32_t *W, int M, float *out) {
+    rotate_in(m, x, sg, K, pack);
+    project(m, W, M, K, pack, out);
 }
 
 void ffn_plain(bn_model *m, const bn_model::Layer &L) {
     const bn_hparams &h = m->hp;
     cudaStream_t st = m->ctx->stream;
     bnk::rms_norm(st, m->RES, L.post_norm, 1, h.hidden, h.rms_eps, m->AN);
-    bnk::rotate_quant(st, m->AN, m->signs, h.hidden, h.hat_block, nullptr, m->PACK_H);
-    bnk::gemv_q81(st, m->ctx->sm_count, L.ffn_gate, h.ffn, h.hidden, m->PACK_H, m->FG, m->GEMV_SCRATCH, nullptr);
-    bnk::gemv_q81(st, m->ctx->sm_count, L.ffn_up, h.ffn, h.hidden, m->PACK_H, m->FU, m->GEMV_SCRATCH, nullptr);
+    rotate_in(m, m->AN, m->signs, h.hidden, m->PACK_H);
+    project(m, L.ffn_gate, h.ffn, h.hidden, m->PACK_H, m->FG);
+    project(m, L.ffn_up, h.ffn, h.hidden, m->PACK_H, m->FU);
     bnk::swiglu(st, m->FG, m->FU, h.ffn, m->FS);
     rot_project(m, m->FS, m->signs + h.hidden, h.ffn, m->PACK_F, L.ffn_down, h.hidden, m->D);
     bnk::add_inplace(st, m->RES, m->D, h.hidden);
@@ -166,9 +178,9 @@ void gdn_plain(bn_model *m, const bn_model::Layer &L) {
     bnk::gemv_f32_small(st, L.alpha_w, NH, h.hidden, m->AN, m->ALPHA);
     bnk::gemv_f32_small(st, L.beta_w, NH, h.hidden, m->AN, m->BETA);
     bnk::gdn_gates(st, m->ALPHA, m->BETA, L.dt_bias, L.ssm_a, NH, m->G, m->BT);
-    bnk::rotate_quant(st, m->AN, m->signs, h.hidden, h.hat_block, nullptr, m->PACK_H);
-    bnk::gemv_q81(st, m->ctx->sm_count, L.qkv, C, h.hidden, m->PACK_H, m->QKV, m->GEMV_SCRATCH, nullptr);
-    bnk::gemv_q81(st, m->ctx->sm_count, L.gate_w, IN, h.hidden, m->PACK_H, m->Z, m->GEMV_SCRATCH, nullptr);
+    rotate_in(m, m->AN, m->signs, h.hidden, m->PACK_H);
+    project(m, L.qkv, C, h.hidden, m->PACK_H, m->QKV);
+    project(m, L.gate_w, IN, h.hidden, m->PACK_H, m->Z);
     gdn_core(m, L);
     bnk::gdn_out(st, gd, m->O, m->Z, L.ssm_norm, h.rms_eps, m->X1);
     rot_project(m, m->X1, m->signs, IN, m->PACK_H, L.ssm_out, h.hidden, m->D);
@@ -182,10 +194,10 @@ void attn_plain(bn_model *m, const bn_model::Layer &L) {
     const bnk::AttnDims a = attn_dims(m);
     const bnk::KvLayer kv = kv_layer(m, L.idx);
     bnk::rms_norm(st, m->RES, L.attn_norm, 1, h.hidden, h.rms_eps, m->AN);
-    bnk::rotate_quant(st, m->AN, m->signs, h.hidden, h.hat_block, nullptr, m->PACK_H);
-    bnk::gemv_q81(st, m->ctx->sm_count, L.q_w, 2 * QD, h.hidden, m->PACK_H, m->QKV, m->GEMV_SCRATCH, nullptr);
-    bnk::gemv_q81(st, m->ctx->sm_count, L.k_w, KD, h.hidden, m->PACK_H, m->KBUF, m->GEMV_SCRATCH, nullptr);
-    bnk::gemv_q81(st, m->ctx->sm_count, L.v_w, KD, h.hidden, m->PACK_H, m->VBUF, m->GEMV_SCRATCH, nullptr);
+    rotate_in(m, m->AN, m->signs, h.hidden, m->PACK_H);
+    project(m, L.q_w, 2 * QD, h.hidden, m->PACK_H, m->QKV);
+    project(m, L.k_w, KD, h.hidden, m->PACK_H, m->KBUF);
+    project(m, L.v_w, KD, h.hidden, m->PACK_H, m->VBUF);
     bnk::attn_prep(st, a, m->QKV, m->KBUF, m->VBUF, L.q_norm, L.k_norm, m->POS, kv, m->Q16F, m->GATEB);
     bnk::attn_decode(st, a, m->Q16F, m->GATEB, m->POS, kv, m->SCORE, m->P16F, m->ESUM, m->PVPART, m->pv_splits, nullptr, m->GOUT, true);
     rot_project(m, m->GOUT, m->signs, QD, m->PACK_H, L.o_w, h.hidden, m->D);
@@ -598,7 +610,9 @@ int bn_model_create(bn_ctx *ctx, const bn_hparams *hp, bn_model **out) {
     BN_REQUIRE(h.attn_interval >= 1 || (h.attn_interval == 0 && h.n_layer <= 64), BN_ERR_ARG,
                "bn_model_create: attn_interval %d must be >= 1, or 0 with an explicit layer mask over at most 64 blocks (have %d)",
                h.attn_interval, h.n_layer);
-    BN_REQUIRE(h.act_mode == 0, BN_ERR_ARG, "bn_model_create: only act_mode 0 (q8_1 activations) is built");
+    BN_REQUIRE(h.act_mode == 0 || h.act_mode == 1, BN_ERR_ARG, "bn_model_create: act_mode is 0 (q8_1 activations) or 1 (fp32 activations, the reference engine's arithmetic)");
+    BN_REQUIRE(h.act_mode == 0 || (h.batch_cols == 0 && h.n_streams <= 1 && h.block_begin == 0 && (h.block_end == 0 || h.block_end == h.n_layer)), BN_ERR_ARG,
+               "bn_model_create: act_mode 1 runs the whole model for one sequence through the stand-alone kernels (no stages, no multi-sequence pass)");
     BN_REQUIRE((h.k_mode | 1) == 1 && (h.v_mode | 1) == 1, BN_ERR_ARG, "bn_model_create: kv modes are 0 (q8_0) or 1 (fp16)");
     BN_REQUIRE(h.n_streams >= 0 && h.n_streams <= 1024, BN_ERR_ARG, "bn_model_create: n_streams %d out of range", h.n_streams);
     BN_REQUIRE(h.block_begin >= 0 && h.block_begin < h.n_layer && (h.block_end == 0 || (h.block_end > h.block_begin && h.block_end <= h.n_layer)),
@@ -694,6 +708,7 @@ int bn_model_finalize(bn_model *m) {
     F(m->ALPHA, 64); F(m->BETA, 64); F(m->G, 64); F(m->BT, 64);
     F(m->SCORE, size_t(h.n_head) * h.cap); F(m->P16F, size_t(h.n_head) * h.cap); F(m->ESUM, size_t(h.n_head) * 1026);
     F(m->PVPART, size_t(m->pv_splits) * QD); F(m->AMV, 64);
+    if (h.act_mode == 1) { F(m->XROT, size_t(std::max(h.hidden, h.ffn))); F(m->F32ACT, 1024 + size_t(16) * maxM); }
     F(m->GEMV_SCRATCH, size_t(maxG) * std::max(maxM, 1));
     slots.push_back({reinterpret_cast<void **>(&m->AMI), carve(64 * 4)});
     slots.push_back({reinterpret_cast<void **>(&m->CANDV), carve(1024 * 4)});
@@ -714,7 +729,7 @@ int bn_model_finalize(bn_model *m) {
     m->KBUF = m->QKV + 2 * QD;
     m->VBUF = m->KBUF + KD;
     m->FU = m->FG + h.ffn;           // [gate | up]
-    m->fused = getenv("BONSAI_NO_FUSE") == nullptr && bnk::phase_supported(h.hidden, h.hidden, h.hat_block) &&
+    m->fused = h.act_mode == 0 && getenv("BONSAI_NO_FUSE") == nullptr && bnk::phase_supported(h.hidden, h.hidden, h.hat_block) &&
                bnk::phase_supported(h.hidden, h.ffn, h.hat_block);
     m->use_pdl = getenv("BONSAI_NO_PDL") == nullptr;
     bnk::g_pdl = m->use_pdl;

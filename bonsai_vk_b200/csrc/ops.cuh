@@ -105,4 +105,9 @@ void argmax_first(cudaStream_t st, const float *x, int n, int *out_idx, float *s
 // first maximum over n_shards x ncol candidates (value, row), shards in ascending row order
 void pick_shards(cudaStream_t st, const float *cands, int n_shards, int ncol, int *out);
 
+// fp32-activation projection (the reference engine's own arithmetic, gemv_ternary.comp): scratch holds
+// gemv_f32act_scratch_floats(M, K, n_splits) floats
+size_t gemv_f32act_scratch_floats(int M, int K, int n_splits);
+void gemv_f32act(cudaStream_t st, const uint8_t *W, int M, int K, const float *x, int n_splits, float *out, float *scratch);
+
 }  // namespace bnk

@@ -192,3 +192,43 @@ def test_whole_token_kernel_matches_the_oracle(ctx):
         assert np.array_equal(gm.residual().view(np.uint32), ores.view(np.uint32)), f"stop after block {stop}"
         gm.reset(); om.reset()
     gm.close(); om.close()
+
+
+def test_fp32_activation_mode_matches_the_oracle(ctx):
+    """act_mode 1 - the reference engine's own projection arithmetic (fp32 rotated activations against the dequantised
+    trits, split rule of runtime_vk/bonsai_weights.h:581-588, gemv_ternary.comp:74-93) - through the whole token
+    schedule: 8 prompt tokens + 24 greedy steps, ids identical to the oracle in the same mode and logits bit for bit
+    after the prompt and at the end. The modes are different arithmetic: their logits must differ."""
+    from bonsai_vk_b200 import BonsaiError
+    hp = synth.tiny(act_mode=1)
+    tensors, signs = synth.make_model(hp, seed=3)
+    gm = Model(ctx, hp, tensors, signs)
+    om = OracleModel(hp, tensors, signs)
+    prompt = [3, 77, 1500, 12, 900, 41, 7, 2047]
+    for pos, t in enumerate(prompt):
+        gt = gm.token(t, pos)
+        ol, _ = om.token(t, pos)
+    assert np.array_equal(gm.logits().view(np.uint32), ol.view(np.uint32)), "logits after the prompt are not the same floats"
+    ot = om.argmax(ol)
+    assert gt == ot
+    picks = gm.decode(gt, len(prompt), 24)
+    want, tok = [], ot
+    for i in range(24):
+        ol, _ = om.token(tok, len(prompt) + i)
+        tok = om.argmax(ol)
+        want.append(tok)
+    assert picks == want
+    assert np.array_equal(gm.logits().view(np.uint32), ol.view(np.uint32)), "final logits are not the same floats"
+    # same weights, q8_1 mode: different numbers
+    g0 = Model(ctx, synth.tiny(), tensors, signs)
+    for pos, t in enumerate(prompt):
+        g0.token(t, pos)
+    g0.decode(gt, len(prompt), 1)
+    gm.reset()
+    for pos, t in enumerate(prompt):
+        gm.token(t, pos)
+    gm.decode(gt, len(prompt), 1)
+    assert not np.array_equal(g0.logits(), gm.logits())
+    g0.close(); gm.close(); om.close()
+    with pytest.raises(BonsaiError, match="act_mode 1"):
+        Model(ctx, synth.tiny(act_mode=1, batch_cols=4, n_streams=4), tensors, signs)

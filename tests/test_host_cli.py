@@ -206,7 +206,7 @@ def tok_file(tmp_path_factory):
 def test_reference_headers_read_our_file_and_tokenise(tok_file):
     """The reference's own gguf_load + model_plan_build (+ contract) + Bpe, compiled unmodified into ref_bind_run, accept
     the synthetic file and tokenise a text prompt; without a GPU the run then stops at bn_init (exit 3)."""
-    r = subprocess.run([REF_BIND, tok_file, "4", "--", "hello world"], capture_output=True, text=True, timeout=120,
+    r = subprocess.run([REF_BIND, tok_file, "4", "--", "hello world"], capture_output=True, text=True, errors="replace", timeout=120,
                        env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
     m = re.search(r"^prompt ids:(.*)$", r.stdout, re.M)
     assert m, r.stdout + r.stderr
@@ -223,8 +223,8 @@ def test_reference_headers_read_our_file_and_tokenise(tok_file):
 def test_reference_host_and_our_host_generate_the_same_ids(exe, tok_file):
     """Text prompt -> the reference's tokenizer -> ids -> bn_model_* (ref_bind_run), against bonsai_run fed the same ids
     through BONSAI_PROMPT_IDS with the reference's run grammar: identical generated ids."""
-    r = subprocess.run([REF_BIND, tok_file, "12", "--", "hello world the"], capture_output=True, text=True, timeout=300,
-                       env=dict(os.environ, BONSAI_CAP="64"))
+    r = subprocess.run([REF_BIND, tok_file, "12", "--", "hello world the"], capture_output=True, text=True, errors="replace",
+                       timeout=300, env=dict(os.environ, BONSAI_CAP="64"))     # the generated ids decode to arbitrary bytes
     assert r.returncode == 0, r.stdout + r.stderr
     prompt = re.search(r"^prompt ids:(.*)$", r.stdout, re.M).group(1).split()
     r2 = run(exe, "run", tok_file, "32", "12", "--", "hello world the", env={"BONSAI_CAP": "64", "BONSAI_PROMPT_IDS": ",".join(prompt)})
