@@ -508,8 +508,13 @@ __global__ void k_set_cols(int *tok, int *pos, size_t arena, int n, ColInit ci, 
     bnk::colp(pos, c * arena)[0] = ci.pos[c];
 }
 
-// the token schedule for ncol sequences at once; m->cur = first sequence
-void enqueue_batch(bn_model *m, int ncol) {
+// the token schedule for ncol sequences at once; m->cur = first sequence.
+// one_sequence (batched prefill): the columns are ncol consecutive positions of ONE sequence (m->cur). Projections,
+// norms, the embedding and the FFN treat them like independent sequences; the recurrent mixer walks the columns in
+// order on the one state (a launch per position: the delta rule is sequential in time); attention inserts every
+// column's K/V row first and then lets column c attend to the prefix that ends at its own position (causal), all
+// columns at once against the one cache. Every column's result is bit-identical to the token-serial schedule.
+void enqueue_batch(bn_model *m, int ncol, bool one_sequence = false) {
     const bn_hparams &h = m->hp;
     cudaStream_t st = m->ctx->stream;
     const int NH = h.gdn_heads, NQ = h.gdn_qk_heads, D = h.gdn_dim, C = 2 * NQ * D + NH * D, IN = NH * D;
@@ -518,6 +523,7 @@ void enqueue_batch(bn_model *m, int ncol) {
     bnk::Cols cols;
     cols.n = ncol; cols.arena = m->arena_bytes; cols.gdn = m->gdn_stream_stride * 4; cols.conv = m->conv_stream_stride * 4;
     cols.kv = m->kv_layer_bytes * m->n_attn;
+    if (one_sequence) { cols.gdn = 0; cols.conv = 0; cols.kv = 0; }
     auto prep = [&](int mode, const float *x, const float *w, const int32_t *sg, int K, uint8_t *img, float *inv_out) {
         bnk::PrepArgs a = {};
         a.x = x; a.x_stride = AS; a.w = w; a.signs = sg; a.K = K; a.hat_block = h.hat_block; a.eps = h.rms_eps; a.ncol = ncol;
@@ -552,6 +558,20 @@ void enqueue_batch(bn_model *m, int ncol) {
             prep(bnk::PREP_NORM, m->RES, L.attn_norm, m->signs, h.hidden, m->IMG_H, m->G + 48);
             gemm(T.in, C + IN, h.hidden, m->IMG_H, m->QKV, nullptr);
             const bnk::GdnDims gd{NH, NQ, D};
+            if (one_sequence) {
+                // position after position on the one recurrent state. The kernel requests its state and conv taps before
+                // its dependency wait (in the decode schedule its predecessor never writes them); here the predecessor is
+                // the previous position's kernel, which does - so from the second position on the launch is a plain,
+                // fully serialised one.
+                const bool pdl_was = bnk::g_pdl;
+                for (int c = 0; c < ncol; ++c) {
+                    if (c == 1) bnk::g_pdl = false;
+                    bnk::gdn_core_fused(st, gd, h.hidden, m->QKV + c * AS, L.conv_w, conv_of(m, 0, L.idx), conv_of(m, 1, L.idx), m->POS + c * AS,
+                                        m->RES + c * AS, m->G + 48 + c * AS, L.attn_norm, L.alpha_w, L.beta_w, L.dt_bias, L.ssm_a,
+                                        gdn_state_of(m, L.idx), m->Z + c * AS, L.ssm_norm, h.rms_eps, m->X1 + c * AS, bnk::Cols());
+                }
+                bnk::g_pdl = pdl_was;
+            } else
             bnk::gdn_core_fused(st, gd, h.hidden, m->QKV, L.conv_w, conv_of(m, 0, L.idx), conv_of(m, 1, L.idx), m->POS, m->RES, m->G + 48,
                                 L.attn_norm, L.alpha_w, L.beta_w, L.dt_bias, L.ssm_a, gdn_state_of(m, L.idx), m->Z, L.ssm_norm, h.rms_eps, m->X1, cols);
             prep(bnk::PREP_PLAIN, m->X1, nullptr, m->signs, IN, m->IMG_H, nullptr);
@@ -563,7 +583,7 @@ void enqueue_batch(bn_model *m, int ncol) {
         prep(bnk::PREP_PLAIN, m->FS, nullptr, m->signs + h.hidden, h.ffn, m->IMG_F, nullptr);
         gemm(T.ffn_down, h.hidden, h.ffn, m->IMG_F, m->RES, m->RES);
     }
-    if (m->b1 != h.n_layer || m->head_sharded) return;
+    if (m->b1 != h.n_layer || m->head_sharded || one_sequence) return;      // (a prefill block picks from its last column only)
     prep(bnk::PREP_NORM, m->RES, m->out_norm, m->signs, h.hidden, m->IMG_H, nullptr);
     gemm(m->t_head, h.vocab, h.hidden, m->IMG_H, m->LOGITS, nullptr);
     bnk::argmax_first(st, m->LOGITS, h.vocab, m->NEXT, m->AMV, m->AMI, cols);
@@ -1022,6 +1042,48 @@ int bn_model_stage_batch(bn_model *m, int stream0, int ncol, const int *tok, con
     else BN_CUDA(cudaMemcpy2DAsync(bn_ptr<char>(out, out_off), size_t(h.hidden) * 4, m->RES, m->arena_bytes, size_t(h.hidden) * 4, ncol,
                                    cudaMemcpyDeviceToDevice, st));
     return BN_OK;
+}
+
+int bn_model_prefill(bn_model *m, const int *toks, int n, int pos0, int *next_tok) {
+    BN_REQUIRE(m && m->finalized && toks, BN_ERR_STATE, "bn_model_prefill: model not finalized or no tokens");
+    const bn_hparams &h = m->hp;
+    BN_REQUIRE(h.batch_cols > 0 && n >= 1 && n <= h.batch_cols, BN_ERR_ARG,
+               "bn_model_prefill: %d tokens per block, the model was created for at most %d (bn_hparams.batch_cols)", n, h.batch_cols);
+    BN_REQUIRE(m->fused && m->b0 == 0 && m->b1 == h.n_layer && !m->head_sharded, BN_ERR_STATE,
+               "bn_model_prefill: needs the whole model on this device and the fused layer kernels");
+    BN_REQUIRE(pos0 >= 0 && pos0 + n <= h.cap, BN_ERR_BOUNDS, "bn_model_prefill: positions %d..%d do not fit the KV capacity %d", pos0, pos0 + n - 1, h.cap);
+    ColInit ci = {};
+    for (int c = 0; c < n; ++c) {
+        BN_REQUIRE(toks[c] >= 0 && toks[c] < h.vocab, BN_ERR_ARG, "bn_model_prefill: token %d outside vocab %d", toks[c], h.vocab);
+        ci.tok[c] = toks[c]; ci.pos[c] = pos0 + c;
+    }
+    cudaStream_t st = m->ctx->stream;
+    m->cur = 0;
+    m->next_pos = pos0 + n;
+    k_set_cols<<<1, 32, 0, st>>>(m->TOK, m->POS, m->arena_bytes, n, ci, nullptr, h.vocab, m->ctx->err_dev);
+    BN_COUNT(1);
+    enqueue_batch(m, n, true);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = m->launch_err;
+    m->launch_err = cudaSuccess;
+    if (e != cudaSuccess) return bn_cuda_fail(e, "prefill schedule");
+    // the pick after the block: output norm + head + first maximum on the last column's residual, through the
+    // single-sequence kernels (whose buffers are column 0's)
+    const size_t AS = m->arena_bytes / 4;
+    if (n > 1) {
+        BN_CUDA(cudaMemcpyAsync(m->RES, m->RES + size_t(n - 1) * AS, size_t(h.hidden) * 4, cudaMemcpyDeviceToDevice, st));
+        BN_CUDA(cudaMemcpyAsync(m->POS, m->POS + size_t(n - 1) * AS, 4, cudaMemcpyDeviceToDevice, st));
+        BN_CUDA(cudaMemcpyAsync(m->TOK, m->TOK + size_t(n - 1) * AS, 4, cudaMemcpyDeviceToDevice, st));
+    }
+    bnk::PhaseArgs a = phase_base(m, m->out_w, h.vocab, h.hidden, m->signs);
+    a.pro = bnk::PRO_NORM; a.x0 = m->RES; a.w = m->out_norm; a.out = m->LOGITS;
+    launch(m, a);
+    bnk::argmax_first(st, m->LOGITS, h.vocab, m->NEXT, m->AMV, m->AMI);
+    if (next_tok) {
+        BN_CUDA(cudaMemcpyAsync(next_tok, m->NEXT, 4, cudaMemcpyDeviceToHost, st));
+        BN_CUDA(cudaStreamSynchronize(st));
+    }
+    return bn_launch_check(m->ctx, "bn_model_prefill");
 }
 
 int bn_model_set_head_rows(bn_model *m, int row_begin, int row_end) {

@@ -92,6 +92,7 @@ def load_library() -> C.CDLL:
         "bn_model_stage_prepare": (i32, [vp, i32, i32]),
         "bn_model_stage": (i32, [vp, i32, i32, i32, vp, sz, vp, sz]),
         "bn_model_stage_batch": (i32, [vp, i32, i32, vp, vp, vp, sz, vp, sz]),
+        "bn_model_prefill": (i32, [vp, vp, i32, i32, C.POINTER(i32)]),
         "bn_model_set_head_rows": (i32, [vp, i32, i32]),
         "bn_model_head_batch": (i32, [vp, i32, vp, sz, vp, sz]),
         "bn_model_pick_batch": (i32, [vp, i32, i32, vp, sz, vp, sz]),
@@ -356,6 +357,14 @@ class Model:
         ta = (C.c_int32 * n)(*[int(t) for t in toks]) if toks is not None else None
         _check(self.ctx.lib.bn_model_stage_batch(self.h, stream0, n, ta, pa, inp.h if inp is not None else None, in_off, out.h, out_off),
                "bn_model_stage_batch")
+
+    def prefill(self, toks, pos0: int, want_next: bool = True):
+        """len(toks) consecutive positions of the sequence in one pass (batched prefill); returns the pick after the last."""
+        n = len(toks)
+        ta = (C.c_int32 * n)(*[int(t) for t in toks])
+        nxt = C.c_int32(-1)
+        _check(self.ctx.lib.bn_model_prefill(self.h, ta, n, pos0, C.byref(nxt) if want_next else None), "bn_model_prefill")
+        return int(nxt.value)
 
     def head_batch(self, ncol: int, inp: "Buffer", out: "Buffer", in_off: int = 0, out_off: int = 0):
         """This model's shard of the output head for ncol sequences: final hidden states in, (value, row) candidates out."""

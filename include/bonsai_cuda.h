@@ -202,6 +202,14 @@ void bn_model_destroy(bn_model *m);
  * (first maximum, as Sampler::pick with temp <= 0); >= 0 stops after that block (alignment harness,
  * reference: BONSAI_LADDER / stop_at_block). next_tok may be NULL (nothing is copied back then). */
 int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *next_tok);
+/* Batched prefill: n consecutive tokens of the sequence at positions pos0 .. pos0+n-1 as ONE pass (the reference feeds
+ * its prompt token by token, runtime_vk/bonsai_forward.h:2752-2757; this reads every projection's weights once per
+ * block of n tokens through the tensor-core kernel). The recurrent mixer walks the n positions in order on the one
+ * state, attention inserts all n K/V rows and lets each position attend causally. Every position's result - cache
+ * rows, recurrent state, the logits of the last one - is bit-identical to n calls of bn_model_token. Needs
+ * bn_hparams.batch_cols >= n and the whole model on this device. next_tok (may be NULL) receives the greedy pick after
+ * the last position. */
+int bn_model_prefill(bn_model *m, const int *toks, int n, int pos0, int *next_tok);
 /* Builds the replayable schedule of a pipeline stage before any traffic flows (reference: the engine records its command
  * buffers and refuses bad plans before the first dispatch, runtime_vk/bonsai_weights.h:349-353): ncol = 0 prepares
  * bn_model_stage for sequence stream0, ncol >= 1 prepares bn_model_stage_batch for the pass over sequences

@@ -232,3 +232,36 @@ def test_fp32_activation_mode_matches_the_oracle(ctx):
     g0.close(); gm.close(); om.close()
     with pytest.raises(BonsaiError, match="act_mode 1"):
         Model(ctx, synth.tiny(act_mode=1, batch_cols=4, n_streams=4), tensors, signs)
+
+
+def test_batched_prefill_equals_the_token_serial_prompt(ctx):
+    """A 21-token prompt fed as blocks of 16 + 5 (one pass per block: projections read once, recurrent mixer walking
+    the positions, causal attention over the block) against the same prompt fed token by token: the pick after the
+    prompt, the logits, every cache row, the recurrent state and the conv taps are the same bits, and so are the 16
+    tokens decoded afterwards. Both are also the oracle's."""
+    hp = synth.tiny(batch_cols=16)
+    tensors, signs = synth.make_model(hp, seed=5)
+    rng = np.random.default_rng(9)
+    prompt = [int(t) for t in rng.integers(0, hp.vocab, size=21)]
+    serial = Model(ctx, synth.tiny(), tensors, signs)
+    for pos, t in enumerate(prompt):
+        nxt_s = serial.token(t, pos)
+    logits_s = serial.logits().copy()
+    blocked = Model(ctx, hp, tensors, signs)
+    blocked.prefill(prompt[:16], 0, want_next=False)
+    nxt_b = blocked.prefill(prompt[16:], 16)
+    assert nxt_b == nxt_s
+    assert np.array_equal(blocked.logits().view(np.uint32), logits_s.view(np.uint32))
+    n_kv = len(prompt) * hp.n_kv * hp.head_dim
+    for what, dt, n in [(L.READ_K_DATA, np.int8, n_kv), (L.READ_K_SCALE, np.uint16, n_kv // 32), (L.READ_V_DATA, np.int8, n_kv),
+                        (L.READ_V_SCALE, np.uint16, n_kv // 32), (L.READ_GDN_STATE, np.float32, hp.gdn_heads * hp.gdn_dim ** 2)]:
+        for idx in range(hp.n_layer // hp.attn_interval if what != L.READ_GDN_STATE else hp.n_layer - hp.n_layer // hp.attn_interval):
+            a, b = serial.read(what, dt, n, idx), blocked.read(what, dt, n, idx)
+            assert np.array_equal(a.view(np.uint8), b.view(np.uint8)), f"read {what} layer {idx} differs"
+    assert blocked.decode(nxt_b, len(prompt), 16) == serial.decode(nxt_s, len(prompt), 16)
+    # and the oracle agrees with both
+    om = OracleModel(synth.tiny(), tensors, signs)
+    for pos, t in enumerate(prompt):
+        ol, _ = om.token(t, pos)
+    assert om.argmax(ol) == nxt_b and np.array_equal(ol.view(np.uint32), logits_s.view(np.uint32))
+    om.close(); serial.close(); blocked.close()
