@@ -803,6 +803,21 @@ int bn_model_reset(bn_model *m) {
     return BN_OK;
 }
 
+int bn_model_reset_stream(bn_model *m, int stream) {
+    BN_REQUIRE(m && m->finalized, BN_ERR_STATE, "bn_model_reset_stream: model not finalized");
+    const bn_hparams &h = m->hp;
+    const int S = h.n_streams > 0 ? h.n_streams : 1;
+    BN_REQUIRE(stream >= 0 && stream < S, BN_ERR_ARG, "bn_model_reset_stream: sequence %d outside [0, %d)", stream, S);
+    cudaStream_t st = m->ctx->stream;
+    if (m->n_gdn) {
+        BN_CUDA(cudaMemsetAsync(m->gdn_state + size_t(stream) * m->gdn_stream_stride, 0, m->gdn_stream_stride * 4, st));
+        BN_CUDA(cudaMemsetAsync(m->conv_hist + size_t(stream) * m->conv_stream_stride, 0, m->conv_stream_stride * 4, st));
+        BN_CUDA(cudaMemsetAsync(m->conv_hist2 + size_t(stream) * m->conv_stream_stride, 0, m->conv_stream_stride * 4, st));
+    }
+    if (m->n_attn) BN_CUDA(cudaMemsetAsync(m->kv + size_t(stream) * m->n_attn * m->kv_layer_bytes, 0, m->kv_layer_bytes * m->n_attn, st));
+    return BN_OK;
+}
+
 void bn_model_destroy(bn_model *m) {
     if (!m) return;
     cudaSetDevice(m->ctx->device);

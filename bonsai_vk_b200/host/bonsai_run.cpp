@@ -18,7 +18,8 @@
 //
 // Environment: BONSAI_PROMPT_IDS (comma separated ids; default "1,2,3,4,5,6,7,8"), BONSAI_CAP (KV capacity in
 // positions, even; default 4096), BONSAI_QCHECK=1 (run the gate after the prefill), BONSAI_DEVICE (CUDA ordinal),
-// BONSAI_STEPWISE=1 (one host call per generated token instead of the device-chained loop).
+// BONSAI_STEPWISE=1 (one host call per generated token instead of the device-chained loop), BONSAI_PREFILL_BLOCK (prompt
+// tokens per prefill pass, default 16; 0 = token by token; the lineage gate always prefills token by token).
 #include "bonsai_host.h"
 
 #include <chrono>
@@ -153,6 +154,12 @@ int main(int argc, char **argv) {
     if (int(prompt.size()) + n_gen > cap)
         return fail(7, "prompt (" + std::to_string(prompt.size()) + ") + generation (" + std::to_string(n_gen) + ") does not fit the KV capacity " + std::to_string(cap));
 
+    // BONSAI_PREFILL_BLOCK: prompt tokens per prefill pass (default 16; 0 or 1 = token by token as the reference does)
+    const char *pb_s = getenv("BONSAI_PREFILL_BLOCK");
+    const int prefill_want = pb_s ? atoi(pb_s) : 16;
+    if (prefill_want < 0 || prefill_want > 32) return fail(2, "BONSAI_PREFILL_BLOCK must be between 0 and 32");
+    const int prefill_block = getenv("BONSAI_QCHECK") ? 0 : prefill_want;
+    if (prefill_block > 1) e.plan.hp.batch_cols = prefill_block;
     const char *dev_s = getenv("BONSAI_DEVICE");
     if (bn_init(dev_s ? atoi(dev_s) : 0, &e.ctx)) return fail(3, bn_last_error());
     int rc = bh::engine_load(e, path, g, size_t(chunk_mib) << 20, why);
@@ -162,11 +169,20 @@ int main(int argc, char **argv) {
 
     t0 = now_ms();
     int next = -1;
-    for (size_t i = 0; i < prompt.size(); ++i)
-        if (bn_model_token(e.model, prompt[i], int(i), -1, i + 1 == prompt.size() ? &next : nullptr)) return fail(3, bn_last_error());
+    if (prefill_block > 1) {
+        // the prompt in blocks: one pass per block reads every projection's weights once (bn_model_prefill)
+        for (size_t i = 0; i < prompt.size(); i += size_t(prefill_block)) {
+            const int n = int(std::min(prompt.size() - i, size_t(prefill_block)));
+            if (bn_model_prefill(e.model, prompt.data() + i, n, int(i), i + n == prompt.size() ? &next : nullptr)) return fail(3, bn_last_error());
+        }
+    } else {
+        for (size_t i = 0; i < prompt.size(); ++i)
+            if (bn_model_token(e.model, prompt[i], int(i), -1, i + 1 == prompt.size() ? &next : nullptr)) return fail(3, bn_last_error());
+    }
     if (bn_sync(e.ctx)) return fail(3, bn_last_error());
     const double prefill_ms = now_ms() - t0;
-    printf("prefill: %zu tokens in %.1f ms (%.2f ms/token, token-serial)\n", prompt.size(), prefill_ms, prefill_ms / prompt.size());
+    if (prefill_block > 1) printf("prefill: %zu tokens in %.1f ms (%.2f ms/token, blocks of %d)\n", prompt.size(), prefill_ms, prefill_ms / prompt.size(), prefill_block);
+    else printf("prefill: %zu tokens in %.1f ms (%.2f ms/token, token-serial)\n", prompt.size(), prefill_ms, prefill_ms / prompt.size());
 
     if (getenv("BONSAI_QCHECK")) {
         const int mask = lineage_gate(e, g, path, prompt, why);

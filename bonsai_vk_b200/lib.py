@@ -92,6 +92,7 @@ def load_library() -> C.CDLL:
         "bn_model_stage_prepare": (i32, [vp, i32, i32]),
         "bn_model_stage": (i32, [vp, i32, i32, i32, vp, sz, vp, sz]),
         "bn_model_stage_batch": (i32, [vp, i32, i32, vp, vp, vp, sz, vp, sz]),
+        "bn_model_reset_stream": (i32, [vp, i32]),
         "bn_model_prefill": (i32, [vp, vp, i32, i32, C.POINTER(i32)]),
         "bn_model_set_head_rows": (i32, [vp, i32, i32]),
         "bn_model_head_batch": (i32, [vp, i32, vp, sz, vp, sz]),
@@ -332,6 +333,9 @@ class Model:
 
     def reset(self):
         _check(self.ctx.lib.bn_model_reset(self.h), "bn_model_reset")
+
+    def reset_stream(self, stream: int):
+        _check(self.ctx.lib.bn_model_reset_stream(self.h, stream), "bn_model_reset_stream")
 
     def token(self, tok: int, pos: int, stop_after: int = -1, want_next: bool = True):
         nxt = C.c_int32(-1)

@@ -197,6 +197,10 @@ int bn_model_set_signs(bn_model *m, const bn_buf *buf, size_t off, int count);
 int bn_model_finalize(bn_model *m);
 /* zero KV, recurrent state and scratch (reference: fwd_reset_state, bonsai_forward.h:2624-2643) */
 int bn_model_reset(bn_model *m);
+/* the same for ONE sequence of a multi-sequence model: its recurrent state, conv taps and KV cache (the reference resets
+ * per request, runtime_vk/bonsai_http.h:592-623; with several conversations in flight only the slot that takes the new
+ * request is cleared). Enqueues only. */
+int bn_model_reset_stream(bn_model *m, int stream);
 void bn_model_destroy(bn_model *m);
 /* one token at absolute position pos. stop_after_block < 0 runs the whole network and the greedy pick
  * (first maximum, as Sampler::pick with temp <= 0); >= 0 stops after that block (alignment harness,
