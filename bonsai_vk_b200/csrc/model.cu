@@ -604,6 +604,10 @@ __global__ void k_set_tok_pos(int *tok, int *pos, int t, int p, const int *tok_s
     bnk::pdl_sync();
     if (threadIdx.x == 0) { tok[0] = tok_src ? checked_tok(tok_src[0], vocab, err) : t; pos[0] = p; }
 }
+__global__ void k_check_signs(const int32_t *sg, int n, int *bad) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && sg[i] != 1 && sg[i] != -1) atomicAdd(bad, 1);
+}
 __global__ void k_fill_u16(uint16_t *p, size_t n, uint16_t v) {
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) p[i] = v;
 }
@@ -658,6 +662,17 @@ int bn_model_set_signs(bn_model *m, const bn_buf *buf, size_t off, int count) {
                "bn_model_set_signs: %d sign values, need hidden + ffn = %d", count, m->hp.hidden + m->hp.ffn);
     BN_RANGE(buf, off, size_t(count) * 4, 16, "bn_model_set_signs");
     m->signs = bn_ptr<int32_t>(buf, off);
+    {   // the kernels apply a sign by flipping the sign bit: every value must be +1 or -1 (prism.hadamard.sign_values)
+        int *bad = nullptr;
+        BN_CUDA(cudaMalloc(&bad, 4));
+        BN_CUDA(cudaMemsetAsync(bad, 0, 4, m->ctx->stream));
+        k_check_signs<<<(count + 255) / 256, 256, 0, m->ctx->stream>>>(m->signs, count, bad);
+        int h_bad = 0;
+        BN_CUDA(cudaMemcpyAsync(&h_bad, bad, 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+        BN_CUDA(cudaStreamSynchronize(m->ctx->stream));
+        cudaFree(bad);
+        BN_REQUIRE(h_bad == 0, BN_ERR_ARG, "bn_model_set_signs: %d sign values are neither +1 nor -1", h_bad);
+    }
     return BN_OK;
 }
 

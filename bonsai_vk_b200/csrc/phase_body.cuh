@@ -113,9 +113,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t *b, uint32_t parity, int *err
 }
 __device__ __forceinline__ void init_barriers(const Smem &s) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(s.full + i, 1); mbar_init(s.empty + i, NWARP); }
-    for (int i = 0; i < 16; ++i) mbar_init(s.done + i, NWARP);
     *s.abort = 0;
-    *s.red_seq = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 __device__ __forceinline__ void bulk_copy(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
@@ -136,6 +134,15 @@ template <bool CG> __device__ __forceinline__ float4 ldf4(const float *p) {
     return CG ? __ldcg(reinterpret_cast<const float4 *>(p)) : *reinterpret_cast<const float4 *>(p);
 }
 
+// t / K rounded to nearest: for a power of two the product with 1/K is the same float (an exact scaling, rounded once
+// when the result is subnormal, as the quotient is) and skips the division sequence. 1 / x below is __frcp_rn, the
+// correctly rounded reciprocal, which is what the division 1.0f / x returns.
+__device__ __forceinline__ float mean_of(float t, int K) {
+    return (K & (K - 1)) == 0 ? __fmul_rn(t, __frcp_rn(float(K))) : __fdiv_rn(t, float(K));
+}
+// x * sign for sign = +1 / -1 (bn_model_set_signs refuses anything else): flipping the sign bit is the same float as the
+// product, zeros and NaNs included, and needs no int -> float conversion
+__device__ __forceinline__ float apply_sign(float x, int sg) { return __uint_as_float(__float_as_uint(x) ^ (uint32_t(sg) & 0x80000000u)); }
 __device__ __forceinline__ float warp_tree128(float e0, float e1, float e2, float e3) {
     float a = __fadd_rn(__fadd_rn(e0, e2), __fadd_rn(e1, e3));
 #pragma unroll
@@ -339,7 +346,9 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
             red[tid >> 1] = sq;
         }
         csync();
-        if (warp == 0) {
+        {
+            // every warp runs the same tree over the 256 partial sums (the same adds in the same order give the same
+            // float in every warp): no second barrier, no trip through shared memory for the factor
             float v[8];
 #pragma unroll
             for (int w = 0; w < 8; ++w) v[w] = red[32 * w + lane];
@@ -347,14 +356,12 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
                                 __fadd_rn(__fadd_rn(v[1], v[5]), __fadd_rn(v[3], v[7])));
 #pragma unroll
             for (int s2 = 16; s2 > 0; s2 >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xFFFFFFFFu, t, s2));
-            if (lane == 0) {
-                const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, float(K)), a.eps)));
-                hinv[0] = r;
-                if (a.inv_out && cta == 0) a.inv_out[0] = r;
+            inv = __frcp_rn(__fsqrt_rn(__fadd_rn(mean_of(t, K), a.eps)));
+            if (tid == 0) {
+                hinv[0] = inv;
+                if (a.inv_out && cta == 0) a.inv_out[0] = inv;
             }
         }
-        csync();
-        inv = hinv[0];
     } else if (a.pro == PRO_NORM) {
         // rms_norm.comp order: 256 lane slices of `per` consecutive elements summed ascending, then the
         // fixed tree p[i] += p[i+s], s = 128..1 (steps 128, 64, 32 across warps, 16..1 inside warp 0)
@@ -384,7 +391,7 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
 #pragma unroll
             for (int s2 = 16; s2 > 0; s2 >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xFFFFFFFFu, t, s2));
             if (lane == 0) {
-                const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, float(K)), a.eps)));
+                const float r = __frcp_rn(__fsqrt_rn(__fadd_rn(mean_of(t, K), a.eps)));
                 hinv[0] = r;
                 if (a.inv_out && cta == 0) a.inv_out[0] = r;
             }
@@ -441,7 +448,7 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
                 }
                 if (merged) {
 #pragma unroll
-                    for (int r = 0; r < 8; ++r) v[r] = __fmul_rn(__fmul_rn(__fmul_rn(xe[r], inv), pl.w[r]), float(sg[r]));
+                    for (int r = 0; r < 8; ++r) v[r] = apply_sign(__fmul_rn(__fmul_rn(xe[r], inv), pl.w[r]), sg[r]);
                 } else if (a.pro == PRO_PLAIN || a.pro == PRO_NORM) {
                     const float4 x0 = ldf4<CG>(a.x0 + tb), x1 = ldf4<CG>(a.x0 + tb + 4);
                     const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
@@ -449,10 +456,10 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
                         const float4 n0 = *reinterpret_cast<const float4 *>(a.w + tb), n1 = *reinterpret_cast<const float4 *>(a.w + tb + 4);
                         const float ne[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
 #pragma unroll
-                        for (int r = 0; r < 8; ++r) v[r] = __fmul_rn(__fmul_rn(__fmul_rn(xv[r], inv), ne[r]), float(sg[r]));
+                        for (int r = 0; r < 8; ++r) v[r] = apply_sign(__fmul_rn(__fmul_rn(xv[r], inv), ne[r]), sg[r]);
                     } else {
 #pragma unroll
-                        for (int r = 0; r < 8; ++r) v[r] = __fmul_rn(xv[r], float(sg[r]));
+                        for (int r = 0; r < 8; ++r) v[r] = apply_sign(xv[r], sg[r]);
                     }
                 } else if (a.pro == PRO_GDN_OUT || a.pro == PRO_GDN_OUT_SZ) {
                     // 8 consecutive values lie in one destination head: one source head, three 32-byte loads
@@ -469,11 +476,11 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
                     for (int r = 0; r < 8; ++r) {
                         const float nrm = __fmul_rn(__fmul_rn(ov[r], hi), nv[r]);
                         const float zz = a.pro == PRO_GDN_OUT ? silu_f(zv[r]) : zv[r];
-                        v[r] = __fmul_rn(__fmul_rn(zz, nrm), float(sg[r]));
+                        v[r] = apply_sign(__fmul_rn(zz, nrm), sg[r]);
                     }
                 } else {
 #pragma unroll
-                    for (int r = 0; r < 8; ++r) v[r] = __fmul_rn(input(tb + r), float(sg[r]));
+                    for (int r = 0; r < 8; ++r) v[r] = apply_sign(input(tb + r), sg[r]);
                 }
 #pragma unroll
                 for (int h = 1; h < 8; h <<= 1)
@@ -523,7 +530,7 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
             }
             csync();
         } else {
-            for (int i = tid; i < HB; i += NT) { const int t = base + i; xs[i] = __fmul_rn(input(t), float(a.signs[t])); }
+            for (int i = tid; i < HB; i += NT) { const int t = base + i; xs[i] = apply_sign(input(t), a.signs[t]); }
             fwht_smem(xs, HB, a.hat_inv);
         }
         BN_STAMP(4);
@@ -546,7 +553,7 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
             amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
             amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
             const float d = amax > 1e-35f ? __fdiv_rn(amax, 127.0f) : 0.0f;
-            const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+            const float id = d != 0.0f ? __frcp_rn(d) : 0.0f;
             int sum = 0;
             uint32_t w0 = 0, w1 = 0;
 #pragma unroll
@@ -627,7 +634,7 @@ __device__ __forceinline__ void main_loop(const PhaseArgs &a, const Work &w, con
                     if (epi == EPI_SILU_FROM && row >= a.epi_arg) accs[t * 16 + row16] = acc;      // silu after the loop
                     else {
                         if (a.out) a.out[row] = acc;
-                        if (a.resid_out) a.resid_out[row] = __fadd_rn(acc, ldf<true>(a.resid_in + row));
+                        if (a.resid_out) a.resid_out[row] = __fadd_rn(acc, ldf<Feed::on>(a.resid_in + row));
                         if (epi == EPI_ARGMAX && (acc > cand_v[tid] || (acc == cand_v[tid] && row < cand_i[tid]))) { cand_v[tid] = acc; cand_i[tid] = row; }
                     }
                 }
