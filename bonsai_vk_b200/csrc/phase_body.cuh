@@ -406,7 +406,7 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
             const float *o = a.x0 + h * 128;
             const float e0 = ldf<CG>(o + lane), e1 = ldf<CG>(o + lane + 32), e2 = ldf<CG>(o + lane + 64), e3 = ldf<CG>(o + lane + 96);
             const float ss = warp_tree128(__fmul_rn(e0, e0), __fmul_rn(e1, e1), __fmul_rn(e2, e2), __fmul_rn(e3, e3));
-            if (lane == 0) hinv[1 + h] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.0f), a.eps)));
+            if (lane == 0) hinv[1 + h] = __frcp_rn(__fsqrt_rn(__fadd_rn(__fmul_rn(ss, 0.0078125f), a.eps)));
         }
         csync();
     }
@@ -554,16 +554,19 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
             amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
             const float d = amax > 1e-35f ? __fdiv_rn(amax, 127.0f) : 0.0f;
             const float id = d != 0.0f ? __frcp_rn(d) : 0.0f;
-            int sum = 0;
-            uint32_t w0 = 0, w1 = 0;
+            // codes: round half away, clamp, then the low byte of (code + 1.5 * 2^23) read as an integer is the code in
+            // two's complement (no float -> int conversion); four bytes are gathered with byte permutes and the sum of the
+            // eight codes is two byte dot products with ones
+            uint32_t q[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 float r = roundf(__fmul_rn(e[i], id));
                 r = fminf(fmaxf(r, -127.0f), 127.0f);
-                const int qi = int(r);
-                sum += qi;
-                if (i < 4) w0 |= (uint32_t(qi) & 0xFFu) << (8 * i); else w1 |= (uint32_t(qi) & 0xFFu) << (8 * (i - 4));
+                q[i] = __float_as_uint(__fadd_rn(r, 12582912.0f));
             }
+            const uint32_t w0 = __byte_perm(__byte_perm(q[0], q[1], 0x0040u), __byte_perm(q[2], q[3], 0x0040u), 0x5410u);
+            const uint32_t w1 = __byte_perm(__byte_perm(q[4], q[5], 0x0040u), __byte_perm(q[6], q[7], 0x0040u), 0x5410u);
+            int sum = __dp4a(int(w0), 0x01010101, __dp4a(int(w1), 0x01010101, 0));
             sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
             sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
             if (live) {
