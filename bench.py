@@ -380,6 +380,7 @@ def main():
     hp = synth.HParams(cap=cap)
     tensors, signs = build_full_model(hp)
     m = Model(ctx, hp, tensors, signs)
+    tensors_cpu, signs_cpu = (tensors, signs) if rank == 0 else (None, None)     # kept for the CPU baseline's whole-token point
     del tensors
     prompt = [int(t) for t in np.random.default_rng(42).integers(0, hp.vocab, size=max(1, a.prompt))]
     nxt = 0
@@ -452,8 +453,45 @@ def main():
                                             "achieved_gbs": ALGO_BYTES_PER_TOKEN / (ms_dev / K / 1000.0) / 1e9,
                                             "frac_of_measured": ALGO_BYTES_PER_TOKEN / (ms_dev / K / 1000.0) / 1e9 / peak,
                                             "frac_of_8000": ALGO_BYTES_PER_TOKEN / (ms_dev / K / 1000.0) / 1e9 / 8000.0}}
+        # the other kernels of the path, each against the same measured peak (algorithmic bytes / device time):
+        # the recurrent core at this run's position, then - after the model is gone - attention and the multi-column
+        # projection through the op-level C ABI on buffers larger than L2
+        us_gdn, _ = m.mixer_sweep_us(reps=5)
+        others = [{"kernel": "k_gdn_split: gated-delta-net core of one layer (2 MiB state read + written, the layer's state of the "
+                             "previous token is still in L2)", "algorithmic_bytes": 4_194_304 + 98_304, "us": us_gdn,
+                   "achieved": (4_194_304 + 98_304) / us_gdn / 1e3, "frac": (4_194_304 + 98_304) / us_gdn / 1e3 / peak}]
         line["cpu_baseline"] = cpu_gemv_tokens_per_s(seconds=12.0)
+        # the end-to-end CPU point: whole decode tokens of this workload through the CPU checker's forward (integer
+        # block dots, fp32 scales - the same arithmetic as the GPU path), single-threaded: 2 tokens after a 1-token prompt
+        try:
+            from tests._oracle import OracleModel
+            t_cpu = time.perf_counter()
+            om = OracleModel(hp, tensors_cpu, signs_cpu, threads=1)
+            ol, _ = om.token(1, 0)
+            t1 = time.perf_counter()
+            for i in range(2):
+                ol, _ = om.token(om.argmax(ol), 1 + i)
+            dt = (time.perf_counter() - t1) / 2
+            om.close()
+            line["cpu_baseline"]["full_token"] = {"value": 1.0 / dt, "unit": "tok/s", "cores": 1, "kind": "port",
+                                                  "sample": "2 whole decode tokens of the 9B-shape model through the CPU checker, single thread"}
+        except Exception as exc:
+            line["cpu_baseline"]["full_token"] = {"error": str(exc)[:200]}
     m.close()
+    if rank == 0:
+        from bonsai_vk_b200 import kernel_lab
+        try:
+            for keys in (4096, 32768):
+                ms_a, nb = kernel_lab.attn_lab([str(keys), "10"], ctx=ctx, quiet=True)
+                others.append({"kernel": f"decode attention, one layer, {keys} keys (prep, scores, softmax sums, PV, combine; q8_0 K and V)",
+                               "algorithmic_bytes": nb, "us": ms_a * 1e3, "achieved": nb / ms_a / 1e6, "frac": nb / ms_a / 1e6 / peak})
+            for ncol in (8, 32):
+                ms_g2, nb = kernel_lab.gemm_lab(["18944", "4096", str(ncol), "3"], ctx=ctx, quiet=True)
+                others.append({"kernel": f"k_ptq_gemm_tc: 18944 x 4096 projection, {ncol} sequences per pass (tcgen05 kind::i8)",
+                               "algorithmic_bytes": nb, "us": ms_g2 * 1e3, "achieved": nb / ms_g2 / 1e6, "frac": nb / ms_g2 / 1e6 / peak})
+        except Exception as exc:
+            others.append({"error": str(exc)[:200]})
+        line["roofline"]["others"] = others
     if rank == 0:
         # the 64-sequence workload of config 4 on this one GPU (no pipeline): the base of the multi-GPU scaling
         try:

@@ -45,6 +45,7 @@ struct bn_model {
     int graph_launches = 0;
     bool fused = true;        // phase kernels (false: one kernel per reference dispatch, env BONSAI_NO_FUSE=1)
     bool phases_only = false; // measurement: enqueue only the projection kernels of the fused schedule
+    bool mixers_only = false; // measurement: enqueue only what runs between a block's projections (recurrent core / attention)
     bool use_pdl = true;      // programmatic dependent launch between phases (env BONSAI_NO_PDL=1 turns it off)
     cudaError_t launch_err = cudaSuccess;
     unsigned long long *stamps = nullptr;   // profiling aid: 8 time stamps per phase kernel of one token
@@ -215,6 +216,7 @@ bnk::PhaseArgs phase_base(bn_model *m, const uint32_t *W, int M, int K, const in
     return a;
 }
 void launch(bn_model *m, const bnk::PhaseArgs &a) {
+    if (m->mixers_only) return;
     cudaError_t e = bnk::launch_phase(m->ctx->stream, m->ctx->sm_count, a, m->use_pdl);
     if (e != cudaSuccess && m->launch_err == cudaSuccess) m->launch_err = e;
 }
@@ -1229,6 +1231,43 @@ int bn_model_gemv_sweep(bn_model *m, int reps, float *ms_per_sweep) {
     cudaEventDestroy(e1);
     *ms_per_sweep = ms / float(reps);
     return BN_OK;
+}
+
+int bn_model_mixer_sweep(bn_model *m, int reps, float *us_per_gdn_layer, float *us_per_attn_layer) {
+    BN_REQUIRE(m && m->finalized && reps > 0 && us_per_gdn_layer && us_per_attn_layer, BN_ERR_ARG, "bn_model_mixer_sweep: bad argument");
+    BN_REQUIRE(m->fused && m->b0 == 0 && m->b1 == m->hp.n_layer, BN_ERR_STATE, "bn_model_mixer_sweep: whole model with the fused kernels only");
+    cudaStream_t st = m->ctx->stream;
+    cudaEvent_t e0, e1;
+    BN_CUDA(cudaEventCreate(&e0));
+    BN_CUDA(cudaEventCreate(&e1));
+    m->cur = 0;
+    float out[2] = {0.0f, 0.0f};
+    for (int kind = 0; kind < 2; ++kind) {         // 0: gated-delta-net cores, 1: attention (insert + decode at POS[0])
+        int n = 0;
+        for (const bn_model::Layer &L : m->layers) n += (L.attn ? 1 : 0) == kind;
+        if (!n) continue;
+        auto sweep = [&]() {
+            m->mixers_only = true;
+            for (const bn_model::Layer &L : m->layers) {
+                if (kind == 0 && !L.attn) gdn_fused(m, L);
+                if (kind == 1 && L.attn) attn_fused(m, L);
+            }
+            m->mixers_only = false;
+        };
+        sweep();
+        BN_CUDA(cudaEventRecord(e0, st));
+        for (int r = 0; r < reps; ++r) sweep();
+        BN_CUDA(cudaEventRecord(e1, st));
+        BN_CUDA(cudaEventSynchronize(e1));
+        float ms = 0.0f;
+        BN_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        out[kind] = ms * 1000.0f / float(reps) / float(n);
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *us_per_gdn_layer = out[0];
+    *us_per_attn_layer = out[1];
+    return bn_launch_check(m->ctx, "bn_model_mixer_sweep");
 }
 
 int bn_model_profile_token(bn_model *m, int tok, int pos, unsigned long long *stamps_out, int max_phases, int *n_phases) {

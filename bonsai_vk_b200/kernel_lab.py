@@ -20,8 +20,9 @@ import sys
 import numpy as np
 
 
-def attn_lab(argv):
-    """One decode-attention layer: 16 query / 4 KV heads, head_dim 256, q8_0 cache of CTX keys, one query token."""
+def attn_lab(argv, ctx=None, quiet=False):
+    """One decode-attention layer: 16 query / 4 KV heads, head_dim 256, q8_0 cache of CTX keys, one query token.
+    Returns (ms per layer, algorithmic bytes)."""
     from bonsai_vk_b200 import Context
     from bonsai_vk_b200 import lib as L
     ctx_len = int(argv[0])
@@ -29,7 +30,7 @@ def attn_lab(argv):
     n_head, n_kv, hd = 16, 4, 256
     QD, KD = n_head * hd, n_kv * hd
     rng = np.random.default_rng(1)
-    ctx = Context(0)
+    ctx = ctx or Context(0)
     dims = L.AttnDimsC(n_head=n_head, n_kv=n_kv, head_dim=hd, n_rot=64, cap=ctx_len + (ctx_len & 1), k_mode=0, v_mode=0,
                        rms_eps=1e-6, rope_base=1e7)
     kvb, scb = ctx.attn_sizes(dims)
@@ -56,18 +57,23 @@ def attn_lab(argv):
     ctx.record(e1)
     ms = ctx.elapsed_ms(e0, e1) / (iters * nlay)
     nbytes = ctx_len * n_kv * hd * 34 // 32 * 2
-    print(f"attention ctx={ctx_len}: {ms * 1000:.2f} us/layer, {nbytes / ms / 1e6:.1f} GB/s of q8_0 K+V bytes "
-          f"({nbytes} algorithmic bytes; {nlay} caches = {nlay * kvb / 1e6:.0f} MB rotation)")
+    if not quiet:
+        print(f"attention ctx={ctx_len}: {ms * 1000:.2f} us/layer, {nbytes / ms / 1e6:.1f} GB/s of q8_0 K+V bytes "
+              f"({nbytes} algorithmic bytes; {nlay} caches = {nlay * kvb / 1e6:.0f} MB rotation)")
+    for b in kvs + [scratch, bk, bv, bq, ones, out]:
+        b.free()
+    return ms, nbytes
     ctx.close()
 
 
-def gemm_lab(argv):
-    """NCOL activation columns against one M x K PTQ1_0 matrix; column 0 is checked against the single-column kernel."""
+def gemm_lab(argv, ctx=None, quiet=False):
+    """NCOL activation columns against one M x K PTQ1_0 matrix; column 0 is checked against the single-column kernel.
+    Returns (ms per pass, PTQ1_0 bytes of the matrix)."""
     from bonsai_vk_b200 import Context, ptq
     M, K, ncol = int(argv[0]), int(argv[1]), int(argv[2])
     iters = int(argv[3]) if len(argv) > 3 and not argv[3].startswith("-") else 5
     tiled = "--native" not in argv
-    ctx = Context(0)
+    ctx = ctx or Context(0)
     rng = np.random.default_rng(3)
     rows = min(M, 8192)
     base = ptq.synth_matrix(rng, rows, K)
@@ -102,7 +108,8 @@ def gemm_lab(argv):
     ctx.gemv_q81(native, M, K, pack, ref)
     ctx.sync()
     same = np.array_equal(got[0].view(np.uint32), ref.download(np.float32, M).view(np.uint32))
-    print(f"column 0 vs single-column kernel: {'bit-identical' if same else 'DIFFERENT'}")
+    if not quiet:
+        print(f"column 0 vs single-column kernel: {'bit-identical' if same else 'DIFFERENT'}")
     e0, e1 = ctx.event(), ctx.event()
     for i in range(ncopies):
         ctx.gemm_q81(wb, M, K, image, ncol, out, w_off=i * step, tiled=tiled)
@@ -114,6 +121,10 @@ def gemm_lab(argv):
     import os
     ms = ctx.elapsed_ms(e0, e1) / (iters * ncopies * max(1, int(os.environ.get("BONSAI_GEMM_REPS", "1"))))
     ops = 2.0 * M * K * ncol
+    if quiet:                       # called from the benchmark: hand back the numbers, keep the caller's context
+        for b in {id(x): x for x in (wb, native, xb, image, out, pack, ref)}.values():
+            b.free()
+        return ms, nbytes
     print(f"gemm {M}x{K} x {ncol} columns ({'tile-major' if tiled else 'native'} weights): {ms * 1000:.1f} us, {nbytes / ms / 1e6:.1f} GB/s of PTQ1_0 bytes, {ops / ms / 1e9:.2f} Top/s "
           f"({ncopies} matrix copies = {ncopies * nbytes / 1e6:.0f} MB rotation)")
     ctx.close()

@@ -101,6 +101,7 @@ def load_library() -> C.CDLL:
         "bn_wrap": (i32, [vp, vp, sz, C.POINTER(vp)]),
         "bn_use_stream": (i32, [vp, vp]),
         "bn_model_gemv_sweep": (i32, [vp, i32, C.POINTER(C.c_float)]),
+        "bn_model_mixer_sweep": (i32, [vp, i32, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
         "bn_model_profile_token": (i32, [vp, i32, i32, vp, i32, C.POINTER(i32)]),
     }
     for name, (res, args) in sig.items():
@@ -394,6 +395,12 @@ class Model:
         _check(self.ctx.lib.bn_model_profile_token(self.h, tok, pos, out.ctypes.data_as(C.c_void_p), max_phases, C.byref(n)),
                "bn_model_profile_token")
         return out[: n.value]
+
+    def mixer_sweep_us(self, reps: int = 3):
+        """(us per gated-delta-net core, us per attention chain) at the current position, device-timed."""
+        a, b = C.c_float(0), C.c_float(0)
+        _check(self.ctx.lib.bn_model_mixer_sweep(self.h, reps, C.byref(a), C.byref(b)), "bn_model_mixer_sweep")
+        return float(a.value), float(b.value)
 
     def gemv_sweep_ms(self, reps: int = 3) -> float:
         ms = C.c_float()

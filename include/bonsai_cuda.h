@@ -274,6 +274,11 @@ int bn_model_decode(bn_model *m, int first_tok, int pos0, int n_steps, int *out_
  * runtime_vk/bonsai_vk.cpp:1452): launch every PTQ1_0 projection of one token back to back on the
  * model's own weights, `reps` times after one untimed pass, and return the CUDA-event time of one sweep */
 int bn_model_gemv_sweep(bn_model *m, int reps, float *ms_per_sweep);
+/* lab: device time of what runs between a block's projections, per layer, averaged over `reps` sweeps of all layers of
+ * the kind: the gated-delta-net core (reads and writes the layer's recurrent state once) and the attention chain (K/V
+ * insert + decode over the prefix that ends at the current position). Advances the recurrent state and rewrites the
+ * cache row of the current position: for measurement on a model that is reset or discarded afterwards. */
+int bn_model_mixer_sweep(bn_model *m, int reps, float *us_per_gdn_layer, float *us_per_attn_layer);
 /* profiling aid (reference: BONSAI_PROFILE per-token ledger, bonsai_forward.h:650-662): run one token with
  * every fused projection kernel recording 8 device time stamps in ns (CTA 0: start, first copies issued,
  * previous kernel done, norm done, rotated input built, quantised, first weights awaited, end).
