@@ -101,6 +101,12 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *b, uint32_t bytes) {
 // bounded wait; on giving up records the fact, raises the CTA's abort flag and returns (no trap, no endless loop)
 __device__ __forceinline__ void mbar_wait(uint64_t *b, uint32_t parity, int *err, volatile int *abort, int limit = 1 << 22) {
     const uint32_t addr = smem_u32(b);
+    {   // the common case: the phase is complete when the wait is reached (one try, no loop bookkeeping)
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (__builtin_expect(ok != 0u, 1)) return;
+    }
     for (int it = 0; it < limit; ++it) {
         uint32_t ok;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
@@ -217,11 +223,13 @@ __device__ __forceinline__ Pow5 pow5(uint32_t v) {
     r.p3 = v * 27u; r.p4 = v * 81u; r.p5 = v * 243u;
     return r;
 }
-// two blocks of the same 16 rows: four independent accumulator chains of four tensor-core steps each
-// (a dependent mma.sync costs tens of cycles; integer adds are exact, so splitting the sum changes nothing)
+// two blocks of the same 16 rows: two independent accumulator chains of eight tensor-core steps each
+// (integer adds are exact, so the order of the steps changes nothing)
 __device__ __forceinline__ void tile_mma2(int (&c)[4], int (&d)[4], const RowRegs &ra, const RowRegs &rb, const uint2 (&B)[8],
                                           const RowRegs &sa, const RowRegs &sb, const uint2 (&C)[8], uint32_t cq) {
-    int c2[4] = {0, 0, 0, 0}, d2[4] = {0, 0, 0, 0};
+    // one accumulator chain per block (8 dependent steps each). Two chains per block, added at the end, were measured
+    // slower: the other three warps of the scheduler hide the chain's latency, the extra adds and zero registers cost.
+    int (&c2)[4] = c, (&d2)[4] = d;
     Pow5 a = pow5(ra.h0), b = pow5(rb.h0), e = pow5(sa.h0), f = pow5(sb.h0);
     mma_u8s8(c, a.p1, b.p1, a.p2, b.p2, B[0].x, B[0].y);
     mma_u8s8(d, e.p1, f.p1, e.p2, f.p2, C[0].x, C[0].y);
@@ -241,8 +249,6 @@ __device__ __forceinline__ void tile_mma2(int (&c)[4], int (&d)[4], const RowReg
     mma_u8s8(d, e.p3, f.p3, e.p4, f.p4, C[6].x, C[6].y);
     mma_u8s8(c2, a.p5, b.p5, ra.hq * cq, rb.hq * cq, B[7].x, B[7].y);
     mma_u8s8(d2, e.p5, f.p5, sa.hq * cq, sb.hq * cq, C[7].x, C[7].y);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { c[i] += c2[i]; d[i] += d2[i]; }
 }
 // exact int -> float for |i| < 2^22 without the conversion unit
 __device__ __forceinline__ float small_int_to_float(int i) { return __fsub_rn(__int_as_float(0x4B400000 + i), 12582912.0f); }
