@@ -130,9 +130,12 @@ def metadata(hp: synth.HParams, signs: np.ndarray, hat_version: int = 1, names: 
 
 def write(path: str, hp: synth.HParams, seed: int = 0, hat_version: int | None = 1, shuffle: bool = False,
           override_dtype: dict[str, int] | None = None, layer_spelling: str | None = None,
-          extra_kv: list[bytes] | None = None, tokenizer=None) -> dict:
+          extra_kv: list[bytes] | None = None, tokenizer=None, repeat: bool = False) -> dict:
     """Write a synthetic model. Tensors are generated one at a time (the 9B shape never sits in memory whole).
     shuffle=True stores the tensors in name-sorted order (as real checkpoints do) instead of layer order.
+    repeat=True reuses one generated tensor per kind of tensor for every block and one 16 384-row chunk for the two
+    vocabulary-sized tensors (synth.make_model_repeated's rule): a file of the full 9B size in seconds, for timing
+    the loader; the values repeat, the bytes and shapes are the real ones.
     Returns {"tensors": n, "bytes": file size}."""
     shapes = synth.tensor_shapes(hp)
     names = sorted(shapes) if shuffle else list(shapes)
@@ -156,9 +159,21 @@ def write(path: str, hp: synth.HParams, seed: int = 0, hat_version: int | None =
     with open(path, "wb") as f:
         f.write(head + b"\0" * pad)
         base = f.tell()
+        cache = {}
         for n, dims, dtype, o, nbytes in recs:
             f.seek(base + o)
-            a = np.ascontiguousarray(synth.make_tensor(hp, seed, n, shapes[n]))
+            if repeat:
+                key = n.split(".", 2)[-1] if n.startswith("blk.") else ("vocab" if shapes[n][0] == "ptq" else n)
+                if key not in cache:
+                    if key == "vocab":
+                        from . import ptq
+                        chunk = ptq.synth_matrix(np.random.default_rng(seed + 1), min(16384, hp.vocab), hp.hidden)
+                        cache[key] = np.concatenate([chunk] * ((hp.vocab + len(chunk) - 1) // len(chunk)), axis=0)[:hp.vocab]
+                    else:
+                        cache[key] = synth.make_tensor(hp, seed, n, shapes[n])
+                a = np.ascontiguousarray(cache[key])
+            else:
+                a = np.ascontiguousarray(synth.make_tensor(hp, seed, n, shapes[n]))
             assert a.nbytes == nbytes, (n, a.nbytes, nbytes)
             f.write(a.tobytes())
         size = f.tell()
@@ -172,5 +187,6 @@ if __name__ == "__main__":
     ap.add_argument("path")
     ap.add_argument("--shape", choices=["tiny", "9b"], default="tiny")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--repeat", action="store_true", help="reuse one tensor per kind for every block (a full-size file in seconds)")
     a = ap.parse_args()
-    print(write(a.path, synth.tiny() if a.shape == "tiny" else synth.HParams(), a.seed))
+    print(write(a.path, synth.tiny() if a.shape == "tiny" else synth.HParams(), a.seed, repeat=a.repeat))
