@@ -614,6 +614,32 @@ __global__ void k_fill_u16(uint16_t *p, size_t n, uint16_t v) {
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) p[i] = v;
 }
 
+// the whole token (schedule + hand-over of the pick to TOK / POS / HIST) as one CUDA graph, captured on first use
+int ensure_token_graph(bn_model *m) {
+    if (m->token_graph) return BN_OK;
+    cudaStream_t st = m->ctx->stream;
+    cudaGraph_t g = nullptr;
+    const unsigned long long before = g_bn_launches;
+    if (getenv("BONSAI_STAMP_GRAPH")) {      // profiling aid: the captured kernels keep writing their time stamps
+        BN_CUDA(cudaMalloc(&m->stamps, 256 * 8 * sizeof(unsigned long long)));
+        BN_CUDA(cudaMemset(m->stamps, 0, 256 * 8 * sizeof(unsigned long long)));
+        m->stamp_idx = 0;
+    }
+    BN_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    enqueue_token(m, -1, true);
+    m->graph_stamps = m->stamps;
+    m->stamps = nullptr;
+    bnk::launch(k_advance, dim3(1), dim3(32), 0, st, m->TOK, m->POS, m->NEXT, m->HIST, m->STEP);
+    cudaError_t e = cudaStreamEndCapture(st, &g);
+    if (e != cudaSuccess) return bn_cuda_fail(e, "cudaStreamEndCapture(token)");
+    m->graph_launches = int(g_bn_launches - before);
+    g_bn_launches = before;               // captured, not launched
+    e = cudaGraphInstantiate(&m->token_graph, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return bn_cuda_fail(e, "cudaGraphInstantiate(token)");
+    return BN_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -876,6 +902,21 @@ int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *nex
         }
         return BN_OK;
     }
+    if (stop_after_block < 0 && getenv("BONSAI_TOKEN_NO_GRAPH") == nullptr) {
+        // the whole token is one graph launch; id and position travel as arguments of a one-thread kernel in front of it
+        // (no host-to-device copy to wait for), the step counter of the hand-over kernel is cleared on the way
+        { const int rc = ensure_token_graph(m); if (rc != BN_OK) return rc; }
+        BN_CUDA(cudaMemsetAsync(m->STEP, 0, 4, st));
+        k_set_tok_pos<<<1, 32, 0, st>>>(m->TOK, m->POS, tok, pos, nullptr, h.vocab, m->ctx->err_dev);
+        BN_COUNT(1);
+        BN_CUDA(cudaGraphLaunch(m->token_graph, st));
+        BN_COUNT(m->graph_launches);
+        if (next_tok) {
+            BN_CUDA(cudaMemcpyAsync(next_tok, m->NEXT, 4, cudaMemcpyDeviceToHost, st));
+            BN_CUDA(cudaStreamSynchronize(st));
+        }
+        return BN_OK;
+    }
     const int tp[2] = {tok, pos};
     BN_CUDA(cudaMemcpyAsync(m->TOK, &tp[0], 4, cudaMemcpyHostToDevice, st));
     BN_CUDA(cudaMemcpyAsync(m->POS, &tp[1], 4, cudaMemcpyHostToDevice, st));
@@ -912,27 +953,7 @@ int bn_model_decode(bn_model *m, int first_tok, int pos0, int n_steps, int *out_
         }
         return BN_OK;
     }
-    if (!m->token_graph) {
-        cudaGraph_t g = nullptr;
-        const unsigned long long before = g_bn_launches;
-        if (getenv("BONSAI_STAMP_GRAPH")) {      // profiling aid: the captured kernels keep writing their time stamps
-            BN_CUDA(cudaMalloc(&m->stamps, 256 * 8 * sizeof(unsigned long long)));
-            BN_CUDA(cudaMemset(m->stamps, 0, 256 * 8 * sizeof(unsigned long long)));
-            m->stamp_idx = 0;
-        }
-        BN_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-        enqueue_token(m, -1, true);
-        m->graph_stamps = m->stamps;
-        m->stamps = nullptr;
-        bnk::launch(k_advance, dim3(1), dim3(32), 0, st, m->TOK, m->POS, m->NEXT, m->HIST, m->STEP);
-        cudaError_t e = cudaStreamEndCapture(st, &g);
-        if (e != cudaSuccess) return bn_cuda_fail(e, "cudaStreamEndCapture(token)");
-        m->graph_launches = int(g_bn_launches - before);
-        g_bn_launches = before;               // captured, not launched
-        e = cudaGraphInstantiate(&m->token_graph, g, 0);
-        cudaGraphDestroy(g);
-        if (e != cudaSuccess) return bn_cuda_fail(e, "cudaGraphInstantiate(token)");
-    }
+    { const int rc = ensure_token_graph(m); if (rc != BN_OK) return rc; }
     const int init[3] = {first_tok, pos0, 0};
     BN_CUDA(cudaMemcpyAsync(m->TOK, &init[0], 4, cudaMemcpyHostToDevice, st));
     BN_CUDA(cudaMemcpyAsync(m->POS, &init[1], 4, cudaMemcpyHostToDevice, st));

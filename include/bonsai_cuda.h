@@ -204,7 +204,9 @@ int bn_model_reset_stream(bn_model *m, int stream);
 void bn_model_destroy(bn_model *m);
 /* one token at absolute position pos. stop_after_block < 0 runs the whole network and the greedy pick
  * (first maximum, as Sampler::pick with temp <= 0); >= 0 stops after that block (alignment harness,
- * reference: BONSAI_LADDER / stop_at_block). next_tok may be NULL (nothing is copied back then). */
+ * reference: BONSAI_LADDER / stop_at_block). next_tok may be NULL (nothing is copied back then). The whole-network
+ * form is one launch of the token's CUDA graph (captured by the first call) behind a small kernel that carries tok and
+ * pos as arguments; the host waits once per call, for the pick, and only when next_tok is given. */
 int bn_model_token(bn_model *m, int tok, int pos, int stop_after_block, int *next_tok);
 /* Batched prefill: n consecutive tokens of the sequence at positions pos0 .. pos0+n-1 as ONE pass (the reference feeds
  * its prompt token by token, runtime_vk/bonsai_forward.h:2752-2757; this reads every projection's weights once per
