@@ -187,3 +187,17 @@ def test_three_overlapping_conversations_on_the_gpu(ctx):
     st, raw = _http(port, "/v1/completions", {"prompt": prompts[0], "max_tokens": n_gen[0]})
     assert json.loads(raw)["choices"][0]["token_ids"] == want[0]
     srv.shutdown(); b.close(); eng.close()
+
+
+def test_full_size_writer_mode_reuses_tensors(tmp_path):
+    """gguf_writer's repeat mode (one generated tensor per kind for every block): same header, shapes and byte counts as
+    the plain mode, readable by the Python reader; blocks of the same kind hold the same bytes."""
+    from bonsai_vk_b200 import gguf_reader, gguf_writer
+    hp = synth.tiny()
+    a, b = str(tmp_path / "plain.gguf"), str(tmp_path / "rep.gguf")
+    ra, rb = gguf_writer.write(a, hp, seed=2), gguf_writer.write(b, hp, seed=2, repeat=True)
+    assert ra == rb
+    hp2, tensors, _ = gguf_reader.load(b, cap=hp.cap)
+    assert hp2.n_layer == hp.n_layer and len(tensors) == ra["tensors"]
+    assert np.array_equal(np.asarray(tensors["blk.0.ffn_up.weight"]), np.asarray(tensors["blk.1.ffn_up.weight"]))
+    assert np.array_equal(np.asarray(tensors["token_embd.weight"]), np.asarray(tensors["output.weight"]))
