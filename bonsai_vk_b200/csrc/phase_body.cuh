@@ -314,6 +314,85 @@ __device__ __forceinline__ void preload(const PhaseArgs &a, int tid, Preload &p)
     }
 }
 
+// butterflies h = 1, 2, 4 inside a thread's 8 consecutive elements, h = 8..128 across the lanes of a warp
+__device__ __forceinline__ void fwht_regs_lanes(float (&v)[8], int lane) {
+#pragma unroll
+    for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (!(r & h)) { const float x = v[r], y = v[r + h]; v[r] = __fadd_rn(x, y); v[r + h] = __fsub_rn(x, y); }
+#pragma unroll
+    for (int m2 = 1; m2 < 32; m2 <<= 1)
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const float pr = __shfl_xor_sync(0xFFFFFFFFu, v[r], m2);
+            v[r] = (lane & m2) ? __fsub_rn(pr, v[r]) : __fadd_rn(v[r], pr);
+        }
+}
+// butterflies h = 256, 512, 1024 inside a thread (elements 256 apart), h = 2048 between lanes l and l^16, then the scale;
+// each thread rewrites only what it read
+__device__ __forceinline__ void fwht_4096_tail(float *xs, int warp, int lane, float hat_inv) {
+    const int i0 = (lane & 15) + 16 * warp + 2048 * (lane >> 4);
+    float u[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) u[r] = xs[i0 + 256 * r];
+#pragma unroll
+    for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (!(r & h)) { const float x = u[r], y = u[r + h]; u[r] = __fadd_rn(x, y); u[r + h] = __fsub_rn(x, y); }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        const float pr = __shfl_xor_sync(0xFFFFFFFFu, u[r], 16);
+        u[r] = (lane & 16) ? __fsub_rn(pr, u[r]) : __fadd_rn(u[r], pr);
+        xs[i0 + 256 * r] = __fmul_rn(u[r], hat_inv);
+    }
+}
+// q8_1 of nsub 32-element sub-blocks of xs: 4 threads per sub-block, 8 consecutive elements each. codes / dsw point at
+// the first sub-block's codes and (d | s) word.
+__device__ __forceinline__ void q81_pass(const float *xs, int8_t *codes, uint32_t *dsw, int nsub, int tid) {
+    for (int sbk0 = 0; sbk0 < nsub; sbk0 += NT / 4) {
+        const int sbk = sbk0 + (tid >> 2), q4 = tid & 3;
+        const bool live = sbk < nsub;
+        float e[8];
+        if (live) {
+            const float4 *src = reinterpret_cast<const float4 *>(xs + sbk * 32 + q4 * 8);
+            const float4 v0 = src[0], v1 = src[1];
+            e[0] = v0.x; e[1] = v0.y; e[2] = v0.z; e[3] = v0.w; e[4] = v1.x; e[5] = v1.y; e[6] = v1.z; e[7] = v1.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) e[i] = 0.0f;
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(e[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+        const float d = amax > 1e-35f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+        const float id = d != 0.0f ? __frcp_rn(d) : 0.0f;
+        // codes: round half away, clamp, then the low byte of (code + 1.5 * 2^23) read as an integer is the code in
+        // two's complement (no float -> int conversion); four bytes are gathered with byte permutes and the sum of the
+        // eight codes is two byte dot products with ones
+        uint32_t q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float r = roundf(__fmul_rn(e[i], id));
+            r = fminf(fmaxf(r, -127.0f), 127.0f);
+            q[i] = __float_as_uint(__fadd_rn(r, 12582912.0f));
+        }
+        const uint32_t w0 = __byte_perm(__byte_perm(q[0], q[1], 0x0040u), __byte_perm(q[2], q[3], 0x0040u), 0x5410u);
+        const uint32_t w1 = __byte_perm(__byte_perm(q[4], q[5], 0x0040u), __byte_perm(q[6], q[7], 0x0040u), 0x5410u);
+        int sum = __dp4a(int(w0), 0x01010101, __dp4a(int(w1), 0x01010101, 0));
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+        if (live) {
+            uint32_t *cw = reinterpret_cast<uint32_t *>(codes + sbk * 32 + q4 * 8);
+            cw[0] = w0; cw[1] = w1;
+            if (q4 == 0) dsw[sbk] = float_to_half_bits(d) | (float_to_half_bits(__fmul_rn(d, float(sum))) << 16);
+        }
+    }
+}
+
 #define BN_STAMP(i) do { if (a.stamps && cta == 0 && threadIdx.x == 0) a.stamps[i] = gtime(); } while (0)
 
 // ---- prologue: int8 codes and (d, s) of the whole rotated input, in shared memory (compute warps only) -----------------
@@ -326,6 +405,7 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
     uint32_t *dsw = s.dsw;
     float *red = s.red, *hinv = s.hinv, *xs = s.xs;
     if (a.pro == PRO_PACKED) {
+        BN_STAMP(3); BN_STAMP(4);
         for (int i = tid; i < nb * 32; i += NT) reinterpret_cast<uint32_t *>(codes)[i] = a.pack[size_t(i >> 5) * Q81_DWORDS + 4 + (i & 31)];
         for (int i = tid; i < nb * 4; i += NT) dsw[i] = a.pack[size_t(i >> 2) * Q81_DWORDS + (i & 3)];
         csync();
@@ -488,40 +568,14 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
 #pragma unroll
                     for (int r = 0; r < 8; ++r) v[r] = apply_sign(input(tb + r), sg[r]);
                 }
-#pragma unroll
-                for (int h = 1; h < 8; h <<= 1)
-#pragma unroll
-                    for (int r = 0; r < 8; ++r)
-                        if (!(r & h)) { const float x = v[r], y = v[r + h]; v[r] = __fadd_rn(x, y); v[r + h] = __fsub_rn(x, y); }
-#pragma unroll
-                for (int m2 = 1; m2 < 32; m2 <<= 1)
-#pragma unroll
-                    for (int r = 0; r < 8; ++r) {
-                        const float pr = __shfl_xor_sync(0xFFFFFFFFu, v[r], m2);
-                        v[r] = (lane & m2) ? __fsub_rn(pr, v[r]) : __fadd_rn(v[r], pr);
-                    }
+                fwht_regs_lanes(v, lane);
                 float4 *dst = reinterpret_cast<float4 *>(xs + tid * 8);
                 dst[0] = make_float4(v[0], v[1], v[2], v[3]);
                 dst[1] = make_float4(v[4], v[5], v[6], v[7]);
             }
             csync();
             if (HB == 4096) {
-                // h = 256, 512, 1024 inside a thread (elements 256 apart), h = 2048 between lanes l and l^16
-                const int i0 = (lane & 15) + 16 * warp + 2048 * (lane >> 4);
-                float u[8];
-#pragma unroll
-                for (int r = 0; r < 8; ++r) u[r] = xs[i0 + 256 * r];
-#pragma unroll
-                for (int h = 1; h < 8; h <<= 1)
-#pragma unroll
-                    for (int r = 0; r < 8; ++r)
-                        if (!(r & h)) { const float x = u[r], y = u[r + h]; u[r] = __fadd_rn(x, y); u[r + h] = __fsub_rn(x, y); }
-#pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    const float pr = __shfl_xor_sync(0xFFFFFFFFu, u[r], 16);
-                    u[r] = (lane & 16) ? __fsub_rn(pr, u[r]) : __fadd_rn(u[r], pr);
-                    xs[i0 + 256 * r] = __fmul_rn(u[r], a.hat_inv);     // each thread rewrites only what it read
-                }
+                fwht_4096_tail(xs, warp, lane, a.hat_inv);
             } else {
                 for (int h = 256; h < HB; h <<= 1) {
                     for (int i = tid; i < (HB >> 1); i += NT) {
@@ -540,47 +594,7 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
             fwht_smem(xs, HB, a.hat_inv);
         }
         BN_STAMP(4);
-        // q8_1: 4 threads per 32-element sub-block, 8 consecutive elements each
-        for (int sbk0 = 0; sbk0 < HB / 32; sbk0 += NT / 4) {
-            const int sbk = sbk0 + (tid >> 2), q4 = tid & 3;
-            const bool live = sbk < HB / 32;
-            float e[8];
-            if (live) {
-                const float4 *src = reinterpret_cast<const float4 *>(xs + sbk * 32 + q4 * 8);
-                const float4 v0 = src[0], v1 = src[1];
-                e[0] = v0.x; e[1] = v0.y; e[2] = v0.z; e[3] = v0.w; e[4] = v1.x; e[5] = v1.y; e[6] = v1.z; e[7] = v1.w;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) e[i] = 0.0f;
-            }
-            float amax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(e[i]));
-            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-            const float d = amax > 1e-35f ? __fdiv_rn(amax, 127.0f) : 0.0f;
-            const float id = d != 0.0f ? __frcp_rn(d) : 0.0f;
-            // codes: round half away, clamp, then the low byte of (code + 1.5 * 2^23) read as an integer is the code in
-            // two's complement (no float -> int conversion); four bytes are gathered with byte permutes and the sum of the
-            // eight codes is two byte dot products with ones
-            uint32_t q[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float r = roundf(__fmul_rn(e[i], id));
-                r = fminf(fmaxf(r, -127.0f), 127.0f);
-                q[i] = __float_as_uint(__fadd_rn(r, 12582912.0f));
-            }
-            const uint32_t w0 = __byte_perm(__byte_perm(q[0], q[1], 0x0040u), __byte_perm(q[2], q[3], 0x0040u), 0x5410u);
-            const uint32_t w1 = __byte_perm(__byte_perm(q[4], q[5], 0x0040u), __byte_perm(q[6], q[7], 0x0040u), 0x5410u);
-            int sum = __dp4a(int(w0), 0x01010101, __dp4a(int(w1), 0x01010101, 0));
-            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-            if (live) {
-                uint32_t *cw = reinterpret_cast<uint32_t *>(codes + base + sbk * 32 + q4 * 8);
-                cw[0] = w0; cw[1] = w1;
-                if (q4 == 0) dsw[(base >> 5) + sbk] = float_to_half_bits(d) | (float_to_half_bits(__fmul_rn(d, float(sum))) << 16);
-            }
-        }
+        q81_pass(xs, codes + base, dsw + (base >> 5), HB / 32, tid);
     }
     csync();
 }

@@ -55,6 +55,11 @@ struct PhaseArgs {
 
 constexpr int PHASE_THREADS = 512;
 size_t phase_smem_bytes(int hat_block);
+// y = silu(gate) * up (n floats, y may be null) and the activation pack of the down projection's rotated, quantised input
+// (signs of n entries; y is written always); the projection then runs with PRO_PACKED.
+bool swiglu_pack_supported(int n, int hat_block);
+// count: one zeroed int per Hadamard block (the kernel leaves it zero).
+void swiglu_pack(cudaStream_t st, const float *gate, const float *up, int n, const int32_t *signs, float hat_inv, float *y, uint32_t *pack, int *count);
 // launches with programmatic dependent launch when pdl is true
 cudaError_t launch_phase(cudaStream_t st, int sm_count, const PhaseArgs &a, bool pdl);
 bool phase_supported(int M, int K, int hat_block);
