@@ -321,13 +321,17 @@ __device__ __forceinline__ void fwht_regs_lanes(float (&v)[8], int lane) {
 #pragma unroll
         for (int r = 0; r < 8; ++r)
             if (!(r & h)) { const float x = v[r], y = v[r + h]; v[r] = __fadd_rn(x, y); v[r + h] = __fsub_rn(x, y); }
+    // the upper lane of a pair takes partner - own, the lower one own + partner: one fused multiply-add with +-1 (the
+    // product is exact, so the result is the rounded difference / sum, bit for bit what fsub / fadd give)
 #pragma unroll
-    for (int m2 = 1; m2 < 32; m2 <<= 1)
+    for (int m2 = 1; m2 < 32; m2 <<= 1) {
+        const float sgn = (lane & m2) ? -1.0f : 1.0f;
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
             const float pr = __shfl_xor_sync(0xFFFFFFFFu, v[r], m2);
-            v[r] = (lane & m2) ? __fsub_rn(pr, v[r]) : __fadd_rn(v[r], pr);
+            v[r] = __fmaf_rn(v[r], sgn, pr);
         }
+    }
 }
 // butterflies h = 256, 512, 1024 inside a thread (elements 256 apart), h = 2048 between lanes l and l^16, then the scale;
 // each thread rewrites only what it read
@@ -341,10 +345,11 @@ __device__ __forceinline__ void fwht_4096_tail(float *xs, int warp, int lane, fl
 #pragma unroll
         for (int r = 0; r < 8; ++r)
             if (!(r & h)) { const float x = u[r], y = u[r + h]; u[r] = __fadd_rn(x, y); u[r + h] = __fsub_rn(x, y); }
+    const float sgn = (lane & 16) ? -1.0f : 1.0f;
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
         const float pr = __shfl_xor_sync(0xFFFFFFFFu, u[r], 16);
-        u[r] = (lane & 16) ? __fsub_rn(pr, u[r]) : __fadd_rn(u[r], pr);
+        u[r] = __fmaf_rn(u[r], sgn, pr);
         xs[i0 + 256 * r] = __fmul_rn(u[r], hat_inv);
     }
 }
