@@ -315,7 +315,8 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
                f"({b1 - b0} blocks per stage), 64 concurrent sequences at context {CTX} (KV marked filled) in {U} micro-batches "
                f"of {MB}, greedy decode; output head " + ("sharded by rows over the stages" if sharded else "on the last stage"),
                parallelism=f"pp{world}", streams=S, context=CTX, microbatch=MB, balance=a.balance, head=a.head)
-    line = dict(base, metric="decode tok/s, 9B ternary (PTQ1_0), 64 streams pipelined", config=cfg, value=tok_s,
+    # the 64-sequence workload is the same at every N: total work fixed
+    line = dict(base, metric="decode tok/s, 9B ternary (PTQ1_0), 64 streams pipelined", scaling="strong", config=cfg, value=tok_s,
                 ms_per_step=ms_dev / K, clocks=clocks, gpu_launches=int(launches),
                 e2e={"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4 * S})
     if rank == 0:
