@@ -170,7 +170,7 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     import torch
     import torch.distributed as dist
     from bonsai_vk_b200 import Context, Model, synth
-    from bonsai_vk_b200.pipeline import Pipeline, ShardedHeadPipeline, split_blocks, split_head_rows
+    from bonsai_vk_b200.pipeline import Pipeline, ShardedHeadPipeline, TwoCudaStreams, split_blocks, split_head_rows
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     fwd, back = dist.new_group(list(range(world))), dist.new_group(list(range(world)))
@@ -267,7 +267,8 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
         pipe = ShardedHeadPipeline(dist, rank, world, U, stage, head_fn, pick_fn,
                                    lambda: torch.zeros(MB * hp.hidden, dtype=torch.float32, device=dev),
                                    lambda: torch.zeros(MB, dtype=torch.int32, device=dev),
-                                   lambda n: torch.zeros(n * MB * 2, dtype=torch.float32, device=dev), fwd, back, mark=mark)
+                                   lambda n: torch.zeros(n * MB * 2, dtype=torch.float32, device=dev), fwd, back, mark=mark,
+                                   lanes=TwoCudaStreams(torch, ctx, work_stream, U) if a.head_lanes == 2 else None)
     else:
         pipe = Pipeline(dist, rank, world, U, stage, lambda: torch.zeros(MB * hp.hidden, dtype=torch.float32, device=dev),
                         lambda: torch.zeros(MB, dtype=torch.int32, device=dev), fwd, back)
@@ -314,7 +315,8 @@ def pipeline_main(a, base, rank, world, local, K, Wm):
     cfg = dict(base["config"], workload=f"config 4: 9B-shape synthetic model layer-pipelined over {world} GPUs "
                f"({b1 - b0} blocks per stage), 64 concurrent sequences at context {CTX} (KV marked filled) in {U} micro-batches "
                f"of {MB}, greedy decode; output head " + ("sharded by rows over the stages" if sharded else "on the last stage"),
-               parallelism=f"pp{world}", streams=S, context=CTX, microbatch=MB, balance=a.balance, head=a.head)
+               parallelism=f"pp{world}", streams=S, context=CTX, microbatch=MB, balance=a.balance, head=a.head,
+               head_lanes=a.head_lanes if sharded else 1)
     # the 64-sequence workload is the same at every N: total work fixed
     line = dict(base, metric="decode tok/s, 9B ternary (PTQ1_0), 64 streams pipelined", scaling="strong", config=cfg, value=tok_s,
                 ms_per_step=ms_dev / K, clocks=clocks, gpu_launches=int(launches),
@@ -348,6 +350,9 @@ def main():
                     help="N > 1: stage split - equal block counts (the benchmark configuration) or byte-balanced with the head on the last stage")
     ap.add_argument("--head", default="sharded", choices=["sharded", "last"],
                     help="N > 1: output head sharded by rows over all stages (default) or whole on the last stage")
+    ap.add_argument("--head-lanes", dest="head_lanes", type=int, default=1, choices=[1, 2],
+                    help="N > 1, sharded head: 1 = head work on the stage passes' stream (default, measured faster), "
+                         "2 = on a second high-priority CUDA stream beside them")
     ap.add_argument("--no-base", dest="no_base", action="store_true", help="N > 1: skip the one-GPU 64-stream base measurement")
     ap.add_argument("--microbatch", type=int, default=0, help="N > 1: sequences per micro-batch (0 = 64 / GPUs, at most 32; 1 = one sequence per pass)")
     a = ap.parse_args()

@@ -69,6 +69,7 @@ struct bn_model {
     // multi-sequence pass (bn_model_stage_batch): per-column arenas, shared activation images, tile-major weights
     int ncols = 1;
     uint8_t *IMG_H = nullptr, *IMG_F = nullptr;
+    uint8_t *IMG_HD = nullptr;            // sharded head: its own activation image, so that the head may run beside a stage pass
     float *GROUPS = nullptr;              // group sums of the projections that are split over K (gemm_tc.cuh)
     uint8_t *tiled = nullptr;
     struct TiledLayer { const uint8_t *in = nullptr, *out = nullptr, *ffn_in = nullptr, *ffn_down = nullptr; };
@@ -499,7 +500,10 @@ int build_batch_side(bn_model *m) {
         }
         if (need) BN_CUDA(cudaMalloc(&m->GROUPS, need * 4));
     }
-    if (m->head_sharded) BN_CUDA(cudaMalloc(&m->CAND, size_t(h.batch_cols) * 8));
+    if (m->head_sharded) {
+        BN_CUDA(cudaMalloc(&m->CAND, size_t(h.batch_cols) * 8));
+        BN_CUDA(cudaMalloc(&m->IMG_HD, bnk::gemm_image_bytes(h.hidden, h.batch_cols)));
+    }
     BN_CUDA(cudaStreamSynchronize(m->ctx->stream));
     return BN_OK;
 }
@@ -888,6 +892,7 @@ void bn_model_destroy(bn_model *m) {
     if (m->tok_bar) cudaFree(m->tok_bar);
     if (m->tok_stamps) cudaFree(m->tok_stamps);
     if (m->IMG_H) cudaFree(m->IMG_H);
+    if (m->IMG_HD) cudaFree(m->IMG_HD);
     if (m->IMG_F) cudaFree(m->IMG_F);
     if (m->GROUPS) cudaFree(m->GROUPS);
     if (m->SWCNT) cudaFree(m->SWCNT);
@@ -1169,18 +1174,19 @@ int bn_model_head_batch(bn_model *m, int ncol, const bn_buf *in, size_t in_off, 
     BN_RANGE(in, in_off, size_t(ncol) * h.hidden * 4, 16, "bn_model_head_batch hidden input");
     BN_RANGE(out, out_off, size_t(ncol) * 8, 8, "bn_model_head_batch candidate output");
     cudaStream_t st = m->ctx->stream;
-    BN_CUDA(cudaMemcpy2DAsync(m->RES, m->arena_bytes, bn_ptr<char>(in, in_off), size_t(h.hidden) * 4, size_t(h.hidden) * 4, ncol, cudaMemcpyDeviceToDevice, st));
+    // Nothing here touches what a stage pass uses (the hidden states are read where they lie, the activation image is the
+    // head's own, logits and pick scratch belong to the head alone on a sharded model, no K-split scratch): the caller may
+    // run the head on another CUDA stream (bn_use_stream) beside a stage pass of the same model.
     const size_t AS = m->arena_bytes / 4;
     bnk::Cols cols;
     cols.n = ncol; cols.arena = m->arena_bytes; cols.gdn = 0; cols.conv = 0; cols.kv = 0;
     bnk::PrepArgs p = {};
-    p.x = m->RES; p.x_stride = AS; p.w = m->out_norm; p.signs = m->signs; p.K = h.hidden; p.hat_block = h.hat_block; p.eps = h.rms_eps; p.ncol = ncol;
-    p.image = m->IMG_H; p.inv_stride = AS; p.mode = bnk::PREP_NORM;
+    p.x = bn_ptr<float>(in, in_off); p.x_stride = size_t(h.hidden); p.w = m->out_norm; p.signs = m->signs; p.K = h.hidden; p.hat_block = h.hat_block; p.eps = h.rms_eps; p.ncol = ncol;
+    p.image = m->IMG_HD; p.inv_stride = AS; p.mode = bnk::PREP_NORM;
     bnk::prep_cols(st, p);
     const int rows = m->head_r1 - m->head_r0;
     bnk::GemmArgs a = {};
-    a.W = m->t_head; a.M = rows; a.K = h.hidden; a.tiled = 1; a.image = m->IMG_H; a.ncol = ncol; a.out = m->LOGITS; a.out_stride = AS; a.err = m->ctx->err_dev;
-    if (m->GROUPS && bnk::gemm_wants_split(m->ctx->sm_count, rows, h.hidden, ncol)) a.groups = m->GROUPS;
+    a.W = m->t_head; a.M = rows; a.K = h.hidden; a.tiled = 1; a.image = m->IMG_HD; a.ncol = ncol; a.out = m->LOGITS; a.out_stride = AS; a.err = m->ctx->err_dev;
     cudaError_t e = bnk::launch_gemm(st, m->ctx->sm_count, a, m->use_pdl);
     if (e != cudaSuccess) return bn_cuda_fail(e, "bn_model_head_batch");
     bnk::argmax_first(st, m->LOGITS, rows, m->NEXT, m->AMV, m->AMI, cols, m->CAND, m->head_r0);

@@ -142,6 +142,60 @@ def split_head_rows(vocab: int, world: int, tile: int = 128) -> List[Tuple[int, 
     return out
 
 
+class NoLanes:
+    """Head work and stage work on one queue (the default): nothing to order."""
+
+    def head_begin(self, m: int): pass
+    def head_end(self, m: int): pass
+    def stage_begin(self, n: int): pass
+    def stage_end(self, n: int): pass
+    def finish(self): pass
+
+
+class TwoCudaStreams:
+    """Head work on a second, high-priority CUDA stream: on every rank but the first it then overlaps the stage passes
+    (which are full of small launches that leave most of the GPU idle), and every rank answers the head collectives at
+    once instead of after its current pass. `ctx` is the library context whose kernels follow torch's current stream."""
+
+    def __init__(self, torch, ctx, work_stream, n_units: int):
+        self.torch, self.ctx, self.work, self.U = torch, ctx, work_stream, n_units
+        self.side = torch.cuda.Stream(device=work_stream.device, priority=-1)
+        self.ev_stage, self.ev_head = {}, {}
+
+    def _on(self, stream):
+        self.torch.cuda.set_stream(stream)
+        self.ctx.use_stream(stream.cuda_stream)
+
+    def head_begin(self, m: int):
+        ev = self.ev_stage.pop(m, None)
+        if ev is not None:
+            self.side.wait_event(ev)
+        self._on(self.side)
+
+    def head_end(self, m: int):
+        ev = self.torch.cuda.Event()
+        ev.record(self.side)
+        self.ev_head[m] = ev
+        self._on(self.work)
+
+    def stage_begin(self, n: int):
+        ev = self.ev_head.pop(n - self.U, None)
+        if ev is not None:
+            self.work.wait_event(ev)
+
+    def stage_end(self, n: int):
+        ev = self.torch.cuda.Event()
+        ev.record(self.work)
+        self.ev_stage[n] = ev
+        self.ev_stage.pop(n - 2 * self.U, None)
+
+    def finish(self):
+        for ev in self.ev_head.values():
+            self.work.wait_event(ev)
+        self.ev_head.clear()
+        self.ev_stage.clear()
+
+
 class ShardedHeadPipeline:
     """The same ring of stages with the output head spread over all of them (the reference charges the whole head to the
     last GPU of its split, runtime_vk/gpu_fleet.h:1013-1020, which makes that stage the long one at 4 blocks per GPU).
@@ -159,12 +213,21 @@ class ShardedHeadPipeline:
     rank every rank reaches collective m without needing anything a later collective would provide - the schedule
     cannot deadlock even on a backend whose collectives block the host.
 
-    stage_fn(u, step, pos, tok_first, tok_in, hidden_in, hidden_out); picks are collected on rank 0."""
+    stage_fn(u, step, pos, tok_first, tok_in, hidden_in, hidden_out); picks are collected on rank 0.
+
+    `lanes` (optional) lets the head work run on a second device queue beside the stage work. It is told where each kind
+    of work starts and ends, in the order the host issues it, and has to keep three orderings between the two queues:
+    head work of instance m after stage work of m (the last stage's pass wrote the hidden state that is broadcast);
+    stage work of instance n after head work of n - units (rank 0: the token it enters with; last stage: its pass
+    overwrites the hidden state the head read); everything joined at finish(). The host-side order of the collectives is
+    the same with and without it, so the deadlock argument above does not change. See `NoLanes` for the interface."""
 
     def __init__(self, dist, rank: int, world: int, n_units: int, stage_fn: Callable, head_fn: Callable, pick_fn: Callable,
-                 new_hidden: Callable, new_token: Callable, new_cand: Callable, fwd_group=None, head_group=None, mark: Callable = None):
+                 new_hidden: Callable, new_token: Callable, new_cand: Callable, fwd_group=None, head_group=None, mark: Callable = None,
+                 lanes=None):
         self.dist, self.rank, self.world, self.U = dist, rank, world, n_units
         self.mark = mark or (lambda name: None)        # profiling aid: called at the phase boundaries of every slot
+        self.lanes = lanes or NoLanes()
         self.stage_fn, self.head_fn, self.pick_fn = stage_fn, head_fn, pick_fn
         self.first, self.last = rank == 0, rank == world - 1
         self.fwd, self.head = fwd_group, head_group
@@ -179,6 +242,7 @@ class ShardedHeadPipeline:
 
     def _head_work(self, m: int, collect: bool):
         d, u, P = self.dist, m % self.U, self.world
+        self.lanes.head_begin(m)
         self.mark("slot")
         if P > 1:
             d.broadcast(self.h_fin[u], src=P - 1, group=self.head, async_op=True).wait()
@@ -196,6 +260,7 @@ class ShardedHeadPipeline:
             self.mark("pick")
             if collect:
                 self.picks[u].append(self.t_in[u].clone())
+        self.lanes.head_end(m)
 
     def run(self, first_tokens, pos0, n_steps: int, collect: bool = True):
         d, U, P = self.dist, self.U, self.world
@@ -221,7 +286,9 @@ class ShardedHeadPipeline:
                     send_h[u] = None
                 out = self.h_out[u]
             self.mark("recv")
+            self.lanes.stage_begin(n)
             self.stage_fn(u, step, pos, first_tokens[u] if (self.first and step == 0) else None, tok_in, hin, out)
+            self.lanes.stage_end(n)
             self.mark("stage")
             if not self.last:
                 send_h[u] = d.isend(out, dst=self.rank + 1, group=self.fwd)
@@ -230,6 +297,7 @@ class ShardedHeadPipeline:
         for h in send_h:
             if h is not None:
                 h.wait()
+        self.lanes.finish()
         if not (self.first and collect):
             return None
         return [[int(t.item()) if t.numel() == 1 else [int(v) for v in t.tolist()] for t in row] for row in self.picks]

@@ -220,10 +220,29 @@ WORKER_SH = textwrap.dedent('''
                 if v > best or (v == best and i < idx):
                     best, idx = v, i
             tok[c] = idx
+    class Lanes:                           # records what a two-queue implementation is told, in host order
+        def __init__(self): self.log = []
+        def head_begin(self, m): self.log.append(("hb", m))
+        def head_end(self, m): self.log.append(("he", m))
+        def stage_begin(self, n): self.log.append(("sb", n))
+        def stage_end(self, n): self.log.append(("se", n))
+        def finish(self): self.log.append(("fin", -1))
+    lanes = Lanes()
     p = ShardedHeadPipeline(dist, rank, world, U, stage, head_fn, pick_fn, lambda: torch.zeros(MB * H),
-                            lambda: torch.zeros(MB, dtype=torch.int32), lambda n: torch.zeros(n * MB * 2), fwd, head)
+                            lambda: torch.zeros(MB, dtype=torch.int32), lambda n: torch.zeros(n * MB * 2), fwd, head, lanes=lanes)
     first = [[3 + u * MB + c for c in range(MB)] for u in range(U)]
     picks = p.run(first, [10 * u for u in range(U)], T)
+    # the orderings a second queue has to be able to express with events that already exist when they are needed:
+    at = {e: i for i, e in enumerate(lanes.log)}
+    N = T * U
+    assert lanes.log[-1] == ("fin", -1) and len(lanes.log) == 4 * N + 1
+    for n in range(N):
+        assert at[("sb", n)] < at[("se", n)] and at[("hb", n)] < at[("he", n)]
+        assert at[("se", n)] < at[("hb", n)], "head work of an instance is issued after its stage work"
+        if n >= U:
+            assert at[("he", n - U)] < at[("sb", n)], "the pick of the previous step is issued before the stage work that needs it"
+    for (k0, _), (k1, _) in zip(lanes.log, lanes.log[1:]):      # head and stage sections never nest
+        assert (k0, k1) not in (("hb", "sb"), ("sb", "hb"), ("hb", "hb"), ("sb", "sb"))
     if rank == 0:
         want = []
         for u in range(U):
