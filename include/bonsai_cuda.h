@@ -252,7 +252,9 @@ int bn_model_set_head_rows(bn_model *m, int row_begin, int row_end);
 /* One shard of the head for ncol sequences: (in, in_off) holds the final hidden state, ncol x hidden fp32; output norm,
  * rotation, this model's rows of the head and the first maximum over them. Writes ncol candidates to (out, out_off):
  * 8 bytes each, fp32 value then int32 row in the whole vocabulary (0x7FFFFFFF when no row of the shard qualified).
- * Enqueues only. */
+ * Enqueues only. It reads the hidden states where they lie and uses no scratch that a stage pass uses, so it may be
+ * enqueued on another stream (bn_use_stream around the call) while a stage pass of the same model runs; two head calls
+ * must not overlap each other. */
 int bn_model_head_batch(bn_model *m, int ncol, const bn_buf *in, size_t in_off, bn_buf *out, size_t out_off);
 /* The pick over all shards: (cands, cands_off) holds n_shards x ncol candidates, shards in ascending row order; the
  * first maximum of every sequence (Sampler::pick's rule, runtime_vk/bonsai_forward.h:2568-2570: greater value, then
