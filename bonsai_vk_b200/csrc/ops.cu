@@ -375,7 +375,7 @@ k_gdn_split(int heads, int qk_heads, int hidden, const float *__restrict__ qkv, 
             float *__restrict__ y, float scale) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    __shared__ float sq[128], sk[128], sv[32], so[32], sgb[2];
+    __shared__ float sq[128], sk[128], sv[32], so[128], sgb[2];   // so: the head's 128 outputs, every quarter pushed here by its CTA
     extern __shared__ float4 dyn[];                // [3][hidden/4]: normed residual, row h of ssm_alpha, row h of ssm_beta
     const int unit = blockIdx.x, h = unit >> 2, q4 = unit & 3, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hq = h % qk_heads, n4 = hidden / 4;
@@ -464,22 +464,26 @@ k_gdn_split(int heads, int qk_heads, int hidden, const float *__restrict__ qkv, 
 #pragma unroll
         for (int e = 0; e < 4; ++e) { s[e] = fmaf(kk[e], u, s[e]); Sr[lane + 32 * e] = s[e]; }
         const float ov = warp_tree128(__fmul_rn(s[0], qq[0]), __fmul_rn(s[1], qq[1]), __fmul_rn(s[2], qq[2]), __fmul_rn(s[3], qq[3]));
-        if (lane == 0) so[jl] = __fmul_rn(ov, scale);
+        // lanes 0..3 push the value into the so[] of the cluster's four CTAs (distributed shared memory): after the one
+        // cluster barrier below everybody reads its own shared memory only, so nobody has to wait for a neighbour to leave
+        if (lane < 4) cluster.map_shared_rank(so, lane)[j] = __fmul_rn(ov, scale);
     }
-    cluster.sync();                                 // the four quarters of the head's output are in the four CTAs' so[]
+    // this CTA's share of the gate, off the tail (a double-precision exp): lane l of warp 0 finishes output q4 * 32 + l
+    float gz = 0.0f, nw = 0.0f;
+    if (warp == 0) { gz = silu_f(z[h * 128 + q4 * 32 + lane]); nw = ssm_norm[q4 * 32 + lane]; }
+    cluster.sync();                                 // the head's 128 outputs are in every CTA's so[]
     if (warp == 0) {
-        // per-head RMS over all 128 outputs: lane l holds elements l, l+32, l+64, l+96 = index l of quarters 0..3
+        // per-head RMS over all 128 outputs: lane l holds elements l, l+32, l+64, l+96
         float e[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) e[i] = cluster.map_shared_rank(so, i)[lane];
+        for (int i = 0; i < 4; ++i) e[i] = so[i * 32 + lane];
         const float ss = warp_tree128(__fmul_rn(e[0], e[0]), __fmul_rn(e[1], e[1]), __fmul_rn(e[2], e[2]), __fmul_rn(e[3], e[3]));
         const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.0f), eps)));
         const int sub = heads / qk_heads, hd = sub * (h % qk_heads) + h / qk_heads;
         const int d = q4 * 32 + lane;               // this CTA finishes its own quarter
-        const float nrm = __fmul_rn(__fmul_rn(e[q4], inv), ssm_norm[d]);
-        y[hd * 128 + d] = __fmul_rn(silu_f(z[h * 128 + d]), nrm);
+        const float nrm = __fmul_rn(__fmul_rn(so[d], inv), nw);
+        y[hd * 128 + d] = __fmul_rn(gz, nrm);
     }
-    cluster.sync();                                 // nobody leaves while a neighbour may still read its shared memory
 }
 
 // per-head RMS (no weight; 128 squares, tree), * ssm_norm, swiglu(z, .), v-grouped permutation
