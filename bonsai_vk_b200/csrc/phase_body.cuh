@@ -39,7 +39,8 @@ struct SL {   // shared-memory layout, byte offsets from a 128-byte aligned base
     static constexpr int bars = ring + STAGES * STAGE_BYTES;               // full[STAGES], empty[STAGES], abort flag
     static constexpr int op = bars + (2 * STAGES + 16) * 8 + 64;                  // the running phase's record (whole-token kernel)
     static constexpr int feed = op + 512;                                  // whole-token kernel: this CTA's item table of the token's projections
-    static constexpr int hinv = feed + 32 * 216;                           // norm factors (survive until the next norm)
+    static constexpr int btab = feed + 32 * 216;                           // operand-build table, [4][32] x 16 bytes (build_btab)
+    static constexpr int hinv = btab + 2048;                               // norm factors (survive until the next norm)
     static constexpr int codes = hinv + 128 * 4;                           // int8 codes of the whole input (K bytes)
     static constexpr int ds = codes + MAXK;                                // (fp16 d | fp16 s) per sub-block
     static constexpr int red = ds + (MAXK / 128) * 16;
@@ -63,6 +64,7 @@ struct Smem {
     int8_t *codes;
     uint32_t *dsw;
     float *red, *sv, *accs, *hinv, *xs;
+    uint4 *btab;
     uint64_t *full, *empty, *done;
     volatile int *abort;
     volatile uint32_t *red_seq;
@@ -77,6 +79,7 @@ __device__ __forceinline__ Smem carve(unsigned char *smem) {
     s.abort = reinterpret_cast<volatile int *>(s.done + 16);
     s.red_seq = reinterpret_cast<volatile uint32_t *>(s.abort + 1);
     s.hinv = reinterpret_cast<float *>(smem + SL::hinv);
+    s.btab = reinterpret_cast<uint4 *>(smem + SL::btab);
     s.codes = reinterpret_cast<int8_t *>(smem + SL::codes);
     s.dsw = reinterpret_cast<uint32_t *>(smem + SL::ds);
     s.red = reinterpret_cast<float *>(smem + SL::red);
@@ -173,43 +176,54 @@ __device__ __forceinline__ void fwht_smem(float *s, int N, float inv) {
     csync();
 }
 
-// Operand registers of one block for this lane, straight from the block's int8 codes (32 dwords in element
-// order). Word L pairs with A-register L (quant.cuh: three byte pairs x five levels, then the qh pair):
-// bytes 1 and 3 hold the activation codes of the two weight bytes' elements at level t (even column) or
-// t+1 (odd column), zero when that element lies outside this lane's sub-block column; bytes 0 and 2 are
-// zero (they face the residue bytes of the product registers). Same table as quant.cuh coef().
-__device__ __forceinline__ void build_breg(const uint32_t *c32, int g, int tig, uint2 (&B)[8]) {
-    const int csb = g >> 1;
-    const bool odd = g & 1;
-    const int dwf = (tig == 0) ? 0 : (tig == 1) ? 2 : (tig == 2) ? 3 : 5;
-    const int dws = tig < 2 ? 1 : 4;
-    uint32_t w[16];
-#pragma unroll
-    for (int hd = 0; hd < 3; ++hd) {
+// Operand registers of one block for a lane, straight from the block's int8 codes (32 dwords in element order). Word L
+// pairs with A-register L (quant.cuh: three byte pairs x five levels, then the qh pair): bytes 1 and 3 hold the
+// activation codes of the two weight bytes' elements at level t (even column) or t+1 (odd column), zero when that element
+// lies outside this lane's sub-block column; bytes 0 and 2 are zero (they face the residue bytes of the product
+// registers). Same table as quant.cuh coef().
+// Which code dword a word comes from and which two of its bytes it takes depends on the lane only, so it is worked out
+// once per kernel (build_btab, before the kernel waits for its input) and kept in shared memory as one entry per (lane,
+// word): byte offset of the dword << 16 | byte-permute selector (0x4444 = all zero). Building a block's 16 words is then
+// a load and a permute per word.
+__device__ __forceinline__ void build_btab(uint4 *btab, int tid) {          // the first 512 threads, one entry each
+    const int lane = tid >> 4, i = tid & 15, g = lane >> 2, tig = lane & 3, csb = g >> 1, odd = g & 1;
+    uint32_t off = 0u, sel = 0x4444u;
+    if (i < 15) {
+        const int hd = i / 5, t = i - hd * 5;
+        const int dwf = (tig == 0) ? 0 : (tig == 1) ? 2 : (tig == 2) ? 3 : 5;
+        const int dws = tig < 2 ? 1 : 4;
         const int dw = hd < 2 ? dwf : dws;
         const int h = hd == 0 ? 0 : (hd == 1 ? 1 : (tig & 1));
-        const uint32_t sel = h ? 0x3414u : 0x2404u;          // [0, b_h, 0, b_(h+2)]
         const bool cls_a = dw < 4;                            // bytes 0..15 vs bytes 16..23
         const int base = cls_a ? dw : 16 + dw, stride = cls_a ? 4 : 2;
-        uint32_t P[6];
-#pragma unroll
-        for (int t = 0; t < 5; ++t) {
-            const int sb = cls_a ? (t >> 1) : (t < 2 ? 2 : 3);
-            const uint32_t x = c32[base + stride * t];
-            P[t] = (sb == csb) ? __byte_perm(x, 0u, sel) : 0u;
+        const int ts = t + odd;                               // odd columns pair level t with the element of level t + 1
+        if (ts <= 4) {
+            const int sb = cls_a ? (ts >> 1) : (ts < 2 ? 2 : 3);
+            if (sb == csb) { off = uint32_t(base + stride * ts); sel = h ? 0x3414u : 0x2404u; }     // [0, b_h, 0, b_(h+2)]
         }
-        P[5] = 0u;
-#pragma unroll
-        for (int t = 0; t < 5; ++t) w[hd * 5 + t] = odd ? P[t + 1] : P[t];
+    } else {
+        const int t = tig + odd;                              // qh pair: level tig, elements 120+2t, 121+2t
+        if (csb == 3 && t <= 3) { off = uint32_t(30 + (t >> 1)); sel = (t & 1) ? 0x3424u : 0x1404u; }
     }
-    {
-        const int t = tig + (odd ? 1 : 0);                    // qh pair: level tig, elements 120+2t, 121+2t
-        uint32_t v = 0u;
-        if (csb == 3 && t <= 3) v = __byte_perm(c32[30 + (t >> 1)], 0u, (t & 1) ? 0x3424u : 0x1404u);
-        w[15] = v;
-    }
+    reinterpret_cast<uint32_t *>(btab)[((i >> 2) * 32 + lane) * 4 + (i & 3)] = ((off * 4u) << 16) | sel;
+}
+struct BTab { uint4 e[4]; };
+__device__ __forceinline__ BTab load_btab(const uint4 *btab, int lane) {
+    BTab t;
 #pragma unroll
-    for (int m = 0; m < 8; ++m) B[m] = make_uint2(w[2 * m], w[2 * m + 1]);
+    for (int k = 0; k < 4; ++k) t.e[k] = btab[k * 32 + lane];
+    return t;
+}
+__device__ __forceinline__ uint32_t breg_word(const unsigned char *cb, uint32_t e) {
+    return __byte_perm(*reinterpret_cast<const uint32_t *>(cb + (e >> 16)), 0u, e & 0xFFFFu);
+}
+__device__ __forceinline__ void build_breg(const uint32_t *c32, const BTab &t, uint2 (&B)[8]) {
+    const unsigned char *cb = reinterpret_cast<const unsigned char *>(c32);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        B[2 * k] = make_uint2(breg_word(cb, t.e[k].x), breg_word(cb, t.e[k].y));
+        B[2 * k + 1] = make_uint2(breg_word(cb, t.e[k].z), breg_word(cb, t.e[k].w));
+    }
 }
 
 struct RowRegs { uint32_t h0, h1, h2, hq; };
@@ -679,8 +693,9 @@ __device__ __forceinline__ void main_loop(const PhaseArgs &a, const Work &w, con
             fresh = false;
             if (active) {
                 const int b0 = chunk * CH + 2 * warp;
-                build_breg(reinterpret_cast<const uint32_t *>(s.codes) + b0 * 32, g, tig, B0);
-                build_breg(reinterpret_cast<const uint32_t *>(s.codes) + b0 * 32 + 32, g, tig, B1);
+                const BTab bt = load_btab(s.btab, lane);
+                build_breg(reinterpret_cast<const uint32_t *>(s.codes) + b0 * 32, bt, B0);
+                build_breg(reinterpret_cast<const uint32_t *>(s.codes) + b0 * 32 + 32, bt, B1);
                 const uint32_t w0 = s.dsw[b0 * 4 + tig], w1 = s.dsw[b0 * 4 + 4 + tig];
                 d0 = half_bits_to_float(w0); s0w = half_bits_to_float(w0 >> 16);
                 d1 = half_bits_to_float(w1); s1w = half_bits_to_float(w1 >> 16);

@@ -25,7 +25,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_phase_gemv(const PhaseArgs a) {
     // constants of the prologue (norm weights, sign vector) do not depend on the previous grid either
     Preload pl;
     pl.on = false;
-    if (!copy_warp) preload(a, tid, pl);
+    if (!copy_warp) {
+        preload(a, tid, pl);
+        build_btab(s.btab, tid);          // (read after the barriers of the prologue)
+    }
     BN_STAMP(1);
     // everything above touched only constant weights; from here on we read the previous grid's output
     asm volatile("griddepcontrol.wait;" ::: "memory");

@@ -579,6 +579,7 @@ __global__ void __launch_bounds__(NT, 1) k_token(const TokenArgs ta) {
         if (tid == 0) {
             init_barriers(s);
         }
+        build_btab(s.btab, tid);
         __syncthreads();
         if (tid == 0) {
             int n = 0, cum = 0;
