@@ -287,3 +287,49 @@ def test_sharded_head_schedule_on_gloo(world, units, tmp_path):
                 p.kill()
     assert all(p.returncode == 0 for p in procs), outs
     assert "PIPELINE_OK" in outs[0]
+
+
+def test_two_cuda_streams_orders_the_two_queues():
+    """`TwoCudaStreams` against a stand-in for torch.cuda: the head queue waits for the stage work of the same instance,
+    the stage queue for the head work one step of units earlier, the library context follows the queue in use, and
+    finish() joins what is left."""
+    from bonsai_vk_b200.pipeline import TwoCudaStreams
+
+    log = []
+
+    class Event:
+        def __init__(self): self.on = None
+        def record(self, stream): self.on = stream.name
+
+    class Stream:
+        def __init__(self, device=None, priority=0, name="side"): self.device, self.name, self.cuda_stream = device, name, hash(name)
+        def wait_event(self, ev): log.append(("wait", self.name, ev.on))
+
+    event_cls, stream_cls = Event, Stream
+
+    class Cuda:
+        Event = event_cls
+        def Stream(self, device=None, priority=0): assert priority == -1; return stream_cls(device, priority)
+        def set_stream(self, s): log.append(("current", s.name))
+
+    class Torch: cuda = Cuda()
+
+    class Ctx:
+        def use_stream(self, h): log.append(("ctx", h))
+
+    work = Stream(name="work")
+    lanes = TwoCudaStreams(Torch, Ctx(), work, n_units=2)
+    lanes.stage_begin(0); lanes.stage_end(0)
+    lanes.stage_begin(1); lanes.stage_end(1)
+    lanes.head_begin(0); lanes.head_end(0)          # head work of instance 0 ...
+    lanes.stage_begin(2); lanes.stage_end(2)        # ... before the stage work of instance 2 = 0 + units
+    lanes.head_begin(1); lanes.head_end(1)
+    lanes.finish()
+    waits = [(e[1], e[2]) for e in log if e[0] == "wait"]           # (the queue that waits, the queue the event was recorded on)
+    # head 0 waits for stage 0's event (recorded on work); stage 2 waits for head 0's (recorded on side); head 1 for stage 1;
+    # finish joins head 1 into work
+    assert waits == [("side", "work"), ("work", "side"), ("side", "work"), ("work", "side")]
+    cur = [e[1] for e in log if e[0] == "current"]
+    assert cur == ["side", "work", "side", "work"]
+    assert [e[1] for e in log if e[0] == "ctx"] == [hash("side"), hash("work"), hash("side"), hash("work")]
+    assert not lanes.ev_head and not lanes.ev_stage
