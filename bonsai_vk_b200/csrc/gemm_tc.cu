@@ -16,6 +16,7 @@
 //   8 epilogue warps read D with tcgen05.ld and do the fp32 combination for their row and half of the columns
 // Every wait is bounded: on giving up the kernel records it in the error word and drains.
 #include "gemm_tc.cuh"
+#include "rotate_quant.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -514,18 +515,9 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, Cfg<NCP>::CTAS) k_ptq_g
 
 // ---- activation image: [rms norm] -> signs -> Hadamard per hat_block -> q8_1 codes and scales -----------------
 // grid (K / chunk, padded columns), 512 threads; chunk = hat_block (or 1024 without rotation)
-__device__ __forceinline__ float block_tree_sum(float *p, int n) {
-    for (int s = n >> 1; s > 0; s >>= 1) {
-        __syncthreads();
-        if (int(threadIdx.x) < s) p[threadIdx.x] = __fadd_rn(p[threadIdx.x], p[threadIdx.x + s]);
-    }
-    __syncthreads();
-    return p[0];
-}
-
 __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, int ncp) {
     pdl_sync();
-    extern __shared__ float s[];                   // chunk floats
+    extern __shared__ __align__(16) float s[];     // chunk floats
     __shared__ float part[256];
     const int cg = blockIdx.y, tid = threadIdx.x;
     const int c = cg;
@@ -547,22 +539,39 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
     }
     const float *x = a.x + size_t(cg) * a.x_stride;
     float inv = 1.0f;
+    const int lane_id = tid & 31, warp_id = tid >> 5;
     if (a.mode == PREP_NORM) {
-        // same partial sums as the stand-alone norm kernel: 256 lanes, each its consecutive run, then the tree
+        // same partial sums as the stand-alone norm kernel: 256 lanes, each its consecutive run, then the fixed tree
+        // p[i] += p[i + s], s = 128 .. 1 - run by every warp on its own (the same adds in the same order give the same float
+        // in every warp), so one barrier instead of nine
         const int per = (a.K + 255) / 256;
         if (tid < 256) {
             float acc = 0.0f;
-            for (int i = 0; i < per; ++i) {
-                const int d = tid * per + i;
-                if (d < a.K) { const float v = x[d]; acc = __fadd_rn(acc, __fmul_rn(v, v)); }
+            if (per == 16 && a.K == 4096) {
+                const float4 *xv = reinterpret_cast<const float4 *>(x + tid * 16);
+                const float4 v0 = xv[0], v1 = xv[1], v2 = xv[2], v3 = xv[3];
+                const float e[16] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w, v2.x, v2.y, v2.z, v2.w, v3.x, v3.y, v3.z, v3.w};
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc = __fadd_rn(acc, __fmul_rn(e[i], e[i]));
+            } else {
+                for (int i = 0; i < per; ++i) {
+                    const int d = tid * per + i;
+                    if (d < a.K) { const float v = x[d]; acc = __fadd_rn(acc, __fmul_rn(v, v)); }
+                }
             }
             part[tid] = acc;
         }
-        const float ss = block_tree_sum(part, 256);
-        inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, float(a.K)), a.eps)));
+        __syncthreads();
+        float v[8];
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v[w] = part[32 * w + lane_id];
+        float t = __fadd_rn(__fadd_rn(__fadd_rn(v[0], v[4]), __fadd_rn(v[2], v[6])),
+                            __fadd_rn(__fadd_rn(v[1], v[5]), __fadd_rn(v[3], v[7])));
+#pragma unroll
+        for (int s2 = 16; s2 > 0; s2 >>= 1) t = __fadd_rn(t, __shfl_xor_sync(0xFFFFFFFFu, t, s2));
+        inv = __frcp_rn(__fsqrt_rn(__fadd_rn(mean_of(t, a.K), a.eps)));
         if (a.inv_out && blockIdx.x == 0 && tid == 0) a.inv_out[size_t(cg) * a.inv_stride] = inv;
     }
-    const int lane_id = tid & 31, warp_id = tid >> 5;
     if (a.signs && chunk >= 256) {
         // Sylvester butterflies (a+c, a-c), h ascending, as hat4096.comp:41-60: h = 1, 2, 4 inside a thread's 8
         // consecutive elements, h = 8..128 across lanes; then through shared memory (h = 256..1024 inside a thread and
@@ -581,18 +590,7 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
             }
 #pragma unroll
             for (int r = 0; r < 8; ++r) v[r] = __fmul_rn(v[r], float(sg[r]));
-#pragma unroll
-            for (int h = 1; h < 8; h <<= 1)
-#pragma unroll
-                for (int r = 0; r < 8; ++r)
-                    if (!(r & h)) { const float p = v[r], q = v[r + h]; v[r] = __fadd_rn(p, q); v[r + h] = __fsub_rn(p, q); }
-#pragma unroll
-            for (int m2 = 1; m2 < 32; m2 <<= 1)
-#pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    const float pr = __shfl_xor_sync(0xFFFFFFFFu, v[r], m2);
-                    v[r] = (lane_id & m2) ? __fsub_rn(pr, v[r]) : __fadd_rn(v[r], pr);
-                }
+            fwht_regs_lanes(v, lane_id);
             float4 *dst = reinterpret_cast<float4 *>(s + tid * 8);
             dst[0] = make_float4(v[0], v[1], v[2], v[3]);
             dst[1] = make_float4(v[4], v[5], v[6], v[7]);
@@ -600,21 +598,7 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
         __syncthreads();
         const float hinv = 1.0f / sqrtf(float(chunk));
         if (chunk == 4096) {
-            const int i0 = (lane_id & 15) + 16 * warp_id + 2048 * (lane_id >> 4);
-            float u[8];
-#pragma unroll
-            for (int r = 0; r < 8; ++r) u[r] = s[i0 + 256 * r];
-#pragma unroll
-            for (int h = 1; h < 8; h <<= 1)
-#pragma unroll
-                for (int r = 0; r < 8; ++r)
-                    if (!(r & h)) { const float p = u[r], q = u[r + h]; u[r] = __fadd_rn(p, q); u[r + h] = __fsub_rn(p, q); }
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                const float pr = __shfl_xor_sync(0xFFFFFFFFu, u[r], 16);
-                u[r] = (lane_id & 16) ? __fsub_rn(pr, u[r]) : __fadd_rn(u[r], pr);
-                s[i0 + 256 * r] = __fmul_rn(u[r], hinv);        // each thread rewrites only what it read
-            }
+            fwht_4096_tail(s, warp_id, lane_id, hinv);
         } else {
             for (int h = 256; h < chunk; h <<= 1) {
                 for (int i = tid; i < (chunk >> 1); i += 512) {
@@ -650,29 +634,32 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
         }
     }
     __syncthreads();
-    // q8_1 per 32 values (a warp): d = amax/127 (0 below 1e-35), q = round-half-away(v/d), s = d * sum(q), both rounded to fp16
-    const int lane = tid & 31;
-    for (int e = tid; e < chunk; e += 512) {
-        const float v = s[e];
-        float amax = fabsf(v);
+    // q8_1 per 32 values: four threads per sub-block, eight consecutive values each (quant8_of32); the eight codes are one
+    // 8-byte store into the image, (d, s) rounded to fp16 as the q8_1 record keeps them and stored as fp32 d and -s
+    for (int sbk0 = 0; sbk0 < chunk / 32; sbk0 += 128) {
+        const int sbk = sbk0 + (tid >> 2), q4 = tid & 3;
+        const bool live = sbk < chunk / 32;
+        float e[8];
+        if (live) {
+            const float4 *src = reinterpret_cast<const float4 *>(s + sbk * 32 + q4 * 8);
+            const float4 v0 = src[0], v1 = src[1];
+            e[0] = v0.x; e[1] = v0.y; e[2] = v0.z; e[3] = v0.w; e[4] = v1.x; e[5] = v1.y; e[6] = v1.z; e[7] = v1.w;
+        } else {
 #pragma unroll
-        for (int k = 16; k > 0; k >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, k));
-        const float d = amax > 1e-35f ? __fdiv_rn(amax, 127.0f) : 0.0f;
-        const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-        float r = roundf(__fmul_rn(v, id));
-        r = fminf(fmaxf(r, -127.0f), 127.0f);
-        const int qi = int(r);
-        int sum = qi;
-#pragma unroll
-        for (int k = 16; k > 0; k >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, k);
-        const size_t b = (base + e) / 128;
-        const int sb = (e & 127) >> 5, kh = (e >> 4) & 1;
-        unsigned char *blk = image + b * blk_bytes;
-        blk[(c / 8) * 1024 + (sb * 2 + kh) * 128 + (c & 7) * 16 + (e & 15)] = uint8_t(int8_t(qi));
-        if (lane == 0) {    // (d, s) rounded to fp16 as the q8_1 record keeps them, stored as fp32 d and -s in the pair entry
-            float *ent = reinterpret_cast<float *>(blk + size_t(ncp) * 128 + (c / 8) * 256 + (sb * 4 + ((c & 7) >> 1)) * 16);
-            ent[c & 1] = half_bits_to_float(float_to_half_bits(d));
-            ent[2 + (c & 1)] = -half_bits_to_float(float_to_half_bits(__fmul_rn(d, float(sum))));
+            for (int i = 0; i < 8; ++i) e[i] = 0.0f;
+        }
+        const Q8x8 q = quant8_of32(e);
+        if (live) {
+            const int e0 = sbk * 32 + q4 * 8;
+            const size_t b = (base + e0) / 128;
+            const int sb = (e0 & 127) >> 5, kh = (e0 >> 4) & 1;
+            unsigned char *blk = image + b * blk_bytes;
+            *reinterpret_cast<uint2 *>(blk + (c / 8) * 1024 + (sb * 2 + kh) * 128 + (c & 7) * 16 + (e0 & 15)) = make_uint2(q.w0, q.w1);
+            if (q4 == 0) {
+                float *ent = reinterpret_cast<float *>(blk + size_t(ncp) * 128 + (c / 8) * 256 + (sb * 4 + ((c & 7) >> 1)) * 16);
+                ent[c & 1] = half_bits_to_float(float_to_half_bits(q.d));
+                ent[2 + (c & 1)] = -half_bits_to_float(float_to_half_bits(__fmul_rn(q.d, float(q.sum))));
+            }
         }
     }
 }

@@ -25,6 +25,7 @@
 #pragma once
 #include "phase_gemv.cuh"
 #include "quant.cuh"
+#include "rotate_quant.cuh"
 
 namespace bnk {
 namespace phase {
@@ -143,15 +144,6 @@ template <bool CG> __device__ __forceinline__ float4 ldf4(const float *p) {
     return CG ? __ldcg(reinterpret_cast<const float4 *>(p)) : *reinterpret_cast<const float4 *>(p);
 }
 
-// t / K rounded to nearest: for a power of two the product with 1/K is the same float (an exact scaling, rounded once
-// when the result is subnormal, as the quotient is) and skips the division sequence. 1 / x below is __frcp_rn, the
-// correctly rounded reciprocal, which is what the division 1.0f / x returns.
-__device__ __forceinline__ float mean_of(float t, int K) {
-    return (K & (K - 1)) == 0 ? __fmul_rn(t, __frcp_rn(float(K))) : __fdiv_rn(t, float(K));
-}
-// x * sign for sign = +1 / -1 (bn_model_set_signs refuses anything else): flipping the sign bit is the same float as the
-// product, zeros and NaNs included, and needs no int -> float conversion
-__device__ __forceinline__ float apply_sign(float x, int sg) { return __uint_as_float(__float_as_uint(x) ^ (uint32_t(sg) & 0x80000000u)); }
 __device__ __forceinline__ float warp_tree128(float e0, float e1, float e2, float e3) {
     float a = __fadd_rn(__fadd_rn(e0, e2), __fadd_rn(e1, e3));
 #pragma unroll
@@ -328,45 +320,6 @@ __device__ __forceinline__ void preload(const PhaseArgs &a, int tid, Preload &p)
     }
 }
 
-// butterflies h = 1, 2, 4 inside a thread's 8 consecutive elements, h = 8..128 across the lanes of a warp
-__device__ __forceinline__ void fwht_regs_lanes(float (&v)[8], int lane) {
-#pragma unroll
-    for (int h = 1; h < 8; h <<= 1)
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-            if (!(r & h)) { const float x = v[r], y = v[r + h]; v[r] = __fadd_rn(x, y); v[r + h] = __fsub_rn(x, y); }
-    // the upper lane of a pair takes partner - own, the lower one own + partner: one fused multiply-add with +-1 (the
-    // product is exact, so the result is the rounded difference / sum, bit for bit what fsub / fadd give)
-#pragma unroll
-    for (int m2 = 1; m2 < 32; m2 <<= 1) {
-        const float sgn = (lane & m2) ? -1.0f : 1.0f;
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const float pr = __shfl_xor_sync(0xFFFFFFFFu, v[r], m2);
-            v[r] = __fmaf_rn(v[r], sgn, pr);
-        }
-    }
-}
-// butterflies h = 256, 512, 1024 inside a thread (elements 256 apart), h = 2048 between lanes l and l^16, then the scale;
-// each thread rewrites only what it read
-__device__ __forceinline__ void fwht_4096_tail(float *xs, int warp, int lane, float hat_inv) {
-    const int i0 = (lane & 15) + 16 * warp + 2048 * (lane >> 4);
-    float u[8];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) u[r] = xs[i0 + 256 * r];
-#pragma unroll
-    for (int h = 1; h < 8; h <<= 1)
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-            if (!(r & h)) { const float x = u[r], y = u[r + h]; u[r] = __fadd_rn(x, y); u[r + h] = __fsub_rn(x, y); }
-    const float sgn = (lane & 16) ? -1.0f : 1.0f;
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        const float pr = __shfl_xor_sync(0xFFFFFFFFu, u[r], 16);
-        u[r] = __fmaf_rn(u[r], sgn, pr);
-        xs[i0 + 256 * r] = __fmul_rn(u[r], hat_inv);
-    }
-}
 // q8_1 of nsub 32-element sub-blocks of xs: 4 threads per sub-block, 8 consecutive elements each. codes / dsw point at
 // the first sub-block's codes and (d | s) word.
 __device__ __forceinline__ void q81_pass(const float *xs, int8_t *codes, uint32_t *dsw, int nsub, int tid) {
@@ -382,32 +335,11 @@ __device__ __forceinline__ void q81_pass(const float *xs, int8_t *codes, uint32_
 #pragma unroll
             for (int i = 0; i < 8; ++i) e[i] = 0.0f;
         }
-        float amax = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(e[i]));
-        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-        const float d = amax > 1e-35f ? __fdiv_rn(amax, 127.0f) : 0.0f;
-        const float id = d != 0.0f ? __frcp_rn(d) : 0.0f;
-        // codes: round half away, clamp, then the low byte of (code + 1.5 * 2^23) read as an integer is the code in
-        // two's complement (no float -> int conversion); four bytes are gathered with byte permutes and the sum of the
-        // eight codes is two byte dot products with ones
-        uint32_t q[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            float r = roundf(__fmul_rn(e[i], id));
-            r = fminf(fmaxf(r, -127.0f), 127.0f);
-            q[i] = __float_as_uint(__fadd_rn(r, 12582912.0f));
-        }
-        const uint32_t w0 = __byte_perm(__byte_perm(q[0], q[1], 0x0040u), __byte_perm(q[2], q[3], 0x0040u), 0x5410u);
-        const uint32_t w1 = __byte_perm(__byte_perm(q[4], q[5], 0x0040u), __byte_perm(q[6], q[7], 0x0040u), 0x5410u);
-        int sum = __dp4a(int(w0), 0x01010101, __dp4a(int(w1), 0x01010101, 0));
-        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+        const Q8x8 q = quant8_of32(e);
         if (live) {
             uint32_t *cw = reinterpret_cast<uint32_t *>(codes + sbk * 32 + q4 * 8);
-            cw[0] = w0; cw[1] = w1;
-            if (q4 == 0) dsw[sbk] = float_to_half_bits(d) | (float_to_half_bits(__fmul_rn(d, float(sum))) << 16);
+            cw[0] = q.w0; cw[1] = q.w1;
+            if (q4 == 0) dsw[sbk] = float_to_half_bits(q.d) | (float_to_half_bits(__fmul_rn(q.d, float(q.sum))) << 16);
         }
     }
 }
