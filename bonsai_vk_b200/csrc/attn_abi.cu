@@ -33,7 +33,8 @@ Scr scratch_layout(const bn_attn_dims &d) {
 }
 int check_dims(const bn_attn_dims *d, const char *who) {
     BN_REQUIRE(d, BN_ERR_ARG, "%s: null dims", who);
-    BN_REQUIRE(d->head_dim == 256 && d->n_head == 4 * d->n_kv && d->n_kv > 0, BN_ERR_ARG, "%s: head_dim must be 256 and n_head = 4 x n_kv", who);
+    BN_REQUIRE(d->head_dim == 256 && d->n_kv > 0 && d->n_head % d->n_kv == 0, BN_ERR_ARG, "%s: head_dim must be 256 and n_head a multiple of n_kv", who);
+    { const int g = d->n_head / d->n_kv; BN_REQUIRE((g == 1 || g == 2 || g == 4 || g == 8) && d->n_head <= 256, BN_ERR_ARG, "%s: %d query heads per kv head (1, 2, 4 or 8 are built)", who, g); }
     BN_REQUIRE(d->cap > 0 && d->cap % 2 == 0 && d->n_rot > 0 && d->n_rot <= 256 && d->n_rot % 2 == 0, BN_ERR_ARG, "%s: bad cap or rope dims", who);
     BN_REQUIRE((d->k_mode | 1) == 1 && (d->v_mode | 1) == 1, BN_ERR_ARG, "%s: kv modes are 0 (q8_0) or 1 (fp16)", who);
     return BN_OK;

@@ -21,8 +21,8 @@ int bn_gemm_act_quant(bn_ctx *ctx, const bn_buf *x, size_t x_off, size_t x_strid
     BN_RANGE(x, x_off, (size_t(ncol - 1) * x_stride + K) * 4, 4, "bn_gemm_act_quant x");
     BN_RANGE(image, image_off, bnk::gemm_image_bytes(K, ncol), 128, "bn_gemm_act_quant image");
     if (signs) {
-        BN_REQUIRE(hat_block >= 32 && hat_block <= 4096 && (hat_block & (hat_block - 1)) == 0 && K % hat_block == 0, BN_ERR_ARG,
-                   "bn_gemm_act_quant: hadamard block %d must be a power of two in [32, 4096] dividing K", hat_block);
+        BN_REQUIRE(hat_block >= 16 && hat_block <= 4096 && (hat_block & (hat_block - 1)) == 0 && K % hat_block == 0, BN_ERR_ARG,
+                   "bn_gemm_act_quant: hadamard block %d must be a power of two in [16, 4096] dividing K", hat_block);
         BN_RANGE(signs, signs_off, size_t(K) * 4, 4, "bn_gemm_act_quant signs");
     }
     bnk::PrepArgs a = {};

@@ -515,7 +515,8 @@ __global__ void __launch_bounds__(Cfg<NCP>::NWARPS * 32, Cfg<NCP>::CTAS) k_ptq_g
 
 // ---- activation image: [rms norm] -> signs -> Hadamard per hat_block -> q8_1 codes and scales -----------------
 // grid (K / chunk, padded columns), 512 threads; chunk = hat_block (or 1024 without rotation)
-__global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, int ncp) {
+// chunk = the values one CTA takes: a Hadamard block (hb), or 32 when the Hadamard block is smaller than a q8_1 sub-block
+__global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, int hb, int ncp) {
     pdl_sync();
     extern __shared__ __align__(16) float s[];     // chunk floats
     __shared__ float part[256];
@@ -527,12 +528,12 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
     if (cg >= a.ncol) {                             // padding column: zero codes and scales
         for (int e = tid * 16; e < chunk; e += 512 * 16) {
             const size_t b = (base + e) / 128;
-            const int sb = (e & 127) >> 5, kh = (e >> 4) & 1;
+            const int sb = int((base + e) & 127) >> 5, kh = (e >> 4) & 1;
             *reinterpret_cast<uint4 *>(image + b * blk_bytes + (c / 8) * 1024 + (sb * 2 + kh) * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
         }
         for (int e = tid * 32; e < chunk; e += 512 * 32) {
             const size_t b = (base + e) / 128;
-            float *ent = reinterpret_cast<float *>(image + b * blk_bytes + size_t(ncp) * 128 + (c / 8) * 256 + ((((e & 127) >> 5) * 4) + ((c & 7) >> 1)) * 16);
+            float *ent = reinterpret_cast<float *>(image + b * blk_bytes + size_t(ncp) * 128 + (c / 8) * 256 + (((int((base + e) & 127) >> 5) * 4) + ((c & 7) >> 1)) * 16);
             ent[c & 1] = 0.0f; ent[2 + (c & 1)] = 0.0f;
         }
         return;
@@ -619,8 +620,8 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
             s[i] = v;
         }
         if (a.signs) {
-            const float hinv = 1.0f / sqrtf(float(chunk));
-            for (int h = 1; h < chunk; h <<= 1) {
+            const float hinv = 1.0f / sqrtf(float(hb));
+            for (int h = 1; h < hb; h <<= 1) {
                 __syncthreads();
                 for (int i = tid; i < (chunk >> 1); i += 512) {
                     const int j = ((i & ~(h - 1)) << 1) | (i & (h - 1));
@@ -652,7 +653,7 @@ __global__ void __launch_bounds__(512) k_prep_cols(const PrepArgs a, int chunk, 
         if (live) {
             const int e0 = sbk * 32 + q4 * 8;
             const size_t b = (base + e0) / 128;
-            const int sb = (e0 & 127) >> 5, kh = (e0 >> 4) & 1;
+            const int sb = int((base + e0) & 127) >> 5, kh = (e0 >> 4) & 1;       // (a chunk may be a part of a 128-value block)
             unsigned char *blk = image + b * blk_bytes;
             *reinterpret_cast<uint2 *>(blk + (c / 8) * 1024 + (sb * 2 + kh) * 128 + (c & 7) * 16 + (e0 & 15)) = make_uint2(q.w0, q.w1);
             if (q4 == 0) {
@@ -762,11 +763,11 @@ void repack_tiles(cudaStream_t st, const uint32_t *W, int M, int K, uint32_t *ou
 }
 
 void prep_cols(cudaStream_t st, const PrepArgs &a) {
-    const int chunk = a.signs ? a.hat_block : 1024;
+    const int chunk = a.signs ? (a.hat_block < 32 ? 32 : a.hat_block) : 1024;
     const int ncp = gemm_padded_cols(a.ncol);
     static bool attr = false;
     if (!attr) { cudaFuncSetAttribute(k_prep_cols, cudaFuncAttributeMaxDynamicSharedMemorySize, 4096 * 4); attr = true; }
-    launch(k_prep_cols, dim3(a.K / chunk, ncp), dim3(512), size_t(chunk) * 4, st, a, chunk, ncp);
+    launch(k_prep_cols, dim3(a.K / chunk, ncp), dim3(512), size_t(chunk) * 4, st, a, chunk, a.signs ? a.hat_block : chunk, ncp);
 }
 
 cudaError_t launch_wait_selftest_tc(cudaStream_t st, int *err) {

@@ -344,6 +344,7 @@ bool build_token_ops(bn_model *m) {
     if (!m->fused || m->b0 != 0 || m->b1 != h.n_layer) return false;
     if (!bnk::token_supported(sm, h.hat_block, h.hidden)) return false;
     if (h.hidden > 4096 || h.ffn % 16 || D != 128) return false;               // swiglu pairs need one chunk of K
+    if (h.n_head != 4 * h.n_kv) return false;                                   // its attention phases are written for four query heads per kv head
     if ((h.cap + m->pv_splits - 1) / m->pv_splits > 512) return false;         // probabilities of one split in shared memory
     if (((h.hidden + 15) / 16 + sm - 1) / sm > 64) return false;               // multi-chunk running sums: 64 tiles per CTA
     m->cur = 0;
@@ -661,12 +662,13 @@ int bn_model_create(bn_ctx *ctx, const bn_hparams *hp, bn_model **out) {
     BN_REQUIRE(ctx && hp && out, BN_ERR_ARG, "bn_model_create: null argument");
     const bn_hparams &h = *hp;
     BN_REQUIRE(h.n_layer > 0 && h.hidden > 0 && h.ffn > 0 && h.vocab > 0, BN_ERR_ARG, "bn_model_create: bad sizes");
-    BN_REQUIRE(h.hat_block >= 128 && h.hat_block <= 4096 && (h.hat_block & (h.hat_block - 1)) == 0, BN_ERR_ARG,
-               "bn_model_create: hadamard block %d must be a power of two in [128, 4096]", h.hat_block);
+    BN_REQUIRE(h.hat_block >= 16 && h.hat_block <= 4096 && (h.hat_block & (h.hat_block - 1)) == 0, BN_ERR_ARG,
+               "bn_model_create: hadamard block %d must be a power of two in [16, 4096]", h.hat_block);   // the reference's range, bonsai_model.h:853-858
     BN_REQUIRE(h.hidden % h.hat_block == 0 && h.ffn % h.hat_block == 0, BN_ERR_ARG,
                "bn_model_create: hadamard block %d must divide hidden %d and ffn %d", h.hat_block, h.hidden, h.ffn);
     BN_REQUIRE(h.head_dim == 256 && h.gdn_dim == 128, BN_ERR_ARG, "bn_model_create: head_dim must be 256 and gdn_dim 128");
-    BN_REQUIRE(h.n_head == 4 * h.n_kv, BN_ERR_ARG, "bn_model_create: n_head must be 4 x n_kv");
+    BN_REQUIRE(h.n_kv > 0 && h.n_head % h.n_kv == 0 && h.n_head <= 256, BN_ERR_ARG, "bn_model_create: n_head must be a multiple of n_kv");
+    { const int g = h.n_head / h.n_kv; BN_REQUIRE(g == 1 || g == 2 || g == 4 || g == 8, BN_ERR_ARG, "bn_model_create: %d query heads per kv head (1, 2, 4 or 8 are built)", g); }
     BN_REQUIRE(h.n_head * h.head_dim == h.hidden, BN_ERR_ARG, "bn_model_create: n_head * head_dim must equal hidden");
     BN_REQUIRE(h.gdn_heads * h.gdn_dim == h.hidden, BN_ERR_ARG, "bn_model_create: gdn inner size must equal hidden");
     BN_REQUIRE(h.gdn_heads <= 64 && h.gdn_heads % h.gdn_qk_heads == 0, BN_ERR_ARG, "bn_model_create: bad gdn head counts");

@@ -24,8 +24,9 @@ __device__ __forceinline__ float block_tree_sum(float *p, int n) {
 
 // in-place Sylvester-Walsh-Hadamard butterflies over N floats in shared memory, h ascending
 // (reference: runtime_vk/shaders/hat4096.comp:41-60), then the 1/sqrt(N) factor.
-__device__ __forceinline__ void fwht_smem(float *s, int N, float inv) {
-    for (int h = 1; h < N; h <<= 1) {
+// N values = N / hb independent transforms of width hb side by side.
+__device__ __forceinline__ void fwht_smem(float *s, int N, int hb, float inv) {
+    for (int h = 1; h < hb; h <<= 1) {
         __syncthreads();
         for (int i = threadIdx.x; i < (N >> 1); i += blockDim.x) {
             const int j = ((i & ~(h - 1)) << 1) | (i & (h - 1));
@@ -40,16 +41,17 @@ __device__ __forceinline__ void fwht_smem(float *s, int N, float inv) {
 }
 
 // ---- rotation (+ quantisation) -------------------------------------------------------------------
-// one CTA of 512 threads per `block`-wide chunk: y = H(s . x); optional q8_1 pack of the chunk.
+// one CTA of 512 threads per span (a Hadamard block of `hb` values, or 128 values = one quantiser block when the Hadamard
+// block is smaller): y = H(s . x); optional q8_1 pack of the span.
 __global__ void __launch_bounds__(512) k_rotate_quant(const float *__restrict__ x, const int32_t *__restrict__ signs,
-                                                      int block, float inv, float *__restrict__ y,
+                                                      int block, int hb, float inv, float *__restrict__ y,
                                                       uint32_t *__restrict__ q81, uint32_t *__restrict__ table) {
     bnk::pdl_sync();
     extern __shared__ float s[];                   // block floats + 4 x 128 bytes
     int8_t *qs = reinterpret_cast<int8_t *>(s + block);
     const size_t base = size_t(blockIdx.x) * block;
     for (int i = threadIdx.x; i < block; i += blockDim.x) s[i] = __fmul_rn(x[base + i], float(signs[base + i]));
-    fwht_smem(s, block, inv);
+    fwht_smem(s, block, hb, inv);
     if (y) for (int i = threadIdx.x; i < block; i += blockDim.x) y[base + i] = s[i];
     if (q81) {
         const int grp = threadIdx.x >> 7, i = threadIdx.x & 127;       // 4 groups of 128 threads
@@ -68,7 +70,7 @@ __global__ void __launch_bounds__(512) k_rotate_inv(const float *__restrict__ x,
     extern __shared__ float s[];
     const size_t base = size_t(blockIdx.x) * block;
     for (int i = threadIdx.x; i < block; i += blockDim.x) s[i] = x[base + i];
-    fwht_smem(s, block, inv);
+    fwht_smem(s, block, block, inv);
     for (int i = threadIdx.x; i < block; i += blockDim.x) y[base + i] = __fmul_rn(s[i], float(signs[base + i]));
 }
 
@@ -690,6 +692,54 @@ __global__ void __launch_bounds__(256) k_attn_scores(bnk::AttnDims a, const floa
     if (j < nfill) score[size_t(kvh * GQA + g) * a.cap + j] = v[0];
 }
 
+// The same scores for any number of query heads per kv head (the kernel above is laid out for four): a warp takes 8
+// consecutive keys of one kv head and walks the query heads one after the other - per (key, head) the same fmaf chain over
+// the lane's 8 dims and the same xor-butterfly tree, so the same floats.
+template <int KMODE>
+__global__ void __launch_bounds__(256) k_attn_scores_any(bnk::AttnDims a, int gqa, const float *__restrict__ q16f,
+                                                         const int *__restrict__ pos_ptr, bnk::KvLayer kv,
+                                                         float *__restrict__ score, unsigned *__restrict__ counters, bnk::Cols cols) {
+    bnk::pdl_sync();
+    { const size_t col = blockIdx.z; q16f = bnk::colp(q16f, col * cols.arena); pos_ptr = bnk::colp(pos_ptr, col * cols.arena); kv.k_data = bnk::colp(kv.k_data, col * cols.kv); kv.k_scale = bnk::colp(kv.k_scale, col * cols.kv); score = bnk::colp(score, col * cols.arena); counters = bnk::colp(counters, col * cols.arena); }
+    const int kvh = blockIdx.y, lane = threadIdx.x & 31, hd = a.head_dim;
+    if (blockIdx.x == 0 && kvh == 0) for (int i = threadIdx.x; i < a.n_head; i += 256) counters[i] = 0u;
+    const int nfill = pos_ptr[0] + 1;
+    const int jb = (blockIdx.x * 8 + (threadIdx.x >> 5)) * 8;
+    if (jb >= nfill) return;
+    float kf[8][8];                              // this lane's 8 dims of the 8 keys
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int j = min(jb + u, nfill - 1);
+        const size_t row = (size_t(j) * a.n_kv + kvh) * hd;
+        if (KMODE == 1) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(kv.k_data) + row + lane * 8);
+            const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h2[e]); kf[u][2 * e] = f.x; kf[u][2 * e + 1] = f.y; }
+        } else {
+            const uint2 raw = *reinterpret_cast<const uint2 *>(reinterpret_cast<const int8_t *>(kv.k_data) + row + lane * 8);
+            const float sc = half_bits_to_float(kv.k_scale[row / 32 + (lane >> 2)]);
+            const int8_t *c8 = reinterpret_cast<const int8_t *>(&raw);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) kf[u][e] = __fmul_rn(sc, float(int(c8[e])));
+        }
+    }
+    for (int g = 0; g < gqa; ++g) {
+        const float4 *qv = reinterpret_cast<const float4 *>(q16f + size_t(kvh * gqa + g) * hd + lane * 8);
+        const float4 q0 = qv[0], q1 = qv[1];
+        const float qe[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc = fmaf(qe[e], kf[u][e], acc);
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, off));
+            if (lane == u && jb + u < nfill) score[size_t(kvh * gqa + g) * a.cap + jb + u] = acc;
+        }
+    }
+}
+
 // Softmax numerators and their sum, spread over EXPSUM_PARTS CTAs per head with the summation order of one
 // 1024-thread CTA: "virtual thread" vt adds the keys vt, vt+1024, ... ascending, and the 1024 partial sums are
 // then combined by the fixed tree (attn_qk_softmax.comp / attn_vk.h:175-190 in the regrouped order the CPU
@@ -890,7 +940,8 @@ bool g_pdl = true;
 void rotate_quant(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y, uint32_t *pack) {
     const float inv = 1.0f / sqrtf(float(block));
     uint32_t *q81 = pack, *table = pack ? pack + size_t(n / 128) * Q81_DWORDS : nullptr;
-    launch(k_rotate_quant, dim3(n / block), dim3(512), size_t(block) * 4 + 512, st, x, signs, block, inv, y, q81, table); 
+    const int span = block < 128 ? 128 : block;
+    launch(k_rotate_quant, dim3(n / span), dim3(512), size_t(span) * 4 + 512, st, x, signs, span, block, inv, y, q81, table);
 }
 void rotate_inv(cudaStream_t st, const float *x, const int32_t *signs, int n, int block, float *y, Cols cols) {
     launch(k_rotate_inv, dim3(n / block, 1, cols.z()), dim3(512), size_t(block) * 4, st, x, signs, block, 1.0f / sqrtf(float(block)), y, cols); 
@@ -964,10 +1015,26 @@ void attn_decode(cudaStream_t st, AttnDims a, const float *q16f, const float *ga
     float *total = esum + size_t(a.n_head) * 1024;
     unsigned *counters = reinterpret_cast<unsigned *>(total + a.n_head);
     const dim3 sg((a.cap + 63) / 64, a.n_kv, cols.z());
-    if (a.k_mode == 1) launch(k_attn_scores<4, 1>, sg, dim3(256), 0, st, a, q16f, pos_ptr, kv, score, counters, cols);
-    else launch(k_attn_scores<4, 0>, sg, dim3(256), 0, st, a, q16f, pos_ptr, kv, score, counters, cols);
+    const int gqa = a.n_head / a.n_kv;            // 1, 2, 4 or 8 (checked where the dimensions enter: bn_model_create, the attention ABI)
+    if (gqa == 4) {
+        if (a.k_mode == 1) launch(k_attn_scores<4, 1>, sg, dim3(256), 0, st, a, q16f, pos_ptr, kv, score, counters, cols);
+        else launch(k_attn_scores<4, 0>, sg, dim3(256), 0, st, a, q16f, pos_ptr, kv, score, counters, cols);
+    } else {
+        if (a.k_mode == 1) launch(k_attn_scores_any<1>, sg, dim3(256), 0, st, a, gqa, q16f, pos_ptr, kv, score, counters, cols);
+        else launch(k_attn_scores_any<0>, sg, dim3(256), 0, st, a, gqa, q16f, pos_ptr, kv, score, counters, cols);
+    }
     launch(k_attn_expsum, dim3(a.n_head, EXPSUM_PARTS, cols.z()), dim3(1024), 0, st, a, pos_ptr, score, 1.0f / sqrtf(float(a.head_dim)), p16f, esum, cols);
-    launch(k_attn_pv<4>, dim3(a.n_kv, splits, cols.z()), dim3(256), size_t(4) * ((a.cap + splits - 1) / splits) * 4, st, a, static_cast<const float *>(p16f), static_cast<const float *>(total), pos_ptr, kv, splits, pv_part, cols);
+    const dim3 pg(a.n_kv, splits, cols.z());
+    const size_t ps_bytes = size_t(gqa) * ((a.cap + splits - 1) / splits) * 4;
+    const float *pe = static_cast<const float *>(p16f), *tot = static_cast<const float *>(total);
+    if (gqa == 4) launch(k_attn_pv<4>, pg, dim3(256), ps_bytes, st, a, pe, tot, pos_ptr, kv, splits, pv_part, cols);
+    else if (gqa == 1) launch(k_attn_pv<1>, pg, dim3(256), ps_bytes, st, a, pe, tot, pos_ptr, kv, splits, pv_part, cols);
+    else if (gqa == 2) launch(k_attn_pv<2>, pg, dim3(256), ps_bytes, st, a, pe, tot, pos_ptr, kv, splits, pv_part, cols);
+    else {
+        static bool attr = false;
+        if (!attr) { cudaFuncSetAttribute(k_attn_pv<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); attr = true; }
+        launch(k_attn_pv<8>, pg, dim3(256), ps_bytes, st, a, pe, tot, pos_ptr, kv, splits, pv_part, cols);
+    }
     if (!combine) return;
     const int n = a.n_head * a.head_dim;
     launch(k_attn_combine, dim3((n + 255) / 256, 1, cols.z()), dim3(256), 0, st, a, pv_part, splits, pos_ptr, gate, pregate, gated, cols); 

@@ -51,7 +51,7 @@ struct SL {   // shared-memory layout, byte offsets from a 128-byte aligned base
     // everything from `codes` on is free for the other phases of the whole-token kernel while no projection runs
     static constexpr int scratch = codes;
 };
-__host__ __device__ constexpr int smem_bytes(int hat_block) { return SL::xs + hat_block * 4 + 128; }
+__host__ __device__ constexpr int smem_bytes(int hat_block) { return SL::xs + (hat_block < 32 ? 32 : hat_block) * 4 + 128; }
 
 // the kernel's dynamic shared memory, named here so that every function can form its addresses from the symbol itself
 // (a pointer passed through a function argument would turn shared-memory accesses into generic ones)
@@ -153,8 +153,10 @@ __device__ __forceinline__ float warp_tree128(float e0, float e1, float e2, floa
 
 // Sylvester-Walsh-Hadamard butterflies, h ascending (hat4096.comp:41-60), any thread mapping gives the
 // same floats because every stage is a set of independent (a+c, a-c) pairs.
-__device__ __forceinline__ void fwht_smem(float *s, int N, float inv) {
-    for (int h = 1; h < N; h <<= 1) {
+// N values = N / hb independent transforms of width hb side by side (a butterfly of distance h < hb never leaves its
+// hb-aligned block).
+__device__ __forceinline__ void fwht_smem(float *s, int N, int hb, float inv) {
+    for (int h = 1; h < hb; h <<= 1) {
         csync();
         for (int i = threadIdx.x; i < (N >> 1); i += NT) {
             const int j = ((i & ~(h - 1)) << 1) | (i & (h - 1));
@@ -449,8 +451,10 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
     }
     const int HB = a.hat_block;
     const bool fast = HB >= 256;                 // register/shuffle butterflies need 8 elements x >= 32 threads
-    for (int hb = 0; hb < K / HB; ++hb) {
-        const int base = hb * HB;
+    // a span = one Hadamard block, or the 32 values of a q8_1 sub-block when the Hadamard block is smaller than that
+    const int SP = HB < 32 ? 32 : HB;
+    for (int hb = 0; hb < K / SP; ++hb) {
+        const int base = hb * SP;
         csync();
         // the input value at absolute index t, before the sign
         auto input = [&](int t) -> float {
@@ -541,11 +545,11 @@ __device__ __forceinline__ void prologue(const PhaseArgs &a, const Smem &s, cons
             }
             csync();
         } else {
-            for (int i = tid; i < HB; i += NT) { const int t = base + i; xs[i] = apply_sign(input(t), a.signs[t]); }
-            fwht_smem(xs, HB, a.hat_inv);
+            for (int i = tid; i < SP; i += NT) { const int t = base + i; xs[i] = apply_sign(input(t), a.signs[t]); }
+            fwht_smem(xs, SP, HB, a.hat_inv);
         }
         BN_STAMP(4);
-        q81_pass(xs, codes + base, dsw + (base >> 5), HB / 32, tid);
+        q81_pass(xs, codes + base, dsw + (base >> 5), SP / 32, tid);
     }
     csync();
 }

@@ -119,7 +119,7 @@ bool phase_supported(int M, int K, int hat_block) {
     const int nb = K / 128;
     if (K % 512 || K > phase::MAXK || M < 1) return false;
     if (nb > phase::MAXCH && nb % phase::MAXCH) return false;
-    if (hat_block < 32 || hat_block > 4096 || K % hat_block || (hat_block & (hat_block - 1))) return false;
+    if (hat_block < 16 || hat_block > 4096 || K % hat_block || (hat_block & (hat_block - 1))) return false;
     return true;
 }
 

@@ -102,7 +102,7 @@ __device__ __forceinline__ void embed_phase(const TokenArgs &ta, const Smem &s, 
             const int trit = int((v * 3u) >> 8);
             xs[i] = __fmul_rn(float(trit) - 1.0f, half_bits_to_float(blk[6] >> 16));
         }
-        fwht_smem(xs, HB, inv);
+        fwht_smem(xs, HB, HB, inv);
         for (int i = tid; i < HB; i += NT) ta.res[base + i] = __fmul_rn(xs[i], float(ta.signs[base + i]));
     }
     csync();

@@ -1,4 +1,4 @@
-"""One GQA decode-attention layer (16 query / 4 KV heads, head_dim 256, rope theta 1e7 on the first 64 dims, cache
+"""One GQA decode-attention layer (16 query / 4 KV heads - and 8, 2 or 1 query heads per KV head -, head_dim 256, rope theta 1e7 on the first 64 dims, cache
 filled from N(0,1) rows) at contexts 4096 and 32768, through the op-level C ABI: q8_0 K and V, and the reference's
 own cache layout (fp16 K with q8_0 V, runtime_vk/shaders/attn_norm_rope2.comp:26-49; fp16 K and V, attn_vk.h).
 Checked against the CPU oracle on the same rows: cache bytes (q8_0 codes, fp16 words) and per-head outputs.
@@ -21,9 +21,12 @@ def _p(a):
     return a.ctypes.data_as(C.c_void_p)
 
 
-@pytest.mark.parametrize("ctx_len,k_mode,v_mode", [(300, 0, 0), (4096, 0, 0), (32768, 0, 0), (300, 1, 0), (4096, 1, 0), (4096, 1, 1)])
-def test_decode_attention_layer(ctx, ctx_len, k_mode, v_mode):
-    n_head, n_kv, hd = 16, 4, 256
+@pytest.mark.parametrize("ctx_len,k_mode,v_mode,heads", [(300, 0, 0, (16, 4)), (4096, 0, 0, (16, 4)), (32768, 0, 0, (16, 4)), (300, 1, 0, (16, 4)),
+                                                         (4096, 1, 0, (16, 4)), (4096, 1, 1, (16, 4)),
+                                                         # other numbers of query heads per kv head (8, 2, 1): the general scores kernel
+                                                         (1500, 0, 0, (8, 1)), (1500, 1, 0, (8, 4)), (777, 0, 0, (4, 4)), (777, 1, 1, (8, 1))])
+def test_decode_attention_layer(ctx, ctx_len, k_mode, v_mode, heads):
+    n_head, n_kv, hd = heads[0], heads[1], 256
     QD, KD = n_head * hd, n_kv * hd
     rng = np.random.default_rng(ctx_len)
     k_rows = rng.standard_normal((ctx_len, KD)).astype(np.float32)

@@ -80,8 +80,11 @@ def test_gemm_columns_equal_the_single_column_projection(ctx, oracle, M, K, ncol
         assert rel.max() <= 1e-5
 
 
-def test_gemm_with_rotation(ctx, oracle):
-    M, K, ncol, hb = 1024, 3072, 5, 1024
+@pytest.mark.parametrize("hb", [1024, 256, 64, 32, 16])
+def test_gemm_with_rotation(ctx, oracle, hb):
+    """Rotation per Hadamard block in front of the multi-column projection, down to the smallest block the reference
+    accepts (16, runtime_vk/bonsai_model.h:853-858: smaller than a q8_1 sub-block)."""
+    M, K, ncol = 1024, 3072, 5
     rng = np.random.default_rng(11)
     W = ptq.synth_matrix(rng, M, K)
     X = rng.standard_normal((ncol, K)).astype(np.float32)

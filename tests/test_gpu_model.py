@@ -154,6 +154,57 @@ def test_explicit_layer_list_model(ctx):
     gm.close(); om.close()
 
 
+@pytest.mark.parametrize("n_kv", [2, 4])
+def test_other_query_heads_per_kv_head(ctx, n_kv):
+    """The tiny model with 2 and 1 query heads per kv head instead of 4 (n_head x head_dim = hidden stays, as the reference's
+    own plan check demands, runtime_vk/bonsai_model.h:993-998): prompt and greedy decode against the oracle, logits bit for
+    bit."""
+    hp = synth.tiny(n_kv=n_kv)
+    tensors, signs = synth.make_model(hp, seed=11 + n_kv)
+    gm, om = Model(ctx, hp, tensors, signs), OracleModel(hp, tensors, signs)
+    rng = np.random.default_rng(n_kv)
+    toks = [int(x) for x in rng.integers(0, hp.vocab, size=6)]
+    gt = ot = None
+    for pos, t in enumerate(toks):
+        gt = gm.token(t, pos)
+        ol, _ = om.token(t, pos)
+        ot = om.argmax(ol)
+        assert np.array_equal(gm.logits().view(np.uint32), ol.view(np.uint32)), f"logits differ at position {pos}"
+    stream_g, stream_o = [], []
+    for i in range(10):
+        stream_g.append(gt); stream_o.append(ot)
+        gt = gm.token(gt, len(toks) + i)
+        ol, _ = om.token(ot, len(toks) + i)
+        ot = om.argmax(ol)
+    assert stream_g == stream_o
+    gm.close(); om.close()
+
+
+@pytest.mark.parametrize("hat_block", [16, 64, 256])
+def test_small_hadamard_blocks(ctx, hat_block):
+    """The tiny model with Hadamard blocks of 16, 64 and 256 (the reference covers powers of two from 16 to 4096,
+    runtime_vk/bonsai_model.h:853-858): the fused schedule and the stand-alone kernel lineage (BONSAI_NO_FUSE) against the
+    oracle, logits bit for bit."""
+    import os
+    hp = synth.tiny(hat_block=hat_block)
+    tensors, signs = synth.make_model(hp, seed=hat_block)
+    om = OracleModel(hp, tensors, signs)
+    toks = [int(x) for x in np.random.default_rng(hat_block).integers(0, hp.vocab, size=5)]
+    want = [om.token(t, pos)[0].copy() for pos, t in enumerate(toks)]
+    for no_fuse in (False, True):
+        if no_fuse:
+            os.environ["BONSAI_NO_FUSE"] = "1"
+        try:
+            gm = Model(ctx, hp, tensors, signs)
+        finally:
+            os.environ.pop("BONSAI_NO_FUSE", None)
+        for pos, t in enumerate(toks):
+            gm.token(t, pos)
+            assert np.array_equal(gm.logits().view(np.uint32), want[pos].view(np.uint32)), f"hat_block {hat_block}, no_fuse {no_fuse}: logits differ at position {pos}"
+        gm.close()
+    om.close()
+
+
 def test_whole_token_kernel_matches_the_oracle(ctx):
     """The one-launch-per-token kernel (opt-in, BONSAI_TOKEN_KERNEL=1: every phase of a token in one cooperative launch with
     grid barriers, the weight ring fed by the compute warps themselves) runs the same arithmetic in the same order: prompt
