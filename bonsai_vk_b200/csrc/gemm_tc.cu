@@ -687,8 +687,18 @@ __global__ void k_gemm_sum_groups(const float *__restrict__ groups, int ngroups,
     pdl_sync();
     const int row = blockIdx.x * blockDim.x + threadIdx.x, c = blockIdx.y;
     if (row >= M || c >= ncol) return;
-    float s = groups[size_t(c) * M + row];
-    for (int g = 1; g < ngroups; ++g) s = __fadd_rn(s, groups[(size_t(g) * ncp + c) * M + row]);
+    const size_t gs = size_t(ncp) * M;
+    const float *gp = groups + size_t(c) * M + row;
+    float s = gp[0];
+    int g = 1;
+    for (; g + 8 <= ngroups; g += 8) {              // eight group sums in flight, added in ascending order
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = gp[size_t(g + u) * gs];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) s = __fadd_rn(s, v[u]);
+    }
+    for (; g < ngroups; ++g) s = __fadd_rn(s, gp[size_t(g) * gs]);
     if (resid) s = __fadd_rn(s, resid[size_t(c) * resid_stride + row]);
     out[size_t(c) * out_stride + row] = s;
 }
