@@ -1345,7 +1345,9 @@ int bn_model_read(bn_model *m, int what, int index, void *dst, size_t bytes) {
     const void *src = nullptr;
     size_t have = 0;
     switch (what) {
-        case BN_READ_LOGITS: src = m->LOGITS; have = size_t(h.vocab) * 4; break;
+        case BN_READ_LOGITS:
+            BN_REQUIRE(index >= 0 && index < m->ncols, BN_ERR_ARG, "bn_model_read: logits of column %d, the model has %d", index, m->ncols);
+            src = m->LOGITS + size_t(index) * (m->arena_bytes / 4); have = size_t(h.vocab) * 4; break;
         case BN_READ_RESIDUAL: src = m->RES; have = size_t(h.hidden) * 4; break;
         case BN_READ_GDN_STATE:
             BN_REQUIRE(index >= 0 && index < m->n_gdn, BN_ERR_ARG, "bn_model_read: gdn layer %d out of range", index);

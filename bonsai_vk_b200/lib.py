@@ -412,8 +412,9 @@ class Model:
         _check(self.ctx.lib.bn_model_read(self.h, what, index, out.ctypes.data_as(C.c_void_p), out.nbytes), "bn_model_read")
         return out
 
-    def logits(self):
-        return self.read(READ_LOGITS, np.float32, self.hp.vocab)
+    def logits(self, col: int = 0):
+        """Logits of the last token; col = the column of a multi-sequence pass."""
+        return self.read(READ_LOGITS, np.float32, self.hp.vocab, index=col)
 
     def residual(self):
         return self.read(READ_RESIDUAL, np.float32, self.hp.hidden)

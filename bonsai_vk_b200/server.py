@@ -13,6 +13,10 @@ own picks, and leaves when it hits a stop id, max_tokens or the context capacity
 dummy token at position 0 (a pass costs the same whatever the number of live columns). 429 is kept for the case the
 reference uses it for - no capacity left - which is now S conversations instead of one.
 
+Sampling: a request that asks for a temperature above zero (fields as the reference reads them, bonsai_http.h:595-608:
+temperature, top_p, top_k, seed, repetition_penalty, presence_penalty, frequency_penalty) is sampled on the host from its
+column's logits with the reference's sampler arithmetic (sampler.py); every other request takes the device's greedy pick.
+
 The tokenizer and the chat template stay on the reference's side of the boundary (its Bpe / chat::render produce ids):
 requests carry token ids - "prompt": [ids] on /v1/completions (the token-array form of that API) or "prompt_ids" on
 /v1/chat/completions - and replies carry "token_ids" beside a text field that lists the ids. A text-only request is
@@ -29,14 +33,17 @@ import time
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 from typing import List, Optional
 
+from .sampler import sampler_from_request
+
 
 class Busy(Exception):
     """Every slot holds a conversation."""
 
 
 class Conversation:
-    def __init__(self, prompt: List[int], max_tokens: int, stop: set):
+    def __init__(self, prompt: List[int], max_tokens: int, stop: set, sampler=None):
         self.prompt, self.max_tokens, self.stop = list(prompt), int(max_tokens), set(stop)
+        self.sampler = sampler             # None: the device's greedy pick; else sampler.Sampler over the step's logits
         self.pos = 0                       # position of the token fed at the next step
         self.out: List[int] = []
         self.events: "queue.Queue" = queue.Queue()     # ("tok", id) ... ("end", finish_reason)
@@ -49,7 +56,8 @@ class Conversation:
 
 class Batcher:
     """Continuous batching over an engine with `slots` sequences in groups of `group`:
-    engine.step(g, toks, pos) -> picks (one per column of group g), engine.reset_slot(s), engine.cap, engine.vocab."""
+    engine.step(g, toks, pos) -> picks (one per column of group g), engine.reset_slot(s), engine.cap, engine.vocab, and -
+    only for conversations that sample - engine.logits(g, i): the logits of column i after the last step of group g."""
 
     def __init__(self, engine):
         self.e = engine
@@ -67,14 +75,14 @@ class Batcher:
         with self.lock:
             return sum(c is not None for c in self.conv)
 
-    def submit(self, prompt: List[int], max_tokens: int, stop=()) -> Conversation:
+    def submit(self, prompt: List[int], max_tokens: int, stop=(), sampler=None) -> Conversation:
         if not prompt:
             raise ValueError("the prompt holds no token id")
         if any((not isinstance(t, int)) or t < 0 or t >= self.e.vocab for t in prompt):
             raise ValueError(f"prompt ids must be integers in [0, {self.e.vocab})")
         if len(prompt) >= self.e.cap:
             raise ValueError(f"the prompt ({len(prompt)} tokens) does not fit the context capacity {self.e.cap}")
-        c = Conversation(prompt, max(1, max_tokens), stop)
+        c = Conversation(prompt, max(1, max_tokens), stop, sampler)
         with self.lock:
             free = [s for s in range(self.S) if self.conv[s] is None]
             if not free:
@@ -108,7 +116,9 @@ class Batcher:
                     c.pos += 1
                     if c.pos < len(c.prompt):
                         continue                                  # still feeding the prompt: the pick is not used
-                    t = int(picks[i])
+                    # a sampling conversation reads its column's logits and picks on the host over its own generation so
+                    # far, as the reference does (bonsai_forward.h:2892); everybody else takes the device's first maximum
+                    t = int(c.sampler.pick(self.e.logits(g, i), c.out)) if c.sampler is not None else int(picks[i])
                     c.out.append(t)
                     c.events.put(("tok", t))
                     if t in c.stop:
@@ -154,6 +164,9 @@ class GpuEngine:
         self.m.stage_batch(g * self.group, toks, pos, None, self.tok)
         self.ctx.sync()
         return self.tok.download(self.np.int32, self.group)
+
+    def logits(self, g: int, i: int):
+        return self.m.logits(i)            # column i of the pass that just ran (the caller reads before the next step)
 
     def close(self):
         self.m.close()
@@ -222,7 +235,7 @@ def make_handler(batcher: Batcher, model_name: str):
                                           "token ids - \"prompt_ids\": [...] on /v1/chat/completions, \"prompt\": [...] on /v1/completions"))
             stop = req.get("stop_ids") or []
             try:
-                conv = batcher.submit(ids, int(req.get("max_tokens", 1024)), [int(t) for t in stop])
+                conv = batcher.submit(ids, int(req.get("max_tokens", 1024)), [int(t) for t in stop], sampler_from_request(req))
             except Busy:
                 return self._send(*_error(429, "rate_limit_error", f"all {batcher.S} conversation slots are generating; retry shortly"))
             except ValueError as ex:

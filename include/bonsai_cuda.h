@@ -288,7 +288,9 @@ int bn_model_mixer_sweep(bn_model *m, int reps, float *us_per_gdn_layer, float *
  * previous kernel done, norm done, rotated input built, quantised, first weights awaited, end).
  * stamps_out receives [n_phases][8]. */
 int bn_model_profile_token(bn_model *m, int tok, int pos, unsigned long long *stamps_out, int max_phases, int *n_phases);
-/* copy a device-side result or state region to the host (reference: act_rd / kv_dump) */
+/* copy a device-side result or state region to the host (reference: act_rd / kv_dump). index = the recurrent or
+ * attention layer for the state / cache selectors; for BN_READ_LOGITS the column of the last multi-sequence pass (0 for
+ * a single sequence) - what a host-side sampler reads (reference: Sampler::pick over the logits, bonsai_forward.h:2544) */
 int bn_model_read(bn_model *m, int what, int index, void *dst, size_t bytes);
 
 #ifdef __cplusplus

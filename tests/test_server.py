@@ -67,6 +67,45 @@ def test_scheduler_continuous_batching():
     b.close()
 
 
+def test_scheduler_samples_on_the_host_when_asked():
+    """A conversation with a sampler picks from its own column's logits over its own generation; its neighbour in the
+    same group keeps the engine's greedy pick."""
+    from bonsai_vk_b200.sampler import Sampler
+
+    class LogitEngine(FakeEngine):
+        def step(self, g, toks, pos):
+            self.last = (g, list(toks), list(pos))
+            return super().step(g, toks, pos)
+
+        def logits(self, g, i):                       # a peak at the greedy pick, a second one ten ids further
+            gg, toks, pos = self.last
+            assert gg == g
+            lg = np.full(self.vocab, -30.0, dtype=np.float32)
+            top = (7 * toks[i] + 3 * pos[i] + 1) % self.vocab
+            lg[top] = 5.0
+            lg[(top + 10) % self.vocab] = 4.5
+            return lg
+
+    e = LogitEngine()
+    b = server.Batcher(e)
+    greedy = b.submit([5, 6, 7], 6)
+    argmax = b.submit([5, 6, 7], 6, sampler=Sampler(temp=1.0, top_k=1, rep_penalty=1.0, presence_penalty=0.0))
+    mixed = b.submit([5, 6, 7], 200, sampler=Sampler(temp=1.0, rep_penalty=1.0, presence_penalty=0.0, seed=11))
+    for c in (greedy, argmax, mixed):
+        _drain(c)
+    assert greedy.out == _serial([5, 6, 7], 6)
+    assert argmax.out == greedy.out                   # top_k = 1 leaves only the maximum
+    # the sampled conversation follows its own tokens: every step is one of the two peaks of the token it fed
+    seq = [5, 6, 7] + mixed.out
+    seconds = 0
+    for p in range(2, len(seq) - 1):
+        top = (7 * seq[p] + 3 * p + 1) % 1000
+        assert seq[p + 1] in (top, (top + 10) % 1000)
+        seconds += seq[p + 1] != top
+    assert 0 < seconds < len(mixed.out)               # both peaks are drawn (weights 0.62 : 0.38)
+    b.close()
+
+
 def test_scheduler_refuses_when_full_and_checks_requests():
     e = FakeEngine()
     gate = threading.Event()
@@ -186,6 +225,11 @@ def test_three_overlapping_conversations_on_the_gpu(ctx):
     # a slot that served one conversation serves the next from a clean state
     st, raw = _http(port, "/v1/completions", {"prompt": prompts[0], "max_tokens": n_gen[0]})
     assert json.loads(raw)["choices"][0]["token_ids"] == want[0]
+    # a request that samples reads its column's logits on the host; with top_k = 1 and the penalties off only the
+    # maximum survives, so the stream must be the greedy one (whatever column the conversation landed in)
+    st, raw = _http(port, "/v1/completions", {"prompt": prompts[2], "max_tokens": n_gen[2], "temperature": 0.8, "top_k": 1,
+                                              "repetition_penalty": 1.0, "presence_penalty": 0.0})
+    assert st == 200 and json.loads(raw)["choices"][0]["token_ids"] == want[2]
     srv.shutdown(); b.close(); eng.close()
 
 
