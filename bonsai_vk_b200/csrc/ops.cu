@@ -381,6 +381,9 @@ k_gdn_split(int heads, int qk_heads, int hidden, const float *__restrict__ qkv, 
     extern __shared__ float4 dyn[];                // [3][hidden/4]: normed residual, row h of ssm_alpha, row h of ssm_beta
     const int unit = blockIdx.x, h = unit >> 2, q4 = unit & 3, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hq = h % qk_heads, n4 = hidden / 4;
+    // "I am running": the matching wait sits in front of the first store into a neighbour's shared memory, which must
+    // not happen before that neighbour has started (by then everybody has long arrived - nobody waits here)
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     const bool odd = pos_ptr[0] & 1;               // a token at position p reads taps from buffer p & 1, writes the other
     const float *hist_rd = odd ? hist1 : hist0;
     float *hist_wr = odd ? hist0 : hist1;
@@ -453,6 +456,7 @@ k_gdn_split(int heads, int qk_heads, int hidden, const float *__restrict__ qkv, 
         kk[0] = __fmul_rn(b0, ik); kk[1] = __fmul_rn(b1, ik); kk[2] = __fmul_rn(b2, ik); kk[3] = __fmul_rn(b3, ik);
     }
     __syncthreads();
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // all four CTAs of the head are running
     const float eg = exp_f(sgb[0]), bt = sgb[1];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
