@@ -21,6 +21,7 @@
 // BONSAI_STEPWISE=1 (one host call per generated token instead of the device-chained loop), BONSAI_PREFILL_BLOCK (prompt
 // tokens per prefill pass, default 16; 0 = token by token; the lineage gate always prefills token by token).
 #include "bonsai_host.h"
+#include "bonsai_sampler.h"
 
 #include <chrono>
 #include <cmath>
@@ -104,6 +105,24 @@ int main(int argc, char **argv) {
         fprintf(stderr, "usage: %s run [model.gguf] [chunk_MiB] [n_tokens] [-- \"prompt\"] | info [model.gguf] | <model.gguf> info | <model.gguf> run [n_gen]\n", argv[0]);
         return 2;
     }
+    if (!strcmp(argv[1], "sampler-check")) {
+        // No GPU: read cases from stdin and print the pick and the generator state of each (the knobs come from the
+        // environment as in `run`). A case is: n, then n logits, then m, then m history ids (text, whitespace separated).
+        bh::Sampler sp;
+        sp.from_env();
+        unsigned n = 0;
+        while (scanf("%u", &n) == 1 && n > 0 && n < (1u << 24)) {
+            std::vector<float> lg(n);
+            for (unsigned i = 0; i < n; ++i) if (scanf("%f", &lg[i]) != 1) return 2;
+            unsigned m = 0;
+            if (scanf("%u", &m) != 1 || m > (1u << 24)) return 2;
+            std::vector<int> hist(m);
+            for (unsigned i = 0; i < m; ++i) if (scanf("%d", &hist[i]) != 1) return 2;
+            const int t = sp.pick(lg.data(), n, hist);
+            printf("%d %llu\n", t, (unsigned long long)sp.rng);
+        }
+        return 0;
+    }
     // everything after "--" is the prompt text and not a positional argument
     int npos = argc;
     std::string text_prompt;
@@ -158,7 +177,12 @@ int main(int argc, char **argv) {
     const char *pb_s = getenv("BONSAI_PREFILL_BLOCK");
     const int prefill_want = pb_s ? atoi(pb_s) : 16;
     if (prefill_want < 0 || prefill_want > 32) return fail(2, "BONSAI_PREFILL_BLOCK must be between 0 and 32");
-    const int prefill_block = getenv("BONSAI_QCHECK") ? 0 : prefill_want;
+    // BONSAI_TEMP above zero: tokens are sampled on the host from the logits, as the reference's `run` does
+    // (bonsai_forward.h:2657-2664, 2892); the prompt is then fed token by token so that the logits read back are its last
+    // token's. Without it the device's greedy pick is used.
+    bh::Sampler sampler;
+    const bool sampling = sampler.from_env() && !getenv("BONSAI_QCHECK");
+    const int prefill_block = (getenv("BONSAI_QCHECK") || sampling) ? 0 : prefill_want;
     if (prefill_block > 1) e.plan.hp.batch_cols = prefill_block;
     const char *dev_s = getenv("BONSAI_DEVICE");
     if (bn_init(dev_s ? atoi(dev_s) : 0, &e.ctx)) return fail(3, bn_last_error());
@@ -195,7 +219,19 @@ int main(int argc, char **argv) {
     out[0] = next;
     t0 = now_ms();
     double t_first = 0;
-    if (getenv("BONSAI_STEPWISE")) {
+    if (sampling) {
+        std::vector<float> logits(size_t(e.plan.hp.vocab));
+        std::vector<int> gen;
+        for (int i = 0; i < n_gen; ++i) {
+            if (i > 0 && bn_model_token(e.model, out[i - 1], int(prompt.size()) + i - 1, -1, nullptr)) return fail(3, bn_last_error());
+            if (bn_model_read(e.model, BN_READ_LOGITS, 0, logits.data(), logits.size() * sizeof(float))) return fail(3, bn_last_error());
+            out[i] = sampler.pick(logits.data(), uint32_t(logits.size()), gen);
+            gen.push_back(out[i]);
+            if (i == 1) t_first = now_ms() - t0;
+        }
+        printf("sampled: temp %.2f top_k %d top_p %.2f repetition %.2f presence %.2f frequency %.2f\n", sampler.temp, sampler.top_k, sampler.top_p,
+               sampler.rep_penalty, sampler.presence_penalty, sampler.freq_penalty);
+    } else if (getenv("BONSAI_STEPWISE")) {
         for (int i = 1; i < n_gen; ++i) {
             if (bn_model_token(e.model, out[i - 1], int(prompt.size()) + i - 1, -1, &out[i])) return fail(3, bn_last_error());
             if (i == 1) t_first = now_ms() - t0;

@@ -127,6 +127,23 @@ def test_run_matches_the_checker_and_passes_the_gate(exe, files):
 
 
 @pytest.mark.gpu
+def test_run_samples_on_the_host_when_asked(exe, files):
+    """BONSAI_TEMP above zero switches `run` to the host-side sampler over the logits read back per token (reference:
+    bonsai_forward.h:2657-2664, 2892). With BONSAI_TOPK=1 and the penalties off only the maximum survives, so the ids
+    must be the greedy run's; with the default knobs and a fixed seed two runs agree with each other."""
+    base = {"BONSAI_PROMPT_IDS": "3,77,1500,12,900", "BONSAI_CAP": "64"}
+    greedy = run(exe, files["ok"], "run", "16", env=base)
+    assert greedy.returncode == 0, greedy.stdout + greedy.stderr
+    top1 = run(exe, files["ok"], "run", "16", env=dict(base, BONSAI_TEMP="0.8", BONSAI_TOPK="1", BONSAI_REP_PENALTY="1", BONSAI_PRESENCE="0"))
+    assert top1.returncode == 0, top1.stdout + top1.stderr
+    assert "sampled: temp 0.80 top_k 1" in top1.stdout
+    assert _ids(top1.stdout) == _ids(greedy.stdout)
+    a = run(exe, files["ok"], "run", "16", env=dict(base, BONSAI_TEMP="1.5", BONSAI_SEED="42"))
+    b = run(exe, files["ok"], "run", "16", env=dict(base, BONSAI_TEMP="1.5", BONSAI_SEED="42"))
+    assert a.returncode == 0 and _ids(a.stdout) == _ids(b.stdout) and len(_ids(a.stdout)) == 16
+
+
+@pytest.mark.gpu
 def test_run_with_an_explicit_layer_list(exe, tmp_path):
     """A file whose layer kinds come from `attention.layer_types` (an irregular pattern no interval can express):
     loader -> decode gives the checker's token ids and the lineage gate passes."""

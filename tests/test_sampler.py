@@ -114,3 +114,30 @@ def test_request_fields():
     assert sampler_from_request({}) is None and sampler_from_request({"temperature": 0}) is None
     s = sampler_from_request({"temperature": 0.9, "top_k": 40, "top_p": 0.95, "seed": 7, "repetition_penalty": 1.2, "presence_penalty": -1})
     assert (s.temp, s.top_k, s.top_p, s.rng, s.rep_penalty, s.presence_penalty) == (0.9, 40, 0.95, 7, 1.2, 0.5)
+
+
+@pytest.mark.parametrize("env", [dict(BONSAI_TEMP="0.7"), dict(BONSAI_TEMP="1.1", BONSAI_TOPK="7", BONSAI_SEED="12345"),
+                                 dict(BONSAI_TEMP="0.9", BONSAI_TOPP="0.7", BONSAI_REP_PENALTY="1.3", BONSAI_PRESENCE="0", BONSAI_FREQ="0.2")])
+def test_cpp_host_sampler_equals_the_python_one(env):
+    """The `run` command's sampler (host/bonsai_sampler.h) through `bonsai_run sampler-check` (no GPU needed): the same picks
+    and the same generator states as sampler.Sampler over a sequence of cases that share one generator."""
+    import os
+    import subprocess
+
+    from bonsai_vk_b200 import build
+    exe = build.build_host()
+    rng = np.random.default_rng(5)
+    py = Sampler(temp=float(env["BONSAI_TEMP"]), top_k=int(env.get("BONSAI_TOPK", 0)), top_p=float(env.get("BONSAI_TOPP", 1.0)),
+                 seed=int(env.get("BONSAI_SEED", 88172645463325252)), rep_penalty=float(env.get("BONSAI_REP_PENALTY", 1.15)),
+                 presence_penalty=float(env.get("BONSAI_PRESENCE", 0.5)), freq_penalty=float(env.get("BONSAI_FREQ", 0.0)))
+    text, want = [], []
+    for _ in range(30):
+        n = int(rng.integers(5, 120))
+        logits = (rng.standard_normal(n) * 3).astype(np.float32)
+        hist = [int(t) for t in rng.integers(0, n, size=int(rng.integers(0, 90)))]
+        text.append(f"{n} " + " ".join(repr(float(v)) for v in logits) + f" {len(hist)} " + " ".join(map(str, hist)))
+        t = py.pick(logits, hist)
+        want.append(f"{t} {py.rng}")
+    r = subprocess.run([exe, "sampler-check"], input="\n".join(text) + "\n0\n", capture_output=True, text=True, env=dict(os.environ, **env), timeout=60)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.split("\n")[:len(want)] == want
