@@ -3,6 +3,7 @@
 import ctypes as C
 
 import numpy as np
+import pytest
 
 from bonsai_vk_b200 import synth
 from tests._oracle import OracleModel
@@ -47,12 +48,18 @@ def test_rotation_order(oracle):
         assert np.array_equal(y3[b * n:(b + 1) * n], oracle.fwht(x3[b * n:(b + 1) * n] * s3[b * n:(b + 1) * n], n))
 
 
-def test_attention_vs_reference_mirror(oracle, ref):
+@pytest.mark.parametrize("n_kv", [1, 2, 4])
+def test_attention_vs_reference_mirror(oracle, ref, n_kv):
     """fp16 K / fp16 V with fp16-rounded probabilities is the configuration attn_vk.h mirrors
     (attn_forward<true>). In the reference's own order (attn_order 0: head-norm squares, softmax sum and PV all
     serial ascending) the oracle must reproduce the mirror bit for bit: both fp16 matmul operands (q16 of every
-    token, the K arena), the pre-gate output and the gated output of the last token."""
-    hp = synth.tiny(k_mode=1, v_mode=1, cap=64, n_layer=4)
+    token, the K arena), the pre-gate output and the gated output of the last token. That holds for the 4:1 head ratio
+    of the 9B on all three cases. With 2 and 1 query heads per kv head (other random rows) one rotated K element in
+    24 576 lands one fp16 step away: the mirror takes cos / sin / pow from the C library's float routines, which are
+    not always correctly rounded, the oracle (and the kernels) evaluate them in double and round once - so for those
+    ratios the test allows fp16 operands one step apart in at most 1e-4 of the elements and asserts the outputs to
+    1e-5 of the row RMS instead of bit for bit."""
+    hp = synth.tiny(k_mode=1, v_mode=1, cap=64, n_layer=4, n_kv=n_kv)
     tensors, signs = synth.make_model(hp, seed=3)
     om = OracleModel(hp, tensors, signs, attn_order=0)
     b = 3   # the attention block of the tiny model
@@ -80,10 +87,19 @@ def test_attention_vs_reference_mirror(oracle, ref):
         ref.ref_attn_forward(seq, hp.cap, hp.n_head, hp.n_kv, hd, hp.n_rot, C.c_float(hp.rms_eps), C.c_float(hp.rope_base),
                              _p(q_in), _p(kin), _p(vin), _p(g_in), _p(qn), _p(kn), _p(upos), 1,
                              _p(r_pre), _p(r_gated), None, _p(r_q16), _p(r_kc))
-        assert np.array_equal(r_q16.view(np.uint16).reshape(seq, QD), q16), "fp16 query operands differ from attn_vk.h"
-        assert np.array_equal(r_kc.view(np.uint16).reshape(hp.cap, KD)[:seq], k16), "fp16 K arena differs from attn_vk.h"
-        assert np.array_equal(pre.view(np.uint32), r_pre[-1].view(np.uint32)), "pre-gate output is not bit-identical to attn_vk.h"
-        assert np.array_equal(gated.view(np.uint32), r_gated[-1].view(np.uint32)), "gated output is not bit-identical to attn_vk.h"
+        rq, rk = r_q16.view(np.uint16).reshape(seq, QD), r_kc.view(np.uint16).reshape(hp.cap, KD)[:seq]
+        if n_kv == 1:
+            assert np.array_equal(rq, q16), "fp16 query operands differ from attn_vk.h"
+            assert np.array_equal(rk, k16), "fp16 K arena differs from attn_vk.h"
+            assert np.array_equal(pre.view(np.uint32), r_pre[-1].view(np.uint32)), "pre-gate output is not bit-identical to attn_vk.h"
+            assert np.array_equal(gated.view(np.uint32), r_gated[-1].view(np.uint32)), "gated output is not bit-identical to attn_vk.h"
+        else:
+            for got, want, name in ((q16, rq, "query"), (k16, rk, "K")):
+                step = np.abs(got.astype(np.int32) - want.astype(np.int32))
+                assert step.max() <= 1 and np.count_nonzero(step) <= 1e-4 * step.size + 1, f"fp16 {name} operands: {np.count_nonzero(step)} differ, worst {step.max()} steps"
+            rms = np.sqrt(np.mean(r_pre[-1].astype(np.float64).reshape(hp.n_head, hd) ** 2, axis=1, keepdims=True))
+            assert np.max(np.abs(pre.reshape(hp.n_head, hd) - r_pre[-1].reshape(hp.n_head, hd)) / rms) <= 1e-5
+            assert np.max(np.abs(gated.reshape(hp.n_head, hd) - r_gated[-1].reshape(hp.n_head, hd)) / rms) <= 1e-5
     om.close()
 
 
