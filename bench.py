@@ -374,6 +374,12 @@ def main():
         line = dict(base, impl="reference", value=cb["value"], ms_per_step=1000.0 / cb["value"], cpu_baseline=cb,
                     e2e={"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                     gpu_launches=0)
+        if max(world, a.gpus) > 1:
+            # the arm that is compared with the pipelined line: same metric, a step = one token of each of the 64 sequences.
+            # The CPU path has no pipeline and no batching gain: its aggregate rate is its per-token rate.
+            line.update(metric="decode tok/s, 9B ternary (PTQ1_0), 64 streams pipelined", scaling="strong", ms_per_step=64 * 1000.0 / cb["value"],
+                        config=dict(base["config"], workload="config 4: 64 concurrent sequences of the 9B-shape synthetic model, greedy decode - the "
+                                    "reference's CPU arithmetic on the host cores (projection weights only, as in the one-GPU arm)", streams=64))
         print(json.dumps(line))
         return
 
